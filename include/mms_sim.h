@@ -1,0 +1,155 @@
+/*
+ * mms_sim.h — C ABI of the B200 placement-evaluation simulator.
+ *
+ * One call scores a BATCH of candidate placements against ONE request trace
+ * on the current CUDA device.  It replaces, for that path, what AlpaServe's
+ * PlacementEvaluator does one candidate at a time
+ * (alpa_serve/placement_policy/base_policy.py:175-189 calling
+ * alpa_serve/simulator/controller.py:308 approximate_one_case).
+ *
+ * Conventions
+ *  - every pointer in the structs below is a DEVICE pointer unless its
+ *    comment says "host"; the caller owns all buffers;
+ *  - calls are stream-ordered on `stream` (a cudaStream_t passed as void*);
+ *    no call synchronises the device, none allocates device memory;
+ *  - the return value is 0 or a negative MMS_ERR_* code; per-candidate
+ *    conditions found on the device are reported in `status[b]`;
+ *  - results are bit-identical to the reference's numba/Python simulator on
+ *    the same inputs (fp64, same operation order).
+ */
+#ifndef MMS_SIM_H_
+#define MMS_SIM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MMS_OK 0
+#define MMS_ERR_ARG (-1)          /* null pointer, negative size, bad flag       */
+#define MMS_ERR_UNSUPPORTED (-2)  /* shape outside the limits listed below       */
+#define MMS_ERR_CUDA (-3)         /* a CUDA runtime call failed (see last_error) */
+#define MMS_ERR_NO_DEVICE (-4)
+
+/* Shape limits of the kernels (checked, never assumed). */
+#define MMS_MAX_GROUPS 255        /* groups per candidate                        */
+#define MMS_MAX_SLOTS 256         /* sum of pipeline stages over a candidate     */
+#define MMS_MAX_PLACED 65535      /* (group, model) pairs per candidate          */
+#define MMS_MAX_STAGES 255        /* stages of one group                         */
+
+/* status[b] bits */
+#define MMS_STATUS_OK 0u
+#define MMS_STATUS_HEAP_OVERFLOW 1u   /* batching: event heap capacity exceeded  */
+#define MMS_STATUS_QUEUE_LEFT 2u      /* batching: a request stayed queued       */
+#define MMS_STATUS_BAD_INDEX 4u       /* a table index was out of range          */
+
+/* flags */
+#define MMS_FLAG_PER_REQUEST 1u   /* also write finish[b][i] and good[b][i]      */
+#define MMS_FLAG_LEGACY_CLOCK 2u  /* one clock per group: controller.py:506-558  */
+
+/* The request trace: what controller.py:323-339 caches per Workload
+ * (model_ids, slos) plus Workload.arrivals (simulator/workload.py:272). */
+typedef struct {
+    int64_t num_requests;          /* N */
+    const double *arrivals;        /* f64[N]                                     */
+    const int32_t *model_ids;      /* i32[N]; -1 = model not registered          */
+    const float *slos;             /* f32[N]                                     */
+} mms_trace;
+
+/* B candidate placements, the tables of controller.py:418-476 in a compact
+ * form.  Group g of a candidate owns the clock slots
+ * [slot, slot + stages) of that candidate's clock vector.
+ *
+ *  model_off  u16[B][M+1]  CSR offsets into model_rep
+ *  model_rep  u16[B][P]    for model m, its groups in ascending group id
+ *                          (row order of m_id2g_id, controller.py:418-422):
+ *                          low byte = group id, high byte = that group's
+ *                          LAST clock slot
+ *  group_info u32[B][G]    bits 0-7 first clock slot, 8-15 stages (pp),
+ *                          16-31 column of the latency table
+ *  latency    f32[M][C][S] seconds per stage, already rounded to f32 the way
+ *                          controller.py:467-476 does; column = parallel
+ *                          config.  With latency_stride != 0 candidate b
+ *                          reads its own table at latency + b*stride (the
+ *                          dense per-group table of the reference: C == G).
+ *  With MMS_FLAG_LEGACY_CLOCK: S == 2 and latency[m][c] = {sum, max} of
+ *  controller.py:440-441, every group has 1 stage.
+ */
+typedef struct {
+    int32_t num_candidates;        /* B */
+    int32_t num_models;            /* M */
+    int32_t max_groups;            /* G: row length of group_info and outputs    */
+    int32_t max_placed;            /* P: row length of model_rep                 */
+    int32_t max_slots;             /* T: clock slots per candidate (<= 256)      */
+    int32_t max_stages;            /* S: last axis of latency                    */
+    int32_t num_columns;           /* C */
+    int32_t reserved;
+    const uint16_t *model_off;
+    const uint16_t *model_rep;
+    const uint32_t *group_info;
+    const float *latency;
+    int64_t latency_stride;        /* elements; 0 = one table for all candidates */
+} mms_placements;
+
+/* How numpy sums N doubles (pairwise, blocks of <= 128, eight interleaved
+ * partial sums): the order np.mean(finish - start) uses at
+ * controller.py:402.  The plan depends on N only. */
+typedef struct {
+    int32_t num_leaves;
+    int32_t reserved;
+    const int32_t *leaf_start;     /* i32[num_leaves + 1], leaf_start[0] == 0    */
+    const uint8_t *leaf_merges;    /* u8[num_leaves]: pair-sums after each leaf  */
+} mms_sum_plan;
+
+/* Scratch the caller provides (size from mms_sim_workspace_bytes). */
+typedef struct {
+    void *ptr;
+    size_t bytes;
+} mms_workspace;
+
+typedef struct {
+    int32_t *model_num_requests;   /* i32[B][M]                                  */
+    int32_t *model_num_good;       /* i32[B][M]                                  */
+    int32_t *group_num_requests;   /* i32[B][G]                                  */
+    int32_t *group_num_good;       /* i32[B][G] or NULL                          */
+    int64_t *good_total;           /* i64[B]: sum(good)                          */
+    double *latency_sum;           /* f64[B]: numpy-ordered sum(finish - start)  */
+    uint32_t *status;              /* u32[B]                                     */
+    double *finish;                /* f64[B][N] with MMS_FLAG_PER_REQUEST        */
+    uint8_t *good;                 /* u8[B][N]  with MMS_FLAG_PER_REQUEST        */
+} mms_results;
+
+/* Library and device -------------------------------------------------------*/
+int mms_abi_version(void);
+/* Text of the last failing CUDA call on this thread ("" if none). */
+const char *mms_last_error(void);
+
+/* Summation plan (host side; replaces nothing in the reference — it restates
+ * numpy's reduction order, reached from controller.py:402). */
+int32_t mms_sum_plan_leaves(int64_t num_requests);
+int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start /*host*/,
+                      uint8_t *leaf_merges /*host*/);
+
+/* Per-model request counts of a trace (model_num_requests of
+ * controller.py:587 does not depend on the placement). hist: i32[M]. */
+int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models,
+                              int32_t *hist, void *stream);
+
+/* Bytes of scratch mms_sim_mixed needs for this shape. */
+size_t mms_sim_workspace_bytes(int64_t num_requests, const mms_placements *cands,
+                               uint32_t flags);
+
+/* simulate_requests_mixed (controller.py:561-628) — or simulate_requests
+ * (controller.py:506-558) with MMS_FLAG_LEGACY_CLOCK — for every candidate,
+ * followed by the fast_stats reductions of controller.py:393-403. */
+int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands,
+                  const mms_sum_plan *plan, const int32_t *model_hist,
+                  const mms_workspace *ws, const mms_results *out,
+                  uint32_t flags, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MMS_SIM_H_ */

@@ -1,0 +1,106 @@
+"""ctypes binding of libmms_sim.so (the C ABI declared in include/mms_sim.h).
+
+There is no CPU fallback: if the library is missing, or no CUDA device is
+present when a compute entry point is called, the call raises.
+"""
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libmms_sim.so")
+
+MMS_OK = 0
+ERRORS = {
+    -1: "MMS_ERR_ARG (bad argument)",
+    -2: "MMS_ERR_UNSUPPORTED (shape outside the kernel limits)",
+    -3: "MMS_ERR_CUDA (a CUDA call failed)",
+    -4: "MMS_ERR_NO_DEVICE",
+}
+
+MAX_GROUPS = 255
+MAX_SLOTS = 256
+MAX_PLACED = 65535
+MAX_STAGES = 255
+
+STATUS_HEAP_OVERFLOW = 1
+STATUS_QUEUE_LEFT = 2
+STATUS_BAD_INDEX = 4
+
+FLAG_PER_REQUEST = 1
+FLAG_LEGACY_CLOCK = 2
+
+# Every symbol include/mms_sim.h declares.
+EXPORTS = (
+    "mms_abi_version", "mms_last_error", "mms_sum_plan_leaves", "mms_sum_plan_fill",
+    "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
+)
+
+_vp = ctypes.c_void_p
+
+
+class Trace(ctypes.Structure):
+    _fields_ = [("num_requests", ctypes.c_int64), ("arrivals", _vp), ("model_ids", _vp),
+                ("slos", _vp)]
+
+
+class Placements(ctypes.Structure):
+    _fields_ = [("num_candidates", ctypes.c_int32), ("num_models", ctypes.c_int32),
+                ("max_groups", ctypes.c_int32), ("max_placed", ctypes.c_int32),
+                ("max_slots", ctypes.c_int32), ("max_stages", ctypes.c_int32),
+                ("num_columns", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("model_off", _vp), ("model_rep", _vp), ("group_info", _vp), ("latency", _vp),
+                ("latency_stride", ctypes.c_int64)]
+
+
+class SumPlan(ctypes.Structure):
+    _fields_ = [("num_leaves", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("leaf_start", _vp), ("leaf_merges", _vp)]
+
+
+class Workspace(ctypes.Structure):
+    _fields_ = [("ptr", _vp), ("bytes", ctypes.c_size_t)]
+
+
+class Results(ctypes.Structure):
+    _fields_ = [("model_num_requests", _vp), ("model_num_good", _vp),
+                ("group_num_requests", _vp), ("group_num_good", _vp), ("good_total", _vp),
+                ("latency_sum", _vp), ("status", _vp), ("finish", _vp), ("good", _vp)]
+
+
+_lib = None
+
+
+def lib():
+    """Loads the extension; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m mms_b200.build` "
+            "(there is no CPU fallback)")
+    L = ctypes.CDLL(LIB_PATH)
+    L.mms_abi_version.restype = ctypes.c_int
+    L.mms_last_error.restype = ctypes.c_char_p
+    L.mms_sum_plan_leaves.restype = ctypes.c_int32
+    L.mms_sum_plan_leaves.argtypes = [ctypes.c_int64]
+    L.mms_sum_plan_fill.restype = ctypes.c_int
+    L.mms_sum_plan_fill.argtypes = [ctypes.c_int64, _vp, _vp]
+    L.mms_trace_model_histogram.restype = ctypes.c_int
+    L.mms_trace_model_histogram.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
+    L.mms_sim_workspace_bytes.restype = ctypes.c_size_t
+    L.mms_sim_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
+                                          ctypes.c_uint32]
+    L.mms_sim_mixed.restype = ctypes.c_int
+    L.mms_sim_mixed.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
+                                ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(Workspace),
+                                ctypes.POINTER(Results), ctypes.c_uint32, _vp]
+    _lib = L
+    return L
+
+
+def check(rc, what):
+    if rc != MMS_OK:
+        msg = ERRORS.get(rc, f"code {rc}")
+        detail = lib().mms_last_error().decode(errors="replace")
+        raise RuntimeError(f"{what}: {msg}" + (f" [{detail}]" if detail and rc == -3 else ""))

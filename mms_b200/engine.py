@@ -1,0 +1,334 @@
+"""Host side of the GPU simulator: trace upload, placement encoding, launch.
+
+The three steps mirror what the reference does per candidate in
+alpa_serve/simulator/controller.py:410-503 (approximate_one_case_one_placement
+builds m_id2g_id / num_stages / stage_latency, then calls the numba kernel),
+but for a whole list of candidates at once and in the compact form that
+include/mms_sim.h describes.  PyTorch is used for device memory and streams
+only; all compute goes through the C ABI in libmms_sim.so.
+"""
+import ctypes
+from itertools import chain
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from . import _native as nat
+
+inf = 1e100      # alpa_serve/util.py:23
+
+
+def _require_cuda():
+    if not torch.cuda.is_available():
+        raise RuntimeError("mms_b200 needs a CUDA device: the simulator has no CPU path")
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() > 0 else ctypes.c_void_p(0)
+
+
+def _stream_ptr():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _to_device(arr: np.ndarray, device, pinned=False):
+    t = torch.from_numpy(np.ascontiguousarray(arr))
+    if pinned:
+        t = t.pin_memory()
+    return t.to(device, non_blocking=pinned)
+
+
+class DeviceTrace:
+    """A request trace resident on one GPU: arrivals f64[N], model ids i32[N]
+    (-1 = unknown model), SLOs f32[N] — the arrays controller.py:335-336
+    caches per workload — plus what depends on the trace alone: the per-model
+    request counts (controller.py:587) and numpy's summation plan for N."""
+
+    def __init__(self, arrivals, model_ids, slos, num_models: int, device=None):
+        _require_cuda()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        arrivals = np.ascontiguousarray(arrivals, dtype=np.float64)
+        model_ids = np.ascontiguousarray(model_ids, dtype=np.int32)
+        slos = np.ascontiguousarray(slos, dtype=np.float32)
+        if not (len(arrivals) == len(model_ids) == len(slos)):
+            raise ValueError("arrivals, model_ids and slos must have one entry per request")
+        self.num_requests = int(len(arrivals))
+        self.num_models = int(num_models)
+        self.host_arrivals = arrivals
+        self.h2d_bytes = arrivals.nbytes + model_ids.nbytes + slos.nbytes
+        L = nat.lib()
+        with torch.cuda.device(self.device):
+            self.arrivals = _to_device(arrivals, self.device)
+            self.model_ids = _to_device(model_ids, self.device)
+            self.slos = _to_device(slos, self.device)
+            n_leaves = L.mms_sum_plan_leaves(self.num_requests)
+            if n_leaves < 0:
+                nat.check(n_leaves, "mms_sum_plan_leaves")
+            leaf_start = np.zeros(n_leaves + 1, np.int32)
+            leaf_merges = np.zeros(max(n_leaves, 1), np.uint8)
+            nat.check(L.mms_sum_plan_fill(self.num_requests, leaf_start.ctypes.data,
+                                          leaf_merges.ctypes.data), "mms_sum_plan_fill")
+            self.num_leaves = n_leaves
+            self.leaf_start = _to_device(leaf_start, self.device)
+            self.leaf_merges = _to_device(leaf_merges, self.device)
+            self.model_hist = torch.zeros(max(self.num_models, 1), dtype=torch.int32,
+                                          device=self.device)
+            tr = self.c_trace()
+            nat.check(L.mms_trace_model_histogram(ctypes.byref(tr), self.num_models,
+                                                  _ptr(self.model_hist), _stream_ptr()),
+                      "mms_trace_model_histogram")
+
+    def c_trace(self):
+        return nat.Trace(self.num_requests, _ptr(self.arrivals), _ptr(self.model_ids),
+                         _ptr(self.slos))
+
+    def c_plan(self):
+        return nat.SumPlan(self.num_leaves, 0, _ptr(self.leaf_start), _ptr(self.leaf_merges))
+
+
+class LatencyTable:
+    """stage latency per (model, parallel config, stage) in f32, with the
+    0.9 %-per-stage penalty of controller.py:467-476 folded in.  Column c is
+    the parallel config `configs[c]`; a config a model has no profile for is
+    +inf (the f32 cast of 1e100), so such a replica never meets an SLO."""
+
+    def __init__(self, prof_ress: Sequence, batch_size: int = 1):
+        self.prof_ress = list(prof_ress)
+        self.batch_size = batch_size
+        self.configs: List = []
+        self.column = {}
+        self.max_stages = 1
+        self._host = np.zeros((len(self.prof_ress), 0, 1), np.float32)
+        self._device = None
+
+    def columns_for(self, configs) -> None:
+        new = [c for c in dict.fromkeys(configs) if c not in self.column]
+        if not new:
+            return
+        for c in new:
+            self.column[c] = len(self.configs)
+            self.configs.append(c)
+        S = max([self.max_stages] + [int(c.pp) for c in new])
+        M, C = len(self.prof_ress), len(self.configs)
+        tab = np.zeros((M, C, S), np.float32)
+        old = self._host
+        tab[:, :old.shape[1], :old.shape[2]] = old
+        with np.errstate(over="ignore"):
+            for m, prof in enumerate(self.prof_ress):
+                for c in new:
+                    col = self.column[c]
+                    value = prof.para_dict.get(c, None)
+                    if value:
+                        stages = value.latency[self.batch_size]
+                        penalty = 0.009 * len(stages)
+                        for k in range(int(c.pp)):
+                            tab[m, col, k] = stages[k] * (1 + penalty)
+                    else:
+                        tab[m, col, :] = np.float32(inf)
+        self._host = tab
+        self.max_stages = S
+        self._device = None
+
+    @property
+    def host(self):
+        return self._host
+
+    def device(self, dev):
+        if self._device is None or self._device.device != dev:
+            self._device = _to_device(self._host, dev)
+        return self._device
+
+
+class EncodedBatch:
+    """Host arrays of a placement batch in the layout of mms_placements."""
+
+    def __init__(self, B, M, G, P, T, S, C, model_off, model_rep, group_info, num_groups,
+                 num_replicas):
+        self.B, self.M, self.G, self.P, self.T, self.S, self.C = B, M, G, P, T, S, C
+        self.model_off = model_off        # u16[B][M+1]
+        self.model_rep = model_rep        # u16[B][P]
+        self.group_info = group_info      # u32[B][G]
+        self.num_groups = num_groups      # i64[B]
+        self.num_replicas = num_replicas  # i64[B]: sum of len(group_models)
+
+    @property
+    def nbytes(self):
+        return self.model_off.nbytes + self.model_rep.nbytes + self.group_info.nbytes
+
+
+def encode_placements(placements: Sequence, table: LatencyTable, num_models: int) -> EncodedBatch:
+    """List of ModelPlacement -> compact tables.  Each placement is taken as
+    given: group order decides dispatch ties (controller.py:596 is a strict
+    '<' over groups in ascending id), so nothing is re-sorted."""
+    B = len(placements)
+    M = int(num_models)
+    table.columns_for(chain.from_iterable(p.group_configs for p in placements))
+    colmap = table.column
+
+    n_groups = np.fromiter((len(p.group_configs) for p in placements), np.int64, B)
+    tot_groups = int(n_groups.sum())
+    cfg_col = np.fromiter((colmap[c] for p in placements for c in p.group_configs),
+                          np.int64, tot_groups)
+    cfg_pp = np.fromiter((c.pp for p in placements for c in p.group_configs),
+                         np.int64, tot_groups)
+    n_in_group = np.fromiter((len(ms) for p in placements for ms in p.group_models),
+                             np.int64, tot_groups)
+    if len(n_in_group) != tot_groups:
+        raise ValueError("group_configs and group_models differ in length")
+    tot_placed = int(n_in_group.sum())
+    placed_model = np.fromiter(
+        chain.from_iterable(chain.from_iterable(p.group_models for p in placements)),
+        np.int64, tot_placed)
+    if tot_placed and (placed_model.min() < 0 or placed_model.max() >= M):
+        raise IndexError("model id in group_models is out of range")
+
+    G = int(n_groups.max()) if B else 0
+    grp_first = np.concatenate(([0], np.cumsum(n_groups)))[:-1]     # first flat group of b
+    grp_b = np.repeat(np.arange(B), n_groups)                       # candidate of flat group
+    grp_g = np.arange(tot_groups) - grp_first[grp_b]                # group id inside b
+    # clock slots: exclusive prefix sum of stages inside each candidate
+    csum = np.cumsum(cfg_pp)
+    base = np.concatenate(([0], csum))[grp_first]
+    slot_first = (csum - cfg_pp) - base[grp_b]
+    slots_per_b = np.zeros(B, np.int64)
+    np.add.at(slots_per_b, grp_b, cfg_pp)
+    T = int(slots_per_b.max()) if B else 0
+    S = int(table.max_stages)
+    C = len(table.configs)
+    if G > nat.MAX_GROUPS or T > nat.MAX_SLOTS or S > nat.MAX_STAGES:
+        raise NotImplementedError(
+            f"placement too large for the kernels: {G} groups (max {nat.MAX_GROUPS}), "
+            f"{T} pipeline stages in total (max {nat.MAX_SLOTS})")
+
+    group_info = np.zeros((B, max(G, 1)), np.uint32)
+    group_info[grp_b, grp_g] = (slot_first | (cfg_pp << 8) | (cfg_col << 16)).astype(np.uint32)
+
+    # (candidate, model, group) triples, ordered by model then group inside b
+    pl_grp = np.repeat(np.arange(tot_groups), n_in_group)           # flat group of each pair
+    pl_b = grp_b[pl_grp]
+    pl_g = grp_g[pl_grp]
+    order = np.lexsort((pl_g, placed_model, pl_b))
+    pl_b, pl_g, pl_m, pl_grp = pl_b[order], pl_g[order], placed_model[order], pl_grp[order]
+    placed_per_b = np.bincount(pl_b, minlength=B) if tot_placed else np.zeros(B, np.int64)
+    P = int(placed_per_b.max()) if B else 0
+    if P > nat.MAX_PLACED:
+        raise NotImplementedError(f"{P} (group, model) pairs in one placement (max {nat.MAX_PLACED})")
+    pair_first = np.concatenate(([0], np.cumsum(placed_per_b)))[:-1]
+    pos = np.arange(tot_placed) - pair_first[pl_b]
+    last_slot = slot_first[pl_grp] + cfg_pp[pl_grp] - 1
+    model_rep = np.zeros((B, max(P, 1)), np.uint16)
+    model_rep[pl_b, pos] = (pl_g | (last_slot << 8)).astype(np.uint16)
+    counts = np.zeros((B, M + 1), np.int64)
+    np.add.at(counts, (pl_b, pl_m + 1), 1)
+    model_off = np.cumsum(counts, axis=1).astype(np.uint16)
+
+    return EncodedBatch(B, M, max(G, 1), max(P, 1), max(T, 1), S, C, model_off, model_rep,
+                        group_info, n_groups, placed_per_b.astype(np.int64))
+
+
+class BatchResult:
+    """Outputs of one launch, as numpy arrays on the host."""
+    __slots__ = ("model_num_requests", "model_num_good", "group_num_requests",
+                 "group_num_good", "good_total", "latency_sum", "status", "finish", "good")
+
+
+def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+            latency, latency_stride, flags, want_group_good, pinned=False):
+    """Uploads the tables, runs mms_sim_mixed on the current stream, downloads
+    the results.  Returns (BatchResult, h2d_bytes, d2h_bytes)."""
+    _require_cuda()
+    L = nat.lib()
+    dev = trace.device
+    N = trace.num_requests
+    res = BatchResult()
+    with torch.cuda.device(dev):
+        d_off = _to_device(model_off, dev, pinned)
+        d_rep = _to_device(model_rep, dev, pinned)
+        d_info = _to_device(group_info, dev, pinned)
+        d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev, pinned)
+        h2d = model_off.nbytes + model_rep.nbytes + group_info.nbytes
+        cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), _ptr(d_info),
+                               _ptr(d_lat), int(latency_stride))
+        need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), flags)
+        ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        ws = nat.Workspace(_ptr(ws_t), need)
+        i32 = dict(dtype=torch.int32, device=dev)
+        o_mreq = torch.empty((B, max(M, 1)), **i32)
+        o_mgood = torch.empty((B, max(M, 1)), **i32)
+        o_greq = torch.empty((B, G), **i32)
+        o_ggood = torch.empty((B, G), **i32) if want_group_good else None
+        o_total = torch.empty(B, dtype=torch.int64, device=dev)
+        o_lsum = torch.empty(B, dtype=torch.float64, device=dev)
+        o_status = torch.zeros(B, dtype=torch.int32, device=dev)
+        full = bool(flags & nat.FLAG_PER_REQUEST)
+        o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev) if full else None
+        o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev) if full else None
+        out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood),
+                          _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good))
+        tr, plan = trace.c_trace(), trace.c_plan()
+        rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
+                             _ptr(trace.model_hist), ctypes.byref(ws), ctypes.byref(out),
+                             flags, _stream_ptr())
+        nat.check(rc, "mms_sim_mixed")
+        res.model_num_requests = o_mreq.cpu().numpy()[:, :M]
+        res.model_num_good = o_mgood.cpu().numpy()[:, :M]
+        res.group_num_requests = o_greq.cpu().numpy()
+        res.group_num_good = o_ggood.cpu().numpy() if want_group_good else None
+        res.good_total = o_total.cpu().numpy()
+        res.latency_sum = o_lsum.cpu().numpy()
+        res.status = o_status.cpu().numpy().astype(np.uint32)
+        res.finish = o_fin.cpu().numpy()[:, :N] if full else None
+        res.good = o_good.cpu().numpy()[:, :N].astype(bool) if full else None
+        d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
+                                     res.group_num_requests, res.good_total, res.latency_sum,
+                                     res.status))
+        if full:
+            d2h += res.finish.nbytes + res.good.nbytes
+    if np.any(res.status):
+        bad = int(np.flatnonzero(res.status)[0])
+        raise RuntimeError(f"simulator kernel reported status {int(res.status[bad])} "
+                           f"for candidate {bad} (bad table index or capacity overflow)")
+    return res, h2d, d2h
+
+
+def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
+              per_request=False, group_good=False, pinned=False):
+    """Simulates every placement of `enc` against `trace`
+    (simulate_requests_mixed, controller.py:561-628)."""
+    flags = nat.FLAG_PER_REQUEST if per_request else 0
+    res, h2d, d2h = _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
+                            enc.model_off, enc.model_rep, enc.group_info,
+                            table.device(trace.device), 0, flags, group_good, pinned)
+    return res, h2d, d2h
+
+
+def encode_dense(m_id2g_id, num_stages, num_models):
+    """One candidate given as the reference's dense tables (m_id2g_id [M][*]
+    with -1 ending a row, num_stages [G]) -> (model_off, model_rep,
+    group_info, T) with latency column = group id."""
+    m2g = np.asarray(m_id2g_id, dtype=np.int64).reshape(num_models, -1)
+    ns = np.asarray(num_stages, dtype=np.int64)
+    G = len(ns)
+    if G > nat.MAX_GROUPS or (G and ns.max() > nat.MAX_STAGES) or ns.sum() > nat.MAX_SLOTS:
+        raise NotImplementedError("placement too large for the kernels")
+    slot_first = np.cumsum(ns) - ns
+    info = (slot_first | (ns << 8) | (np.arange(G) << 16)).astype(np.uint32).reshape(1, -1)
+    rows, offs = [], [0]
+    for m in range(num_models):
+        row = m2g[m]
+        stop = np.flatnonzero(row < 0)
+        row = row[:stop[0]] if len(stop) else row
+        if len(row) and (row.max() >= G):
+            raise IndexError("group id in m_id2g_id is out of range")
+        rows.append(row | ((slot_first[row] + ns[row] - 1) << 8))
+        offs.append(offs[-1] + len(row))
+    rep = np.concatenate(rows).astype(np.uint16) if rows and offs[-1] else np.zeros(0, np.uint16)
+    if offs[-1] > nat.MAX_PLACED:
+        raise NotImplementedError("too many (group, model) pairs")
+    rep = rep.reshape(1, -1) if len(rep) else np.zeros((1, 1), np.uint16)
+    off = np.asarray(offs, dtype=np.uint16).reshape(1, -1)
+    if info.shape[1] == 0:
+        info = np.zeros((1, 1), np.uint32)
+    return off, rep, info, max(int(ns.sum()), 1)

@@ -1,0 +1,171 @@
+"""Placement datatypes and the batched PlacementEvaluator.
+
+Mirror of alpa_serve/placement_policy/base_policy.py:18-264.  The evaluator
+keeps the reference's constructor and its get_scores / get_stats contract
+(list of candidate placements in, list of scores or stats tuples out), but
+scores the whole list with one GPU launch instead of one simulator call per
+candidate (base_policy.py:175-189).
+"""
+import dataclasses
+from typing import List, Sequence
+
+import numpy as np
+
+from . import engine
+from .profiling import ParallelConfig, ProfilingResult  # noqa: F401 (re-exported)
+from .simulator import fast_stats, workload_arrays
+from .workload import GammaProcess, Workload
+
+inf = 1e100      # alpa_serve/util.py:23
+
+
+@dataclasses.dataclass
+class ModelPlacement:
+    """base_policy.py:18-55: the parallel config of every device group and
+    the model ids each group serves."""
+    group_configs: Sequence[ParallelConfig]
+    group_models: Sequence[Sequence[int]]
+
+    def add_model(self, group_id: int, model_id: int):
+        models = list(self.group_models)
+        models[group_id] = list(models[group_id]) + [model_id]
+        return ModelPlacement(self.group_configs, models)
+
+    def normalize(self):
+        """Sort the models inside each group, then the groups by their model
+        tuple (base_policy.py:29-35)."""
+        models = tuple(tuple(sorted(ms)) for ms in self.group_models)
+        order = sorted(range(len(models)), key=lambda i: models[i])
+        return ModelPlacement(tuple(self.group_configs[i] for i in order),
+                              tuple(models[i] for i in order))
+
+    def copy(self):
+        return ModelPlacement(list(self.group_configs), [list(ms) for ms in self.group_models])
+
+    def verify(self, model_datas, cluster_env):
+        """base_policy.py:41-55: every group fits the memory budget and holds
+        each model at most once."""
+        for c, ms in zip(self.group_configs, self.group_models):
+            mem = sum(_weight_mem(model_datas[m], c) for m in ms)
+            assert mem <= cluster_env.mem_budget
+            assert len(set(ms)) == len(ms)
+
+
+@dataclasses.dataclass
+class ModelPlacementWithReplacement:
+    """base_policy.py:58-68: placements[k] is in force from start_times[k]."""
+    start_times: List[float]
+    placements: List[ModelPlacement]
+
+    def verify(self, model_datas, cluster_env):
+        for p in self.placements:
+            p.verify(model_datas, cluster_env)
+
+    def __str__(self):
+        return f"ModelPlacementWithReplacement(num_segments={len(self.placements)})"
+
+
+@dataclasses.dataclass
+class ModelData:
+    """base_policy.py:71-77."""
+    name: str
+    slo: float
+    rate: float
+    cv: float
+    profiling_result: ProfilingResult
+
+
+@dataclasses.dataclass
+class ClusterEnv:
+    """base_policy.py:80-84."""
+    num_devices: int
+    mem_budget: float
+    num_devices_per_node: int = 8
+
+
+def _weight_mem(model_data, config):
+    entry = model_data.profiling_result.para_dict.get(config)
+    return max(entry.weight_mem) if entry is not None else inf
+
+
+def gen_train_workload(model_datas, seed: int = 0, simulation_min_duration: float = 100,
+                       simulation_min_samples: int = 30000) -> Workload:
+    """The trace a search trains on when none is given (base_policy.py:267-281):
+    one Gamma process per model, seed + model index, merged."""
+    total_rate = sum(d.rate for d in model_datas)
+    duration = max(simulation_min_duration, simulation_min_samples / total_rate)
+    parts = [GammaProcess(d.rate, d.cv).generate_workload(d.name, 0, duration=duration,
+                                                          slo=d.slo, seed=seed + i)
+             for i, d in enumerate(model_datas)]
+    return Workload.merge(*parts)
+
+
+class PlacementEvaluator:
+    """Scores candidate placements on the GPU (base_policy.py:143-264).
+
+    `method` must be "fast_simulator" (the only method the reference's
+    searches use); `parallel` is accepted for signature compatibility and
+    ignored — the batch is the parallelism.
+    """
+
+    def __init__(self, model_datas, cluster_env, workload, method: str = "fast_simulator",
+                 parallel: bool = False, device=None):
+        if method != "fast_simulator":
+            raise NotImplementedError("only the fast_simulator method runs on the GPU")
+        self.parallel = parallel
+        self.model_datas = model_datas
+        self.cluster_env = cluster_env
+        self.workload = workload
+        self.method = method
+        workload.cached_data = None                    # base_policy.py:155
+        workload.enable_simulator_cache = True         # base_policy.py:170
+        self.model_names = tuple(d.name for d in model_datas)
+        self.prof_ress = tuple(d.profiling_result for d in model_datas)
+        model_ids, slos = workload_arrays(workload, self.model_names)
+        workload.cached_data = (model_ids, slos, self.model_names, self.prof_ress)
+        self.trace = engine.DeviceTrace(workload.arrivals, model_ids, slos,
+                                        len(self.model_names), device=device)
+        self.table = engine.LatencyTable(self.prof_ress)
+        self.last_h2d_bytes = 0
+        self.last_d2h_bytes = 0
+
+    # -- the batched core ---------------------------------------------------
+    def evaluate(self, sols: Sequence[ModelPlacement], pinned=False):
+        """One launch for the whole list; returns (EncodedBatch, BatchResult)."""
+        enc = engine.encode_placements(sols, self.table, len(self.model_names))
+        res, h2d, d2h = engine.run_batch(self.trace, enc, self.table, pinned=pinned)
+        self.last_h2d_bytes, self.last_d2h_bytes = h2d, d2h
+        return enc, res
+
+    def scores_from(self, enc, res) -> List[float]:
+        """goodput - latency_mean/10000 + num_replicas/1e6 (base_policy.py:225-226)
+        with goodput = np.mean(good), latency_mean = np.mean(finish - start)."""
+        n = self.trace.num_requests
+        goodput = res.good_total.astype(np.float64) / n
+        latency_mean = res.latency_sum / n
+        scores = goodput - latency_mean / 10000 + enc.num_replicas / 1000000
+        return [np.float64(s) for s in scores]
+
+    # -- the reference's interface --------------------------------------------
+    def get_scores(self, sols: Sequence[ModelPlacement]) -> List[float]:
+        if not len(sols):
+            return []
+        enc, res = self.evaluate(sols)
+        return self.scores_from(enc, res)
+
+    def get_stats(self, sols: Sequence[ModelPlacement]):
+        """[(goodput, per-model goodput, group_num_requests, StatsResult)]
+        per candidate (base_policy.py:228-264)."""
+        if not len(sols):
+            return []
+        enc, res = self.evaluate(sols)
+        start = self.trace.host_arrivals
+        out = []
+        for b in range(enc.B):
+            g = int(enc.num_groups[b])
+            stats = fast_stats(self.model_names, start, res.latency_sum[b], res.good_total[b],
+                               res.model_num_requests[b], res.model_num_good[b],
+                               res.group_num_requests[b, :g])
+            out.append((stats.goodput, [x.goodput for x in stats.per_model_stats],
+                        stats.group_num_requests, stats))
+        return out

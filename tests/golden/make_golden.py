@@ -1,0 +1,172 @@
+"""Generates the golden fixtures in this directory from the LIVE reference.
+
+Run on a machine that has the reference checkout (see oracle/reference.py):
+
+    python tests/golden/make_golden.py
+
+Every fixture holds seeded inputs together with what the reference's own
+code (numba kernels, the pure-Python batching simulator, PlacementEvaluator)
+returned for them.  The tests compare the CPU checker and the CUDA path
+against these files; nothing at test time needs the reference.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from mms_b200 import cases  # noqa: E402
+from oracle import reference  # noqa: E402
+
+
+def digest(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def random_kernel_inputs(seed, N=4000, M=12, G=6, S=4, batch_cols=0):
+    """Inputs for the low-level kernels with every awkward feature at once:
+    unknown models (-1), a model without replica, groups with 1/2/4 stages,
+    +inf latencies, replicated models, near-tied clocks."""
+    rng = np.random.RandomState(seed)
+    tstamps = np.cumsum(rng.gamma(0.25, 4 * 0.02, size=N))
+    model_ids = rng.randint(-1, M, size=N).astype(np.int32)
+    slos = rng.choice([0.2, 0.35, 0.5, 1.0], size=N).astype(np.float32)
+    num_stages = rng.choice([1, 2, 4], size=G).astype(np.int32)
+    num_stages[0] = S
+    m2g = np.full((M, G), -1, np.int32)
+    for m in range(M - 1):                      # model M-1 stays replica-less
+        reps = np.sort(rng.choice(G, size=rng.randint(1, 4), replace=False))
+        m2g[m, :len(reps)] = reps
+    shape = (M, G, S) if not batch_cols else (M, G, S, batch_cols)
+    lat = rng.uniform(0.005, 0.06, size=shape).astype(np.float32)
+    if batch_cols:
+        lat = np.sort(lat, axis=-1)             # larger batches take longer
+    holes = rng.rand(M, G) < 0.08
+    lat[holes] = np.float32(np.inf)
+    g2m = np.full((G, M), -1, np.int32)
+    fill = [0] * G
+    for m in range(M):
+        for g in m2g[m]:
+            if g >= 0:
+                g2m[g, fill[g]] = m
+                fill[g] += 1
+    return tstamps, model_ids, slos, m2g, g2m, num_stages, lat
+
+
+def main():
+    ref = reference.load()
+    C = ref.controller
+
+    # ---- low-level kernels -------------------------------------------------
+    ts, mid, slo, m2g, g2m, ns, lat = random_kernel_inputs(11)
+    N = len(ts)
+    fin = np.empty(N); good = np.empty(N, bool)
+    cnt = C.simulate_requests_mixed(fin, good, ts, mid, slo, m2g, ns, lat, N)
+    np.savez_compressed(os.path.join(HERE, "kernel_mixed.npz"), tstamps=ts, model_ids=mid,
+                        slos=slo, m_id2g_id=m2g, num_stages=ns, stage_latency=lat,
+                        finish=fin, good=good, model_num_requests=cnt[0],
+                        model_num_good=cnt[1], group_num_requests=cnt[2],
+                        group_num_good=cnt[3])
+
+    gmax = lat.max(axis=2); gsum = lat.sum(axis=2, dtype=np.float32)
+    fin = np.empty(N); good = np.empty(N, bool)
+    cnt = C.simulate_requests(fin, good, ts, mid, slo, m2g, gmax, gsum, N)
+    np.savez_compressed(os.path.join(HERE, "kernel_legacy.npz"), tstamps=ts, model_ids=mid,
+                        slos=slo, m_id2g_id=m2g, group_max_latency=gmax,
+                        group_sum_latency=gsum, finish=fin, good=good,
+                        model_num_requests=cnt[0], model_num_good=cnt[1],
+                        group_num_requests=cnt[2], group_num_good=cnt[3])
+
+    ref.util.batchsize_config[:] = [1, 2, 4, 8]
+    ts, mid, slo, m2g, g2m, ns, lat = random_kernel_inputs(12, N=3000, batch_cols=4)
+    N = len(ts)
+    fin = np.empty(N); good = np.empty(N, bool)
+    cnt = C.simulate_requests_mixed_batching(fin, good, ts, mid, slo, m2g, g2m, ns, lat, N)
+    np.savez_compressed(os.path.join(HERE, "kernel_batching.npz"), tstamps=ts, model_ids=mid,
+                        slos=slo, m_id2g_id=m2g, g_id2m_id=g2m, num_stages=ns,
+                        stage_latency=lat, batchsize_config=np.array([1, 2, 4, 8], np.int32),
+                        finish=fin, good=good, model_num_requests=cnt[0],
+                        model_num_good=cnt[1], group_num_requests=cnt[2],
+                        group_num_good=cnt[3])
+
+    # ---- the fixed 4 x pp2 placement, full size ------------------------------
+    case = cases.fixed_pipeline_case()
+    datas, env, rw, pls = reference.to_reference_case(case)
+    names = [d.name for d in datas]; profs = [d.profiling_result for d in datas]
+    n2i = {m: i for i, m in enumerate(names)}
+    mids = np.array([n2i.get(r.model_name, -1) for r in rw.requests], dtype=np.int32)
+    slos = np.array([r.slo for r in rw.requests], dtype=np.float32)
+    (start, fin, good, mreq, mgood, greq, ggood) = C.approximate_one_case_one_placement(
+        pls[0], names, profs, mids, slos, rw.arrivals)
+    ev = ref.base_policy.PlacementEvaluator(datas, env, rw, "fast_simulator", False)
+    score = ev.get_scores(pls)[0]
+    np.savez_compressed(
+        os.path.join(HERE, "case_fixed_pipeline.npz"),
+        num_requests=len(start), arrivals_sha256=digest(rw.arrivals),
+        model_ids_sha256=digest(mids), finish_sha256=digest(fin),
+        good_sha256=digest(good.astype(np.uint8)), finish_head=fin[:2048], good_head=good[:2048],
+        model_num_requests=mreq, model_num_good=mgood, group_num_requests=greq,
+        group_num_good=ggood, goodput=np.mean(good), latency_mean=np.mean(fin - start),
+        score=score)
+
+    # ---- a candidate batch, shrunk (two minutes of the one-hour trace) ------------
+    case = cases.candidate_batch_case(num_candidates=48, duration=120.0)
+    datas, env, rw, pls = reference.to_reference_case(case)
+    ev = ref.base_policy.PlacementEvaluator(datas, env, rw, "fast_simulator", False)
+    scores = np.array(ev.get_scores(pls), dtype=np.float64)
+    stats = ev.get_stats(pls)
+    M = len(datas)
+    G = max(len(p.group_configs) for p in pls)
+    greq = np.zeros((len(pls), G), np.int32)
+    mgood_rate = np.zeros((len(pls), M))
+    goodput = np.zeros(len(pls)); lat_mean = np.zeros(len(pls))
+    for b, (gp, per_model, group_req, full) in enumerate(stats):
+        greq[b, :len(group_req)] = group_req
+        mgood_rate[b] = per_model
+        goodput[b] = gp
+        lat_mean[b] = full.latency_mean
+    names = [d.name for d in datas]; profs = [d.profiling_result for d in datas]
+    mids, slos = rw.cached_data[0], rw.cached_data[1]
+    fins = np.zeros((4, len(rw.arrivals))); goods = np.zeros((4, len(rw.arrivals)), bool)
+    for b in range(4):
+        out = C.approximate_one_case_one_placement(pls[b], names, profs, mids, slos, rw.arrivals)
+        fins[b], goods[b] = out[1], out[2]
+    np.savez_compressed(
+        os.path.join(HERE, "case_candidates.npz"),
+        num_candidates=len(pls), duration=120.0, num_requests=len(rw.arrivals),
+        arrivals_sha256=digest(rw.arrivals), scores=scores, goodput=goodput,
+        latency_mean=lat_mean, model_goodput=mgood_rate, group_num_requests=greq,
+        finish_first4=fins, good_first4=goods)
+
+    # ---- the same with batching (pure-Python reference: keep it small) ------------
+    case = cases.candidate_batch_case(num_candidates=12, duration=60.0, batching=True)
+    datas, env, rw, pls = reference.to_reference_case(case)
+    names = [d.name for d in datas]; profs = [d.profiling_result for d in datas]
+    n2i = {m: i for i, m in enumerate(names)}
+    mids = np.array([n2i.get(r.model_name, -1) for r in rw.requests], dtype=np.int32)
+    slos = np.array([r.slo for r in rw.requests], dtype=np.float32)
+    N = len(rw.arrivals)
+    fins = np.zeros((len(pls), N)); goods = np.zeros((len(pls), N), bool)
+    mgood = np.zeros((len(pls), M), np.int32); mreq = np.zeros((len(pls), M), np.int32)
+    G = max(len(p.group_configs) for p in pls)
+    greq = np.zeros((len(pls), G), np.int32); ggood = np.zeros((len(pls), G), np.int32)
+    for b, p in enumerate(pls):
+        out = C.approximate_one_case_one_placement(p, names, profs, mids, slos, rw.arrivals,
+                                                   enable_batching=True)
+        fins[b], goods[b] = out[1], out[2]
+        mreq[b], mgood[b] = out[3], out[4]
+        greq[b, :len(out[5])] = out[5]; ggood[b, :len(out[6])] = out[6]
+    np.savez_compressed(
+        os.path.join(HERE, "case_candidates_batching.npz"),
+        num_candidates=len(pls), duration=60.0, num_requests=N,
+        arrivals_sha256=digest(rw.arrivals), finish=fins, good=goods,
+        model_num_requests=mreq, model_num_good=mgood, group_num_requests=greq,
+        group_num_good=ggood)
+    print("golden fixtures written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,123 @@
+"""The CPU checker against the golden outputs of the live reference."""
+import hashlib
+
+import numpy as np
+import pytest
+
+from mms_b200 import cases
+from mms_b200.simulator import workload_arrays
+from oracle import cpu, tables
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def same_counters(got, g):
+    for arr, key in zip(got, ("model_num_requests", "model_num_good", "group_num_requests",
+                              "group_num_good")):
+        assert np.array_equal(arr, g[key]), key
+
+
+def test_mixed_kernel_matches_numba(golden):
+    g = golden("kernel_mixed")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    got = cpu.simulate_requests_mixed(fin, good, g["tstamps"], g["model_ids"], g["slos"],
+                                      g["m_id2g_id"], g["num_stages"], g["stage_latency"], N)
+    assert fin.tobytes() == g["finish"].tobytes()      # bit-exact fp64
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+    assert 0.2 < good.mean() < 0.95                    # both branches are exercised
+
+
+def test_legacy_kernel_matches_numba(golden):
+    g = golden("kernel_legacy")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    got = cpu.simulate_requests(fin, good, g["tstamps"], g["model_ids"], g["slos"],
+                                g["m_id2g_id"], g["group_max_latency"],
+                                g["group_sum_latency"], N)
+    assert fin.tobytes() == g["finish"].tobytes()
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+
+
+def test_batching_kernel_matches_python_reference(golden):
+    g = golden("kernel_batching")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    got = cpu.simulate_requests_mixed_batching(
+        fin, good, g["tstamps"], g["model_ids"], g["slos"], g["m_id2g_id"], g["g_id2m_id"],
+        g["num_stages"], g["stage_latency"], N, tuple(g["batchsize_config"]))
+    assert fin.tobytes() == g["finish"].tobytes()
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+
+
+def test_fixed_pipeline_case_full_size(golden):
+    g = golden("case_fixed_pipeline")
+    case = cases.fixed_pipeline_case()
+    w = case.workload
+    assert len(w) == int(g["num_requests"])
+    assert sha(w.arrivals) == str(g["arrivals_sha256"])   # numpy's Gamma stream is unchanged
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(w, names)
+    assert sha(mids) == str(g["model_ids_sha256"])
+    fin, good, mreq, mgood, greq, ggood = tables.one_placement(
+        case.placements[0], profs, mids, slos, w.arrivals)
+    assert sha(fin) == str(g["finish_sha256"])
+    assert sha(good.astype(np.uint8)) == str(g["good_sha256"])
+    same_counters((mreq, mgood, greq, ggood), g)
+    assert np.mean(good) == float(g["goodput"])
+    assert cpu.latency_mean(fin, w.arrivals) == float(g["latency_mean"])
+    assert tables.score(case.placements[0], fin, good, w.arrivals) == float(g["score"])
+
+
+def test_candidate_batch_scores(golden):
+    g = golden("case_candidates")
+    case = cases.candidate_batch_case(num_candidates=int(g["num_candidates"]),
+                                      duration=float(g["duration"]))
+    w = case.workload
+    assert sha(w.arrivals) == str(g["arrivals_sha256"])
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(w, names)
+    for b, p in enumerate(case.placements):
+        fin, good, mreq, mgood, greq, _ = tables.one_placement(p, profs, mids, slos, w.arrivals)
+        assert tables.score(p, fin, good, w.arrivals) == g["scores"][b]
+        assert np.array_equal(greq, g["group_num_requests"][b, :len(greq)])
+        assert np.array_equal(mgood / (mreq + 1e-6), g["model_goodput"][b])
+        if b < 4:
+            assert fin.tobytes() == g["finish_first4"][b].tobytes()
+            assert np.array_equal(good, g["good_first4"][b])
+
+
+def test_candidate_batch_with_batching(golden):
+    g = golden("case_candidates_batching")
+    case = cases.candidate_batch_case(num_candidates=int(g["num_candidates"]),
+                                      duration=float(g["duration"]), batching=True)
+    w = case.workload
+    assert sha(w.arrivals) == str(g["arrivals_sha256"])
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(w, names)
+    for b, p in enumerate(case.placements):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(
+            p, profs, mids, slos, w.arrivals, batchsize_config=(1, 2, 4, 8))
+        assert fin.tobytes() == g["finish"][b].tobytes(), b
+        assert np.array_equal(good, g["good"][b])
+        assert np.array_equal(mreq, g["model_num_requests"][b])
+        assert np.array_equal(mgood, g["model_num_good"][b])
+        assert np.array_equal(greq, g["group_num_requests"][b, :len(greq)])
+        assert np.array_equal(ggood, g["group_num_good"][b, :len(ggood)])
+
+
+@pytest.mark.parametrize("n", [0, 1, 5, 7, 8, 9, 100, 127, 128, 129, 136, 1000, 4097, 57949,
+                               180715])
+def test_pairwise_sum_is_numpys_order(n):
+    a = np.random.RandomState(n).gamma(0.3, 1.0, size=n)
+    assert cpu.pairwise_sum(a) == float(np.add.reduce(a))
+    if n:
+        assert cpu.pairwise_sum(a) / n == float(np.mean(a))

@@ -1,0 +1,329 @@
+"""Benchmark of the placement-evaluation hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload: the batched candidate evaluation — 4096 random placements of 32
+models on 64 devices scored against one one-hour Gamma trace (about 180 k
+requests).  One step = one pass of the simulator over the whole batch.
+Metric: candidate-placements x requests simulated per second.  Prints one
+JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "candidate_placements_x_requests_per_sec"
+UNIT = "candidate*request/s"
+BYTES_PER_UNIT = 16          # f64 arrival + i32 model id + f32 slo, read once per candidate
+NUM_CANDIDATES = 4096
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--candidates", type=int, default=NUM_CANDIDATES)
+    ap.add_argument("--duration", type=float, default=3600.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--chunk", type=int, default=0, help="requests per chunk (0 auto, <0 one)")
+    ap.add_argument("--run-in", type=int, default=0, help="run-in requests per chunk (0 auto)")
+    return ap.parse_args()
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clocks and throttle reasons while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index = index
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _poll(self):
+        try:
+            out = subprocess.run(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+            f = [x.strip() for x in out.strip().splitlines()[0].split(",")]
+            self.samples.append(float(f[0]))
+            self.max_mhz = float(f[1])
+            for name, v in zip(self.NAMES, f[2:]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._poll()
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def build_case(args, placement_seed):
+    from mms_b200 import cases
+    return cases.candidate_batch_case(num_candidates=args.candidates, duration=args.duration,
+                                      placement_seed=placement_seed)
+
+
+def dense_batch(case, count):
+    """Dense per-candidate tables for the CPU checker (untimed set-up)."""
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    sols = case.placements[:count]
+    G = max(len(p.group_configs) for p in sols)
+    M = len(profs)
+    m2g = np.full((len(sols), M, G), -1, np.int32)
+    ns = np.ones((len(sols), G), np.int32)
+    S = max(c.pp for p in sols for c in p.group_configs)
+    lat = np.full((len(sols), M, G, S), np.float32(np.inf), np.float32)
+    for b, p in enumerate(sols):
+        a, _, n, l = tables.dense_tables(p, profs)
+        g = len(n)
+        m2g[b, :, :g] = a[:, :g]
+        ns[b, :g] = n
+        lat[b, :, :g, :l.shape[2]] = l
+    return mids, slos, m2g, ns, lat
+
+
+def cpu_port_rate(case, count, threads):
+    """Times the C restatement of the reference's numba kernel (plus the
+    reductions the score needs) over `count` candidates on `threads` host
+    threads.  Returns units per second."""
+    from oracle import cpu
+    mids, slos, m2g, ns, lat = dense_batch(case, count)
+    arr = case.workload.arrivals
+    cpu.score_batch(arr, mids, slos, m2g[:threads], ns[:threads], lat[:threads], threads)
+    t0 = time.perf_counter()
+    cpu.score_batch(arr, mids, slos, m2g, ns, lat, threads)
+    dt = time.perf_counter() - t0
+    return count * len(arr) / dt, dt
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (here: the C port of
+    its numba kernel, all host threads), on the same workload and metric."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    case = build_case(args, 0)
+    threads = os.cpu_count() or 1
+    per_step = min(args.candidates, max(threads * 16, 256))
+    rates = []
+    for i in range(args.warmup + args.steps):
+        rate, dt = cpu_port_rate(case, per_step, threads)
+        if i >= args.warmup:
+            rates.append((rate, dt))
+    value = float(np.mean([r for r, _ in rates]))
+    ms = float(np.mean([d for _, d in rates])) * 1e3
+    sample = f"{per_step} of {args.candidates} candidates x {len(case.workload)} requests per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": "candidate-batch: 64 devices, 32 models, 4096 placements, "
+                               "1 h Gamma trace", "num_candidates": args.candidates,
+                   "num_requests": len(case.workload), "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_b200(args):
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+    from mms_b200 import _native as nat
+    from mms_b200 import engine
+    from mms_b200.placement import PlacementEvaluator
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # every rank scores its own 4096 candidates (weak scaling) on the same trace
+    case = build_case(args, placement_seed=rank)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload, device=dev,
+                            options=engine.sim_options(args.chunk, args.run_in))
+    N, B = ev.trace.num_requests, len(case.placements)
+    L = nat.lib()
+
+    # ---- device-resident arm: tables already in HBM, time the C-ABI call ----
+    enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
+    d_off = torch.from_numpy(enc.model_off).to(dev)
+    d_rep = torch.from_numpy(enc.model_rep).to(dev)
+    d_info = torch.from_numpy(enc.group_info).to(dev)
+    d_lat = ev.table.device(dev)
+    P = engine._ptr
+    cands = nat.Placements(enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, 0, P(d_off), P(d_rep),
+                           P(d_info), P(d_lat), 0)
+    opts = engine.sim_options(args.chunk, args.run_in)
+    need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts), 0)
+    ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    ws = nat.Workspace(P(ws_t), need)
+    i32 = dict(dtype=torch.int32, device=dev)
+    o = [torch.empty((B, enc.M), **i32), torch.empty((B, enc.M), **i32),
+         torch.empty((B, enc.G), **i32), torch.empty(B, dtype=torch.int64, device=dev),
+         torch.empty(B, dtype=torch.float64, device=dev), torch.zeros(B, **i32)]
+    redo = torch.zeros(B, **i32)
+    out = nat.Results(P(o[0]), P(o[1]), P(o[2]), None, P(o[3]), P(o[4]), P(o[5]), None, None,
+                      P(redo))
+    tr, plan = ev.trace.c_trace(), ev.trace.c_plan()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB of L2
+    best = torch.zeros(2, dtype=torch.float64, device=dev)
+    gathered = torch.zeros(2 * world, dtype=torch.float64, device=dev)
+
+    def step():
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
+                             P(ev.trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
+                             ctypes.byref(out), 0, stream)
+        nat.check(rc, "mms_sim_mixed")
+        if world > 1:   # the search's argmax over all ranks' candidates
+            score = o[3].double() / N - o[4] / N / 10000
+            top = torch.max(score, dim=0)
+            best[0], best[1] = top.values, (top.indices + rank * B).double()
+            dist.all_gather_into_tensor(gathered, best)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    barrier()
+    times = []
+    with ClockSampler(local) as clk:
+        for _ in range(args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+    barrier()
+    total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    assert int(o[5].abs().sum().item()) == 0, "kernel status words are not clean"
+    units_per_step = B * N * world
+    value = units_per_step * args.steps / (total_ms * 1e-3)
+
+    # ---- end-to-end arm: host buffers in, scores out, through the evaluator ----
+    e2e_times, h2d, d2h = [], 0, 0
+    for i in range(2 + min(args.steps, 3)):
+        barrier()
+        t0 = time.perf_counter()
+        ev.trace = engine.DeviceTrace(case.workload.arrivals, ev.workload.cached_data[0],
+                                      ev.workload.cached_data[1], len(ev.model_names), dev)
+        scores = ev.get_scores(case.placements)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if i >= 2:
+            e2e_times.append(dt)
+        h2d = ev.trace.h2d_bytes + ev.last_h2d_bytes
+        d2h = ev.last_d2h_bytes
+    e2e_t = torch.tensor([float(np.mean(e2e_times))], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = units_per_step / float(e2e_t.item())
+
+    if rank == 0:
+        peak, which = hbm_peak()
+        kern_s = (np.mean(times) * 1e-3)
+        achieved = B * N * BYTES_PER_UNIT / kern_s / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": "candidate-batch: 64 devices, 32 models, 4096 placements "
+                                   "per GPU, 1 h Gamma trace (Zipf 0.9 rates, 50 req/s, CV 3)",
+                       "num_candidates_per_gpu": B, "num_requests": N,
+                       "parallelism": f"candidates sharded over {world} GPU(s)",
+                       "l2": "256 MiB buffer written between timed steps"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": which,
+                         "bytes_per_unit": BYTES_PER_UNIT},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": 3 * args.steps,
+            "chunks_resimulated_per_candidate": float(redo.float().mean().item()),
+            "chunks_resimulated_hist": np.bincount(redo.cpu().numpy()).tolist(),
+            "clocks": clk.summary(),
+            "best_score": float(np.max(scores)),
+        }
+        if not args.no_cpu_baseline:
+            count = min(B, 512)
+            rate, dt = cpu_port_rate(case, count, 1)
+            line["cpu_baseline"] = {
+                "value": rate, "unit": UNIT, "cores": 1, "kind": "port",
+                "sample": f"{count} of {B} candidates x {N} requests, {dt:.1f} s"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

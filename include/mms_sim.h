@@ -38,6 +38,7 @@ extern "C" {
 #define MMS_MAX_SLOTS 256         /* sum of pipeline stages over a candidate     */
 #define MMS_MAX_PLACED 65535      /* (group, model) pairs per candidate          */
 #define MMS_MAX_STAGES 255        /* stages of one group                         */
+#define MMS_MAX_COLUMNS 255       /* columns of the latency table                */
 
 /* status[b] bits */
 #define MMS_STATUS_OK 0u
@@ -63,12 +64,14 @@ typedef struct {
  * [slot, slot + stages) of that candidate's clock vector.
  *
  *  model_off  u16[B][M+1]  CSR offsets into model_rep
- *  model_rep  u16[B][P]    for model m, its groups in ascending group id
+ *  model_rep  u32[B][P]    for model m, its groups in ascending group id
  *                          (row order of m_id2g_id, controller.py:418-422):
- *                          low byte = group id, high byte = that group's
- *                          LAST clock slot
- *  group_info u32[B][G]    bits 0-7 first clock slot, 8-15 stages (pp),
- *                          16-31 column of the latency table
+ *                          bits 0-7 group id, 8-15 the group's first clock
+ *                          slot, 16-23 its stages (pp), 24-31 its column in
+ *                          the latency table
+ *  group_info u32[B][G]    bits 0-7 first clock slot, 8-15 stages (0 = row
+ *                          padding), bit 16 set when the group serves a
+ *                          model that has more than one replica
  *  latency    f32[M][C][S] seconds per stage, already rounded to f32 the way
  *                          controller.py:467-476 does; column = parallel
  *                          config.  With latency_stride != 0 candidate b
@@ -84,14 +87,26 @@ typedef struct {
     int32_t max_placed;            /* P: row length of model_rep                 */
     int32_t max_slots;             /* T: clock slots per candidate (<= 256)      */
     int32_t max_stages;            /* S: last axis of latency                    */
-    int32_t num_columns;           /* C */
+    int32_t num_columns;           /* C (<= 255)                                 */
     int32_t reserved;
     const uint16_t *model_off;
-    const uint16_t *model_rep;
+    const uint32_t *model_rep;
     const uint32_t *group_info;
     const float *latency;
     int64_t latency_stride;        /* elements; 0 = one table for all candidates */
 } mms_placements;
+
+/* How the trace is cut for time-parallel execution.  A candidate's requests
+ * are split into chunks of about chunk_requests; every chunk is simulated
+ * speculatively from idle clocks after warmup_requests of run-in, then a
+ * chain pass keeps a chunk only if the state it started from is equivalent
+ * to the true state at that point and re-simulates it otherwise, so results
+ * never depend on these two numbers.  Zero = let the library choose;
+ * chunk_requests < 0 = one chunk (plain sequential simulation). */
+typedef struct {
+    int32_t chunk_requests;
+    int32_t warmup_requests;
+} mms_sim_options;
 
 /* How numpy sums N doubles (pairwise, blocks of <= 128, eight interleaved
  * partial sums): the order np.mean(finish - start) uses at
@@ -119,6 +134,7 @@ typedef struct {
     uint32_t *status;              /* u32[B]                                     */
     double *finish;                /* f64[B][N] with MMS_FLAG_PER_REQUEST        */
     uint8_t *good;                 /* u8[B][N]  with MMS_FLAG_PER_REQUEST        */
+    int32_t *resimulated;          /* i32[B] or NULL: chunks the chain pass redid */
 } mms_results;
 
 /* Library and device -------------------------------------------------------*/
@@ -133,21 +149,24 @@ int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start /*host*/,
                       uint8_t *leaf_merges /*host*/);
 
 /* Per-model request counts of a trace (model_num_requests of
- * controller.py:587 does not depend on the placement). hist: i32[M]. */
+ * controller.py:587 does not depend on the placement).  hist: i32[M+1]; the
+ * last entry counts positions where the arrival times are not finite or
+ * decrease — the time-parallel path needs it to be 0 and the kernels fall
+ * back to one chunk per candidate when it is not. */
 int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models,
                               int32_t *hist, void *stream);
 
-/* Bytes of scratch mms_sim_mixed needs for this shape. */
+/* Bytes of scratch mms_sim_mixed needs for this shape and these options. */
 size_t mms_sim_workspace_bytes(int64_t num_requests, const mms_placements *cands,
-                               uint32_t flags);
+                               const mms_sim_options *opts, uint32_t flags);
 
 /* simulate_requests_mixed (controller.py:561-628) — or simulate_requests
  * (controller.py:506-558) with MMS_FLAG_LEGACY_CLOCK — for every candidate,
  * followed by the fast_stats reductions of controller.py:393-403. */
 int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands,
                   const mms_sum_plan *plan, const int32_t *model_hist,
-                  const mms_workspace *ws, const mms_results *out,
-                  uint32_t flags, void *stream);
+                  const mms_sim_options *opts, const mms_workspace *ws,
+                  const mms_results *out, uint32_t flags, void *stream);
 
 #ifdef __cplusplus
 }

@@ -21,6 +21,7 @@ MAX_GROUPS = 255
 MAX_SLOTS = 256
 MAX_PLACED = 65535
 MAX_STAGES = 255
+MAX_COLUMNS = 255
 
 STATUS_HEAP_OVERFLOW = 1
 STATUS_QUEUE_LEFT = 2
@@ -52,6 +53,10 @@ class Placements(ctypes.Structure):
                 ("latency_stride", ctypes.c_int64)]
 
 
+class SimOptions(ctypes.Structure):
+    _fields_ = [("chunk_requests", ctypes.c_int32), ("warmup_requests", ctypes.c_int32)]
+
+
 class SumPlan(ctypes.Structure):
     _fields_ = [("num_leaves", ctypes.c_int32), ("reserved", ctypes.c_int32),
                 ("leaf_start", _vp), ("leaf_merges", _vp)]
@@ -64,7 +69,8 @@ class Workspace(ctypes.Structure):
 class Results(ctypes.Structure):
     _fields_ = [("model_num_requests", _vp), ("model_num_good", _vp),
                 ("group_num_requests", _vp), ("group_num_good", _vp), ("good_total", _vp),
-                ("latency_sum", _vp), ("status", _vp), ("finish", _vp), ("good", _vp)]
+                ("latency_sum", _vp), ("status", _vp), ("finish", _vp), ("good", _vp),
+                ("resimulated", _vp)]
 
 
 _lib = None
@@ -90,11 +96,12 @@ def lib():
     L.mms_trace_model_histogram.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_sim_workspace_bytes.restype = ctypes.c_size_t
     L.mms_sim_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
-                                          ctypes.c_uint32]
+                                          ctypes.POINTER(SimOptions), ctypes.c_uint32]
     L.mms_sim_mixed.restype = ctypes.c_int
     L.mms_sim_mixed.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
-                                ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(Workspace),
-                                ctypes.POINTER(Results), ctypes.c_uint32, _vp]
+                                ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(SimOptions),
+                                ctypes.POINTER(Workspace), ctypes.POINTER(Results),
+                                ctypes.c_uint32, _vp]
     _lib = L
     return L
 

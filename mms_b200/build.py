@@ -10,7 +10,10 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 REPO_DIR = os.path.dirname(PKG_DIR)
 LIB_PATH = os.path.join(PKG_DIR, "libmms_sim.so")
 SOURCES = [os.path.join(PKG_DIR, "csrc", "mms_sim.cu")]
-HEADERS = [os.path.join(REPO_DIR, "include", "mms_sim.h")]
+HEADERS = [os.path.join(REPO_DIR, "include", "mms_sim.h"),
+           os.path.join(PKG_DIR, "csrc", "sim_core.cuh"),
+           os.path.join(PKG_DIR, "csrc", "sim_chunk.cuh"),
+           os.path.join(PKG_DIR, "csrc", "mms_abi.inl")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

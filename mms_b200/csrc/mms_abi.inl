@@ -1,0 +1,277 @@
+// mms_abi.inl — host side of the C ABI (included at the end of mms_sim.cu).
+namespace mms {
+
+thread_local char g_last_error[256] = "";
+
+static int cuda_fail(cudaError_t e, const char *what)
+{
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    return MMS_ERR_CUDA;
+}
+
+#define MMS_CUDA(call)                                             \
+    do {                                                           \
+        cudaError_t e_ = (call);                                   \
+        if (e_ != cudaSuccess) return mms::cuda_fail(e_, #call);   \
+    } while (0)
+
+// numpy's pairwise split of n elements starting at `base`.
+static void plan_rec(int64_t base, int64_t n, int32_t *leaf_start, uint8_t *merges, int32_t &count)
+{
+    if (n <= 128) {
+        if (leaf_start) { leaf_start[count] = (int32_t)base; merges[count] = 0; }
+        ++count;
+        return;
+    }
+    int64_t half = n / 2;
+    half -= half % 8;
+    plan_rec(base, half, leaf_start, merges, count);
+    plan_rec(base + half, n - half, leaf_start, merges, count);
+    if (merges) merges[count - 1] += 1;
+}
+
+static int32_t plan_leaves(int64_t n)
+{
+    if (n <= 0) return 0;
+    int32_t count = 0;
+    plan_rec(0, n, nullptr, nullptr, count);
+    return count;
+}
+
+struct Geometry {
+    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters;
+    size_t smem_stream, smem_repair;
+    size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items;
+    size_t total;
+};
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// Chunking, shared-memory and scratch geometry of one call.
+static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *opts,
+                     uint32_t flags, bool group_good, Geometry *g)
+{
+    if (!c || N < 0 || c->num_candidates < 0 || c->num_models < 0 || c->max_groups < 0 ||
+        c->max_placed < 0 || c->max_slots < 0 || c->max_stages < 1 || c->num_columns < 0)
+        return MMS_ERR_ARG;
+    if (N > 0x7FFFFFFF) return MMS_ERR_UNSUPPORTED;
+    if (c->max_groups > MMS_MAX_GROUPS || c->max_slots > MMS_MAX_SLOTS ||
+        c->max_placed > MMS_MAX_PLACED || c->max_stages > MMS_MAX_STAGES ||
+        c->num_columns > MMS_MAX_COLUMNS)
+        return MMS_ERR_UNSUPPORTED;
+    if ((flags & MMS_FLAG_LEGACY_CLOCK) && c->max_stages != 2) return MMS_ERR_ARG;
+
+    const int64_t B = c->num_candidates;
+    int64_t chunk = opts ? opts->chunk_requests : 0;
+    int64_t warm = opts ? opts->warmup_requests : 0;
+    // segments: the unit of state snapshots, counter flushes and repairs
+    const int64_t seg = 1024;
+    const int64_t NS = N / seg > 0 ? N / seg : 1;
+    int64_t spc;                                   // segments per chunk
+    if (chunk < 0 || N < 8192 || B == 0) {
+        spc = NS;
+    } else if (chunk > 0) {
+        spc = (chunk + seg / 2) / seg;
+    } else {
+        // enough streams for about three waves of resident warps on 148 SMs,
+        // but never chunks shorter than 4 segments
+        int64_t K = (148LL * 5 * 32 * 3 + B - 1) / B;
+        if (K > NS / 4) K = NS / 4;
+        if (K < 1) K = 1;
+        spc = (NS + K - 1) / K;
+    }
+    if (spc < 1) spc = 1;
+    if (spc > NS) spc = NS;
+    const int64_t K = (NS + spc - 1) / spc;
+    if (warm <= 0) warm = 2048;
+    g->K = (int32_t)K; g->NS = (int32_t)NS; g->seg_len = (int32_t)seg;
+    g->seg_per_chunk = (int32_t)spc; g->warmup = (int32_t)warm;
+
+    // the shared table goes on chip as f64, with 8 readable entries of padding
+    const size_t lat_elems = (size_t)c->num_models * c->num_columns * c->max_stages + 8;
+    g->lat_smem_elems = (c->latency_stride == 0 && lat_elems * sizeof(double) <= (size_t)kLatSmemBytes)
+                            ? (int32_t)lat_elems : 0;
+    const SmemLayout L = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
+                                     c->max_stages, group_good, g->lat_smem_elems);
+    g->n_counters = L.n_counters;
+    g->smem_stream = L.total;
+    g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
+    g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
+    if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+
+    size_t off = 0;
+    g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
+    g->off_counters = off;    off += align256(sizeof(uint32_t) * (size_t)NS * L.n_counters * B);
+    g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kRepairRounds + 1));
+    g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
+    g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
+    g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
+    g->total = off;
+    return MMS_OK;
+}
+
+template <bool kFull, bool kGroupGood, bool kLegacy>
+static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
+{
+    auto stream_k = sim_stream_kernel<kFull, kGroupGood, kLegacy>;
+    MMS_CUDA(cudaFuncSetAttribute(stream_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)g.smem_stream));
+    const int64_t streams = (int64_t)ka.B * ka.K;
+    stream_k<<<(unsigned)((streams + kLanes - 1) / kLanes), kLanes, g.smem_stream, st>>>(ka);
+    MMS_CUDA(cudaGetLastError());
+    if (ka.K > 1) {
+        auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy>;
+        auto chain_k = sim_chain_kernel<kFull, kGroupGood, kLegacy>;
+        MMS_CUDA(cudaFuncSetAttribute(repair_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)g.smem_repair));
+        MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)g.smem_repair));
+        const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
+        for (int r = 0; r < kRepairRounds; ++r) {
+            ka.round = r;
+            validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(ka);
+            MMS_CUDA(cudaGetLastError());
+            // sized for the worst case; blocks past the work list return at once
+            repair_k<<<(unsigned)((bounds + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
+            MMS_CUDA(cudaGetLastError());
+        }
+        chain_k<<<(unsigned)((ka.B + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
+        MMS_CUDA(cudaGetLastError());
+    }
+    return MMS_OK;
+}
+
+}  // namespace mms
+
+extern "C" {
+
+int mms_abi_version(void) { return 3; }
+
+const char *mms_last_error(void) { return mms::g_last_error; }
+
+int32_t mms_sum_plan_leaves(int64_t num_requests)
+{
+    if (num_requests > 0x7FFFFFFF) return MMS_ERR_UNSUPPORTED;
+    return mms::plan_leaves(num_requests);
+}
+
+int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start, uint8_t *leaf_merges)
+{
+    if (num_requests < 0 || !leaf_start || !leaf_merges) return MMS_ERR_ARG;
+    if (num_requests > 0x7FFFFFFF) return MMS_ERR_UNSUPPORTED;
+    int32_t count = 0;
+    if (num_requests > 0) mms::plan_rec(0, num_requests, leaf_start, leaf_merges, count);
+    leaf_start[count] = (int32_t)num_requests;
+    return MMS_OK;
+}
+
+int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models, int32_t *hist,
+                              void *stream)
+{
+    if (!trace || !hist || num_models < 0 || trace->num_requests < 0) return MMS_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    MMS_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * ((size_t)num_models + 1), st));
+    if (trace->num_requests == 0) return MMS_OK;
+    if (!trace->model_ids || !trace->arrivals) return MMS_ERR_ARG;
+    if (((size_t)num_models + 1) * sizeof(int32_t) > 48 * 1024) return MMS_ERR_UNSUPPORTED;
+    const int threads = 256;
+    int64_t want = (trace->num_requests + threads - 1) / threads;
+    const int blocks = (int)(want < 592 ? want : 592);   // 4 blocks per SM on 148 SMs
+    mms::histogram_kernel<<<blocks, threads, sizeof(int32_t) * ((size_t)num_models + 1), st>>>(
+        trace->arrivals, trace->model_ids, trace->num_requests, num_models, hist);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
+size_t mms_sim_workspace_bytes(int64_t num_requests, const mms_placements *cands,
+                               const mms_sim_options *opts, uint32_t flags)
+{
+    mms::Geometry g;
+    if (mms::plan_call(num_requests, cands, opts, flags, true, &g) != MMS_OK) return 0;
+    return g.total;
+}
+
+int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms_sum_plan *plan,
+                  const int32_t *model_hist, const mms_sim_options *opts, const mms_workspace *ws,
+                  const mms_results *out, uint32_t flags, void *stream)
+{
+    using namespace mms;
+    if (!trace || !cands || !plan || !ws || !out) return MMS_ERR_ARG;
+    if (flags & ~(MMS_FLAG_PER_REQUEST | MMS_FLAG_LEGACY_CLOCK)) return MMS_ERR_ARG;
+    const int64_t N = trace->num_requests;
+    const bool gg = out->group_num_good != nullptr;
+    Geometry g;
+    int rc = plan_call(N, cands, opts, flags, gg, &g);
+    if (rc) return rc;
+    const int32_t B = cands->num_candidates;
+    if (B == 0) return MMS_OK;
+    if (!out->model_num_requests || !out->model_num_good || !out->group_num_requests ||
+        !out->good_total || !out->latency_sum || !out->status || !model_hist)
+        return MMS_ERR_ARG;
+    if (N > 0 && (!trace->arrivals || !trace->model_ids || !trace->slos)) return MMS_ERR_ARG;
+    if (!cands->model_off || !cands->group_info || !cands->model_rep || !cands->latency)
+        return MMS_ERR_ARG;
+    const bool full = (flags & MMS_FLAG_PER_REQUEST) != 0;
+    if (full && N > 0 && (!out->finish || !out->good)) return MMS_ERR_ARG;
+    if (plan->num_leaves != plan_leaves(N)) return MMS_ERR_ARG;
+    if (plan->num_leaves > 0 && (!plan->leaf_start || !plan->leaf_merges)) return MMS_ERR_ARG;
+    if (g.total > 0 && (!ws->ptr || ws->bytes < g.total)) return MMS_ERR_ARG;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char *scratch = (unsigned char *)ws->ptr;
+    KernelArgs ka;
+    memset(&ka, 0, sizeof(ka));
+    ka.arrivals = trace->arrivals; ka.model_ids = trace->model_ids; ka.slos = trace->slos;
+    ka.N = N; ka.model_hist = model_hist;
+    ka.B = B; ka.M = cands->num_models; ka.G = cands->max_groups; ka.P = cands->max_placed;
+    ka.T = cands->max_slots; ka.S = cands->max_stages; ka.C = cands->num_columns;
+    ka.model_off = cands->model_off; ka.model_rep = cands->model_rep;
+    ka.group_info = cands->group_info; ka.latency = cands->latency;
+    ka.latency_stride = cands->latency_stride;
+    ka.lat_smem_elems = g.lat_smem_elems;
+    ka.K = g.K; ka.NS = g.NS; ka.seg_len = g.seg_len; ka.seg_per_chunk = g.seg_per_chunk;
+    ka.warmup = g.warmup;
+    ka.num_leaves = plan->num_leaves; ka.leaf_start = plan->leaf_start;
+    ka.leaf_sums = (double *)(scratch + g.off_leaf);
+    ka.seg_counters = (uint32_t *)(scratch + g.off_counters);
+    ka.work_count = (uint32_t *)(scratch + g.off_work_count);
+    ka.work_items = (uint32_t *)(scratch + g.off_work_items);
+    ka.seg_end = (double *)(scratch + g.off_seg_end);
+    ka.chunk_start = (double *)(scratch + g.off_chunk_start);
+    ka.status = out->status;
+    ka.finish = out->finish; ka.good = out->good;
+    ka.resimulated = out->resimulated;
+
+    MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)B, st));
+    MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kRepairRounds + 1), st));
+    if (out->resimulated)
+        MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)B, st));
+    const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;
+    const int variant = (full ? 4 : 0) | (gg ? 2 : 0) | (legacy ? 1 : 0);
+    switch (variant) {
+        case 0: rc = launch_sim<false, false, false>(ka, g, st); break;
+        case 1: rc = launch_sim<false, false, true>(ka, g, st); break;
+        case 2: rc = launch_sim<false, true, false>(ka, g, st); break;
+        case 3: rc = launch_sim<false, true, true>(ka, g, st); break;
+        case 4: rc = launch_sim<true, false, false>(ka, g, st); break;
+        case 5: rc = launch_sim<true, false, true>(ka, g, st); break;
+        case 6: rc = launch_sim<true, true, false>(ka, g, st); break;
+        default: rc = launch_sim<true, true, true>(ka, g, st); break;
+    }
+    if (rc) return rc;
+
+    const int threads = 128;
+    const int64_t cells = (int64_t)B * g.n_counters;
+    sum_counters_kernel<<<(unsigned)((cells + threads - 1) / threads), threads, 0, st>>>(
+        B, ka.M, ka.G, ka.NS, g.n_counters, plan->num_leaves, ka.seg_counters, model_hist,
+        out->model_num_requests, out->model_num_good, out->group_num_requests,
+        out->group_num_good);
+    MMS_CUDA(cudaGetLastError());
+    finalize_kernel<<<(B + 31) / 32, 32, 0, st>>>(
+        B, ka.M, plan->num_leaves, plan->leaf_merges, ka.leaf_sums, out->model_num_good,
+        out->good_total, out->latency_sum, out->status);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,219 @@
+// sim_chunk.cuh — kernel arguments, trace geometry and the chunk runner.
+//
+// Geometry.  The trace is cut at leaf boundaries of numpy's pairwise sum into
+// SEGMENTS of about seg_len requests (the last one takes the remainder); a
+// CHUNK is seg_per_chunk consecutive segments.  Per (candidate, segment) the
+// kernels keep the clock vector at the segment's end and the counters of the
+// segment; per (candidate, chunk) the clock vector the chunk was started
+// from.  All of it is laid out [..][entry][candidate] so that the 32
+// candidates of a warp touch consecutive addresses.
+#pragma once
+#include "sim_core.cuh"
+
+namespace mms {
+
+struct KernelArgs {
+    // trace
+    const double *arrivals;
+    const int32_t *model_ids;
+    const float *slos;
+    int64_t N;
+    const int32_t *model_hist;    // [M + 1]; last entry = unsorted/non-finite positions
+    // placements
+    int32_t B, M, G, P, T, S, C;
+    const uint16_t *model_off;
+    const uint32_t *model_rep;
+    const uint32_t *group_info;
+    const float *latency;
+    int64_t latency_stride;
+    int32_t lat_smem_elems;
+    // geometry
+    int32_t K;                    // chunks
+    int32_t NS;                   // segments
+    int32_t seg_len;              // requests per segment (nominal)
+    int32_t seg_per_chunk;
+    int32_t warmup;               // run-in requests before a speculative chunk
+    // summation plan
+    int32_t num_leaves;
+    const int32_t *leaf_start;
+    // scratch
+    double *leaf_sums;            // [num_leaves][B]
+    double *seg_end;              // [NS][T][B]   clock vector after each segment
+    double *chunk_start;          // [K][T][B]    clock vector each chunk started from
+    uint32_t *seg_counters;       // [NS][n_counters][B]
+    uint32_t *work_count;         // [rounds]
+    uint32_t *work_items;         // [B * K]: chunk * B + candidate
+    int32_t round;
+    // outputs
+    uint32_t *status;             // [B]
+    double *finish;               // [B][N] or null
+    uint8_t *good;                // [B][N] or null
+    int32_t *resimulated;         // [B] or null
+};
+
+// First leaf whose first request is at or after request index `pos`.
+__device__ inline int32_t leaf_lower_bound(const int32_t *leaf_start, int32_t num_leaves,
+                                           int64_t pos)
+{
+    int32_t lo = 0, hi = num_leaves;
+    while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if ((int64_t)leaf_start[mid] < pos) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
+// First leaf of segment q (q == NS: one past the last leaf).
+__device__ inline int32_t seg_leaf(const KernelArgs &a, int32_t q)
+{
+    if (q <= 0) return 0;
+    if (q >= a.NS) return a.num_leaves;
+    return leaf_lower_bound(a.leaf_start, a.num_leaves, (int64_t)q * a.seg_len);
+}
+
+// True when the trace can be cut (sorted, finite arrival times).
+__device__ inline bool can_chunk(const KernelArgs &a)
+{
+    return a.K > 1 && a.model_hist[a.M] == 0;
+}
+
+// Two clock vectors X and Y, taken at a point where every later arrival is
+// >= tau, lead to identical futures (every later finish time, good flag and
+// counter) when
+//  (1) each slot holds the same value in both, or a value < tau in both — a
+//      clock that is already in the past only ever enters max(t, clock) with
+//      t >= tau, so its exact value cannot matter — EXCEPT
+//  (2) the last-stage clock of a group that serves a model with several
+//      replicas: dispatch compares those clocks with '<' (controller.py:595-598),
+//      so for the ones in the past the ORDER among them (ties included) must
+//      agree as well.  A clock in the past is below every clock that is not,
+//      in both vectors, so mixed comparisons agree by (1).
+// Each accepted request overwrites clocks with values >= tau that are equal
+// in both runs, so the relation is preserved step by step, and it is
+// transitive.  LoadX / LoadY map a clock slot to its value.
+template <typename LoadX, typename LoadY, typename Stale>
+__device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X, LoadY Y,
+                                         double tau, Stale stale)
+{
+    int n_stale = 0;
+    for (int g = 0; g < a.G; ++g) {
+        const uint32_t info = a.group_info[(size_t)b * a.G + g];
+        const uint32_t slot = info & 0xFFu, ns = (info >> 8) & 0xFFu;
+        const bool contested = (info >> 16) & 1u;
+        for (uint32_t k = 0; k < ns; ++k) {
+            const double x = X(slot + k), y = Y(slot + k);
+            const bool past = x < tau && y < tau;
+            if (!(x == y || past)) return false;
+            if (past && contested && k == ns - 1 && x != y) stale(n_stale++) = (uint8_t)(slot + k);
+        }
+    }
+    // Order of every past last-stage clock that differs between X and Y
+    // against the last-stage clocks of all contested groups.
+    for (int u = 0; u < n_stale; ++u) {
+        const uint32_t su = stale(u);
+        const double xu = X(su), yu = Y(su);
+        for (int g = 0; g < a.G; ++g) {
+            const uint32_t info = a.group_info[(size_t)b * a.G + g];
+            const uint32_t ns = (info >> 8) & 0xFFu;
+            if (ns == 0 || !((info >> 16) & 1u)) continue;
+            const uint32_t sv = (info & 0xFFu) + ns - 1;
+            const double xv = X(sv), yv = Y(sv);
+            if ((xu < xv) != (yu < yv) || (xu > xv) != (yu > yv)) return false;
+        }
+    }
+    return true;
+}
+
+__device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, int n_counters,
+                                      int32_t q, int64_t b)
+{
+    for (int c = 0; c < n_counters; ++c) {
+        a.seg_counters[((size_t)q * n_counters + c) * a.B + b] = SM_U32(counters + c * kLanes);
+        SM_U32(counters + c * kLanes) = 0;
+    }
+}
+
+// Runs chunk j of candidate b on this lane: requests [begin, first) as run-in
+// (nothing recorded; `first` is the chunk's first request), then the chunk's
+// segments, recording counters, per-request outputs (kFull) and one latency
+// sum per leaf.  Within a leaf the latency of request k goes to partial sum
+// k mod 8, as numpy's pairwise sum does: the eight partial sums rotate
+// through p0 so that the loop holds ONE copy of the step.
+//
+//   speculative (repair == false): the clock vector after the run-in is
+//       stored as the chunk's start state, and every segment's end state.
+//   repair: the lane's clocks already hold the true state at `first`.  After
+//       each segment the new state is compared with the one stored by the
+//       previous run of that segment; once they are equivalent the rest of
+//       the chunk is known to be right already and the lane stops.
+// Returns the number of segments simulated.
+template <bool kFull, bool kGroupGood, bool kLegacy>
+__device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint32_t counters,
+                                    int n_counters, int64_t b, int32_t j, int64_t begin,
+                                    bool repair, bool snapshots, uint32_t old_state,
+                                    uint32_t stale_buf)
+{
+    double *fin_out = kFull ? a.finish + (size_t)b * a.N : nullptr;
+    uint8_t *good_out = kFull ? a.good + (size_t)b * a.N : nullptr;
+    const int32_t q0 = j * a.seg_per_chunk;
+    const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
+    int32_t q = q0;
+    int32_t leaf = seg_leaf(a, q0);
+    int32_t seg_stop = seg_leaf(a, q0 + 1);
+    const int64_t first = leaf < a.num_leaves ? a.leaf_start[leaf] : a.N;
+    leaf -= 1;                      // the run-in counts as a leaf that is not recorded
+    int64_t i = begin, span_end = first;
+    bool record = false;
+    int32_t done = 0;
+    pipe_prime(ln, p, begin);
+    for (;;) {
+        const int64_t body_end = record ? i + ((span_end - i) & ~(int64_t)7) : i;
+        double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
+        double r = 0.0;
+        for (; i < span_end; ++i) {
+            const double d = sim_step<kFull, kGroupGood, kLegacy>(ln, p, i, record, fin_out,
+                                                                  good_out);
+            if (i < body_end) {
+                const double s = p0 + d;
+                p0 = p1; p1 = p2; p2 = p3; p3 = p4; p4 = p5; p5 = p6; p6 = p7; p7 = s;
+                if (i + 1 == body_end)
+                    r = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7));
+            } else {
+                r += d;
+            }
+        }
+        if (!record) {
+            if (!repair && snapshots)   // the state this speculative chunk starts from
+                for (int t = 0; t < a.T; ++t)
+                    a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
+        } else {
+            a.leaf_sums[(size_t)leaf * a.B + b] = r;
+            if (leaf + 1 == seg_stop) {             // segment q is complete
+                ++done;
+                flush_counters(a, counters, n_counters, q, b);
+                bool settled = false;
+                if (repair && snapshots) {
+                    const double tau = a.arrivals[span_end < a.N ? span_end : a.N - 1];
+                    for (int t = 0; t < a.T; ++t)
+                        SM_F64(old_state + t * kLanes) = a.seg_end[((size_t)q * a.T + t) * a.B + b];
+                    settled = span_end < a.N && states_equivalent(
+                        a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
+                        [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
+                        [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
+                }
+                if (settled) return done;
+                if (snapshots)
+                    for (int t = 0; t < a.T; ++t)
+                        a.seg_end[((size_t)q * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
+                if (++q >= q1) return done;
+                seg_stop = seg_leaf(a, q + 1);
+            }
+        }
+        ++leaf;
+        if (leaf >= a.num_leaves) return done;      // only an empty trace gets here
+        record = true;
+        span_end = a.leaf_start[leaf + 1];
+    }
+}
+
+}  // namespace mms

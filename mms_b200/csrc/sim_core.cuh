@@ -1,0 +1,270 @@
+// sim_core.cuh — per-lane simulator state and the per-request step.
+//
+// One THREAD simulates one stream of requests for one candidate placement
+// (alpa_serve/simulator/controller.py:579-622 is the loop body restated in
+// sim_step below).  Mutable state (stage clocks, counters) and the
+// candidate's placement tables live in shared memory as [entry][lane], so
+// lane-private accesses fall on distinct banks.  Everything is addressed by
+// 32-bit element offsets into the block's one dynamic shared array, which
+// keeps the accesses plain LDS/STS with immediate offsets.  The dependent
+// chain per request is kept short: trace values are fetched two requests
+// ahead and the replica list one request ahead (neither depends on simulator
+// state), the clocks of up to 4 replicas and of up to 8 pipeline stages are
+// loaded together, and the max/add chain runs in registers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "mms_sim.h"
+
+namespace mms {
+
+constexpr double kInf = 1e100;          // alpa_serve/util.py:23
+constexpr double kOverhead = 0.011;     // controller.py:575
+constexpr int kLanes = 32;              // streams per block (one warp)
+constexpr int kClockPad = 8;            // readable slots past the last clock
+constexpr int kRepPad = 4;              // readable entries past the last replica
+
+extern __shared__ __align__(16) unsigned char smem[];
+
+#define SM_F64(i) (reinterpret_cast<double *>(smem)[(i)])
+#define SM_U32(i) (reinterpret_cast<uint32_t *>(smem)[(i)])
+#define SM_U16(i) (reinterpret_cast<uint16_t *>(smem)[(i)])
+
+// On-chip replica entry: group | LAST clock slot << 8 | stages << 16 | column << 24.
+// (The caller's model_rep carries the FIRST slot; setup converts.)
+__device__ __forceinline__ uint32_t rep_group(uint32_t e) { return e & 0xFFu; }
+__device__ __forceinline__ uint32_t rep_last(uint32_t e) { return (e >> 8) & 0xFFu; }
+__device__ __forceinline__ uint32_t rep_stages(uint32_t e) { return (e >> 16) & 0xFFu; }
+__device__ __forceinline__ uint32_t rep_column(uint32_t e) { return e >> 24; }
+
+struct SmemLayout {
+    size_t clocks, stage_tmp, latency, counters, model_rep, model_off, total;
+    int n_counters, tmp_stages;
+};
+
+// lat_elems: entries of the shared latency table kept on chip as f64 (0 =
+// read the f32 table from global memory).
+__host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, int S,
+                                                  bool group_good, int lat_elems)
+{
+    SmemLayout L;
+    size_t off = 0;
+    L.clocks = off;     off += sizeof(double) * (size_t)(T + kClockPad) * kLanes;
+    L.tmp_stages = S > 8 ? S - 8 : 0;
+    L.stage_tmp = off;  off += sizeof(double) * (size_t)L.tmp_stages * kLanes;
+    L.latency = off;    off += sizeof(double) * (size_t)lat_elems;
+    L.n_counters = M + G + (group_good ? G : 0);
+    L.counters = off;   off += sizeof(uint32_t) * (size_t)L.n_counters * kLanes;
+    L.model_rep = off;  off += sizeof(uint32_t) * (size_t)(P + kRepPad) * kLanes;
+    L.model_off = off;  off += sizeof(uint16_t) * (size_t)(M + 2) * kLanes;
+    L.total = (off + 15) & ~(size_t)15;
+    return L;
+}
+
+// A lane's view of its state: element offsets into the typed views of the
+// shared array, already including the lane; entries are kLanes apart.
+struct Lane {
+    uint32_t clk;             // f64 index of clock slot 0
+    uint32_t tmp;             // f64 index, stages beyond the 8th of a deep pipeline
+    uint32_t lat_sm;          // f64 index of the on-chip latency table
+    uint32_t model_good;      // u32 index, [M]
+    uint32_t group_req;       // u32 index, [G]
+    uint32_t group_good;      // u32 index, [G]
+    uint32_t moff;            // u16 index, [M + 2]
+    uint32_t mrep;            // u32 index, [P + kRepPad]
+    const float *lat_gl;      // this candidate's table in global memory
+    bool lat_on_chip;
+    int32_t M, C, S;
+    uint32_t status;
+};
+
+// Requests in flight: the current one is ready to execute (its replica list
+// is in registers), the next has its trace values only.
+struct Pipe {
+    double ts; float slo; int32_t m; uint32_t lo, n, e0, e1, e2, e3;
+    double ts1; float slo1; int32_t m1;
+    const double *arrivals; const int32_t *model_ids; const float *slos;
+    int64_t last;             // highest readable request index
+};
+
+__device__ __forceinline__ int32_t clean_model(Lane &ln, int32_t m)
+{
+    if (m >= ln.M) { ln.status |= MMS_STATUS_BAD_INDEX; return -1; }
+    return m;
+}
+
+__device__ __forceinline__ void pipe_tables(const Lane &ln, int32_t m, uint32_t &lo, uint32_t &n,
+                                            uint32_t &e0, uint32_t &e1, uint32_t &e2, uint32_t &e3)
+{
+    const uint32_t mm = m < 0 ? 0u : (uint32_t)m;
+    const uint32_t o = ln.moff + mm * kLanes;
+    lo = SM_U16(o);
+    const uint32_t hi = SM_U16(o + kLanes);
+    n = m < 0 ? 0u : hi - lo;
+    const uint32_t r = ln.mrep + lo * kLanes;
+    e0 = SM_U32(r);
+    e1 = SM_U32(r + kLanes);
+    e2 = SM_U32(r + 2 * kLanes);
+    e3 = SM_U32(r + 3 * kLanes);
+}
+
+// Fills the pipe so that request `i` is ready to execute.
+__device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int64_t i)
+{
+    const int64_t i0 = i < p.last ? i : p.last;
+    const int64_t i1 = i + 1 < p.last ? i + 1 : p.last;
+    p.ts = __ldg(p.arrivals + i0); p.slo = __ldg(p.slos + i0);
+    p.m = clean_model(ln, __ldg(p.model_ids + i0));
+    p.ts1 = __ldg(p.arrivals + i1); p.slo1 = __ldg(p.slos + i1);
+    p.m1 = clean_model(ln, __ldg(p.model_ids + i1));
+    pipe_tables(ln, p.m, p.lo, p.n, p.e0, p.e1, p.e2, p.e3);
+}
+
+// Executes request `i` (controller.py:579-622, or :519-555 with kLegacy) and
+// advances the pipe.  Returns finish - arrival, which is 0.0 for a dropped
+// request (the reference stores finish = arrival for those).
+//   record  update counters and per-request outputs (off during run-in)
+// The step is large; callers keep a single call site per kernel so that the
+// hot loop stays inside the instruction cache.
+template <bool kFull, bool kGroupGood, bool kLegacy>
+__device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int64_t i, bool record,
+                                           double *finish_out, uint8_t *good_out)
+{
+    const double ts = p.ts;
+    const float slo_f = p.slo;
+    const int32_t m = p.m;
+    const uint32_t n = p.n, lo = p.lo, e0 = p.e0, e1 = p.e1, e2 = p.e2, e3 = p.e3;
+
+    // ---- state-independent fetches for the requests behind this one -------
+    uint32_t lo1, n1, f0, f1, f2, f3;
+    pipe_tables(ln, p.m1, lo1, n1, f0, f1, f2, f3);
+    const int64_t i2 = i + 2 < p.last ? i + 2 : p.last;
+    const double ts2 = __ldg(p.arrivals + i2);
+    const float slo2 = __ldg(p.slos + i2);
+    const int32_t m2raw = __ldg(p.model_ids + i2);
+
+    // ---- :589-598 replica whose last-stage clock is strictly smallest ------
+    double fin = ts;
+    bool ok = false;
+    if (n > 0) {
+        const double c0 = SM_F64(ln.clk + rep_last(e0) * kLanes);
+        const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
+        const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
+        const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
+        double best = kInf;
+        uint32_t pick = 0;
+        bool found = false;
+        if (c0 < best) { best = c0; pick = e0; found = true; }
+        if (n > 1 && c1 < best) { best = c1; pick = e1; found = true; }
+        if (n > 2 && c2 < best) { best = c2; pick = e2; found = true; }
+        if (n > 3 && c3 < best) { best = c3; pick = e3; found = true; }
+        for (uint32_t r = 4; r < n; ++r) {
+            const uint32_t e = SM_U32(ln.mrep + (lo + r) * kLanes);
+            const double c = SM_F64(ln.clk + rep_last(e) * kLanes);
+            if (c < best) { best = c; pick = e; found = true; }
+        }
+        if (found) {
+            const uint32_t g = rep_group(pick);
+            const uint32_t ns = kLegacy ? 1u : rep_stages(pick);
+            const uint32_t ck = ln.clk + (rep_last(pick) + 1 - ns) * kLanes;   // first slot
+            const uint32_t row = ((uint32_t)m * ln.C + rep_column(pick)) * ln.S;
+            double f;
+            double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
+            // all stage clocks and latencies are fetched at once; the max/add
+            // chain then runs in registers
+            const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
+                         k3 = SM_F64(ck + 3 * kLanes), k4 = SM_F64(ck + 4 * kLanes),
+                         k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
+                         k7 = SM_F64(ck + 7 * kLanes);
+            double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
+            if (ln.lat_on_chip) {
+                // rows are padded so that 8 entries are always readable
+                const uint32_t lr = ln.lat_sm + row;
+                l0 = SM_F64(lr); l1 = SM_F64(lr + 1); l2 = SM_F64(lr + 2); l3 = SM_F64(lr + 3);
+                l4 = SM_F64(lr + 4); l5 = SM_F64(lr + 5); l6 = SM_F64(lr + 6); l7 = SM_F64(lr + 7);
+            } else {
+                const float *lat = ln.lat_gl + row;
+                const int sm = ln.S - 1;   // clamp reads to the table row
+                l0 = (double)__ldg(lat); l1 = (double)__ldg(lat + (1 < sm ? 1 : sm));
+                if (ns > 2) {
+                    l2 = (double)__ldg(lat + (2 < sm ? 2 : sm));
+                    l3 = (double)__ldg(lat + (3 < sm ? 3 : sm));
+                    l4 = (double)__ldg(lat + (4 < sm ? 4 : sm));
+                    l5 = (double)__ldg(lat + (5 < sm ? 5 : sm));
+                    l6 = (double)__ldg(lat + (6 < sm ? 6 : sm));
+                    l7 = (double)__ldg(lat + (7 < sm ? 7 : sm));
+                }
+            }
+            if (kLegacy) {
+                // :543-544 one clock per group; latency row = {sum, max}
+                const double start = fmax(k0, ts);
+                f = start + l0 + kOverhead;
+                t0 = start + l1;
+            } else {
+                // :605-610
+                double t = fmax(ts, k0) + l0;
+                t0 = t;
+                if (ns > 1) {
+                    t = fmax(t, k1) + l1; t1 = t;
+                    if (ns > 2) {
+                        t = fmax(t, k2) + l2; t2 = t;
+                        t = ns > 3 ? fmax(t, k3) + l3 : t; t3 = t;
+                        if (ns > 4) {
+                            t = fmax(t, k4) + l4; t4 = t;
+                            t = ns > 5 ? fmax(t, k5) + l5 : t; t5 = t;
+                            t = ns > 6 ? fmax(t, k6) + l6 : t; t6 = t;
+                            t = ns > 7 ? fmax(t, k7) + l7 : t; t7 = t;
+                            for (uint32_t k = 8; k < ns; ++k) {
+                                const double lk = ln.lat_on_chip
+                                    ? SM_F64(ln.lat_sm + row + k)
+                                    : (double)__ldg(ln.lat_gl + row + k);
+                                t = fmax(t, SM_F64(ck + k * kLanes)) + lk;
+                                SM_F64(ln.tmp + (k - 8) * kLanes) = t;
+                            }
+                        }
+                    }
+                }
+                f = t + kOverhead;                               // :610
+            }
+            if (record) atomicAdd(&SM_U32(ln.group_req + g * kLanes), 1u);   // :611
+            if (f - ts <= (double)slo_f) {                       // :613-619
+                fin = f;
+                ok = true;
+                SM_F64(ck) = t0;
+                if (ns > 1) {
+                    SM_F64(ck + kLanes) = t1;
+                    if (ns > 2) {
+                        SM_F64(ck + 2 * kLanes) = t2;
+                        if (ns > 3) SM_F64(ck + 3 * kLanes) = t3;
+                        if (ns > 4) {
+                            SM_F64(ck + 4 * kLanes) = t4;
+                            if (ns > 5) SM_F64(ck + 5 * kLanes) = t5;
+                            if (ns > 6) SM_F64(ck + 6 * kLanes) = t6;
+                            if (ns > 7) SM_F64(ck + 7 * kLanes) = t7;
+                            for (uint32_t k = 8; k < ns; ++k)
+                                SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
+                        }
+                    }
+                }
+                if (record) {
+                    atomicAdd(&SM_U32(ln.model_good + (uint32_t)m * kLanes), 1u);
+                    if (kGroupGood) atomicAdd(&SM_U32(ln.group_good + g * kLanes), 1u);
+                }
+            }
+        }
+    }
+    if (kFull && record) {
+        finish_out[i] = fin;
+        good_out[i] = ok ? 1 : 0;
+    }
+
+    // ---- advance the pipe ---------------------------------------------------
+    p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1;
+    p.lo = lo1; p.n = n1; p.e0 = f0; p.e1 = f1; p.e2 = f2; p.e3 = f3;
+    p.ts1 = ts2; p.slo1 = slo2; p.m1 = clean_model(ln, m2raw);
+    return fin - ts;
+}
+
+}  // namespace mms

@@ -73,7 +73,7 @@ class DeviceTrace:
             self.num_leaves = n_leaves
             self.leaf_start = _to_device(leaf_start, self.device)
             self.leaf_merges = _to_device(leaf_merges, self.device)
-            self.model_hist = torch.zeros(max(self.num_models, 1), dtype=torch.int32,
+            self.model_hist = torch.zeros(self.num_models + 1, dtype=torch.int32,
                                           device=self.device)
             tr = self.c_trace()
             nat.check(L.mms_trace_model_histogram(ctypes.byref(tr), self.num_models,
@@ -148,7 +148,7 @@ class EncodedBatch:
                  num_replicas):
         self.B, self.M, self.G, self.P, self.T, self.S, self.C = B, M, G, P, T, S, C
         self.model_off = model_off        # u16[B][M+1]
-        self.model_rep = model_rep        # u16[B][P]
+        self.model_rep = model_rep        # u32[B][P]
         self.group_info = group_info      # u32[B][G]
         self.num_groups = num_groups      # i64[B]
         self.num_replicas = num_replicas  # i64[B]: sum of len(group_models)
@@ -197,13 +197,11 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     T = int(slots_per_b.max()) if B else 0
     S = int(table.max_stages)
     C = len(table.configs)
-    if G > nat.MAX_GROUPS or T > nat.MAX_SLOTS or S > nat.MAX_STAGES:
+    if G > nat.MAX_GROUPS or T > nat.MAX_SLOTS or S > nat.MAX_STAGES or C > nat.MAX_COLUMNS:
         raise NotImplementedError(
             f"placement too large for the kernels: {G} groups (max {nat.MAX_GROUPS}), "
-            f"{T} pipeline stages in total (max {nat.MAX_SLOTS})")
-
-    group_info = np.zeros((B, max(G, 1)), np.uint32)
-    group_info[grp_b, grp_g] = (slot_first | (cfg_pp << 8) | (cfg_col << 16)).astype(np.uint32)
+            f"{T} pipeline stages in total (max {nat.MAX_SLOTS}), {C} parallel configs "
+            f"(max {nat.MAX_COLUMNS})")
 
     # (candidate, model, group) triples, ordered by model then group inside b
     pl_grp = np.repeat(np.arange(tot_groups), n_in_group)           # flat group of each pair
@@ -217,12 +215,18 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
         raise NotImplementedError(f"{P} (group, model) pairs in one placement (max {nat.MAX_PLACED})")
     pair_first = np.concatenate(([0], np.cumsum(placed_per_b)))[:-1]
     pos = np.arange(tot_placed) - pair_first[pl_b]
-    last_slot = slot_first[pl_grp] + cfg_pp[pl_grp] - 1
-    model_rep = np.zeros((B, max(P, 1)), np.uint16)
-    model_rep[pl_b, pos] = (pl_g | (last_slot << 8)).astype(np.uint16)
+    model_rep = np.zeros((B, max(P, 1)), np.uint32)
+    model_rep[pl_b, pos] = (pl_g | (slot_first[pl_grp] << 8) | (cfg_pp[pl_grp] << 16)
+                            | (cfg_col[pl_grp] << 24)).astype(np.uint32)
     counts = np.zeros((B, M + 1), np.int64)
     np.add.at(counts, (pl_b, pl_m + 1), 1)
     model_off = np.cumsum(counts, axis=1).astype(np.uint16)
+    # a group is contested when one of its models has more than one replica
+    replicas = counts[pl_b, pl_m + 1]
+    contested = np.zeros(tot_groups, np.int64)
+    np.maximum.at(contested, pl_grp, (replicas > 1).astype(np.int64))
+    group_info = np.zeros((B, max(G, 1)), np.uint32)
+    group_info[grp_b, grp_g] = (slot_first | (cfg_pp << 8) | (contested << 16)).astype(np.uint32)
 
     return EncodedBatch(B, M, max(G, 1), max(P, 1), max(T, 1), S, C, model_off, model_rep,
                         group_info, n_groups, placed_per_b.astype(np.int64))
@@ -231,11 +235,18 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
 class BatchResult:
     """Outputs of one launch, as numpy arrays on the host."""
     __slots__ = ("model_num_requests", "model_num_good", "group_num_requests",
-                 "group_num_good", "good_total", "latency_sum", "status", "finish", "good")
+                 "group_num_good", "good_total", "latency_sum", "status", "finish", "good",
+                 "resimulated")
+
+
+def sim_options(chunk_requests=0, warmup_requests=0):
+    """How the trace is cut for time-parallel execution (mms_sim_options):
+    0 lets the library choose, chunk_requests < 0 forces one chunk."""
+    return nat.SimOptions(int(chunk_requests), int(warmup_requests))
 
 
 def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
-            latency, latency_stride, flags, want_group_good, pinned=False):
+            latency, latency_stride, flags, want_group_good, pinned=False, options=None):
     """Uploads the tables, runs mms_sim_mixed on the current stream, downloads
     the results.  Returns (BatchResult, h2d_bytes, d2h_bytes)."""
     _require_cuda()
@@ -243,6 +254,7 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
     dev = trace.device
     N = trace.num_requests
     res = BatchResult()
+    opts = options if options is not None else sim_options()
     with torch.cuda.device(dev):
         d_off = _to_device(model_off, dev, pinned)
         d_rep = _to_device(model_rep, dev, pinned)
@@ -251,7 +263,10 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         h2d = model_off.nbytes + model_rep.nbytes + group_info.nbytes
         cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), _ptr(d_info),
                                _ptr(d_lat), int(latency_stride))
-        need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), flags)
+        need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts), flags)
+        if need == 0 and B > 0:
+            raise NotImplementedError("placement batch outside the kernel limits "
+                                      "(see MMS_MAX_* in include/mms_sim.h)")
         ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         ws = nat.Workspace(_ptr(ws_t), need)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -262,15 +277,17 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         o_total = torch.empty(B, dtype=torch.int64, device=dev)
         o_lsum = torch.empty(B, dtype=torch.float64, device=dev)
         o_status = torch.zeros(B, dtype=torch.int32, device=dev)
+        o_redo = torch.zeros(B, dtype=torch.int32, device=dev)
         full = bool(flags & nat.FLAG_PER_REQUEST)
         o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev) if full else None
         o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev) if full else None
         out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood),
-                          _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good))
+                          _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good),
+                          _ptr(o_redo))
         tr, plan = trace.c_trace(), trace.c_plan()
         rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
-                             _ptr(trace.model_hist), ctypes.byref(ws), ctypes.byref(out),
-                             flags, _stream_ptr())
+                             _ptr(trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
+                             ctypes.byref(out), flags, _stream_ptr())
         nat.check(rc, "mms_sim_mixed")
         res.model_num_requests = o_mreq.cpu().numpy()[:, :M]
         res.model_num_good = o_mgood.cpu().numpy()[:, :M]
@@ -279,6 +296,7 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         res.good_total = o_total.cpu().numpy()
         res.latency_sum = o_lsum.cpu().numpy()
         res.status = o_status.cpu().numpy().astype(np.uint32)
+        res.resimulated = o_redo.cpu().numpy()
         res.finish = o_fin.cpu().numpy()[:, :N] if full else None
         res.good = o_good.cpu().numpy()[:, :N].astype(bool) if full else None
         d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
@@ -294,14 +312,13 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
 
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
-              per_request=False, group_good=False, pinned=False):
+              per_request=False, group_good=False, pinned=False, options=None):
     """Simulates every placement of `enc` against `trace`
     (simulate_requests_mixed, controller.py:561-628)."""
     flags = nat.FLAG_PER_REQUEST if per_request else 0
-    res, h2d, d2h = _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
-                            enc.model_off, enc.model_rep, enc.group_info,
-                            table.device(trace.device), 0, flags, group_good, pinned)
-    return res, h2d, d2h
+    return _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
+                   enc.model_off, enc.model_rep, enc.group_info,
+                   table.device(trace.device), 0, flags, group_good, pinned, options)
 
 
 def encode_dense(m_id2g_id, num_stages, num_models):
@@ -311,24 +328,27 @@ def encode_dense(m_id2g_id, num_stages, num_models):
     m2g = np.asarray(m_id2g_id, dtype=np.int64).reshape(num_models, -1)
     ns = np.asarray(num_stages, dtype=np.int64)
     G = len(ns)
-    if G > nat.MAX_GROUPS or (G and ns.max() > nat.MAX_STAGES) or ns.sum() > nat.MAX_SLOTS:
+    if G > nat.MAX_COLUMNS or (G and ns.max() > nat.MAX_STAGES) or ns.sum() > nat.MAX_SLOTS:
         raise NotImplementedError("placement too large for the kernels")
     slot_first = np.cumsum(ns) - ns
-    info = (slot_first | (ns << 8) | (np.arange(G) << 16)).astype(np.uint32).reshape(1, -1)
     rows, offs = [], [0]
+    contested = np.zeros(G, np.int64)
     for m in range(num_models):
         row = m2g[m]
         stop = np.flatnonzero(row < 0)
         row = row[:stop[0]] if len(stop) else row
         if len(row) and (row.max() >= G):
             raise IndexError("group id in m_id2g_id is out of range")
-        rows.append(row | ((slot_first[row] + ns[row] - 1) << 8))
+        if len(row) > 1:
+            contested[row] = 1
+        rows.append(row | (slot_first[row] << 8) | (ns[row] << 16) | (row << 24))
         offs.append(offs[-1] + len(row))
-    rep = np.concatenate(rows).astype(np.uint16) if rows and offs[-1] else np.zeros(0, np.uint16)
     if offs[-1] > nat.MAX_PLACED:
         raise NotImplementedError("too many (group, model) pairs")
-    rep = rep.reshape(1, -1) if len(rep) else np.zeros((1, 1), np.uint16)
+    rep = np.concatenate(rows).astype(np.uint32) if rows and offs[-1] else np.zeros(0, np.uint32)
+    rep = rep.reshape(1, -1) if len(rep) else np.zeros((1, 1), np.uint32)
     off = np.asarray(offs, dtype=np.uint16).reshape(1, -1)
+    info = (slot_first | (ns << 8) | (contested << 16)).astype(np.uint32).reshape(1, -1)
     if info.shape[1] == 0:
         info = np.zeros((1, 1), np.uint32)
     return off, rep, info, max(int(ns.sum()), 1)

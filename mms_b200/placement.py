@@ -109,7 +109,7 @@ class PlacementEvaluator:
     """
 
     def __init__(self, model_datas, cluster_env, workload, method: str = "fast_simulator",
-                 parallel: bool = False, device=None):
+                 parallel: bool = False, device=None, options=None):
         if method != "fast_simulator":
             raise NotImplementedError("only the fast_simulator method runs on the GPU")
         self.parallel = parallel
@@ -126,6 +126,8 @@ class PlacementEvaluator:
         self.trace = engine.DeviceTrace(workload.arrivals, model_ids, slos,
                                         len(self.model_names), device=device)
         self.table = engine.LatencyTable(self.prof_ress)
+        self.options = options          # engine.sim_options(...) or None
+        self.last_resimulated = None
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
 
@@ -133,8 +135,10 @@ class PlacementEvaluator:
     def evaluate(self, sols: Sequence[ModelPlacement], pinned=False):
         """One launch for the whole list; returns (EncodedBatch, BatchResult)."""
         enc = engine.encode_placements(sols, self.table, len(self.model_names))
-        res, h2d, d2h = engine.run_batch(self.trace, enc, self.table, pinned=pinned)
+        res, h2d, d2h = engine.run_batch(self.trace, enc, self.table, pinned=pinned,
+                                         options=self.options)
         self.last_h2d_bytes, self.last_d2h_bytes = h2d, d2h
+        self.last_resimulated = res.resimulated
         return enc, res
 
     def scores_from(self, enc, res) -> List[float]:

@@ -31,6 +31,19 @@ def _counters(res, M, G, b=0):
     return mreq, mgood, greq, ggood
 
 
+# How the trace is cut for time-parallel execution; None = library default.
+# Results do not depend on it (tests sweep it).
+_options = None
+
+
+def set_chunking(chunk_requests=0, warmup_requests=0):
+    """Overrides the chunk length / run-in of the time-parallel execution for
+    the entry points of this module (0, 0 restores the default)."""
+    global _options
+    _options = None if (chunk_requests == 0 and warmup_requests == 0) \
+        else engine.sim_options(chunk_requests, warmup_requests)
+
+
 def _run_dense(finish, good, tstamps, model_ids, slos, m_id2g_id, num_stages, latency,
                num_requests, flags):
     """One candidate in the reference's dense layout; fills finish/good."""
@@ -46,7 +59,8 @@ def _run_dense(finish, good, tstamps, model_ids, slos, m_id2g_id, num_stages, la
         return z(M, np.int32), z(M, np.int32), z(G, np.int32), z(G, np.int32)
     off, rep, info, T = engine.encode_dense(m_id2g_id, num_stages, M)
     res, _, _ = engine._launch(trace, 1, M, G, rep.shape[1], T, S, G, off, rep, info,
-                               latency, 0, flags | nat.FLAG_PER_REQUEST, True)
+                               latency, 0, flags | nat.FLAG_PER_REQUEST, True,
+                               options=_options)
     finish[:N] = res.finish[0]
     good[:N] = res.good[0]
     return _counters(res, M, G)
@@ -115,7 +129,8 @@ def approximate_one_case_one_placement(placement, model_names, prof_ress, model_
         z = np.zeros
         return (arrivals, arrivals.copy(), np.zeros(N, bool), trace.model_hist.cpu().numpy()[:M],
                 z(M, np.int32), z(0, np.int32), z(0, np.int32))
-    res, _, _ = engine.run_batch(trace, enc, table, per_request=True, group_good=True)
+    res, _, _ = engine.run_batch(trace, enc, table, per_request=True, group_good=True,
+                                 options=_options)
     finish[:] = res.finish[0]
     good[:] = res.good[0]
     return (arrivals, finish, good) + tuple(_counters(res, M, G))

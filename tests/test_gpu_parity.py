@@ -1,0 +1,194 @@
+"""CUDA path (through the C ABI) against the CPU checker and the golden files."""
+import hashlib
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def loaded():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from mms_b200 import _native
+    _native.lib()          # raises if the extension was not built: no fallback
+    return True
+
+
+def same_counters(got, g):
+    for arr, key in zip(got, ("model_num_requests", "model_num_good", "group_num_requests",
+                              "group_num_good")):
+        assert np.array_equal(arr, g[key]), key
+
+
+def test_mixed_kernel_golden(loaded, golden):
+    from mms_b200 import simulator
+    g = golden("kernel_mixed")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    got = simulator.simulate_requests_mixed(fin, good, g["tstamps"], g["model_ids"], g["slos"],
+                                            g["m_id2g_id"], g["num_stages"],
+                                            g["stage_latency"], N)
+    assert fin.tobytes() == g["finish"].tobytes()
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+
+
+def test_legacy_kernel_golden(loaded, golden):
+    from mms_b200 import simulator
+    g = golden("kernel_legacy")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    got = simulator.simulate_requests(fin, good, g["tstamps"], g["model_ids"], g["slos"],
+                                      g["m_id2g_id"], g["group_max_latency"],
+                                      g["group_sum_latency"], N)
+    assert fin.tobytes() == g["finish"].tobytes()
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+
+
+def test_fixed_pipeline_case_full_size(loaded, golden):
+    from mms_b200 import cases, simulator
+    g = golden("case_fixed_pipeline")
+    case = cases.fixed_pipeline_case()
+    w = case.workload
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = simulator.workload_arrays(w, names)
+    out = simulator.approximate_one_case_one_placement(case.placements[0], names, profs, mids,
+                                                       slos, w.arrivals)
+    assert sha(out[1]) == str(g["finish_sha256"])
+    assert sha(out[2].astype(np.uint8)) == str(g["good_sha256"])
+    same_counters(out[3:], g)
+
+
+def test_evaluator_scores_golden(loaded, golden):
+    from mms_b200 import cases
+    from mms_b200.placement import PlacementEvaluator
+    g = golden("case_candidates")
+    case = cases.candidate_batch_case(num_candidates=int(g["num_candidates"]),
+                                      duration=float(g["duration"]))
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            "fast_simulator", False)
+    scores = ev.get_scores(case.placements)
+    assert np.array(scores).tobytes() == g["scores"].tobytes()      # bit-exact fp64
+    stats = ev.get_stats(case.placements)
+    for b, (goodput, per_model, group_req, full) in enumerate(stats):
+        assert goodput == g["goodput"][b]
+        assert full.latency_mean == g["latency_mean"][b]
+        assert np.array_equal(np.array(per_model), g["model_goodput"][b])
+        assert np.array_equal(np.array(group_req), g["group_num_requests"][b, :len(group_req)])
+        assert isinstance(group_req, tuple)
+
+
+def test_evaluator_against_cpu_checker_hour_trace(loaded):
+    """Full-length trace (about 180 k requests), 96 candidates: every reduced
+    output equals the checker's."""
+    from mms_b200 import cases
+    from mms_b200.placement import PlacementEvaluator
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=96, placement_seed=5)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload)
+    enc, res = ev.evaluate(case.placements)
+    scores = ev.scores_from(enc, res)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    for b in range(0, 96, 5):
+        p = case.placements[b]
+        fin, good, mreq, mgood, greq, _ = tables.one_placement(p, profs, mids, slos,
+                                                               case.workload.arrivals)
+        assert scores[b] == tables.score(p, fin, good, case.workload.arrivals), b
+        assert np.array_equal(res.model_num_good[b], mgood)
+        assert np.array_equal(res.model_num_requests[b], mreq)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
+        assert res.good_total[b] == np.count_nonzero(good)
+
+
+@pytest.mark.parametrize("n", [0, 1, 7, 8, 9, 129, 1001])
+def test_short_and_ragged_traces(loaded, n):
+    from mms_b200 import simulator
+    from oracle import cpu
+    rng = np.random.RandomState(n)
+    M, G, S = 5, 3, 2
+    ts = np.cumsum(rng.gamma(0.5, 0.05, size=n))
+    mid = rng.randint(-1, M, size=n).astype(np.int32)
+    slo = np.full(n, 0.3, np.float32)
+    m2g = np.array([[0, 1, -1], [1, -1, -1], [2, 0, 1], [-1, -1, -1], [0, -1, -1]], np.int32)
+    ns = np.array([2, 1, 2], np.int32)
+    lat = rng.uniform(0.01, 0.08, size=(M, G, S)).astype(np.float32)
+    lat[1, 1, :] = lat[0, 1, :] = 0.05          # equal clocks on ties
+    fin = np.empty(n); good = np.empty(n, bool)
+    efin = np.empty(n); egood = np.empty(n, bool)
+    got = simulator.simulate_requests_mixed(fin, good, ts, mid, slo, m2g, ns, lat, n)
+    exp = cpu.simulate_requests_mixed(efin, egood, ts, mid, slo, m2g, ns, lat, n)
+    assert fin.tobytes() == efin.tobytes()
+    assert np.array_equal(good, egood)
+    for a, b in zip(got, exp):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("chunk,run_in", [(-1, 0), (1024, 2048), (4096, 1), (2048, 64),
+                                          (8192, 2048), (0, 0)])
+def test_results_do_not_depend_on_chunking(loaded, chunk, run_in):
+    """Speculative chunks are kept only when provably equivalent, so any cut of
+    the trace — even a run-in of one request, which makes nearly every chunk
+    wrong and re-simulated — gives the sequential results bit for bit."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import PlacementEvaluator
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=40, duration=900.0, placement_seed=9)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            options=engine.sim_options(chunk, run_in))
+    enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
+    res, _, _ = engine.run_batch(ev.trace, enc, ev.table, per_request=True, group_good=True,
+                                 options=ev.options)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    if chunk == 4096:
+        assert res.resimulated.sum() > 0        # the repair path really ran
+    for b, p in enumerate(case.placements):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(p, profs, mids, slos, arr)
+        assert res.finish[b].tobytes() == fin.tobytes(), (b, chunk)
+        assert np.array_equal(res.good[b], good)
+        assert np.array_equal(res.model_num_good[b], mgood)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
+        assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)
+        assert res.latency_sum[b] == float(np.add.reduce(fin - arr))
+
+
+def test_unsorted_trace_falls_back_to_one_chunk(loaded):
+    from mms_b200 import simulator
+    from oracle import cpu
+    rng = np.random.RandomState(3)
+    n, M, G, S = 20000, 6, 4, 2
+    ts = np.cumsum(rng.gamma(0.5, 0.02, size=n))
+    ts[5000:5010] = ts[5000:5010][::-1]          # arrivals out of order
+    mid = rng.randint(-1, M, size=n).astype(np.int32)
+    slo = np.full(n, 0.4, np.float32)
+    m2g = np.full((M, G), -1, np.int32)
+    for m in range(M):
+        m2g[m, :2] = np.sort(rng.choice(G, 2, replace=False))
+    ns = np.array([2, 1, 2, 1], np.int32)
+    lat = rng.uniform(0.01, 0.05, size=(M, G, S)).astype(np.float32)
+    fin = np.empty(n); good = np.empty(n, bool)
+    efin = np.empty(n); egood = np.empty(n, bool)
+    simulator.set_chunking(1024, 16)
+    try:
+        got = simulator.simulate_requests_mixed(fin, good, ts, mid, slo, m2g, ns, lat, n)
+    finally:
+        simulator.set_chunking()
+    exp = cpu.simulate_requests_mixed(efin, egood, ts, mid, slo, m2g, ns, lat, n)
+    assert fin.tobytes() == efin.tobytes()
+    assert np.array_equal(good, egood)
+    for a, b in zip(got, exp):
+        assert np.array_equal(a, b)

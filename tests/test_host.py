@@ -1,0 +1,127 @@
+"""Host-side logic that needs no GPU: library exports, encoders, plans."""
+import ctypes
+import os
+import re
+
+import numpy as np
+
+from mms_b200 import _native as nat
+from mms_b200 import build as mms_build
+from mms_b200 import cases, engine
+from mms_b200.placement import ModelPlacement
+from mms_b200.profiling import ParallelConfig
+from oracle import tables
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    mms_build.build()
+    lib = ctypes.CDLL(nat.LIB_PATH)
+    header = open(os.path.join(ROOT, "include", "mms_sim.h")).read()
+    declared = set(re.findall(r"\b(mms_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(nat.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert nat.lib().mms_abi_version() >= 1
+
+
+def decode(enc, table, b):
+    """Compact tables of candidate b -> the reference's dense tables."""
+    G = int(enc.num_groups[b])
+    M = enc.M
+    info = enc.group_info[b, :G].astype(np.int64)
+    slot, ns, contested = info & 0xFF, (info >> 8) & 0xFF, (info >> 16) & 1
+    col = np.zeros(G, np.int64)
+    m2g = np.full((M, max(G, 1)), -1, np.int32)
+    shared = np.zeros(G, np.int64)
+    for m in range(M):
+        lo, hi = int(enc.model_off[b, m]), int(enc.model_off[b, m + 1])
+        ents = enc.model_rep[b, lo:hi].astype(np.int64)
+        gs = ents & 0xFF
+        assert np.array_equal((ents >> 8) & 0xFF, slot[gs])
+        assert np.array_equal((ents >> 16) & 0xFF, ns[gs])
+        col[gs] = ents >> 24
+        m2g[m, :hi - lo] = gs
+        if hi - lo > 1:
+            shared[gs] = 1
+    assert np.array_equal(shared, contested)
+    S = int(ns.max()) if G else 1
+    lat = np.zeros((M, G, S), np.float32)
+    for g in range(G):
+        lat[:, g, :ns[g]] = table.host[:, col[g], :ns[g]]
+    # clock slots of consecutive groups tile [0, sum of stages)
+    assert np.array_equal(slot, np.cumsum(ns) - ns)
+    return m2g, ns.astype(np.int32), lat
+
+
+def test_encoder_round_trip_on_random_placements():
+    case = cases.candidate_batch_case(num_candidates=40, duration=5.0)
+    profs = [d.profiling_result for d in case.model_datas]
+    table = engine.LatencyTable(profs)
+    sols = list(case.placements)
+    sols.append(ModelPlacement([ParallelConfig(1, 1, 8)] * 8, [[] for _ in range(8)]))
+    sols.append(ModelPlacement([ParallelConfig(1, 2, 4), ParallelConfig(1, 1, 1)],
+                               [[3, 1, 2], [1]]))      # unprofiled config -> +inf
+    enc = engine.encode_placements(sols, table, len(profs))
+    assert enc.B == len(sols)
+    for b, p in enumerate(sols):
+        m2g, ns, lat = decode(enc, table, b)
+        ref_m2g, _, ref_ns, ref_lat = tables.dense_tables(p, profs)
+        assert np.array_equal(ns, ref_ns)
+        assert np.array_equal(m2g, ref_m2g[:, :m2g.shape[1]])
+        for m in range(len(profs)):          # latency of every (model, group) pair in use
+            for g in m2g[m][m2g[m] >= 0]:
+                assert lat[m, g, :ns[g]].tobytes() == ref_lat[m, g, :ns[g]].tobytes()
+        assert enc.num_replicas[b] == sum(len(x) for x in p.group_models)
+
+
+def test_dense_encoder_matches_batch_encoder():
+    case = cases.candidate_batch_case(num_candidates=3, duration=5.0)
+    profs = [d.profiling_result for d in case.model_datas]
+    for p in case.placements:
+        m2g, _, ns, _ = tables.dense_tables(p, profs)
+        off, rep, info, T = engine.encode_dense(m2g, ns, len(profs))
+        table = engine.LatencyTable(profs)
+        enc = engine.encode_placements([p], table, len(profs))
+        assert np.array_equal(off[0], enc.model_off[0])
+        n = off[0, -1]          # same entries up to the latency column
+        assert np.array_equal(rep[0, :n] & 0xFFFFFF, enc.model_rep[0, :n] & 0xFFFFFF)
+        assert np.array_equal(info[0], enc.group_info[0, :info.shape[1]])
+        assert T == enc.T
+
+
+def numpy_order_sum(a, leaf_start, merges):
+    stack = []
+    for leaf in range(len(merges)):
+        x = a[leaf_start[leaf]:leaf_start[leaf + 1]]
+        n = len(x)
+        body = n - n % 8
+        p = [0.0] * 8
+        for i in range(0, body, 8):
+            for j in range(8):
+                p[j] = p[j] + x[i + j]
+        r = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]))
+        for i in range(body, n):
+            r = r + x[i]
+        stack.append(r)
+        for _ in range(merges[leaf]):
+            right = stack.pop()
+            stack[-1] = stack[-1] + right
+    assert len(stack) == 1
+    return stack[0]
+
+
+def test_sum_plan_reproduces_numpy():
+    L = nat.lib()
+    for n in (1, 5, 8, 9, 127, 128, 129, 130, 1000, 4097, 57949):
+        leaves = L.mms_sum_plan_leaves(n)
+        start = np.zeros(leaves + 1, np.int32)
+        merges = np.zeros(leaves, np.uint8)
+        assert L.mms_sum_plan_fill(n, start.ctypes.data, merges.ctypes.data) == 0
+        assert start[0] == 0 and start[-1] == n
+        assert np.all(np.diff(start) <= 128) and np.all(start[1:-1] % 8 == 0)
+        a = np.random.RandomState(n).gamma(0.3, 1.0, size=n)
+        a[::3] = 0.0
+        assert numpy_order_sum(a.tolist(), start, merges) == float(np.add.reduce(a))
+    assert L.mms_sum_plan_leaves(0) == 0

@@ -168,6 +168,44 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands,
                   const mms_sim_options *opts, const mms_workspace *ws,
                   const mms_results *out, uint32_t flags, void *stream);
 
+/* ---- batching simulator -------------------------------------------------
+ * simulate_requests_mixed_batching (controller.py:630-798) for every
+ * candidate.  `cands->latency` is f32[M][C][S][NB] here (NB batch sizes, the
+ * table of controller.py:451-461); the extra tables below give each group's
+ * models (g_id2m_id, controller.py:424-430).  Per-request outputs are always
+ * written (requests finish out of arrival order).
+ *
+ *  group_off u16[B][G+1]  CSR offsets into group_mod
+ *  group_mod u16[B][P]    models of each group in ascending model id
+ *  group_cfg u32[B][G]    bits 0-7 first clock slot, 8-15 stages, 16-31 column
+ *  batch_sizes            alpa_serve.util.batchsize_config (util.py:13): powers
+ *                         of two starting at 1; column log2(bs) of the table
+ *                         is read for batch size bs, as the reference does
+ *  heap_capacity          pending (time, group) events per candidate; 0 picks
+ *                         4*G + 16.  Overflow sets MMS_STATUS_HEAP_OVERFLOW.
+ */
+typedef struct {
+    const uint16_t *group_off;
+    const uint16_t *group_mod;
+    const uint32_t *group_cfg;
+    int32_t num_batch_sizes;       /* NB, 1..8 */
+    int32_t heap_capacity;
+    int32_t batch_sizes[8];
+} mms_batching;
+
+/* next_same[i] = index of the next request with request i's model, or -1:
+ * the per-model FIFO queues of controller.py:648 are runs of this list.
+ * next_same: i32[N], filled once per trace. */
+int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_t *next_same,
+                              void *stream);
+
+size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands);
+
+int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
+                     const mms_batching *batching, const int32_t *next_same,
+                     const mms_sum_plan *plan, const mms_workspace *ws, const mms_results *out,
+                     void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,6 +34,7 @@ FLAG_LEGACY_CLOCK = 2
 EXPORTS = (
     "mms_abi_version", "mms_last_error", "mms_sum_plan_leaves", "mms_sum_plan_fill",
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
+    "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
 )
 
 _vp = ctypes.c_void_p
@@ -73,6 +74,12 @@ class Results(ctypes.Structure):
                 ("resimulated", _vp)]
 
 
+class Batching(ctypes.Structure):
+    _fields_ = [("group_off", _vp), ("group_mod", _vp), ("group_cfg", _vp),
+                ("num_batch_sizes", ctypes.c_int32), ("heap_capacity", ctypes.c_int32),
+                ("batch_sizes", ctypes.c_int32 * 8)]
+
+
 _lib = None
 
 
@@ -102,6 +109,14 @@ def lib():
                                 ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(SimOptions),
                                 ctypes.POINTER(Workspace), ctypes.POINTER(Results),
                                 ctypes.c_uint32, _vp]
+    L.mms_trace_next_same_model.restype = ctypes.c_int
+    L.mms_trace_next_same_model.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
+    L.mms_sim_batching_workspace_bytes.restype = ctypes.c_size_t
+    L.mms_sim_batching_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements)]
+    L.mms_sim_batching.restype = ctypes.c_int
+    L.mms_sim_batching.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
+                                   ctypes.POINTER(Batching), _vp, ctypes.POINTER(SumPlan),
+                                   ctypes.POINTER(Workspace), ctypes.POINTER(Results), _vp]
     _lib = L
     return L
 

@@ -13,6 +13,7 @@ SOURCES = [os.path.join(PKG_DIR, "csrc", "mms_sim.cu")]
 HEADERS = [os.path.join(REPO_DIR, "include", "mms_sim.h"),
            os.path.join(PKG_DIR, "csrc", "sim_core.cuh"),
            os.path.join(PKG_DIR, "csrc", "sim_chunk.cuh"),
+           os.path.join(PKG_DIR, "csrc", "sim_batching.cuh"),
            os.path.join(PKG_DIR, "csrc", "mms_abi.inl")]
 
 NVCC_FLAGS = [

@@ -274,4 +274,107 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     return MMS_OK;
 }
 
+int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_t *next_same,
+                              void *stream)
+{
+    if (!trace || num_models < 0 || trace->num_requests < 0) return MMS_ERR_ARG;
+    if (trace->num_requests > 0x7FFFFFFF) return MMS_ERR_UNSUPPORTED;
+    if (trace->num_requests == 0 || num_models == 0) return MMS_OK;
+    if (!trace->model_ids || !next_same) return MMS_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // requests of unknown models (-1) are never queued; give them a defined value
+    MMS_CUDA(cudaMemsetAsync(next_same, 0xFF, sizeof(int32_t) * (size_t)trace->num_requests, st));
+    mms::next_same_kernel<<<(num_models + 31) / 32, 32, 0, st>>>(
+        trace->model_ids, trace->num_requests, num_models, next_same);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
+size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands)
+{
+    if (!cands || num_requests < 0 || num_requests > 0x7FFFFFFF) return 0;
+    return mms::align256(sizeof(double) * (size_t)mms::plan_leaves(num_requests) *
+                         (size_t)cands->num_candidates + 8);
+}
+
+int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
+                     const mms_batching *batching, const int32_t *next_same,
+                     const mms_sum_plan *plan, const mms_workspace *ws, const mms_results *out,
+                     void *stream)
+{
+    using namespace mms;
+    if (!trace || !cands || !batching || !plan || !ws || !out) return MMS_ERR_ARG;
+    const int64_t N = trace->num_requests;
+    const int32_t B = cands->num_candidates;
+    if (N < 0 || B < 0 || cands->num_models < 0 || cands->max_groups < 0 ||
+        cands->max_placed < 0 || cands->max_slots < 0 || cands->max_stages < 1 ||
+        cands->num_columns < 0)
+        return MMS_ERR_ARG;
+    if (N > 0x7FFFFFFF || cands->max_groups > MMS_MAX_GROUPS || cands->max_slots > MMS_MAX_SLOTS ||
+        cands->max_placed > MMS_MAX_PLACED || cands->max_stages > MMS_MAX_STAGES ||
+        cands->num_columns > MMS_MAX_COLUMNS)
+        return MMS_ERR_UNSUPPORTED;
+    const int NB = batching->num_batch_sizes;
+    if (NB < 1 || NB > 8 || batching->batch_sizes[0] != 1) return MMS_ERR_ARG;
+    if (B == 0) return MMS_OK;
+    if (!out->model_num_requests || !out->model_num_good || !out->group_num_requests ||
+        !out->group_num_good || !out->good_total || !out->latency_sum || !out->status)
+        return MMS_ERR_ARG;
+    if (N > 0 && (!trace->arrivals || !trace->model_ids || !trace->slos || !next_same ||
+                  !out->finish || !out->good))
+        return MMS_ERR_ARG;
+    if (!cands->model_off || !cands->model_rep || !cands->latency || !batching->group_off ||
+        !batching->group_mod || !batching->group_cfg)
+        return MMS_ERR_ARG;
+    if (plan->num_leaves != plan_leaves(N)) return MMS_ERR_ARG;
+    if (plan->num_leaves > 0 && (!plan->leaf_start || !plan->leaf_merges)) return MMS_ERR_ARG;
+    if (!ws->ptr || ws->bytes < mms_sim_batching_workspace_bytes(N, cands)) return MMS_ERR_ARG;
+
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.arrivals = trace->arrivals; a.model_ids = trace->model_ids; a.slos = trace->slos;
+    a.next_same = next_same; a.N = N;
+    a.B = B; a.M = cands->num_models; a.G = cands->max_groups; a.P = cands->max_placed;
+    a.T = cands->max_slots; a.S = cands->max_stages; a.C = cands->num_columns; a.NB = NB;
+    a.H = batching->heap_capacity > 0 ? batching->heap_capacity : 4 * a.G + 16;
+    for (int j = 0; j < NB; ++j) {
+        const int32_t bs = batching->batch_sizes[j];
+        if (bs < 1 || (bs & (bs - 1)) || (j > 0 && bs <= batching->batch_sizes[j - 1]))
+            return MMS_ERR_ARG;
+        int col = 0;
+        while ((1 << col) < bs) ++col;
+        if (col >= NB) return MMS_ERR_ARG;   // the reference would index past the table
+        a.batch_sizes[j] = bs;
+        a.batch_cols[j] = col;
+    }
+    a.model_off = cands->model_off; a.model_rep = cands->model_rep;
+    a.group_off = batching->group_off; a.group_mod = batching->group_mod;
+    a.group_cfg = batching->group_cfg;
+    a.latency = cands->latency; a.latency_stride = cands->latency_stride;
+    a.finish = out->finish; a.good = out->good;
+    a.model_num_requests = out->model_num_requests; a.model_num_good = out->model_num_good;
+    a.group_num_requests = out->group_num_requests; a.group_num_good = out->group_num_good;
+    a.status = out->status;
+    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H);
+    if (L.total > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    MMS_CUDA(cudaFuncSetAttribute(sim_batching_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)L.total));
+    sim_batching_kernel<<<(B + kLanes - 1) / kLanes, kLanes, L.total, st>>>(a);
+    MMS_CUDA(cudaGetLastError());
+    double *leaf_sums = (double *)ws->ptr;
+    if (plan->num_leaves > 0) {
+        const int64_t cells = (int64_t)B * plan->num_leaves;
+        leaf_sums_from_finish_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(
+            out->finish, trace->arrivals, N, B, plan->num_leaves, plan->leaf_start, leaf_sums);
+        MMS_CUDA(cudaGetLastError());
+    }
+    finalize_kernel<<<(B + 31) / 32, 32, 0, st>>>(
+        B, a.M, plan->num_leaves, plan->leaf_merges, leaf_sums, out->model_num_good,
+        out->good_total, out->latency_sum, out->status);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
 }  // extern "C"

@@ -40,6 +40,7 @@
 #include <cstring>
 
 #include "mms_sim.h"
+#include "sim_batching.cuh"
 #include "sim_chunk.cuh"
 
 namespace mms {

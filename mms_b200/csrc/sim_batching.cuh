@@ -1,0 +1,390 @@
+// sim_batching.cuh — the batching simulator, one thread per candidate.
+//
+// Restates simulate_requests_mixed_batching
+// (alpa_serve/simulator/controller.py:630-798; pure Python in the reference:
+// closures, list queues and heapq).  Requests wait in one FIFO queue per
+// MODEL; a group serves, when its first stage frees up, the model whose
+// oldest queued request arrived first, batching as many of that model's
+// queued requests as still meet the head request's deadline.
+//
+// A model's queue always holds a run of consecutive requests of that model,
+// so it is kept as (head index, length) over a per-trace linked list
+// next_same[i] = next request with the model of request i; nothing is stored
+// per queued request.  The heap of (time, group) events, the queues and the
+// clocks are lane-private shared memory, [entry][lane].
+#pragma once
+#include "sim_core.cuh"
+
+namespace mms {
+
+struct BatchArgs {
+    const double *arrivals;
+    const int32_t *model_ids;
+    const float *slos;
+    const int32_t *next_same;     // [N]
+    int64_t N;
+    int32_t B, M, G, P, T, S, C, NB, H;
+    int32_t batch_sizes[8];
+    int32_t batch_cols[8];        // log2 of the batch size: the column the reference reads
+    const uint16_t *model_off;    // [B][M+1]
+    const uint32_t *model_rep;    // [B][P]   group | first slot<<8 | stages<<16 | column<<24
+    const uint16_t *group_off;    // [B][G+1]
+    const uint16_t *group_mod;    // [B][P]   models of each group, ascending
+    const uint32_t *group_cfg;    // [B][G]   first slot | stages<<8 | column<<16
+    const float *latency;         // [M][C][S][NB]
+    int64_t latency_stride;
+    double *finish;               // [B][N]
+    uint8_t *good;                // [B][N]
+    int32_t *model_num_requests;  // [B][M]
+    int32_t *model_num_good;      // [B][M]
+    int32_t *group_num_requests;  // [B][G]
+    int32_t *group_num_good;      // [B][G]
+    uint32_t *status;             // [B]
+};
+
+struct BatchSmem {
+    size_t clocks, idle, heap_t, qhead, qlen, heap_g, counters, model_rep, group_cfg,
+        model_off, group_off, group_mod, total;
+};
+
+__host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int H)
+{
+    BatchSmem L;
+    size_t off = 0;
+    L.clocks = off;    off += sizeof(double) * (size_t)T * kLanes;
+    L.idle = off;      off += sizeof(double) * (size_t)G * kLanes;
+    L.heap_t = off;    off += sizeof(double) * (size_t)H * kLanes;
+    L.qhead = off;     off += sizeof(int32_t) * (size_t)M * kLanes;
+    L.qlen = off;      off += sizeof(int32_t) * (size_t)M * kLanes;
+    L.heap_g = off;    off += sizeof(uint32_t) * (size_t)H * kLanes;
+    L.counters = off;  off += sizeof(uint32_t) * (size_t)(2 * M + 2 * G) * kLanes;
+    L.model_rep = off; off += sizeof(uint32_t) * (size_t)P * kLanes;
+    L.group_cfg = off; off += sizeof(uint32_t) * (size_t)G * kLanes;
+    L.model_off = off; off += sizeof(uint16_t) * (size_t)(M + 1) * kLanes;
+    L.group_off = off; off += sizeof(uint16_t) * (size_t)(G + 1) * kLanes;
+    L.group_mod = off; off += sizeof(uint16_t) * (size_t)P * kLanes;
+    L.total = (off + 15) & ~(size_t)15;
+    return L;
+}
+
+// One candidate's state; every member is an element offset (lane included).
+struct BLane {
+    uint32_t clk, idle, heap_t, heap_g, qhead, qlen;
+    uint32_t model_req, model_good, group_req, group_good;
+    uint32_t mrep, gcfg, moff, goff, gmod;
+    uint32_t heap_n, status;
+    const float *lat;
+    double *finish;
+    uint8_t *good;
+};
+
+// (time, group) ordered like the Python tuples the reference pushes (:728).
+__device__ inline bool event_less(double ta, uint32_t ga, double tb, uint32_t gb)
+{
+    return ta < tb || (ta == tb && ga < gb);
+}
+
+__device__ inline void heap_push(const BatchArgs &a, BLane &ln, double t, uint32_t g)
+{
+    if (ln.heap_n >= (uint32_t)a.H) { ln.status |= MMS_STATUS_HEAP_OVERFLOW; return; }
+    uint32_t i = ln.heap_n++;
+    while (i > 0) {
+        const uint32_t p = (i - 1) >> 1;
+        const double tp = SM_F64(ln.heap_t + p * kLanes);
+        const uint32_t gp = SM_U32(ln.heap_g + p * kLanes);
+        if (!event_less(t, g, tp, gp)) break;
+        SM_F64(ln.heap_t + i * kLanes) = tp;
+        SM_U32(ln.heap_g + i * kLanes) = gp;
+        i = p;
+    }
+    SM_F64(ln.heap_t + i * kLanes) = t;
+    SM_U32(ln.heap_g + i * kLanes) = g;
+}
+
+__device__ inline void heap_pop(BLane &ln, double &t, uint32_t &g)
+{
+    t = SM_F64(ln.heap_t);
+    g = SM_U32(ln.heap_g);
+    const uint32_t n = --ln.heap_n;
+    if (n == 0) return;
+    const double te = SM_F64(ln.heap_t + n * kLanes);
+    const uint32_t ge = SM_U32(ln.heap_g + n * kLanes);
+    uint32_t i = 0;
+    for (;;) {
+        uint32_t c = 2 * i + 1;
+        if (c >= n) break;
+        double tc = SM_F64(ln.heap_t + c * kLanes);
+        uint32_t gc = SM_U32(ln.heap_g + c * kLanes);
+        if (c + 1 < n) {
+            const double tr = SM_F64(ln.heap_t + (c + 1) * kLanes);
+            const uint32_t gr = SM_U32(ln.heap_g + (c + 1) * kLanes);
+            if (event_less(tr, gr, tc, gc)) { c += 1; tc = tr; gc = gr; }
+        }
+        if (!event_less(tc, gc, te, ge)) break;
+        SM_F64(ln.heap_t + i * kLanes) = tc;
+        SM_U32(ln.heap_g + i * kLanes) = gc;
+        i = c;
+    }
+    SM_F64(ln.heap_t + i * kLanes) = te;
+    SM_U32(ln.heap_g + i * kLanes) = ge;
+}
+
+// select_model, :654-664: the group's model whose queue head arrived first.
+__device__ inline int32_t pick_model(const BatchArgs &a, const BLane &ln, uint32_t g)
+{
+    const uint32_t lo = SM_U16(ln.goff + g * kLanes), hi = SM_U16(ln.goff + (g + 1) * kLanes);
+    double first = kInf;
+    int32_t pick = -1;
+    for (uint32_t e = lo; e < hi; ++e) {
+        const uint32_t m = SM_U16(ln.gmod + e * kLanes);
+        if ((int32_t)SM_U32(ln.qlen + m * kLanes) > 0) {
+            const double ts = a.arrivals[(int32_t)SM_U32(ln.qhead + m * kLanes)];
+            if (ts < first) { first = ts; pick = (int32_t)m; }
+        }
+    }
+    return pick;
+}
+
+// check_slo, :666-672.
+__device__ inline bool meets_deadline(const BatchArgs &a, const BLane &ln, double ts, uint32_t m,
+                                      uint32_t slot, uint32_t ns, uint32_t col, int bcol,
+                                      double deadline)
+{
+    const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
+    double t = ts;
+    for (uint32_t k = 0; k < ns; ++k)
+        t = fmax(SM_F64(ln.clk + (slot + k) * kLanes), t) + (double)__ldg(lat + (size_t)k * a.NB);
+    return t + kOverhead <= deadline;
+}
+
+__device__ inline int32_t queue_pop(const BatchArgs &a, BLane &ln, uint32_t m)
+{
+    const int32_t r = (int32_t)SM_U32(ln.qhead + m * kLanes);
+    SM_U32(ln.qhead + m * kLanes) = (uint32_t)a.next_same[r];
+    SM_U32(ln.qlen + m * kLanes) -= 1;
+    return r;
+}
+
+// handle_batched_requests with get_max_batch_under_slo, :674-732.  The
+// reference recurses when a model's whole queue was dropped; the loop is the
+// same tail call.
+__device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int32_t m_in,
+                                   uint32_t g)
+{
+    const uint32_t cfg = SM_U32(ln.gcfg + g * kLanes);
+    const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu, col = cfg >> 16;
+    int32_t m = m_in;
+    while (m >= 0) {
+        // :677-686 drop queue heads that cannot make their deadline even alone
+        int32_t head = -1;
+        while ((int32_t)SM_U32(ln.qlen + m * kLanes) > 0) {
+            const int32_t r = queue_pop(a, ln, m);
+            const double dl = a.arrivals[r] + (double)a.slos[r];
+            if (meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[0], dl)) { head = r; break; }
+            SM_U32(ln.group_req + g * kLanes) += 1;
+            ln.finish[r] = a.arrivals[r];
+            ln.good[r] = 0;
+        }
+        if (head < 0) { m = pick_model(a, ln, g); continue; }      // :709-713
+        // :693-702 grow the batch while the HEAD's deadline still holds
+        const double deadline = a.arrivals[head] + (double)a.slos[head];
+        int32_t bs = 1, bcol = a.batch_cols[0];
+        for (int j = 1; j < a.NB; ++j) {
+            if (a.batch_sizes[j] - 1 > (int32_t)SM_U32(ln.qlen + m * kLanes)) break;
+            if (!meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[j], deadline)) break;
+            bs = a.batch_sizes[j];
+            bcol = a.batch_cols[j];
+        }
+        // :715-725 overhead first, then the stages; clocks move to the new times
+        const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
+        double t = ts + kOverhead, t_first = 0.0;
+        for (uint32_t k = 0; k < ns; ++k) {
+            t = fmax(t, SM_F64(ln.clk + (slot + k) * kLanes)) + (double)__ldg(lat + (size_t)k * a.NB);
+            SM_F64(ln.clk + (slot + k) * kLanes) = t;   // each stage reads only its own clock
+            if (k == 0) t_first = t;
+        }
+        ln.finish[head] = t;
+        ln.good[head] = 1;
+        for (int32_t k = 1; k < bs; ++k) {
+            const int32_t r = queue_pop(a, ln, m);
+            ln.finish[r] = t;
+            ln.good[r] = 1;
+        }
+        // :727-732
+        SM_F64(ln.idle + g * kLanes) = t_first;
+        heap_push(a, ln, t_first, g);
+        SM_U32(ln.group_req + g * kLanes) += (uint32_t)bs;
+        SM_U32(ln.group_good + g * kLanes) += (uint32_t)bs;
+        SM_U32(ln.model_good + m * kLanes) += (uint32_t)bs;
+        return;
+    }
+}
+
+__global__ void __launch_bounds__(kLanes, 1)
+sim_batching_kernel(const BatchArgs a)
+{
+    const int lane = threadIdx.x;
+    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
+    if (b >= a.B) return;
+    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H);
+    BLane ln;
+    ln.clk = (uint32_t)(L.clocks / 8) + lane;
+    ln.idle = (uint32_t)(L.idle / 8) + lane;
+    ln.heap_t = (uint32_t)(L.heap_t / 8) + lane;
+    ln.heap_g = (uint32_t)(L.heap_g / 4) + lane;
+    ln.qhead = (uint32_t)(L.qhead / 4) + lane;
+    ln.qlen = (uint32_t)(L.qlen / 4) + lane;
+    ln.model_req = (uint32_t)(L.counters / 4) + lane;
+    ln.model_good = ln.model_req + (uint32_t)a.M * kLanes;
+    ln.group_req = ln.model_good + (uint32_t)a.M * kLanes;
+    ln.group_good = ln.group_req + (uint32_t)a.G * kLanes;
+    ln.mrep = (uint32_t)(L.model_rep / 4) + lane;
+    ln.gcfg = (uint32_t)(L.group_cfg / 4) + lane;
+    ln.moff = (uint32_t)(L.model_off / 2) + lane;
+    ln.goff = (uint32_t)(L.group_off / 2) + lane;
+    ln.gmod = (uint32_t)(L.group_mod / 2) + lane;
+    ln.heap_n = 0;
+    ln.status = 0;
+    ln.lat = a.latency + (size_t)b * a.latency_stride;
+    ln.finish = a.finish + (size_t)b * a.N;
+    ln.good = a.good + (size_t)b * a.N;
+
+    // tables on chip, every index checked
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
+    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * kLanes) = 0.0;
+    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * kLanes) = 0; SM_U32(ln.qlen + m * kLanes) = 0; }
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * kLanes) = 0;
+    for (int g = 0; g < a.G; ++g) {
+        uint32_t cfg = a.group_cfg[(size_t)b * a.G + g];
+        const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu;
+        if (slot + ns > (uint32_t)a.T || ns > (uint32_t)a.S || (cfg >> 16) >= (uint32_t)a.C) {
+            ln.status |= MMS_STATUS_BAD_INDEX;
+            cfg = 0;
+        }
+        SM_U32(ln.gcfg + g * kLanes) = cfg;
+    }
+    uint32_t prev = 0;
+    for (int m = 0; m <= a.M; ++m) {
+        uint32_t o = a.model_off[(size_t)b * (a.M + 1) + m];
+        if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
+        SM_U16(ln.moff + m * kLanes) = (uint16_t)o;
+        prev = o;
+    }
+    for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
+        uint32_t ent = e < prev ? a.model_rep[(size_t)b * a.P + e] : 0u;
+        if (e < prev) {
+            const uint32_t g = ent & 0xFFu;
+            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (SM_U32(ln.gcfg + g * kLanes) & 0xFFFFu))
+                ln.status |= MMS_STATUS_BAD_INDEX;
+        }
+        SM_U32(ln.mrep + e * kLanes) = ent;
+    }
+    prev = 0;
+    for (int g = 0; g <= a.G; ++g) {
+        uint32_t o = a.group_off[(size_t)b * (a.G + 1) + g];
+        if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
+        SM_U16(ln.goff + g * kLanes) = (uint16_t)o;
+        prev = o;
+    }
+    for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
+        uint32_t m = e < prev ? a.group_mod[(size_t)b * a.P + e] : 0u;
+        if (m >= (uint32_t)a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = 0; }
+        SM_U16(ln.gmod + e * kLanes) = (uint16_t)m;
+    }
+
+    if (!(ln.status & MMS_STATUS_BAD_INDEX)) {
+        for (int64_t i = 0; i < a.N; ++i) {
+            const double ts = a.arrivals[i];
+            // :739-744 groups whose first stage became free before this arrival
+            while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
+                double te; uint32_t ge;
+                heap_pop(ln, te, ge);
+                const int32_t pm = pick_model(a, ln, ge);
+                if (pm < 0) break;                     // the reference breaks here, not continues
+                serve_group(a, ln, te, pm, ge);
+            }
+            int32_t m = a.model_ids[i];
+            if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
+            uint32_t lo = 0, hi = 0;
+            if (m >= 0) { lo = SM_U16(ln.moff + m * kLanes); hi = SM_U16(ln.moff + (m + 1) * kLanes); }
+            if (lo == hi) {                            // :748-757 unknown model or no replica
+                ln.finish[i] = ts;
+                ln.good[i] = 0;
+                continue;
+            }
+            double best = kInf;                        // :759-770
+            uint32_t pick = 0;
+            bool found = false;
+            for (uint32_t e = lo; e < hi; ++e) {
+                const uint32_t ent = SM_U32(ln.mrep + e * kLanes);
+                const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
+                const double c = SM_F64(ln.clk + last * kLanes);
+                if (c < best) { best = c; pick = ent; found = true; }
+            }
+            // :772-773 the request joins its MODEL's queue
+            if ((int32_t)SM_U32(ln.qlen + m * kLanes) == 0) SM_U32(ln.qhead + m * kLanes) = (uint32_t)i;
+            SM_U32(ln.qlen + m * kLanes) += 1;
+            SM_U32(ln.model_req + m * kLanes) += 1;
+            const uint32_t g = pick & 0xFFu;
+            if (found && ts >= SM_F64(ln.idle + g * kLanes))   // :776-778
+                serve_group(a, ln, ts, m, g);
+        }
+        // :781-787 drain
+        while (ln.heap_n > 0) {
+            double te; uint32_t ge;
+            heap_pop(ln, te, ge);
+            const int32_t pm = pick_model(a, ln, ge);
+            if (pm < 0) continue;
+            serve_group(a, ln, te, pm, ge);
+        }
+        for (int m = 0; m < a.M; ++m)                  // :789-790
+            if ((int32_t)SM_U32(ln.qlen + m * kLanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+    }
+    for (int m = 0; m < a.M; ++m) {
+        a.model_num_requests[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_req + m * kLanes);
+        a.model_num_good[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_good + m * kLanes);
+    }
+    for (int g = 0; g < a.G; ++g) {
+        a.group_num_requests[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_req + g * kLanes);
+        a.group_num_good[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_good + g * kLanes);
+    }
+    a.status[b] = ln.status;
+}
+
+// next_same[i] = next request with request i's model, -1 if none; one thread
+// per model walks the trace backwards.
+__global__ void next_same_kernel(const int32_t *model_ids, int64_t N, int32_t M, int32_t *next_same)
+{
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    int32_t last = -1;
+    for (int64_t i = N - 1; i >= 0; --i) {
+        if (model_ids[i] == m) { next_same[i] = last; last = (int32_t)i; }
+    }
+}
+
+// Sum of finish - arrival over one leaf of numpy's pairwise order, read back
+// from the per-request outputs: one thread per (leaf, candidate).
+__global__ void leaf_sums_from_finish_kernel(const double *finish, const double *arrivals,
+                                             int64_t N, int32_t B,
+                                             int32_t num_leaves, const int32_t *leaf_start,
+                                             double *leaf_sums)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (int64_t)B * num_leaves) return;
+    const int32_t leaf = (int32_t)(t % num_leaves);
+    const int64_t b = t / num_leaves;
+    const int64_t s = leaf_start[leaf], e = leaf_start[leaf + 1];
+    const int64_t body_end = s + ((e - s) & ~(int64_t)7);
+    const double *f = finish + (size_t)b * N;
+    double p[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int64_t i = s;
+    for (; i < body_end; i += 8)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) p[j] += f[i + j] - arrivals[i + j];
+    double r = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+    for (; i < e; ++i) r += f[i] - arrivals[i];
+    leaf_sums[(size_t)leaf * B + b] = r;
+}
+
+}  // namespace mms

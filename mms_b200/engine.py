@@ -80,6 +80,20 @@ class DeviceTrace:
                                                   _ptr(self.model_hist), _stream_ptr()),
                       "mms_trace_model_histogram")
 
+    def next_same_model(self):
+        """i32[N] on the device: index of the next request with the same model
+        (the per-model FIFO queues of the batching simulator run along it)."""
+        if getattr(self, "_next_same", None) is None:
+            with torch.cuda.device(self.device):
+                buf = torch.empty(max(self.num_requests, 1), dtype=torch.int32,
+                                  device=self.device)
+                tr = self.c_trace()
+                nat.check(nat.lib().mms_trace_next_same_model(
+                    ctypes.byref(tr), self.num_models, _ptr(buf), _stream_ptr()),
+                    "mms_trace_next_same_model")
+            self._next_same = buf
+        return self._next_same
+
     def c_trace(self):
         return nat.Trace(self.num_requests, _ptr(self.arrivals), _ptr(self.model_ids),
                          _ptr(self.slos))
@@ -94,13 +108,17 @@ class LatencyTable:
     the parallel config `configs[c]`; a config a model has no profile for is
     +inf (the f32 cast of 1e100), so such a replica never meets an SLO."""
 
-    def __init__(self, prof_ress: Sequence, batch_size: int = 1):
+    def __init__(self, prof_ress: Sequence, batch_sizes=None):
+        """batch_sizes None: one latency per stage (batch size 1, table
+        [M][C][S]); else the table gets a last axis over those batch sizes
+        ([M][C][S][NB], controller.py:451-461)."""
         self.prof_ress = list(prof_ress)
-        self.batch_size = batch_size
+        self.batch_sizes = None if batch_sizes is None else [int(b) for b in batch_sizes]
         self.configs: List = []
         self.column = {}
         self.max_stages = 1
-        self._host = np.zeros((len(self.prof_ress), 0, 1), np.float32)
+        tail = () if batch_sizes is None else (len(self.batch_sizes),)
+        self._host = np.zeros((len(self.prof_ress), 0, 1) + tail, np.float32)
         self._device = None
 
     def columns_for(self, configs) -> None:
@@ -112,8 +130,8 @@ class LatencyTable:
             self.configs.append(c)
         S = max([self.max_stages] + [int(c.pp) for c in new])
         M, C = len(self.prof_ress), len(self.configs)
-        tab = np.zeros((M, C, S), np.float32)
         old = self._host
+        tab = np.zeros((M, C, S) + old.shape[3:], np.float32)
         tab[:, :old.shape[1], :old.shape[2]] = old
         with np.errstate(over="ignore"):
             for m, prof in enumerate(self.prof_ress):
@@ -121,12 +139,15 @@ class LatencyTable:
                     col = self.column[c]
                     value = prof.para_dict.get(c, None)
                     if value:
-                        stages = value.latency[self.batch_size]
-                        penalty = 0.009 * len(stages)
+                        penalty = 0.009 * len(value.latency[1])
                         for k in range(int(c.pp)):
-                            tab[m, col, k] = stages[k] * (1 + penalty)
+                            if self.batch_sizes is None:
+                                tab[m, col, k] = value.latency[1][k] * (1 + penalty)
+                            else:
+                                for j, bs in enumerate(self.batch_sizes):
+                                    tab[m, col, k, j] = value.latency[bs][k] * (1 + penalty)
                     else:
-                        tab[m, col, :] = np.float32(inf)
+                        tab[m, col] = np.float32(inf)
         self._host = tab
         self.max_stages = S
         self._device = None
@@ -352,3 +373,96 @@ def encode_dense(m_id2g_id, num_stages, num_models):
     if info.shape[1] == 0:
         info = np.zeros((1, 1), np.uint32)
     return off, rep, info, max(int(ns.sum()), 1)
+
+
+def group_lists(model_off, model_rep, group_info, G):
+    """g_id2m_id of controller.py:424-430 as CSR per candidate, from the
+    compact tables: (group_off u16[B][G+1], group_mod u16[B][P], group_cfg
+    u32[B][G] = first slot | stages << 8 | column << 16)."""
+    B, P = model_rep.shape
+    M = model_off.shape[1] - 1
+    group_off = np.zeros((B, G + 1), np.int64)
+    group_mod = np.zeros((B, P), np.uint16)
+    group_cfg = np.zeros((B, G), np.uint32)
+    for b in range(B):
+        n = int(model_off[b, M])
+        ents = model_rep[b, :n].astype(np.int64)
+        g = ents & 0xFF
+        m = np.repeat(np.arange(M), np.diff(model_off[b].astype(np.int64)))
+        order = np.lexsort((m, g))                  # by group, models ascending
+        group_mod[b, :n] = m[order]
+        group_off[b, 1:] = np.cumsum(np.bincount(g, minlength=G))
+        info = group_info[b].astype(np.int64)
+        cfg = info & 0xFFFF                         # first slot | stages << 8
+        col = np.zeros(G, np.int64)
+        col[g] = ents >> 24
+        group_cfg[b] = (cfg | (col << 16)).astype(np.uint32)
+    return group_off.astype(np.uint16), group_mod, group_cfg
+
+
+def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+                    latency, latency_stride, batch_sizes, heap_capacity=0):
+    """simulate_requests_mixed_batching (controller.py:630-798) for every
+    candidate.  Always returns per-request outputs."""
+    _require_cuda()
+    L = nat.lib()
+    dev = trace.device
+    N = trace.num_requests
+    res = BatchResult()
+    goff, gmod, gcfg = group_lists(model_off, model_rep, group_info, G)
+    with torch.cuda.device(dev):
+        d_off, d_rep = _to_device(model_off, dev), _to_device(model_rep, dev)
+        d_goff, d_gmod, d_gcfg = (_to_device(x, dev) for x in (goff, gmod, gcfg))
+        d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev)
+        cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), None,
+                               _ptr(d_lat), int(latency_stride))
+        bat = nat.Batching(_ptr(d_goff), _ptr(d_gmod), _ptr(d_gcfg), len(batch_sizes),
+                           int(heap_capacity), (ctypes.c_int32 * 8)(*list(batch_sizes)))
+        need = L.mms_sim_batching_workspace_bytes(N, ctypes.byref(cands))
+        ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        ws = nat.Workspace(_ptr(ws_t), need)
+        i32 = dict(dtype=torch.int32, device=dev)
+        o_mreq, o_mgood = torch.zeros((B, max(M, 1)), **i32), torch.zeros((B, max(M, 1)), **i32)
+        o_greq, o_ggood = torch.zeros((B, G), **i32), torch.zeros((B, G), **i32)
+        o_total = torch.zeros(B, dtype=torch.int64, device=dev)
+        o_lsum = torch.zeros(B, dtype=torch.float64, device=dev)
+        o_status = torch.zeros(B, **i32)
+        o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev)
+        o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev)
+        out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood), _ptr(o_total),
+                          _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good), None)
+        tr, plan = trace.c_trace(), trace.c_plan()
+        rc = L.mms_sim_batching(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(bat),
+                                _ptr(trace.next_same_model()), ctypes.byref(plan),
+                                ctypes.byref(ws), ctypes.byref(out), _stream_ptr())
+        nat.check(rc, "mms_sim_batching")
+        res.model_num_requests = o_mreq.cpu().numpy()[:, :M]
+        res.model_num_good = o_mgood.cpu().numpy()[:, :M]
+        res.group_num_requests = o_greq.cpu().numpy()
+        res.group_num_good = o_ggood.cpu().numpy()
+        res.good_total = o_total.cpu().numpy()
+        res.latency_sum = o_lsum.cpu().numpy()
+        res.status = o_status.cpu().numpy().astype(np.uint32)
+        res.resimulated = None
+        res.finish = o_fin.cpu().numpy()[:, :N]
+        res.good = o_good.cpu().numpy()[:, :N].astype(bool)
+    if np.any(res.status):
+        bad = int(np.flatnonzero(res.status)[0])
+        what = {nat.STATUS_HEAP_OVERFLOW: "event heap overflow (raise heap_capacity)",
+                nat.STATUS_QUEUE_LEFT: "a request was left queued",
+                nat.STATUS_BAD_INDEX: "bad table index"}
+        raise RuntimeError(f"batching simulator reported status {int(res.status[bad])} for "
+                           f"candidate {bad}: " + ", ".join(v for k, v in what.items()
+                                                            if res.status[bad] & k))
+    return res
+
+
+def run_batch_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
+                       heap_capacity=0):
+    """Batching simulation of every placement of `enc`; `table` must have been
+    built with batch sizes."""
+    if table.batch_sizes is None:
+        raise ValueError("the latency table has no batch-size axis")
+    return launch_batching(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, enc.model_off,
+                           enc.model_rep, enc.group_info, table.device(trace.device), 0,
+                           table.batch_sizes, heap_capacity)

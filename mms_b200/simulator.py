@@ -22,6 +22,11 @@ from .workload import DEFAULT_WARMUP, PerModelStatsResult, StatsResult, eps
 
 inf = 1e100      # alpa_serve/util.py:23
 
+# Batch sizes the batching simulator may form: the module global
+# alpa_serve.util.batchsize_config (util.py:13).  Like in the reference it is
+# edited in place (`batchsize_config[:] = [1, 2, 4, 8]`).
+batchsize_config = [1, 2, 4, 8, 16]
+
 
 def _counters(res, M, G, b=0):
     mreq = res.model_num_requests[b, :M].astype(np.int32)
@@ -86,13 +91,37 @@ def simulate_requests(finish, good, tstamps, model_ids, slos, m_id2g_id,
                       num_requests, nat.FLAG_LEGACY_CLOCK)
 
 
+def simulate_requests_mixed_batching(finish, good, tstamps, model_ids, slos, m_id2g_id,
+                                     g_id2m_id, num_stages, stage_latency, num_requests):
+    """controller.py:631-798: per-model queues, batches formed at dispatch
+    under the head request's deadline.  stage_latency is
+    [M][G][S][len(batchsize_config)]; g_id2m_id is implied by m_id2g_id and
+    only checked for shape."""
+    lat = np.ascontiguousarray(stage_latency, dtype=np.float32)
+    M, G, S, NB = lat.shape
+    if NB != len(batchsize_config):
+        raise ValueError("stage_latency's last axis must match batchsize_config")
+    N = int(num_requests)
+    trace = engine.DeviceTrace(np.asarray(tstamps)[:N], np.asarray(model_ids)[:N],
+                               np.asarray(slos)[:N], M)
+    if G == 0 or M == 0:
+        finish[:N] = np.asarray(tstamps)[:N]
+        good[:N] = False
+        z = np.zeros
+        return z(M, np.int32), z(M, np.int32), z(G, np.int32), z(G, np.int32)
+    off, rep, info, T = engine.encode_dense(m_id2g_id, num_stages, M)
+    res = engine.launch_batching(trace, 1, M, G, rep.shape[1], T, S, G, off, rep, info, lat, 0,
+                                 list(batchsize_config))
+    finish[:N] = res.finish[0]
+    good[:N] = res.good[0]
+    return _counters(res, M, G)
+
+
 def approximate_one_case_one_placement(placement, model_names, prof_ress, model_ids, slos,
                                        arrivals, mixed=True, enable_batching=False):
     """controller.py:410-503: simulate one ModelPlacement on one trace.
     Returns (start, finish, good, model_num_requests, model_num_good_requests,
     group_num_requests, group_num_good_requests)."""
-    if enable_batching:
-        raise NotImplementedError("batching is served by simulate_requests_mixed_batching")
     M = len(model_names)
     G = len(placement.group_configs)
     N = len(arrivals)
@@ -123,8 +152,13 @@ def approximate_one_case_one_placement(placement, model_names, prof_ress, model_
         return (arrivals, finish, good) + tuple(counters)
 
     trace = engine.DeviceTrace(arrivals, model_ids, slos, M)
-    table = engine.LatencyTable(prof_ress)
+    table = engine.LatencyTable(prof_ress, list(batchsize_config) if enable_batching else None)
     enc = engine.encode_placements([placement], table, M)
+    if enable_batching and G > 0:
+        res = engine.run_batch_batching(trace, enc, table)
+        finish[:] = res.finish[0]
+        good[:] = res.good[0]
+        return (arrivals, finish, good) + tuple(_counters(res, M, G))
     if G == 0:
         z = np.zeros
         return (arrivals, arrivals.copy(), np.zeros(N, bool), trace.model_hist.cpu().numpy()[:M],

@@ -192,3 +192,71 @@ def test_unsorted_trace_falls_back_to_one_chunk(loaded):
     assert np.array_equal(good, egood)
     for a, b in zip(got, exp):
         assert np.array_equal(a, b)
+
+
+def test_batching_kernel_golden(loaded, golden):
+    from mms_b200 import simulator
+    g = golden("kernel_batching")
+    N = len(g["tstamps"])
+    fin = np.empty(N); good = np.empty(N, bool)
+    simulator.batchsize_config[:] = [int(x) for x in g["batchsize_config"]]
+    try:
+        got = simulator.simulate_requests_mixed_batching(
+            fin, good, g["tstamps"], g["model_ids"], g["slos"], g["m_id2g_id"], g["g_id2m_id"],
+            g["num_stages"], g["stage_latency"], N)
+    finally:
+        simulator.batchsize_config[:] = [1, 2, 4, 8, 16]
+    assert fin.tobytes() == g["finish"].tobytes()
+    assert np.array_equal(good, g["good"])
+    same_counters(got, g)
+
+
+def test_batching_candidates_golden(loaded, golden):
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    g = golden("case_candidates_batching")
+    case = cases.candidate_batch_case(num_candidates=int(g["num_candidates"]),
+                                      duration=float(g["duration"]), batching=True)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    trace = engine.DeviceTrace(case.workload.arrivals, mids, slos, len(names))
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(names))
+    res = engine.run_batch_batching(trace, enc, table)
+    for b in range(enc.B):
+        G = int(enc.num_groups[b])
+        assert res.finish[b].tobytes() == g["finish"][b].tobytes(), b
+        assert np.array_equal(res.good[b], g["good"][b])
+        assert np.array_equal(res.model_num_requests[b], g["model_num_requests"][b])
+        assert np.array_equal(res.model_num_good[b], g["model_num_good"][b])
+        assert np.array_equal(res.group_num_requests[b, :G], g["group_num_requests"][b, :G])
+        assert np.array_equal(res.group_num_good[b, :G], g["group_num_good"][b, :G])
+        assert res.latency_sum[b] == float(np.add.reduce(g["finish"][b] - case.workload.arrivals))
+        assert res.good_total[b] == int(g["good"][b].sum())
+
+
+def test_batching_against_cpu_checker_long(loaded):
+    """A 20-minute trace, 64 candidates: every per-request output equals the
+    checker's pure restatement of the Python reference."""
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=64, duration=1200.0, batching=True,
+                                      placement_seed=4)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    trace = engine.DeviceTrace(arr, mids, slos, len(names))
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(names))
+    res = engine.run_batch_batching(trace, enc, table)
+    for b in range(0, 64, 3):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(
+            case.placements[b], profs, mids, slos, arr, batchsize_config=(1, 2, 4, 8))
+        assert res.finish[b].tobytes() == fin.tobytes(), b
+        assert np.array_equal(res.good[b], good)
+        assert np.array_equal(res.model_num_requests[b], mreq)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
+        assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)

@@ -125,3 +125,20 @@ def test_sum_plan_reproduces_numpy():
         a[::3] = 0.0
         assert numpy_order_sum(a.tolist(), start, merges) == float(np.add.reduce(a))
     assert L.mms_sum_plan_leaves(0) == 0
+
+
+def test_group_lists_match_reference_tables():
+    case = cases.candidate_batch_case(num_candidates=12, duration=5.0, batching=True)
+    profs = [d.profiling_result for d in case.model_datas]
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(profs))
+    goff, gmod, gcfg = engine.group_lists(enc.model_off, enc.model_rep, enc.group_info, enc.G)
+    for b, p in enumerate(case.placements):
+        _, g2m, ns, lat = tables.dense_tables(p, profs, batchsize_config=(1, 2, 4, 8))
+        for g in range(len(ns)):
+            want = g2m[g][g2m[g] >= 0]
+            assert np.array_equal(gmod[b, goff[b, g]:goff[b, g + 1]], want)
+            assert (gcfg[b, g] >> 8) & 0xFF == ns[g]
+            col = int(gcfg[b, g]) >> 16
+            for m in want:
+                assert table.host[m, col, :ns[g], :].tobytes() == lat[m, g, :ns[g], :].tobytes()

@@ -168,6 +168,38 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands,
                   const mms_sim_options *opts, const mms_workspace *ws,
                   const mms_results *out, uint32_t flags, void *stream);
 
+/* ---- mms_sim_mixed for callers that must not allocate -------------------
+ * No counterpart in the reference.
+ *
+ * Some hosts cannot give mms_sim_mixed a workspace: a plugin running inside a
+ * serving process whose framework has already reserved the GPU's memory for
+ * its own pool (a cudaMalloc there fails or is forbidden by the host), or a
+ * latency-critical loop that must not take the driver's allocation lock and
+ * the device-wide synchronisation an allocation or free implies.  This entry
+ * point does the same work with the scratch held in an array that is part of
+ * the library image: MMS_STATIC_SCRATCH_BYTES of device memory on every GPU
+ * that loads the library, held until the process exits.  It calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ *  - Inputs and outputs are passed as for mms_sim_mixed; only `ws` is gone.
+ *  - A shape whose scratch need (mms_sim_workspace_bytes) exceeds
+ *    MMS_STATIC_SCRATCH_BYTES is rejected with MMS_ERR_UNSUPPORTED and a
+ *    message in mms_last_error(); nothing is launched.
+ *  - The first call on a device looks up the array's device address (once
+ *    per device, with that device current).  Make that first call outside
+ *    any stream capture.
+ *  - Every call on a device uses the same array, and the array keeps what the
+ *    previous call left in it.  The call clears what it needs cleared, so
+ *    back-to-back calls on one stream are fine; two calls whose kernels
+ *    overlap on the GPU (different streams, no ordering) race on the array
+ *    and give wrong results.
+ */
+#define MMS_STATIC_SCRATCH_BYTES (32u << 20)
+int mms_sim_mixed_static(const mms_trace *trace, const mms_placements *cands,
+                         const mms_sum_plan *plan, const int32_t *model_hist,
+                         const mms_sim_options *opts, const mms_results *out,
+                         uint32_t flags, void *stream);
+
 /* ---- batching simulator -------------------------------------------------
  * simulate_requests_mixed_batching (controller.py:630-798) for every
  * candidate.  `cands->latency` is f32[M][C][S][NB] here (NB batch sizes, the

@@ -30,11 +30,13 @@ STATUS_BAD_INDEX = 4
 FLAG_PER_REQUEST = 1
 FLAG_LEGACY_CLOCK = 2
 
+STATIC_SCRATCH_BYTES = 32 << 20
+
 # Every symbol include/mms_sim.h declares.
 EXPORTS = (
     "mms_abi_version", "mms_last_error", "mms_sum_plan_leaves", "mms_sum_plan_fill",
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
-    "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
+    "mms_sim_mixed_static", "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
 )
 
 _vp = ctypes.c_void_p
@@ -109,6 +111,10 @@ def lib():
                                 ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(SimOptions),
                                 ctypes.POINTER(Workspace), ctypes.POINTER(Results),
                                 ctypes.c_uint32, _vp]
+    L.mms_sim_mixed_static.restype = ctypes.c_int
+    L.mms_sim_mixed_static.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
+                                       ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(SimOptions),
+                                       ctypes.POINTER(Results), ctypes.c_uint32, _vp]
     L.mms_trace_next_same_model.restype = ctypes.c_int
     L.mms_trace_next_same_model.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_sim_batching_workspace_bytes.restype = ctypes.c_size_t

@@ -274,6 +274,55 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     return MMS_OK;
 }
 
+}  // extern "C"
+
+namespace mms {
+
+// Scratch of mms_sim_mixed_static.  In host code this name is only a handle
+// for cudaGetSymbolAddress, never an address a kernel can use.
+static __device__ __align__(256) unsigned char g_static_scratch[MMS_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static void *g_static_scratch_ptr[kMaxDevices];   // device address, per device ordinal
+
+}  // namespace mms
+
+extern "C" {
+
+int mms_sim_mixed_static(const mms_trace *trace, const mms_placements *cands,
+                         const mms_sum_plan *plan, const int32_t *model_hist,
+                         const mms_sim_options *opts, const mms_results *out,
+                         uint32_t flags, void *stream)
+{
+    if (!trace || !cands) return MMS_ERR_ARG;
+    const size_t need = mms_sim_workspace_bytes(trace->num_requests, cands, opts, flags);
+    if (need == 0 && cands->num_candidates > 0) {
+        snprintf(mms::g_last_error, sizeof(mms::g_last_error),
+                 "mms_sim_mixed_static: shape outside the kernel limits");
+        return MMS_ERR_UNSUPPORTED;
+    }
+    if (need > (size_t)MMS_STATIC_SCRATCH_BYTES) {
+        snprintf(mms::g_last_error, sizeof(mms::g_last_error),
+                 "mms_sim_mixed_static: needs %zu bytes of scratch, the built-in array holds %u; "
+                 "use fewer candidates per call or mms_sim_mixed with a caller workspace",
+                 need, (unsigned)MMS_STATIC_SCRATCH_BYTES);
+        return MMS_ERR_UNSUPPORTED;
+    }
+    int dev = -1;
+    MMS_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= mms::kMaxDevices) return MMS_ERR_NO_DEVICE;
+    if (!mms::g_static_scratch_ptr[dev]) {
+        // once per device, with that device current
+        void *p = nullptr;
+        MMS_CUDA(cudaGetSymbolAddress(&p, mms::g_static_scratch));
+        mms::g_static_scratch_ptr[dev] = p;
+    }
+    mms_workspace ws;
+    ws.ptr = mms::g_static_scratch_ptr[dev];
+    ws.bytes = (size_t)MMS_STATIC_SCRATCH_BYTES;
+    return mms_sim_mixed(trace, cands, plan, model_hist, opts, &ws, out, flags, stream);
+}
+
 int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_t *next_same,
                               void *stream)
 {

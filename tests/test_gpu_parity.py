@@ -260,3 +260,43 @@ def test_batching_against_cpu_checker_long(loaded):
         assert np.array_equal(res.model_num_requests[b], mreq)
         assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
         assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)
+
+
+@pytest.mark.parametrize("chunk,run_in", [(2048, 256), (4096, 2048), (0, 0)])
+def test_twin_groups_keep_exact_counters(loaded, chunk, run_in):
+    """Placements full of interchangeable groups (same config, same models):
+    speculative chunks may come out with twins' roles swapped; counters per
+    group must still be the reference's."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement, PlacementEvaluator
+    from mms_b200.profiling import ParallelConfig
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=1, duration=1500.0, num_models=8,
+                                      num_devices=16, total_rate=40.0, cv=3.0)
+    c1, c2, c4 = (ParallelConfig(1, 1, p) for p in (1, 2, 4))
+    sols = [
+        ModelPlacement([c1] * 8 + [c2] * 4, [[0, 3]] * 4 + [[1, 4]] * 4 + [[2, 5, 6]] * 2 + [[7, 2]] * 2),
+        ModelPlacement([c2] * 8, [[0, 1, 3, 4, 6, 7]] * 8),
+        ModelPlacement([c4, c4, c2, c2, c1, c1, c1, c1],
+                       [[2, 5, 0], [2, 5, 0], [1, 3], [1, 3], [4], [4], [6, 7], [7, 6]]),
+        ModelPlacement([c1] * 16, [[0]] * 3 + [[1]] * 3 + [[3, 4]] * 5 + [[6, 7, 0]] * 5),
+    ]
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            options=engine.sim_options(chunk, run_in))
+    enc = engine.encode_placements(sols, ev.table, len(ev.model_names))
+    res, _, _ = engine.run_batch(ev.trace, enc, ev.table, per_request=True, group_good=True,
+                                 options=ev.options)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    assert len(arr) > 30000
+    for b, p in enumerate(sols):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(p, profs, mids, slos, arr)
+        assert res.finish[b].tobytes() == fin.tobytes(), b
+        assert np.array_equal(res.good[b], good)
+        assert np.array_equal(res.model_num_good[b], mgood)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq), b
+        assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood), b
+        assert res.latency_sum[b] == float(np.add.reduce(fin - arr))

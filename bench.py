@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--chunk", type=int, default=0, help="requests per chunk (0 auto, <0 one)")
     ap.add_argument("--run-in", type=int, default=0, help="run-in requests per chunk (0 auto)")
+    ap.add_argument("--rounds", type=int, default=0, help="validate+repair rounds (0 auto)")
+    ap.add_argument("--repair-segments", type=int, default=0,
+                    help="segments a repair runs per round (0 auto, <0 no cap)")
     return ap.parse_args()
 
 
@@ -200,7 +203,7 @@ def run_b200(args):
     # every rank scores its own 4096 candidates (weak scaling) on the same trace
     case = build_case(args, placement_seed=rank)
     ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload, device=dev,
-                            options=engine.sim_options(args.chunk, args.run_in))
+                            options=engine.sim_options(args.chunk, args.run_in, args.rounds, args.repair_segments))
     N, B = ev.trace.num_requests, len(case.placements)
     L = nat.lib()
 
@@ -213,8 +216,9 @@ def run_b200(args):
     P = engine._ptr
     cands = nat.Placements(enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, 0, P(d_off), P(d_rep),
                            P(d_info), P(d_lat), 0)
-    opts = engine.sim_options(args.chunk, args.run_in)
-    need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts), 0)
+    opts = engine.sim_options(args.chunk, args.run_in, args.rounds, args.repair_segments)
+    need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts),
+                                     nat.FLAG_NO_GROUP_GOOD)
     ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     ws = nat.Workspace(P(ws_t), need)
     i32 = dict(dtype=torch.int32, device=dev)
@@ -233,7 +237,7 @@ def run_b200(args):
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
                              P(ev.trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
-                             ctypes.byref(out), 0, stream)
+                             ctypes.byref(out), nat.FLAG_NO_GROUP_GOOD, stream)
         nat.check(rc, "mms_sim_mixed")
         if world > 1:   # the search's argmax over all ranks' candidates
             score = o[3].double() / N - o[4] / N / 10000

@@ -49,6 +49,8 @@ extern "C" {
 /* flags */
 #define MMS_FLAG_PER_REQUEST 1u   /* also write finish[b][i] and good[b][i]      */
 #define MMS_FLAG_LEGACY_CLOCK 2u  /* one clock per group: controller.py:506-558  */
+#define MMS_FLAG_NO_GROUP_GOOD 4u /* group_num_good is not wanted (not written);
+                                     pass the same flags to the workspace query  */
 
 /* The request trace: what controller.py:323-339 caches per Workload
  * (model_ids, slos) plus Workload.arrivals (simulator/workload.py:272). */
@@ -106,6 +108,9 @@ typedef struct {
 typedef struct {
     int32_t chunk_requests;
     int32_t warmup_requests;
+    int32_t repair_rounds;         /* validate+repair rounds before the chain pass (0 = default) */
+    int32_t repair_segments;       /* segments (of 1024 requests) one repair may run per round;
+                                      it goes on in the next round (0 = default, <0 = no cap) */
 } mms_sim_options;
 
 /* How numpy sums N doubles (pairwise, blocks of <= 128, eight interleaved

@@ -29,6 +29,7 @@ STATUS_BAD_INDEX = 4
 
 FLAG_PER_REQUEST = 1
 FLAG_LEGACY_CLOCK = 2
+FLAG_NO_GROUP_GOOD = 4
 
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -57,7 +58,8 @@ class Placements(ctypes.Structure):
 
 
 class SimOptions(ctypes.Structure):
-    _fields_ = [("chunk_requests", ctypes.c_int32), ("warmup_requests", ctypes.c_int32)]
+    _fields_ = [("chunk_requests", ctypes.c_int32), ("warmup_requests", ctypes.c_int32),
+                ("repair_rounds", ctypes.c_int32), ("repair_segments", ctypes.c_int32)]
 
 
 class SumPlan(ctypes.Structure):

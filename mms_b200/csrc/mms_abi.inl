@@ -39,9 +39,10 @@ static int32_t plan_leaves(int64_t n)
 }
 
 struct Geometry {
-    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters;
+    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap;
     size_t smem_stream, smem_repair;
-    size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items;
+    size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
+        off_repair_from;
     size_t total;
 };
 
@@ -62,6 +63,22 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     if ((flags & MMS_FLAG_LEGACY_CLOCK) && c->max_stages != 2) return MMS_ERR_ARG;
 
     const int64_t B = c->num_candidates;
+    // blocks that fit an SM at once, from the kernel's shared-memory use
+    const size_t lat_elems0 = (size_t)c->num_models * c->num_columns * c->max_stages + 8;
+    const int lat_on_chip0 = (c->latency_stride == 0 && lat_elems0 * sizeof(float) <= (size_t)kLatSmemBytes)
+                                 ? (int)lat_elems0 : 0;
+    const SmemLayout L0 = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
+                                      c->max_stages, group_good, lat_on_chip0);
+    int sm_count = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        sm_count = 148;
+    }
+    int64_t per_sm = (int64_t)(233472 / (L0.total + 1024));
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 32) per_sm = 32;
+    const int64_t resident_slots = (int64_t)sm_count * per_sm;
     int64_t chunk = opts ? opts->chunk_requests : 0;
     int64_t warm = opts ? opts->warmup_requests : 0;
     // segments: the unit of state snapshots, counter flushes and repairs
@@ -73,23 +90,34 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     } else if (chunk > 0) {
         spc = (chunk + seg / 2) / seg;
     } else {
-        // enough streams for about three waves of resident warps on 148 SMs,
-        // but never chunks shorter than 4 segments
-        int64_t K = (148LL * 5 * 32 * 3 + B - 1) / B;
-        if (K > NS / 4) K = NS / 4;
+        // Chunks are the units of parallel work: as many as fill a little over three
+        // waves of the resident blocks (slots = SMs x blocks per SM at this
+        // kernel's shared-memory use), but never chunks shorter than 4
+        // segments.  More chunks mean more boundaries to validate and repair.
+        int64_t Kmax = NS / 4 > 0 ? NS / 4 : 1;
+        int64_t K = B > 0 ? (13 * resident_slots * kLanes) / (4 * B) : 1;
+        if (K > Kmax) K = Kmax;
         if (K < 1) K = 1;
         spc = (NS + K - 1) / K;
     }
     if (spc < 1) spc = 1;
     if (spc > NS) spc = NS;
     const int64_t K = (NS + spc - 1) / spc;
+    if (K * (B > 0 ? B : 1) >= 0x7FFFFFFFLL) return MMS_ERR_UNSUPPORTED;   // work-list encoding
     if (warm <= 0) warm = 2048;
+    int rounds = opts ? opts->repair_rounds : 0;
+    if (rounds <= 0) rounds = kDefaultRepairRounds;
+    if (rounds > kMaxRepairRounds) rounds = kMaxRepairRounds;
+    int cap = opts ? opts->repair_segments : 0;
+    if (cap == 0) cap = kDefaultRepairSegments;
+    if (cap < 0) cap = 0;
+    g->rounds = rounds; g->repair_cap = cap;
     g->K = (int32_t)K; g->NS = (int32_t)NS; g->seg_len = (int32_t)seg;
     g->seg_per_chunk = (int32_t)spc; g->warmup = (int32_t)warm;
 
-    // the shared table goes on chip as f64, with 8 readable entries of padding
+    // the shared table goes on chip (f32), with 8 readable entries of padding
     const size_t lat_elems = (size_t)c->num_models * c->num_columns * c->max_stages + 8;
-    g->lat_smem_elems = (c->latency_stride == 0 && lat_elems * sizeof(double) <= (size_t)kLatSmemBytes)
+    g->lat_smem_elems = (c->latency_stride == 0 && lat_elems * sizeof(float) <= (size_t)kLatSmemBytes)
                             ? (int32_t)lat_elems : 0;
     const SmemLayout L = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
                                      c->max_stages, group_good, g->lat_smem_elems);
@@ -102,7 +130,8 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     size_t off = 0;
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
     g->off_counters = off;    off += align256(sizeof(uint32_t) * (size_t)NS * L.n_counters * B);
-    g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kRepairRounds + 1));
+    g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
+    g->off_repair_from = off; off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
     g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
     g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
@@ -127,7 +156,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
         MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)g.smem_repair));
         const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
-        for (int r = 0; r < kRepairRounds; ++r) {
+        for (int r = 0; r < g.rounds; ++r) {
             ka.round = r;
             validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
@@ -187,7 +216,9 @@ size_t mms_sim_workspace_bytes(int64_t num_requests, const mms_placements *cands
                                const mms_sim_options *opts, uint32_t flags)
 {
     mms::Geometry g;
-    if (mms::plan_call(num_requests, cands, opts, flags, true, &g) != MMS_OK) return 0;
+    if (mms::plan_call(num_requests, cands, opts, flags, !(flags & MMS_FLAG_NO_GROUP_GOOD), &g) !=
+        MMS_OK)
+        return 0;
     return g.total;
 }
 
@@ -197,9 +228,11 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
 {
     using namespace mms;
     if (!trace || !cands || !plan || !ws || !out) return MMS_ERR_ARG;
-    if (flags & ~(MMS_FLAG_PER_REQUEST | MMS_FLAG_LEGACY_CLOCK)) return MMS_ERR_ARG;
+    if (flags & ~(MMS_FLAG_PER_REQUEST | MMS_FLAG_LEGACY_CLOCK | MMS_FLAG_NO_GROUP_GOOD))
+        return MMS_ERR_ARG;
     const int64_t N = trace->num_requests;
-    const bool gg = out->group_num_good != nullptr;
+    const bool gg = !(flags & MMS_FLAG_NO_GROUP_GOOD);
+    if (gg && !out->group_num_good) return MMS_ERR_ARG;
     Geometry g;
     int rc = plan_call(N, cands, opts, flags, gg, &g);
     if (rc) return rc;
@@ -236,6 +269,8 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.seg_counters = (uint32_t *)(scratch + g.off_counters);
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);
     ka.work_items = (uint32_t *)(scratch + g.off_work_items);
+    ka.repair_from = (int32_t *)(scratch + g.off_repair_from);
+    ka.repair_cap = g.repair_cap;
     ka.seg_end = (double *)(scratch + g.off_seg_end);
     ka.chunk_start = (double *)(scratch + g.off_chunk_start);
     ka.status = out->status;
@@ -243,7 +278,8 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.resimulated = out->resimulated;
 
     MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)B, st));
-    MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kRepairRounds + 1), st));
+    MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kMaxRepairRounds + 1), st));
+    MMS_CUDA(cudaMemsetAsync(ka.repair_from, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
     if (out->resimulated)
         MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)B, st));
     const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;

@@ -47,7 +47,9 @@ namespace mms {
 
 constexpr int kMaxSumDepth = 48;        // pair-sum stack of the numpy order
 constexpr int kLatSmemBytes = 32 * 1024;
-constexpr int kRepairRounds = 3;
+constexpr int kMaxRepairRounds = 16;
+constexpr int kDefaultRepairRounds = 3;
+constexpr int kDefaultRepairSegments = -1;   // no cap: measured best on the benchmark shape
 
 // Copies candidate b's tables into this lane's shared memory, checking every
 // index they hold, zeroes its clocks and counters, and returns the lane's view.
@@ -59,7 +61,7 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint
     Lane ln;
     ln.clk = (uint32_t)(L.clocks / sizeof(double)) + lane;
     ln.tmp = (uint32_t)(L.stage_tmp / sizeof(double)) + lane;
-    ln.lat_sm = (uint32_t)(L.latency / sizeof(double));
+    ln.lat_sm = (uint32_t)(L.latency / sizeof(float));
     counters = (uint32_t)(L.counters / sizeof(uint32_t)) + lane;
     n_counters = L.n_counters;
     ln.model_good = counters;
@@ -100,14 +102,15 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint
     return ln;
 }
 
-// The batch's shared latency table, widened to f64 (exact) on its way on chip.
+// The batch's shared latency table goes on chip (f32; widened to f64, exactly,
+// when it is used).
 __device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout &L, int lane)
 {
     if (a.lat_smem_elems) {
-        const uint32_t base = (uint32_t)(L.latency / sizeof(double));
+        const uint32_t base = (uint32_t)(L.latency / sizeof(float));
         const int real = a.M * a.C * a.S;
         for (int i = lane; i < a.lat_smem_elems; i += kLanes)
-            SM_F64(base + i) = i < real ? (double)__ldg(a.latency + i) : 0.0;
+            SM_F32(base + i) = i < real ? __ldg(a.latency + i) : 0.0f;
     }
     __syncwarp();
 }
@@ -115,7 +118,7 @@ __device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout
 __device__ inline void init_pipe(const KernelArgs &a, Pipe &p)
 {
     p.arrivals = a.arrivals; p.model_ids = a.model_ids; p.slos = a.slos;
-    p.last = a.N - 1;
+    p.last = (int32_t)(a.N - 1);
 }
 
 // Extra shared memory of the kernels that repair: the state the previous run
@@ -147,11 +150,11 @@ sim_stream_kernel(const KernelArgs a)
     init_pipe(a, p);
     // not chunked: one chunk holding every segment, plain sequential simulation
     KernelArgs ka = a;
-    int64_t begin = 0;
+    int32_t begin = 0;
     if (!chunked) {
         ka.seg_per_chunk = a.NS;
     } else if (j > 0) {
-        const int64_t first = a.leaf_start[seg_leaf(a, j * a.seg_per_chunk)];
+        const int32_t first = a.leaf_start[seg_leaf(a, j * a.seg_per_chunk)];
         begin = first - a.warmup > 0 ? first - a.warmup : 0;
     }
     run_chunk<kFull, kGroupGood, kLegacy>(ka, ln, p, counters, n_counters, b, j, begin, false,
@@ -175,9 +178,15 @@ __global__ void validate_kernel(const KernelArgs a)
     uint8_t stale[MMS_MAX_GROUPS];
     if (states_equivalent(a, b, [&](uint32_t s) { return X[s * B]; },
                           [&](uint32_t s) { return Y[s * B]; }, tau,
-                          [&](int u) -> uint8_t & { return stale[u]; }))
+                          [&](int u) -> uint8_t & { return stale[u]; })) {
+        if (a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair of this chunk goes on
+            const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
+            a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+        }
         return;
+    }
     for (int s = 0; s < a.T; ++s) Y[s * B] = X[s * B];
+    a.repair_from[(size_t)j * B + b] = -1;             // the whole chunk is redone
     const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
     a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
     if (a.resimulated) atomicAdd(&a.resimulated[b], 1);
@@ -195,7 +204,8 @@ sim_repair_kernel(const KernelArgs a)
     stage_latency_table(a, L, lane);
     const uint32_t w = blockIdx.x * kLanes + lane;
     if (w >= count) return;
-    const uint32_t item = a.work_items[w];
+    const uint32_t item = a.work_items[w] & 0x7FFFFFFFu;
+    const bool resume = (a.work_items[w] >> 31) != 0;
     const int32_t j = (int32_t)(item / (uint32_t)a.B);
     const int64_t b = item % (uint32_t)a.B;
 
@@ -203,13 +213,18 @@ sim_repair_kernel(const KernelArgs a)
     Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
-    for (int t = 0; t < a.T; ++t)
-        SM_F64(ln.clk + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + b];
+    // start of the chunk from the copied-in true state, or where a capped
+    // repair stopped, from the state it left after the segment before
+    const int32_t q_begin = resume ? a.repair_from[(size_t)j * a.B + b] : j * a.seg_per_chunk;
+    const double *src = resume ? a.seg_end + (size_t)(q_begin - 1) * a.T * a.B
+                               : a.chunk_start + (size_t)j * a.T * a.B;
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * kLanes) = src[(size_t)t * a.B + b];
     Pipe p;
     init_pipe(a, p);
-    const int64_t first = a.leaf_start[seg_leaf(a, j * a.seg_per_chunk)];
-    run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, first, true, true,
-                                          old_state, stale_buf);
+    const int32_t first = a.leaf_start[seg_leaf(a, q_begin)];
+    a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy>(
+        a, ln, p, counters, n_counters, b, j, first, true, true, old_state, stale_buf, q_begin,
+        a.repair_cap);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
@@ -241,15 +256,26 @@ sim_chain_kernel(const KernelArgs a)
             SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)q_prev * a.T + t) * a.B + b];
             SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + b];
         }
+        int32_t q_begin = j * a.seg_per_chunk;
+        int32_t begin = (int32_t)first;
         if (states_equivalent(a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
                               [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
-                              [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; }))
-            continue;
+                              [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; })) {
+            // the chunk continues its predecessor; finish a repair a round left capped
+            q_begin = a.repair_from[(size_t)j * a.B + b];
+            if (q_begin < 0) continue;
+            begin = a.leaf_start[seg_leaf(a, q_begin)];
+            for (int t = 0; t < a.T; ++t)
+                SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)(q_begin - 1) * a.T + t) * a.B + b];
+        } else {
+            for (int t = 0; t < a.T; ++t)
+                a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
+        }
         ++redone;
-        for (int t = 0; t < a.T; ++t)
-            a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
-        run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, first, true,
-                                              true, old_state, stale_buf);
+        for (int c = 0; c < n_counters; ++c) SM_U32(counters + c * kLanes) = 0;
+        run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, begin, true,
+                                              true, old_state, stale_buf, q_begin, 0);
+        a.repair_from[(size_t)j * a.B + b] = -1;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
     if (ln.status) atomicOr(&a.status[b], ln.status);

@@ -42,7 +42,9 @@ struct KernelArgs {
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from
     uint32_t *seg_counters;       // [NS][n_counters][B]
     uint32_t *work_count;         // [rounds]
-    uint32_t *work_items;         // [B * K]: chunk * B + candidate
+    uint32_t *work_items;         // [B * K]: chunk * B + candidate; bit 31 = continue a repair
+    int32_t *repair_from;         // [K][B]: segment a capped repair of chunk j stopped at, or -1
+    int32_t repair_cap;           // segments a repair may run per round
     int32_t round;
     // outputs
     uint32_t *status;             // [B]
@@ -145,29 +147,33 @@ __device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, in
 //   repair: the lane's clocks already hold the true state at `first`.  After
 //       each segment the new state is compared with the one stored by the
 //       previous run of that segment; once they are equivalent the rest of
-//       the chunk is known to be right already and the lane stops.
-// Returns the number of segments simulated.
+//       the chunk is known to be right already and the lane stops.  A repair
+//       may start at a later segment q_begin of the chunk (its clocks then
+//       hold the state after segment q_begin - 1) and may be capped at `cap`
+//       segments (0 = no cap).
+// Returns -1 when the chunk is finished (ran to its end, or settled), else
+// the segment at which the capped repair has to be continued.
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint32_t counters,
-                                    int n_counters, int64_t b, int32_t j, int64_t begin,
+                                    int n_counters, int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
-                                    uint32_t stale_buf)
+                                    uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0)
 {
     double *fin_out = kFull ? a.finish + (size_t)b * a.N : nullptr;
     uint8_t *good_out = kFull ? a.good + (size_t)b * a.N : nullptr;
-    const int32_t q0 = j * a.seg_per_chunk;
-    const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
+    const int32_t q0 = q_begin >= 0 ? q_begin : j * a.seg_per_chunk;
+    const int32_t q1 = (j + 1) * a.seg_per_chunk < a.NS ? (j + 1) * a.seg_per_chunk : a.NS;
     int32_t q = q0;
     int32_t leaf = seg_leaf(a, q0);
     int32_t seg_stop = seg_leaf(a, q0 + 1);
-    const int64_t first = leaf < a.num_leaves ? a.leaf_start[leaf] : a.N;
+    const int32_t first = leaf < a.num_leaves ? a.leaf_start[leaf] : (int32_t)a.N;
     leaf -= 1;                      // the run-in counts as a leaf that is not recorded
-    int64_t i = begin, span_end = first;
+    int32_t i = begin, span_end = first;
     bool record = false;
     int32_t done = 0;
     pipe_prime(ln, p, begin);
     for (;;) {
-        const int64_t body_end = record ? i + ((span_end - i) & ~(int64_t)7) : i;
+        const int32_t body_end = record ? i + ((span_end - i) & ~7) : i;
         double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
         double r = 0.0;
         for (; i < span_end; ++i) {
@@ -201,16 +207,17 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
                         [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
                         [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
                 }
-                if (settled) return done;
+                if (settled) return -1;
                 if (snapshots)
                     for (int t = 0; t < a.T; ++t)
                         a.seg_end[((size_t)q * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
-                if (++q >= q1) return done;
+                if (++q >= q1) return -1;
+                if (cap > 0 && done >= cap) return q;
                 seg_stop = seg_leaf(a, q + 1);
             }
         }
         ++leaf;
-        if (leaf >= a.num_leaves) return done;      // only an empty trace gets here
+        if (leaf >= a.num_leaves) return -1;        // only an empty trace gets here
         record = true;
         span_end = a.leaf_start[leaf + 1];
     }

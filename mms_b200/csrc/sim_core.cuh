@@ -31,6 +31,7 @@ extern __shared__ __align__(16) unsigned char smem[];
 #define SM_F64(i) (reinterpret_cast<double *>(smem)[(i)])
 #define SM_U32(i) (reinterpret_cast<uint32_t *>(smem)[(i)])
 #define SM_U16(i) (reinterpret_cast<uint16_t *>(smem)[(i)])
+#define SM_F32(i) (reinterpret_cast<float *>(smem)[(i)])
 
 // On-chip replica entry: group | LAST clock slot << 8 | stages << 16 | column << 24.
 // (The caller's model_rep carries the FIRST slot; setup converts.)
@@ -44,8 +45,8 @@ struct SmemLayout {
     int n_counters, tmp_stages;
 };
 
-// lat_elems: entries of the shared latency table kept on chip as f64 (0 =
-// read the f32 table from global memory).
+// lat_elems: entries of the shared f32 latency table kept on chip (0 = read
+// it from global memory).
 __host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, int S,
                                                   bool group_good, int lat_elems)
 {
@@ -54,7 +55,7 @@ __host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, in
     L.clocks = off;     off += sizeof(double) * (size_t)(T + kClockPad) * kLanes;
     L.tmp_stages = S > 8 ? S - 8 : 0;
     L.stage_tmp = off;  off += sizeof(double) * (size_t)L.tmp_stages * kLanes;
-    L.latency = off;    off += sizeof(double) * (size_t)lat_elems;
+    L.latency = off;    off += sizeof(float) * (size_t)((lat_elems + 3) & ~3);
     L.n_counters = M + G + (group_good ? G : 0);
     L.counters = off;   off += sizeof(uint32_t) * (size_t)L.n_counters * kLanes;
     L.model_rep = off;  off += sizeof(uint32_t) * (size_t)(P + kRepPad) * kLanes;
@@ -68,7 +69,7 @@ __host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, in
 struct Lane {
     uint32_t clk;             // f64 index of clock slot 0
     uint32_t tmp;             // f64 index, stages beyond the 8th of a deep pipeline
-    uint32_t lat_sm;          // f64 index of the on-chip latency table
+    uint32_t lat_sm;          // f32 index of the on-chip latency table
     uint32_t model_good;      // u32 index, [M]
     uint32_t group_req;       // u32 index, [G]
     uint32_t group_good;      // u32 index, [G]
@@ -86,7 +87,7 @@ struct Pipe {
     double ts; float slo; int32_t m; uint32_t lo, n, e0, e1, e2, e3;
     double ts1; float slo1; int32_t m1;
     const double *arrivals; const int32_t *model_ids; const float *slos;
-    int64_t last;             // highest readable request index
+    int32_t last;             // highest readable request index
 };
 
 __device__ __forceinline__ int32_t clean_model(Lane &ln, int32_t m)
@@ -111,10 +112,10 @@ __device__ __forceinline__ void pipe_tables(const Lane &ln, int32_t m, uint32_t 
 }
 
 // Fills the pipe so that request `i` is ready to execute.
-__device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int64_t i)
+__device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 {
-    const int64_t i0 = i < p.last ? i : p.last;
-    const int64_t i1 = i + 1 < p.last ? i + 1 : p.last;
+    const int32_t i0 = i < p.last ? i : p.last;
+    const int32_t i1 = i + 1 < p.last ? i + 1 : p.last;
     p.ts = __ldg(p.arrivals + i0); p.slo = __ldg(p.slos + i0);
     p.m = clean_model(ln, __ldg(p.model_ids + i0));
     p.ts1 = __ldg(p.arrivals + i1); p.slo1 = __ldg(p.slos + i1);
@@ -129,7 +130,7 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int64_t i)
 // The step is large; callers keep a single call site per kernel so that the
 // hot loop stays inside the instruction cache.
 template <bool kFull, bool kGroupGood, bool kLegacy>
-__device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int64_t i, bool record,
+__device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)
 {
     const double ts = p.ts;
@@ -140,7 +141,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int64_t i, bool re
     // ---- state-independent fetches for the requests behind this one -------
     uint32_t lo1, n1, f0, f1, f2, f3;
     pipe_tables(ln, p.m1, lo1, n1, f0, f1, f2, f3);
-    const int64_t i2 = i + 2 < p.last ? i + 2 : p.last;
+    const int32_t i2 = i + 2 < p.last ? i + 2 : p.last;
     const double ts2 = __ldg(p.arrivals + i2);
     const float slo2 = __ldg(p.slos + i2);
     const int32_t m2raw = __ldg(p.model_ids + i2);
@@ -182,8 +183,12 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int64_t i, bool re
             if (ln.lat_on_chip) {
                 // rows are padded so that 8 entries are always readable
                 const uint32_t lr = ln.lat_sm + row;
-                l0 = SM_F64(lr); l1 = SM_F64(lr + 1); l2 = SM_F64(lr + 2); l3 = SM_F64(lr + 3);
-                l4 = SM_F64(lr + 4); l5 = SM_F64(lr + 5); l6 = SM_F64(lr + 6); l7 = SM_F64(lr + 7);
+                l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
+                if (ns > 2) {
+                    l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
+                    l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
+                    l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
+                }
             } else {
                 const float *lat = ln.lat_gl + row;
                 const int sm = ln.S - 1;   // clamp reads to the table row
@@ -218,7 +223,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int64_t i, bool re
                             t = ns > 7 ? fmax(t, k7) + l7 : t; t7 = t;
                             for (uint32_t k = 8; k < ns; ++k) {
                                 const double lk = ln.lat_on_chip
-                                    ? SM_F64(ln.lat_sm + row + k)
+                                    ? (double)SM_F32(ln.lat_sm + row + k)
                                     : (double)__ldg(ln.lat_gl + row + k);
                                 t = fmax(t, SM_F64(ck + k * kLanes)) + lk;
                                 SM_F64(ln.tmp + (k - 8) * kLanes) = t;

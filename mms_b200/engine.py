@@ -8,6 +8,7 @@ include/mms_sim.h describes.  PyTorch is used for device memory and streams
 only; all compute goes through the C ABI in libmms_sim.so.
 """
 import ctypes
+import operator
 from itertools import chain
 from typing import List, Sequence
 
@@ -17,6 +18,7 @@ import torch
 from . import _native as nat
 
 inf = 1e100      # alpa_serve/util.py:23
+_PP = operator.itemgetter(2)     # pipeline degree of a ParallelConfig(dp, op, pp)
 
 
 def _require_cuda():
@@ -185,23 +187,19 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     '<' over groups in ascending id), so nothing is re-sorted."""
     B = len(placements)
     M = int(num_models)
-    table.columns_for(chain.from_iterable(p.group_configs for p in placements))
-    colmap = table.column
-
-    n_groups = np.fromiter((len(p.group_configs) for p in placements), np.int64, B)
-    tot_groups = int(n_groups.sum())
-    cfg_col = np.fromiter((colmap[c] for p in placements for c in p.group_configs),
-                          np.int64, tot_groups)
-    cfg_pp = np.fromiter((c.pp for p in placements for c in p.group_configs),
-                         np.int64, tot_groups)
-    n_in_group = np.fromiter((len(ms) for p in placements for ms in p.group_models),
-                             np.int64, tot_groups)
-    if len(n_in_group) != tot_groups:
+    # One C-level pass per field (itertools/map), no Python-level loop per group.
+    all_cfgs = list(chain.from_iterable(p.group_configs for p in placements))
+    all_groups = list(chain.from_iterable(p.group_models for p in placements))
+    n_groups = np.fromiter(map(len, (p.group_configs for p in placements)), np.int64, B)
+    tot_groups = len(all_cfgs)
+    if len(all_groups) != tot_groups:
         raise ValueError("group_configs and group_models differ in length")
+    table.columns_for(dict.fromkeys(all_cfgs))
+    cfg_col = np.fromiter(map(table.column.__getitem__, all_cfgs), np.int64, tot_groups)
+    cfg_pp = np.fromiter(map(_PP, all_cfgs), np.int64, tot_groups)
+    n_in_group = np.fromiter(map(len, all_groups), np.int64, tot_groups)
     tot_placed = int(n_in_group.sum())
-    placed_model = np.fromiter(
-        chain.from_iterable(chain.from_iterable(p.group_models for p in placements)),
-        np.int64, tot_placed)
+    placed_model = np.fromiter(chain.from_iterable(all_groups), np.int64, tot_placed)
     if tot_placed and (placed_model.min() < 0 or placed_model.max() >= M):
         raise IndexError("model id in group_models is out of range")
 
@@ -213,8 +211,7 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     csum = np.cumsum(cfg_pp)
     base = np.concatenate(([0], csum))[grp_first]
     slot_first = (csum - cfg_pp) - base[grp_b]
-    slots_per_b = np.zeros(B, np.int64)
-    np.add.at(slots_per_b, grp_b, cfg_pp)
+    slots_per_b = np.bincount(grp_b, weights=cfg_pp, minlength=B).astype(np.int64)
     T = int(slots_per_b.max()) if B else 0
     S = int(table.max_stages)
     C = len(table.configs)
@@ -228,7 +225,8 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     pl_grp = np.repeat(np.arange(tot_groups), n_in_group)           # flat group of each pair
     pl_b = grp_b[pl_grp]
     pl_g = grp_g[pl_grp]
-    order = np.lexsort((pl_g, placed_model, pl_b))
+    # one composite key: by candidate, then model, then group id
+    order = np.argsort((pl_b * max(M, 1) + placed_model) * (G + 1) + pl_g, kind="stable")
     pl_b, pl_g, pl_m, pl_grp = pl_b[order], pl_g[order], placed_model[order], pl_grp[order]
     placed_per_b = np.bincount(pl_b, minlength=B) if tot_placed else np.zeros(B, np.int64)
     P = int(placed_per_b.max()) if B else 0
@@ -239,13 +237,12 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     model_rep = np.zeros((B, max(P, 1)), np.uint32)
     model_rep[pl_b, pos] = (pl_g | (slot_first[pl_grp] << 8) | (cfg_pp[pl_grp] << 16)
                             | (cfg_col[pl_grp] << 24)).astype(np.uint32)
-    counts = np.zeros((B, M + 1), np.int64)
-    np.add.at(counts, (pl_b, pl_m + 1), 1)
+    counts = np.bincount(pl_b * (M + 1) + pl_m + 1, minlength=B * (M + 1)).reshape(B, M + 1)
     model_off = np.cumsum(counts, axis=1).astype(np.uint16)
     # a group is contested when one of its models has more than one replica
     replicas = counts[pl_b, pl_m + 1]
-    contested = np.zeros(tot_groups, np.int64)
-    np.maximum.at(contested, pl_grp, (replicas > 1).astype(np.int64))
+    contested = (np.bincount(pl_grp, weights=(replicas > 1), minlength=tot_groups) > 0
+                 ).astype(np.int64)
     group_info = np.zeros((B, max(G, 1)), np.uint32)
     group_info[grp_b, grp_g] = (slot_first | (cfg_pp << 8) | (contested << 16)).astype(np.uint32)
 
@@ -260,10 +257,12 @@ class BatchResult:
                  "resimulated")
 
 
-def sim_options(chunk_requests=0, warmup_requests=0):
+def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_segments=0):
     """How the trace is cut for time-parallel execution (mms_sim_options):
-    0 lets the library choose, chunk_requests < 0 forces one chunk."""
-    return nat.SimOptions(int(chunk_requests), int(warmup_requests))
+    0 lets the library choose, chunk_requests < 0 forces one chunk.  Results
+    never depend on these numbers, only the run time does."""
+    return nat.SimOptions(int(chunk_requests), int(warmup_requests), int(repair_rounds),
+                          int(repair_segments))
 
 
 def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
@@ -276,6 +275,8 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
     N = trace.num_requests
     res = BatchResult()
     opts = options if options is not None else sim_options()
+    if not want_group_good:
+        flags |= nat.FLAG_NO_GROUP_GOOD
     with torch.cuda.device(dev):
         d_off = _to_device(model_off, dev, pinned)
         d_rep = _to_device(model_rep, dev, pinned)

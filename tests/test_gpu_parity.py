@@ -134,9 +134,10 @@ def test_short_and_ragged_traces(loaded, n):
         assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("chunk,run_in", [(-1, 0), (1024, 2048), (4096, 1), (2048, 64),
-                                          (8192, 2048), (0, 0)])
-def test_results_do_not_depend_on_chunking(loaded, chunk, run_in):
+@pytest.mark.parametrize("chunk,run_in,rounds,cap", [
+    (-1, 0, 0, 0), (1024, 2048, 0, 0), (4096, 1, 0, 0), (2048, 64, 2, 1), (8192, 2048, 6, 2),
+    (8192, 16, 1, 1), (0, 0, 0, 0), (0, 0, 16, 3)])
+def test_results_do_not_depend_on_chunking(loaded, chunk, run_in, rounds, cap):
     """Speculative chunks are kept only when provably equivalent, so any cut of
     the trace — even a run-in of one request, which makes nearly every chunk
     wrong and re-simulated — gives the sequential results bit for bit."""
@@ -146,7 +147,7 @@ def test_results_do_not_depend_on_chunking(loaded, chunk, run_in):
     from oracle import tables
     case = cases.candidate_batch_case(num_candidates=40, duration=900.0, placement_seed=9)
     ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
-                            options=engine.sim_options(chunk, run_in))
+                            options=engine.sim_options(chunk, run_in, rounds, cap))
     enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
     res, _, _ = engine.run_batch(ev.trace, enc, ev.table, per_request=True, group_good=True,
                                  options=ev.options)

@@ -35,7 +35,7 @@ def _call(entry, trace, enc, table, opts, per_request):
              status=torch.zeros(B, **i32), redo=torch.zeros(B, **i32),
              fin=torch.zeros((B, N), dtype=torch.float64, device=dev),
              good=torch.zeros((B, N), dtype=torch.uint8, device=dev))
-    flags = nat.FLAG_PER_REQUEST if per_request else 0
+    flags = nat.FLAG_PER_REQUEST if per_request else 0      # group_num_good is wanted
     out = nat.Results(_ptr(o["mreq"]), _ptr(o["mgood"]), _ptr(o["greq"]), _ptr(o["ggood"]),
                       _ptr(o["total"]), _ptr(o["lsum"]), _ptr(o["status"]),
                       _ptr(o["fin"]) if per_request else None,

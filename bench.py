@@ -27,6 +27,9 @@ UNIT = "candidate*request/s"
 BYTES_PER_UNIT = 16          # f64 arrival + i32 model id + f32 slo, read once per candidate
 NUM_CANDIDATES = 4096
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one sim_stream_kernel launch (the dominant
+# kernel) on the default workload, from profiles/launch_list_candidates4096_3600s.md
+STREAM_KERNEL_DRAM_BYTES = 14732288 + 596909312
 
 
 def parse_args():
@@ -307,8 +310,12 @@ def run_b200(args):
                        "parallelism": f"candidates sharded over {world} GPU(s)",
                        "l2": "256 MiB buffer written between timed steps"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": which,
-                         "bytes_per_unit": BYTES_PER_UNIT},
+                         "frac": achieved / peak,
+                         "traffic": (STREAM_KERNEL_DRAM_BYTES
+                                     if (B, args.duration) == (NUM_CANDIDATES, 3600.0) else None),
+                         "traffic_unit": "bytes per sim_stream_kernel launch (ncu, DRAM read+write)",
+                         "peak_source": which, "bytes_per_unit": BYTES_PER_UNIT,
+                         "algorithmic_bytes_per_launch": B * N * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": 3 * args.steps,
@@ -318,7 +325,7 @@ def run_b200(args):
             "best_score": float(np.max(scores)),
         }
         if not args.no_cpu_baseline:
-            count = min(B, 512)
+            count = min(B, 3072)       # about 10 s of one host core
             rate, dt = cpu_port_rate(case, count, 1)
             line["cpu_baseline"] = {
                 "value": rate, "unit": UNIT, "cores": 1, "kind": "port",

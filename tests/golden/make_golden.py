@@ -165,6 +165,23 @@ def main():
         arrivals_sha256=digest(rw.arrivals), finish=fins, good=goods,
         model_num_requests=mreq, model_num_good=mgood, group_num_requests=greq,
         group_num_good=ggood)
+    # ---- whole searches: the placements the reference's policies arrive at ----------
+    import json
+    from mms_b200 import search_cases
+    import alpa_serve.placement_policy as RP
+    out = {}
+    for name, (datas, env, policies) in search_cases.all_cases().items():
+        case = cases.Case(name, datas, env, cases.merged_gamma_trace(datas[:1], 1.0, 0), [])
+        rdatas, renv, _, _ = reference.to_reference_case(case)
+        for pol_name, (cls_name, kwargs) in policies.items():
+            policy = getattr(RP, cls_name)(**kwargs)
+            placement, _ = policy.solve_placement(rdatas, renv)
+            out[f"{name}/{pol_name}"] = {
+                "group_configs": [list(map(int, c)) for c in placement.group_configs],
+                "group_models": [[int(m) for m in ms] for ms in placement.group_models]}
+            print(name, pol_name, out[f"{name}/{pol_name}"]["group_models"])
+    with open(os.path.join(HERE, "policies.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
     print("golden fixtures written to", HERE)
 
 

@@ -41,6 +41,8 @@ def parse_args():
     ap.add_argument("--candidates", type=int, default=NUM_CANDIDATES)
     ap.add_argument("--duration", type=float, default=3600.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--greedy-steps", type=int, default=3,
+                    help="also time this many steps of the full greedy placement search (0 = skip)")
     ap.add_argument("--chunk", type=int, default=0, help="requests per chunk (0 auto, <0 one)")
     ap.add_argument("--run-in", type=int, default=0, help="run-in requests per chunk (0 auto)")
     ap.add_argument("--rounds", type=int, default=0, help="validate+repair rounds (0 auto)")
@@ -295,6 +297,7 @@ def run_b200(args):
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = units_per_step / float(e2e_t.item())
 
+    greedy = greedy_step_timing(args, dev) if (rank == 0 and args.greedy_steps > 0) else None
     if rank == 0:
         peak, which = hbm_peak()
         kern_s = (np.mean(times) * 1e-3)
@@ -324,6 +327,8 @@ def run_b200(args):
             "clocks": clk.summary(),
             "best_score": float(np.max(scores)),
         }
+        if greedy:
+            line["greedy_step"] = greedy
         if not args.no_cpu_baseline:
             count = min(B, 3072)       # about 10 s of one host core
             rate, dt = cpu_port_rate(case, count, 1)
@@ -333,6 +338,41 @@ def run_b200(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def greedy_step_timing(args, dev):
+    """Wall time per step of the full greedy placement search (64 devices, 56
+    models): every step expands all (partition, group, model) additions of the
+    four pipeline partitions and scores them in one launch."""
+    import torch
+    from mms_b200 import cases, search
+    from mms_b200.placement import PlacementEvaluator
+    case = cases.greedy_search_case()
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload, device=dev)
+    starts = search.ModelParallelismSearch(max_op=1).enumerate_group_configs_uneven(
+        case.cluster_env)
+    layers = []
+
+    class Enough(Exception):
+        pass
+
+    def on_layer(n, seconds):
+        torch.cuda.synchronize()
+        layers.append((n, seconds))
+        if len(layers) >= args.greedy_steps + 1:
+            raise Enough()
+    try:
+        search.beam_search_lockstep(starts, case.model_datas, case.cluster_env, ev, 1,
+                                    on_layer=on_layer)
+    except Enough:
+        pass
+    timed = layers[1:] or layers            # the first step also warms up
+    n = float(np.mean([x[0] for x in timed]))
+    sec = float(np.mean([x[1] for x in timed]))
+    return {"ms_per_step": sec * 1e3, "candidates_per_step": n,
+            "num_requests": len(case.workload), "partitions": len(starts),
+            "value": n * len(case.workload) / sec, "unit": UNIT,
+            "includes": "host expansion and dedup, encoding, H2D, kernels, D2H, top-1 per partition"}
 
 
 def main():

@@ -121,3 +121,19 @@ def candidate_batch_case(num_candidates=4096, duration=3600.0, base_seed=0, plac
                                    placement_seed)
     name = "candidates-batching" if batching else "candidates"
     return Case(name, datas, env, merged_gamma_trace(datas, duration, base_seed), placements, bs)
+
+
+# eight latency tables over the three size classes: (single-device seconds, GB)
+SEARCH_CLASSES = ((0.04, 2.6), (0.05, 2.6), (0.06, 2.6), (0.12, 5.2), (0.15, 5.2), (0.18, 5.2),
+                  (0.35, 13.4), (0.40, 13.4))
+
+
+def greedy_search_case(slo_scale=5.0, num_models=56, num_devices=64, total_rate=80.0, cv=4.0,
+                       duration=1800.0, base_seed=1) -> Case:
+    """The full placement search problem: 64 devices, 56 models over eight
+    latency tables, Zipf(0.9) shares of 80 req/s, CV 4, 30 minutes, seed 1.
+    Profiles exist for pipeline degrees 1, 2, 4, 8 (operator parallelism 1),
+    so the search's partitions are 64x1, 32x2, 16x4 and 8x8 devices."""
+    datas = mixed_models(num_models, total_rate, cv, slo_scale, classes=SEARCH_CLASSES)
+    env = ClusterEnv(num_devices, 13 * GB)
+    return Case("greedy-search", datas, env, merged_gamma_trace(datas, duration, base_seed), [])

@@ -173,17 +173,28 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
     int32_t done = 0;
     pipe_prime(ln, p, begin);
     for (;;) {
+        // Within a leaf the latency of request k goes to partial sum k mod 8
+        // (leaves start at multiples of 8).  The latencies of eight requests
+        // are parked in the eight spare clock slots behind the lane's clock
+        // vector (read only as don't-care stages otherwise) and added to the
+        // partial sums together.
         const int32_t body_end = record ? i + ((span_end - i) & ~7) : i;
+        const uint32_t ring = ln.clk + (uint32_t)a.T * kLanes;
         double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
         double r = 0.0;
         for (; i < span_end; ++i) {
             const double d = sim_step<kFull, kGroupGood, kLegacy>(ln, p, i, record, fin_out,
                                                                   good_out);
             if (i < body_end) {
-                const double s = p0 + d;
-                p0 = p1; p1 = p2; p2 = p3; p3 = p4; p4 = p5; p5 = p6; p6 = p7; p7 = s;
-                if (i + 1 == body_end)
-                    r = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7));
+                SM_F64(ring + (uint32_t)(i & 7) * kLanes) = d;
+                if ((i & 7) == 7) {
+                    p0 += SM_F64(ring); p1 += SM_F64(ring + kLanes);
+                    p2 += SM_F64(ring + 2 * kLanes); p3 += SM_F64(ring + 3 * kLanes);
+                    p4 += SM_F64(ring + 4 * kLanes); p5 += SM_F64(ring + 5 * kLanes);
+                    p6 += SM_F64(ring + 6 * kLanes); p7 += SM_F64(ring + 7 * kLanes);
+                    if (i + 1 == body_end)
+                        r = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7));
+                }
             } else {
                 r += d;
             }

@@ -129,6 +129,10 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 //   record  update counters and per-request outputs (off during run-in)
 // The step is large; callers keep a single call site per kernel so that the
 // hot loop stays inside the instruction cache.
+// max of two times.  Times are never NaN (arrivals are checked to be finite,
+// latencies are finite or +inf), so one compare and a select do.
+__device__ __forceinline__ double tmax(double a, double b) { return a > b ? a : b; }
+
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)
@@ -173,6 +177,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
             const uint32_t row = ((uint32_t)m * ln.C + rep_column(pick)) * ln.S;
             double f;
             double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
+            (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
             // all stage clocks and latencies are fetched at once; the max/add
             // chain then runs in registers
             const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
@@ -184,11 +189,9 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
                 // rows are padded so that 8 entries are always readable
                 const uint32_t lr = ln.lat_sm + row;
                 l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
-                if (ns > 2) {
-                    l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
-                    l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
-                    l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
-                }
+                l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
+                l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
+                l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
             } else {
                 const float *lat = ln.lat_gl + row;
                 const int sm = ln.S - 1;   // clamp reads to the table row
@@ -204,58 +207,50 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
             }
             if (kLegacy) {
                 // :543-544 one clock per group; latency row = {sum, max}
-                const double start = fmax(k0, ts);
+                const double start = tmax(k0, ts);
                 f = start + l0 + kOverhead;
                 t0 = start + l1;
             } else {
-                // :605-610
-                double t = fmax(ts, k0) + l0;
-                t0 = t;
-                if (ns > 1) {
-                    t = fmax(t, k1) + l1; t1 = t;
-                    if (ns > 2) {
-                        t = fmax(t, k2) + l2; t2 = t;
-                        t = ns > 3 ? fmax(t, k3) + l3 : t; t3 = t;
-                        if (ns > 4) {
-                            t = fmax(t, k4) + l4; t4 = t;
-                            t = ns > 5 ? fmax(t, k5) + l5 : t; t5 = t;
-                            t = ns > 6 ? fmax(t, k6) + l6 : t; t6 = t;
-                            t = ns > 7 ? fmax(t, k7) + l7 : t; t7 = t;
-                            for (uint32_t k = 8; k < ns; ++k) {
-                                const double lk = ln.lat_on_chip
-                                    ? (double)SM_F32(ln.lat_sm + row + k)
-                                    : (double)__ldg(ln.lat_gl + row + k);
-                                t = fmax(t, SM_F64(ck + k * kLanes)) + lk;
-                                SM_F64(ln.tmp + (k - 8) * kLanes) = t;
-                            }
-                        }
+                // :605-610, written without branches: stages past the group's
+                // last one are computed and thrown away
+                t0 = tmax(ts, k0) + l0;
+                t1 = tmax(t0, k1) + l1;
+                double t = ns > 1 ? t1 : t0;
+                t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
+                t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
+                t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
+                t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
+                t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
+                t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
+                if (ns > 8) {
+                    for (uint32_t k = 8; k < ns; ++k) {
+                        const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
+                                                         : (double)__ldg(ln.lat_gl + row + k);
+                        t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
+                        SM_F64(ln.tmp + (k - 8) * kLanes) = t;
                     }
                 }
                 f = t + kOverhead;                               // :610
             }
-            if (record) atomicAdd(&SM_U32(ln.group_req + g * kLanes), 1u);   // :611
-            if (f - ts <= (double)slo_f) {                       // :613-619
+            if (record) SM_U32(ln.group_req + g * kLanes) += 1u;   // :611
+            const bool accept = f - ts <= (double)slo_f;         // :613-619
+            if (accept) {
                 fin = f;
                 ok = true;
                 SM_F64(ck) = t0;
-                if (ns > 1) {
-                    SM_F64(ck + kLanes) = t1;
-                    if (ns > 2) {
-                        SM_F64(ck + 2 * kLanes) = t2;
-                        if (ns > 3) SM_F64(ck + 3 * kLanes) = t3;
-                        if (ns > 4) {
-                            SM_F64(ck + 4 * kLanes) = t4;
-                            if (ns > 5) SM_F64(ck + 5 * kLanes) = t5;
-                            if (ns > 6) SM_F64(ck + 6 * kLanes) = t6;
-                            if (ns > 7) SM_F64(ck + 7 * kLanes) = t7;
-                            for (uint32_t k = 8; k < ns; ++k)
-                                SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
-                        }
-                    }
-                }
+                if (ns > 1) SM_F64(ck + kLanes) = t1;
+                if (ns > 2) SM_F64(ck + 2 * kLanes) = t2;
+                if (ns > 3) SM_F64(ck + 3 * kLanes) = t3;
+                if (ns > 4) SM_F64(ck + 4 * kLanes) = t4;
+                if (ns > 5) SM_F64(ck + 5 * kLanes) = t5;
+                if (ns > 6) SM_F64(ck + 6 * kLanes) = t6;
+                if (ns > 7) SM_F64(ck + 7 * kLanes) = t7;
+                if (ns > 8)
+                    for (uint32_t k = 8; k < ns; ++k)
+                        SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
                 if (record) {
-                    atomicAdd(&SM_U32(ln.model_good + (uint32_t)m * kLanes), 1u);
-                    if (kGroupGood) atomicAdd(&SM_U32(ln.group_good + g * kLanes), 1u);
+                    SM_U32(ln.model_good + (uint32_t)m * kLanes) += 1u;
+                    if (kGroupGood) SM_U32(ln.group_good + g * kLanes) += 1u;
                 }
             }
         }

@@ -42,7 +42,7 @@ struct Geometry {
     int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
-        off_repair_from;
+        off_repair_from, off_rows;
     size_t total;
 };
 
@@ -90,12 +90,12 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     } else if (chunk > 0) {
         spc = (chunk + seg / 2) / seg;
     } else {
-        // Chunks are the units of parallel work: as many as fill a little over three
+        // Chunks are the units of parallel work: as many as fill just under two
         // waves of the resident blocks (slots = SMs x blocks per SM at this
         // kernel's shared-memory use), but never chunks shorter than 4
         // segments.  More chunks mean more boundaries to validate and repair.
         int64_t Kmax = NS / 4 > 0 ? NS / 4 : 1;
-        int64_t K = B > 0 ? (13 * resident_slots * kLanes) / (4 * B) : 1;
+        int64_t K = B > 0 ? (19 * resident_slots * kLanes) / (10 * B) : 1;
         if (K > Kmax) K = Kmax;
         if (K < 1) K = 1;
         spc = (NS + K - 1) / K;
@@ -128,6 +128,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
 
     size_t off = 0;
+    g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)B * c->num_models + 256);
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
     g->off_counters = off;    off += align256(sizeof(uint32_t) * (size_t)NS * L.n_counters * B);
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
@@ -142,6 +143,11 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
 template <bool kFull, bool kGroupGood, bool kLegacy>
 static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 {
+    const int64_t cells = (int64_t)ka.B * ka.M;
+    if (cells > 0) {
+        build_rows_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka);
+        MMS_CUDA(cudaGetLastError());
+    }
     auto stream_k = sim_stream_kernel<kFull, kGroupGood, kLegacy>;
     MMS_CUDA(cudaFuncSetAttribute(stream_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)g.smem_stream));
@@ -265,6 +271,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.K = g.K; ka.NS = g.NS; ka.seg_len = g.seg_len; ka.seg_per_chunk = g.seg_per_chunk;
     ka.warmup = g.warmup;
     ka.num_leaves = plan->num_leaves; ka.leaf_start = plan->leaf_start;
+    ka.rep_rows = (uint32_t *)(scratch + g.off_rows);
     ka.leaf_sums = (double *)(scratch + g.off_leaf);
     ka.seg_counters = (uint32_t *)(scratch + g.off_counters);
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);

@@ -51,8 +51,42 @@ constexpr int kMaxRepairRounds = 16;
 constexpr int kDefaultRepairRounds = 3;
 constexpr int kDefaultRepairSegments = -1;   // no cap: measured best on the benchmark shape
 
-// Copies candidate b's tables into this lane's shared memory, checking every
-// index they hold, zeroes its clocks and counters, and returns the lane's view.
+// One thread per (candidate, model): checks the model's replica list and
+// writes its 32-byte row (see Lane::rows).  A list with a bad index is
+// reported in the status word and emptied.
+__global__ void build_rows_kernel(const KernelArgs a)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (int64_t)a.B * a.M) return;
+    const int64_t b = t / a.M;
+    const int m = (int)(t % a.M);
+    uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
+    uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
+    bool bad = lo > hi || hi > (uint32_t)a.P;
+    uint32_t e[4] = {1u << 16, 1u << 16, 1u << 16, 1u << 16};   // group 0, slot 0, one stage
+    if (!bad) {
+        for (uint32_t r = lo; r < hi; ++r) {
+            const uint32_t ent = a.model_rep[(size_t)b * a.P + r];
+            const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
+            if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
+                ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
+                bad = true;
+            else if (r - lo < 4)
+                e[r - lo] = rep_to_last(ent);
+        }
+    }
+    if (bad) {
+        atomicOr(&a.status[b], MMS_STATUS_BAD_INDEX);
+        lo = hi = 0;
+        for (int k = 0; k < 4; ++k) e[k] = 1u << 16;
+    }
+    uint4 *row = reinterpret_cast<uint4 *>(a.rep_rows) + (size_t)t * 2;
+    row[0] = make_uint4(e[0], e[1], e[2], e[3]);
+    row[1] = make_uint4(hi - lo, lo, 0u, 0u);
+}
+
+// This lane's view of candidate b: offsets of its shared-memory state (clocks
+// and counters zeroed) and pointers to its tables in global memory.
 template <bool kGroupGood>
 __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint32_t &counters,
                                   int &n_counters)
@@ -67,36 +101,12 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint
     ln.model_good = counters;
     ln.group_req = counters + (uint32_t)a.M * kLanes;
     ln.group_good = counters + (uint32_t)(a.M + a.G) * kLanes;
-    ln.moff = (uint32_t)(L.model_off / sizeof(uint16_t)) + lane;
-    ln.mrep = (uint32_t)(L.model_rep / sizeof(uint32_t)) + lane;
+    ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + (size_t)b * a.M * 2;
+    ln.rep_raw = a.model_rep + (size_t)b * a.P;
     ln.lat_gl = a.latency + (size_t)b * a.latency_stride;
     ln.lat_on_chip = a.lat_smem_elems != 0;
     ln.M = a.M; ln.C = a.C; ln.S = a.S;
     ln.status = 0;
-
-    uint32_t prev = 0;
-    for (int m = 0; m <= a.M; ++m) {
-        uint32_t o = a.model_off[(size_t)b * (a.M + 1) + m];
-        if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
-        SM_U16(ln.moff + m * kLanes) = (uint16_t)o;
-        prev = o;
-    }
-    SM_U16(ln.moff + (a.M + 1) * kLanes) = (uint16_t)prev;
-    for (uint32_t e = 0; e < (uint32_t)(a.P + kRepPad); ++e) {
-        // caller's entry: group | first slot << 8 | stages << 16 | column << 24
-        uint32_t ent = e < prev ? a.model_rep[(size_t)b * a.P + e] : (1u << 16);
-        const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
-        if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
-            ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C) {
-            if (e < prev) ln.status |= MMS_STATUS_BAD_INDEX;
-            ent = 1u << 16;   // group 0, slot 0, one stage: always addressable
-        }
-        const uint32_t ns_ok = (ent >> 16) & 0xFFu, first_ok = (ent >> 8) & 0xFFu;
-        // on chip the entry carries the group's LAST slot
-        SM_U32(ln.mrep + e * kLanes) = (ent & 0xFFFF00FFu) | ((first_ok + ns_ok - 1) << 8);
-    }
-    if (ln.status & MMS_STATUS_BAD_INDEX)   // tables cannot be trusted: no replicas at all
-        for (int m = 0; m <= a.M + 1; ++m) SM_U16(ln.moff + m * kLanes) = 0;
     for (int t = 0; t < a.T + kClockPad; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
     for (int c = 0; c < n_counters; ++c) SM_U32(counters + c * kLanes) = 0;
     return ln;

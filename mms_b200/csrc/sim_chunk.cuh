@@ -37,6 +37,7 @@ struct KernelArgs {
     int32_t num_leaves;
     const int32_t *leaf_start;
     // scratch
+    uint32_t *rep_rows;           // [B][M][8]: replica rows built from model_off/model_rep
     double *leaf_sums;            // [num_leaves][B]
     double *seg_end;              // [NS][T][B]   clock vector after each segment
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from

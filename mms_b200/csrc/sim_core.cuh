@@ -2,9 +2,11 @@
 //
 // One THREAD simulates one stream of requests for one candidate placement
 // (alpa_serve/simulator/controller.py:579-622 is the loop body restated in
-// sim_step below).  Mutable state (stage clocks, counters) and the
-// candidate's placement tables live in shared memory as [entry][lane], so
-// lane-private accesses fall on distinct banks.  Everything is addressed by
+// sim_step below).  Mutable state (stage clocks, counters) lives in shared
+// memory as [entry][lane], so lane-private accesses fall on distinct banks;
+// shared memory is what limits the number of resident warps, so the
+// read-only replica lists stay in global memory (one 32-byte row per model,
+// fetched a whole request ahead, served by L1/L2).  Everything is addressed by
 // 32-bit element offsets into the block's one dynamic shared array, which
 // keeps the accesses plain LDS/STS with immediate offsets.  The dependent
 // chain per request is kept short: trace values are fetched two requests
@@ -24,7 +26,7 @@ constexpr double kInf = 1e100;          // alpa_serve/util.py:23
 constexpr double kOverhead = 0.011;     // controller.py:575
 constexpr int kLanes = 32;              // streams per block (one warp)
 constexpr int kClockPad = 8;            // readable slots past the last clock
-constexpr int kRepPad = 4;              // readable entries past the last replica
+constexpr int kRowWords = 8;            // u32 words of a model's replica row
 
 extern __shared__ __align__(16) unsigned char smem[];
 
@@ -41,13 +43,13 @@ __device__ __forceinline__ uint32_t rep_stages(uint32_t e) { return (e >> 16) & 
 __device__ __forceinline__ uint32_t rep_column(uint32_t e) { return e >> 24; }
 
 struct SmemLayout {
-    size_t clocks, stage_tmp, latency, counters, model_rep, model_off, total;
+    size_t clocks, stage_tmp, latency, counters, total;
     int n_counters, tmp_stages;
 };
 
 // lat_elems: entries of the shared f32 latency table kept on chip (0 = read
 // it from global memory).
-__host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, int S,
+__host__ __device__ inline SmemLayout smem_layout(int M, int G, int /*P*/, int T, int S,
                                                   bool group_good, int lat_elems)
 {
     SmemLayout L;
@@ -58,8 +60,6 @@ __host__ __device__ inline SmemLayout smem_layout(int M, int G, int P, int T, in
     L.latency = off;    off += sizeof(float) * (size_t)((lat_elems + 3) & ~3);
     L.n_counters = M + G + (group_good ? G : 0);
     L.counters = off;   off += sizeof(uint32_t) * (size_t)L.n_counters * kLanes;
-    L.model_rep = off;  off += sizeof(uint32_t) * (size_t)(P + kRepPad) * kLanes;
-    L.model_off = off;  off += sizeof(uint16_t) * (size_t)(M + 2) * kLanes;
     L.total = (off + 15) & ~(size_t)15;
     return L;
 }
@@ -73,19 +73,25 @@ struct Lane {
     uint32_t model_good;      // u32 index, [M]
     uint32_t group_req;       // u32 index, [G]
     uint32_t group_good;      // u32 index, [G]
-    uint32_t moff;            // u16 index, [M + 2]
-    uint32_t mrep;            // u32 index, [P + kRepPad]
+    const uint4 *rows;        // [M][2] replica rows of this candidate (global memory):
+                              //   words 0-3 the first four replicas, word 4 their number,
+                              //   word 5 the model's offset into the caller's model_rep
+    const uint32_t *rep_raw;  // the caller's model_rep row of this candidate
     const float *lat_gl;      // this candidate's table in global memory
     bool lat_on_chip;
     int32_t M, C, S;
     uint32_t status;
 };
 
-// Requests in flight: the current one is ready to execute (its replica list
-// is in registers), the next has its trace values only.
+// Requests in flight.  Request i is ready to execute (its replica row is in
+// registers).  While it executes, the row of request i+1 is loaded (an L1
+// hit: it was prefetched into L1 one step earlier), the row of request i+2
+// is prefetched into L1 and the trace values of request i+3 are fetched.
+// Nothing fetched ahead depends on simulator state.
 struct Pipe {
     double ts; float slo; int32_t m; uint32_t lo, n, e0, e1, e2, e3;
     double ts1; float slo1; int32_t m1;
+    double ts2; float slo2; int32_t m2;
     const double *arrivals; const int32_t *model_ids; const float *slos;
     int32_t last;             // highest readable request index
 };
@@ -96,19 +102,17 @@ __device__ __forceinline__ int32_t clean_model(Lane &ln, int32_t m)
     return m;
 }
 
-__device__ __forceinline__ void pipe_tables(const Lane &ln, int32_t m, uint32_t &lo, uint32_t &n,
-                                            uint32_t &e0, uint32_t &e1, uint32_t &e2, uint32_t &e3)
+__device__ __forceinline__ void fetch_row(const Lane &ln, int32_t m, uint4 &x, uint4 &y)
 {
     const uint32_t mm = m < 0 ? 0u : (uint32_t)m;
-    const uint32_t o = ln.moff + mm * kLanes;
-    lo = SM_U16(o);
-    const uint32_t hi = SM_U16(o + kLanes);
-    n = m < 0 ? 0u : hi - lo;
-    const uint32_t r = ln.mrep + lo * kLanes;
-    e0 = SM_U32(r);
-    e1 = SM_U32(r + kLanes);
-    e2 = SM_U32(r + 2 * kLanes);
-    e3 = SM_U32(r + 3 * kLanes);
+    x = __ldg(ln.rows + 2 * mm);
+    y = __ldg(ln.rows + 2 * mm + 1);
+}
+
+__device__ __forceinline__ void prefetch_row(const Lane &ln, int32_t m)
+{
+    const uint32_t mm = m < 0 ? 0u : (uint32_t)m;
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(ln.rows + 2 * mm));
 }
 
 // Fills the pipe so that request `i` is ready to execute.
@@ -116,12 +120,31 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 {
     const int32_t i0 = i < p.last ? i : p.last;
     const int32_t i1 = i + 1 < p.last ? i + 1 : p.last;
+    const int32_t i2 = i + 2 < p.last ? i + 2 : p.last;
     p.ts = __ldg(p.arrivals + i0); p.slo = __ldg(p.slos + i0);
     p.m = clean_model(ln, __ldg(p.model_ids + i0));
     p.ts1 = __ldg(p.arrivals + i1); p.slo1 = __ldg(p.slos + i1);
     p.m1 = clean_model(ln, __ldg(p.model_ids + i1));
-    pipe_tables(ln, p.m, p.lo, p.n, p.e0, p.e1, p.e2, p.e3);
+    p.ts2 = __ldg(p.arrivals + i2); p.slo2 = __ldg(p.slos + i2);
+    p.m2 = clean_model(ln, __ldg(p.model_ids + i2));
+    uint4 x, y;
+    fetch_row(ln, p.m, x, y);
+    p.e0 = x.x; p.e1 = x.y; p.e2 = x.z; p.e3 = x.w;
+    p.n = p.m < 0 ? 0u : y.x; p.lo = y.y;
+    prefetch_row(ln, p.m1);
 }
+
+// max of two times.  Times are never NaN (arrivals are checked to be finite,
+// latencies are finite or +inf), so one compare and a select do.
+__device__ __forceinline__ double tmax(double a, double b) { return a > b ? a : b; }
+
+// Replica entry as the caller gives it (first clock slot) -> with the LAST slot.
+__device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
+{
+    const uint32_t ns = (e >> 16) & 0xFFu, first = (e >> 8) & 0xFFu;
+    return (e & 0xFFFF00FFu) | (((first + ns - 1) & 0xFFu) << 8);
+}
+
 
 // Executes request `i` (controller.py:579-622, or :519-555 with kLegacy) and
 // advances the pipe.  Returns finish - arrival, which is 0.0 for a dropped
@@ -129,9 +152,6 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 //   record  update counters and per-request outputs (off during run-in)
 // The step is large; callers keep a single call site per kernel so that the
 // hot loop stays inside the instruction cache.
-// max of two times.  Times are never NaN (arrivals are checked to be finite,
-// latencies are finite or +inf), so one compare and a select do.
-__device__ __forceinline__ double tmax(double a, double b) { return a > b ? a : b; }
 
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
@@ -143,12 +163,13 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     const uint32_t n = p.n, lo = p.lo, e0 = p.e0, e1 = p.e1, e2 = p.e2, e3 = p.e3;
 
     // ---- state-independent fetches for the requests behind this one -------
-    uint32_t lo1, n1, f0, f1, f2, f3;
-    pipe_tables(ln, p.m1, lo1, n1, f0, f1, f2, f3);
-    const int32_t i2 = i + 2 < p.last ? i + 2 : p.last;
-    const double ts2 = __ldg(p.arrivals + i2);
-    const float slo2 = __ldg(p.slos + i2);
-    const int32_t m2raw = __ldg(p.model_ids + i2);
+    uint4 x1, y1;
+    fetch_row(ln, p.m1, x1, y1);
+    prefetch_row(ln, p.m2);
+    const int32_t i3 = i + 3 < p.last ? i + 3 : p.last;
+    const double ts3 = __ldg(p.arrivals + i3);
+    const float slo3 = __ldg(p.slos + i3);
+    const int32_t m3raw = __ldg(p.model_ids + i3);
 
     // ---- :589-598 replica whose last-stage clock is strictly smallest ------
     double fin = ts;
@@ -166,7 +187,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
         if (n > 2 && c2 < best) { best = c2; pick = e2; found = true; }
         if (n > 3 && c3 < best) { best = c3; pick = e3; found = true; }
         for (uint32_t r = 4; r < n; ++r) {
-            const uint32_t e = SM_U32(ln.mrep + (lo + r) * kLanes);
+            const uint32_t e = rep_to_last(__ldg(ln.rep_raw + lo + r));
             const double c = SM_F64(ln.clk + rep_last(e) * kLanes);
             if (c < best) { best = c; pick = e; found = true; }
         }
@@ -262,8 +283,10 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
 
     // ---- advance the pipe ---------------------------------------------------
     p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1;
-    p.lo = lo1; p.n = n1; p.e0 = f0; p.e1 = f1; p.e2 = f2; p.e3 = f3;
-    p.ts1 = ts2; p.slo1 = slo2; p.m1 = clean_model(ln, m2raw);
+    p.e0 = x1.x; p.e1 = x1.y; p.e2 = x1.z; p.e3 = x1.w;
+    p.n = p.m1 < 0 ? 0u : y1.x; p.lo = y1.y;
+    p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2;
+    p.ts2 = ts3; p.slo2 = slo3; p.m2 = clean_model(ln, m3raw);
     return fin - ts;
 }
 

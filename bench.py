@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--rounds", type=int, default=0, help="validate+repair rounds (0 auto)")
     ap.add_argument("--repair-segments", type=int, default=0,
                     help="segments a repair runs per round (0 auto, <0 no cap)")
+    ap.add_argument("--no-mirrors", action="store_true",
+                    help="no mirror candidates for placements with interchangeable groups")
     return ap.parse_args()
 
 
@@ -214,13 +216,19 @@ def run_b200(args):
 
     # ---- device-resident arm: tables already in HBM, time the C-ABI call ----
     enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
-    d_off = torch.from_numpy(enc.model_off).to(dev)
-    d_rep = torch.from_numpy(enc.model_rep).to(dev)
-    d_info = torch.from_numpy(enc.group_info).to(dev)
+    ext = None if args.no_mirrors else enc.with_mirrors()
+    h_off, h_rep, h_info = ext[:3] if ext else (enc.model_off, enc.model_rep, enc.group_info)
+    d_off = torch.from_numpy(h_off).to(dev)
+    d_rep = torch.from_numpy(h_rep).to(dev)
+    d_info = torch.from_numpy(h_info).to(dev)
+    d_partner = torch.from_numpy(ext[3]).to(dev) if ext else None
+    d_swap = torch.from_numpy(ext[4]).to(dev) if ext else None
     d_lat = ev.table.device(dev)
     P = engine._ptr
-    cands = nat.Placements(enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, 0, P(d_off), P(d_rep),
-                           P(d_info), P(d_lat), 0)
+    # B placements are scored; the ones with interchangeable groups bring a mirror each
+    Bt = len(h_off)
+    cands = nat.Placements(Bt, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, B if ext else 0,
+                           P(d_off), P(d_rep), P(d_info), P(d_lat), 0, P(d_partner), P(d_swap))
     opts = engine.sim_options(args.chunk, args.run_in, args.rounds, args.repair_segments)
     need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts),
                                      nat.FLAG_NO_GROUP_GOOD)
@@ -321,7 +329,9 @@ def run_b200(args):
                          "algorithmic_bytes_per_launch": B * N * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": 3 * args.steps,
+            # rows, stream, (validate, resolve, repair) per round, chain, counters, finalize
+            "gpu_launches": (5 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps,
+            "mirror_candidates_per_gpu": Bt - B,
             "chunks_resimulated_per_candidate": float(redo.float().mean().item()),
             "chunks_resimulated_hist": np.bincount(redo.cpu().numpy()).tolist(),
             "clocks": clk.summary(),

@@ -81,6 +81,25 @@ typedef struct {
  *                          dense per-group table of the reference: C == G).
  *  With MMS_FLAG_LEGACY_CLOCK: S == 2 and latency[m][c] = {sum, max} of
  *  controller.py:440-441, every group has 1 stage.
+ *
+ * Mirrors (optional, a speed-up only; nothing in the reference corresponds).
+ * Groups with the same parallel config and the same models are
+ * interchangeable, and a chunk simulated speculatively (see mms_sim_options)
+ * often comes out with their roles permuted, which the exact chain pass
+ * then has to re-simulate.  The caller may append, behind the num_scored
+ * candidates it wants results for, MIRROR candidates: a copy of a scored
+ * candidate's tables whose speculative chunks start with the clock vectors
+ * of some groups exchanged.  The chain pass takes each chunk from the
+ * candidate's own run or from one of its mirrors', whichever started from a
+ * state equivalent to the true one, so results stay exact.
+ *   num_scored   candidates [0, num_scored) get outputs (every output array
+ *                has num_scored rows); 0 means all
+ *   partner      i32[B] or NULL: for a scored candidate its first mirror (or
+ *                -1), for a mirror the candidate it mirrors; the mirrors of
+ *                one candidate are consecutive
+ *   mirror_swap  u32[B][2] or NULL: for a mirror, up to four exchanges of two
+ *                groups, applied in order; each is two bytes (group ids a, b),
+ *                0xFF = unused
  */
 typedef struct {
     int32_t num_candidates;        /* B */
@@ -90,12 +109,14 @@ typedef struct {
     int32_t max_slots;             /* T: clock slots per candidate (<= 256)      */
     int32_t max_stages;            /* S: last axis of latency                    */
     int32_t num_columns;           /* C (<= 255)                                 */
-    int32_t reserved;
+    int32_t num_scored;            /* 0 = num_candidates (no mirrors)            */
     const uint16_t *model_off;
     const uint32_t *model_rep;
     const uint32_t *group_info;
     const float *latency;
     int64_t latency_stride;        /* elements; 0 = one table for all candidates */
+    const int32_t *partner;        /* see "Mirrors" above; may be NULL           */
+    const uint32_t *mirror_swap;   /* may be NULL                                */
 } mms_placements;
 
 /* How the trace is cut for time-parallel execution.  A candidate's requests

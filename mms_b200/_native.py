@@ -52,9 +52,9 @@ class Placements(ctypes.Structure):
     _fields_ = [("num_candidates", ctypes.c_int32), ("num_models", ctypes.c_int32),
                 ("max_groups", ctypes.c_int32), ("max_placed", ctypes.c_int32),
                 ("max_slots", ctypes.c_int32), ("max_stages", ctypes.c_int32),
-                ("num_columns", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("num_columns", ctypes.c_int32), ("num_scored", ctypes.c_int32),
                 ("model_off", _vp), ("model_rep", _vp), ("group_info", _vp), ("latency", _vp),
-                ("latency_stride", ctypes.c_int64)]
+                ("latency_stride", ctypes.c_int64), ("partner", _vp), ("mirror_swap", _vp)]
 
 
 class SimOptions(ctypes.Structure):

@@ -42,7 +42,7 @@ struct Geometry {
     int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
-        off_repair_from, off_rows;
+        off_repair_from, off_rows, off_chunk_src;
     size_t total;
 };
 
@@ -61,6 +61,11 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         c->num_columns > MMS_MAX_COLUMNS)
         return MMS_ERR_UNSUPPORTED;
     if ((flags & MMS_FLAG_LEGACY_CLOCK) && c->max_stages != 2) return MMS_ERR_ARG;
+    if (c->num_scored < 0 || c->num_scored > c->num_candidates) return MMS_ERR_ARG;
+    const bool mirrors = c->num_scored != 0 && c->num_scored != c->num_candidates;
+    // per-request outputs come from one run per candidate; mirrors need the partner list
+    if (mirrors && ((flags & MMS_FLAG_PER_REQUEST) || !c->partner || !c->mirror_swap))
+        return MMS_ERR_ARG;
 
     const int64_t B = c->num_candidates;
     // blocks that fit an SM at once, from the kernel's shared-memory use
@@ -134,6 +139,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
     g->off_repair_from = off; off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
+    g->off_chunk_src = off;   off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
     g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
     g->total = off;
@@ -161,16 +167,16 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
                                       (int)g.smem_repair));
         MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)g.smem_repair));
-        const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
+        const int64_t bounds = (int64_t)ka.Bs * (ka.K - 1);
         for (int r = 0; r < g.rounds; ++r) {
             ka.round = r;
-            validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(ka);
+            resolve_kernel<<<(unsigned)((ka.Bs + 31) / 32), 32, 0, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
             // sized for the worst case; blocks past the work list return at once
             repair_k<<<(unsigned)((bounds + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
         }
-        chain_k<<<(unsigned)((ka.B + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
+        chain_k<<<(unsigned)((ka.Bs + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
         MMS_CUDA(cudaGetLastError());
     }
     return MMS_OK;
@@ -180,7 +186,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 
 extern "C" {
 
-int mms_abi_version(void) { return 3; }
+int mms_abi_version(void) { return 4; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 
@@ -262,7 +268,9 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     memset(&ka, 0, sizeof(ka));
     ka.arrivals = trace->arrivals; ka.model_ids = trace->model_ids; ka.slos = trace->slos;
     ka.N = N; ka.model_hist = model_hist;
-    ka.B = B; ka.M = cands->num_models; ka.G = cands->max_groups; ka.P = cands->max_placed;
+    ka.B = B; ka.Bs = cands->num_scored ? cands->num_scored : B;
+    ka.partner = cands->partner; ka.mirror_swap = cands->mirror_swap;
+    ka.M = cands->num_models; ka.G = cands->max_groups; ka.P = cands->max_placed;
     ka.T = cands->max_slots; ka.S = cands->max_stages; ka.C = cands->num_columns;
     ka.model_off = cands->model_off; ka.model_rep = cands->model_rep;
     ka.group_info = cands->group_info; ka.latency = cands->latency;
@@ -277,6 +285,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);
     ka.work_items = (uint32_t *)(scratch + g.off_work_items);
     ka.repair_from = (int32_t *)(scratch + g.off_repair_from);
+    ka.chunk_src = (int32_t *)(scratch + g.off_chunk_src);
     ka.repair_cap = g.repair_cap;
     ka.seg_end = (double *)(scratch + g.off_seg_end);
     ka.chunk_start = (double *)(scratch + g.off_chunk_start);
@@ -284,11 +293,12 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.finish = out->finish; ka.good = out->good;
     ka.resimulated = out->resimulated;
 
-    MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)B, st));
+    MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)ka.Bs, st));
     MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kMaxRepairRounds + 1), st));
     MMS_CUDA(cudaMemsetAsync(ka.repair_from, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
+    MMS_CUDA(cudaMemsetAsync(ka.chunk_src, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
     if (out->resimulated)
-        MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)B, st));
+        MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)ka.Bs, st));
     const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;
     const int variant = (full ? 4 : 0) | (gg ? 2 : 0) | (legacy ? 1 : 0);
     switch (variant) {
@@ -304,15 +314,13 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     if (rc) return rc;
 
     const int threads = 128;
-    const int64_t cells = (int64_t)B * g.n_counters;
+    const int64_t cells = (int64_t)ka.Bs * g.n_counters;
     sum_counters_kernel<<<(unsigned)((cells + threads - 1) / threads), threads, 0, st>>>(
-        B, ka.M, ka.G, ka.NS, g.n_counters, plan->num_leaves, ka.seg_counters, model_hist,
-        out->model_num_requests, out->model_num_good, out->group_num_requests,
+        ka, g.n_counters, out->model_num_requests, out->model_num_good, out->group_num_requests,
         out->group_num_good);
     MMS_CUDA(cudaGetLastError());
-    finalize_kernel<<<(B + 31) / 32, 32, 0, st>>>(
-        B, ka.M, plan->num_leaves, plan->leaf_merges, ka.leaf_sums, out->model_num_good,
-        out->good_total, out->latency_sum, out->status);
+    finalize_kernel<<<(ka.Bs + 31) / 32, 32, 0, st>>>(
+        ka, plan->leaf_merges, out->model_num_good, out->good_total, out->latency_sum);
     MMS_CUDA(cudaGetLastError());
     return MMS_OK;
 }
@@ -462,9 +470,12 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
             out->finish, trace->arrivals, N, B, plan->num_leaves, plan->leaf_start, leaf_sums);
         MMS_CUDA(cudaGetLastError());
     }
+    KernelArgs fa;                         // what finalize_kernel reads; one run per candidate
+    memset(&fa, 0, sizeof(fa));
+    fa.B = fa.Bs = B; fa.M = a.M; fa.num_leaves = plan->num_leaves;
+    fa.leaf_sums = leaf_sums; fa.status = out->status;
     finalize_kernel<<<(B + 31) / 32, 32, 0, st>>>(
-        B, a.M, plan->num_leaves, plan->leaf_merges, leaf_sums, out->model_num_good,
-        out->good_total, out->latency_sum, out->status);
+        fa, plan->leaf_merges, out->model_num_good, out->good_total, out->latency_sum);
     MMS_CUDA(cudaGetLastError());
     return MMS_OK;
 }

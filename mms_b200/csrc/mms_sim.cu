@@ -76,7 +76,7 @@ __global__ void build_rows_kernel(const KernelArgs a)
         }
     }
     if (bad) {
-        atomicOr(&a.status[b], MMS_STATUS_BAD_INDEX);
+        atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
         lo = hi = 0;
         for (int k = 0; k < 4; ++k) e[k] = 1u << 16;
     }
@@ -153,6 +153,12 @@ sim_stream_kernel(const KernelArgs a)
     const int32_t j = (int32_t)(stream / a.B);
     const int64_t b = stream % a.B;
     if (a.N == 0 || (!chunked && j > 0)) return;
+    // a mirror only runs the speculative chunks
+    const bool mirror = b >= a.Bs;
+    if (mirror && (j == 0 || !chunked)) return;
+    const uint64_t swap = (mirror && a.mirror_swap)
+                              ? ((uint64_t)a.mirror_swap[2 * b + 1] << 32) | a.mirror_swap[2 * b]
+                              : ~0ull;
 
     uint32_t counters; int n_counters;
     Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
@@ -168,38 +174,60 @@ sim_stream_kernel(const KernelArgs a)
         begin = first - a.warmup > 0 ? first - a.warmup : 0;
     }
     run_chunk<kFull, kGroupGood, kLegacy>(ka, ln, p, counters, n_counters, b, j, begin, false,
-                                          chunked, 0, 0);
-    if (ln.status) atomicOr(&a.status[b], ln.status);
+                                          chunked, 0, 0, -1, 0, swap);
+    if (ln.status) atomicOr(&a.status[status_row(a, b)], ln.status);
 }
 
-// One thread per chunk boundary (candidate b, chunk j >= 1).
-__global__ void validate_kernel(const KernelArgs a)
+// One thread per scored candidate: follows the chain of chunks.  Chunk j is
+// taken from the first run of it (the candidate's own, then its mirrors')
+// whose start state continues the state the chosen run of chunk j-1 ended in
+// (states_equivalent: equal futures, provably).  Where none does, the true
+// state is copied into the candidate's own chunk and the chunk goes on the
+// work list.  Behind a listed chunk the walk goes on with the old data; the
+// next round (or the chain kernel) sees the repaired one.
+__global__ void resolve_kernel(const KernelArgs a)
 {
-    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (!can_chunk(a) || t >= (int64_t)a.B * (a.K - 1)) return;
-    const int32_t j = (int32_t)(t / a.B) + 1;
-    const int64_t b = t % a.B;
-    const int32_t q_prev = j * a.seg_per_chunk - 1;
-    const int64_t first = a.leaf_start[seg_leaf(a, q_prev + 1)];
-    const double tau = a.arrivals[first];
+    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (!can_chunk(a) || b >= a.Bs) return;
+    int64_t m_end;
+    const int64_t m_first = mirrors_of(a, b, m_end);
     const size_t B = (size_t)a.B;
-    const double *X = a.seg_end + (size_t)q_prev * a.T * B + b;
-    double *Y = a.chunk_start + (size_t)j * a.T * B + b;
     uint8_t stale[MMS_MAX_GROUPS];
-    if (states_equivalent(a, b, [&](uint32_t s) { return X[s * B]; },
-                          [&](uint32_t s) { return Y[s * B]; }, tau,
-                          [&](int u) -> uint8_t & { return stale[u]; })) {
-        if (a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair of this chunk goes on
-            const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
-            a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+    int32_t redone = 0;
+    int64_t prev = b;                                 // whose run of chunk j-1 counts
+    for (int32_t j = 1; j < a.K; ++j) {
+        const int32_t q_prev = j * a.seg_per_chunk - 1;
+        const double tau = a.arrivals[a.leaf_start[seg_leaf(a, q_prev + 1)]];
+        const double *X = a.seg_end + (size_t)q_prev * a.T * B + prev;
+        int64_t src = -1;
+        for (int64_t r = 0; r <= m_end - m_first; ++r) {
+            const int64_t v = r == 0 ? b : m_first + r - 1;
+            const double *Y = a.chunk_start + (size_t)j * a.T * B + v;
+            if (states_equivalent(a, b, [&](uint32_t s) { return X[s * B]; },
+                                  [&](uint32_t s) { return Y[s * B]; }, tau,
+                                  [&](int w) -> uint8_t & { return stale[w]; })) {
+                src = v;
+                break;
+            }
         }
-        return;
+        if (src == b) {
+            if (a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair of this chunk goes on
+                const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
+                a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+            }
+        } else if (src < 0) {
+            double *Y = a.chunk_start + (size_t)j * a.T * B + b;
+            for (int s = 0; s < a.T; ++s) Y[s * B] = X[s * B];
+            a.repair_from[(size_t)j * B + b] = -1;         // the whole chunk is redone
+            const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
+            a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
+            ++redone;
+            src = b;
+        }
+        a.chunk_src[(size_t)j * B + b] = src == b ? -1 : (int32_t)src;
+        prev = src;
     }
-    for (int s = 0; s < a.T; ++s) Y[s * B] = X[s * B];
-    a.repair_from[(size_t)j * B + b] = -1;             // the whole chunk is redone
-    const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
-    a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
-    if (a.resimulated) atomicAdd(&a.resimulated[b], 1);
+    if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
 }
 
 // One thread per chunk on the work list of this round.
@@ -238,9 +266,11 @@ sim_repair_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
-// One thread per candidate: walks the chunk boundaries in order and repairs
-// in place what is still inconsistent.  After it, every chunk was simulated
-// from a state equivalent to the true one.
+// One thread per scored candidate: walks the chunk boundaries in order, takes
+// each chunk from the run (own or mirror's) that continues the chunk before
+// it, and repairs in place, in the candidate's own arrays, what neither
+// continues.  After it, every chunk that counts was simulated from a state
+// equivalent to the true one.
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __global__ void __launch_bounds__(kLanes, 1)
 sim_chain_kernel(const KernelArgs a)
@@ -249,7 +279,9 @@ sim_chain_kernel(const KernelArgs a)
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
     stage_latency_table(a, L, lane);
     const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
-    if (b >= a.B || !can_chunk(a) || a.N == 0) return;
+    if (b >= a.Bs || !can_chunk(a) || a.N == 0) return;
+    int64_t m_end;
+    const int64_t m_first = mirrors_of(a, b, m_end);
 
     uint32_t counters; int n_counters;
     Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
@@ -258,19 +290,26 @@ sim_chain_kernel(const KernelArgs a)
     Pipe p;
     init_pipe(a, p);
     int32_t redone = 0;
+    int64_t prev = b;                                 // whose run of chunk j-1 counts
     for (int32_t j = 1; j < a.K; ++j) {
         const int32_t q_prev = j * a.seg_per_chunk - 1;
         const int64_t first = a.leaf_start[seg_leaf(a, q_prev + 1)];
         const double tau = a.arrivals[first];
         for (int t = 0; t < a.T; ++t) {
-            SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)q_prev * a.T + t) * a.B + b];
+            SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)q_prev * a.T + t) * a.B + prev];
             SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + b];
         }
+        auto continues = [&]() {
+            return states_equivalent(
+                a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
+                [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
+                [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
+        };
         int32_t q_begin = j * a.seg_per_chunk;
         int32_t begin = (int32_t)first;
-        if (states_equivalent(a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
-                              [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
-                              [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; })) {
+        a.chunk_src[(size_t)j * a.B + b] = -1;
+        prev = b;
+        if (continues()) {
             // the chunk continues its predecessor; finish a repair a round left capped
             q_begin = a.repair_from[(size_t)j * a.B + b];
             if (q_begin < 0) continue;
@@ -278,6 +317,17 @@ sim_chain_kernel(const KernelArgs a)
             for (int t = 0; t < a.T; ++t)
                 SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)(q_begin - 1) * a.T + t) * a.B + b];
         } else {
+            bool found = false;
+            for (int64_t m = m_first; m < m_end && !found; ++m) {
+                for (int t = 0; t < a.T; ++t)
+                    SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + m];
+                if (continues()) {
+                    a.chunk_src[(size_t)j * a.B + b] = (int32_t)m;
+                    prev = m;
+                    found = true;
+                }
+            }
+            if (found) continue;
             for (int t = 0; t < a.T; ++t)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
         }
@@ -291,23 +341,29 @@ sim_chain_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
-// Adds the per-segment counters: one thread per (counter, candidate).
-__global__ void sum_counters_kernel(int32_t B, int32_t M, int32_t G, int32_t NS, int32_t n_counters,
-                                    int32_t num_leaves, const uint32_t *seg_counters,
-                                    const int32_t *model_hist, int32_t *model_num_requests,
-                                    int32_t *model_num_good, int32_t *group_num_requests,
-                                    int32_t *group_num_good)
+// Adds the per-segment counters of the runs that count: one thread per
+// (counter, scored candidate).
+__global__ void sum_counters_kernel(const KernelArgs a, int32_t n_counters,
+                                    int32_t *model_num_requests, int32_t *model_num_good,
+                                    int32_t *group_num_requests, int32_t *group_num_good)
 {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (int64_t)B * n_counters) return;
-    const int c = (int)(t / B);
-    const int64_t b = t % B;
+    if (t >= (int64_t)a.Bs * n_counters) return;
+    const int c = (int)(t / a.Bs);
+    const int64_t b = t % a.Bs;
+    const int32_t M = a.M, G = a.G;
     uint32_t v = 0;
-    if (num_leaves > 0)
-        for (int q = 0; q < NS; ++q) v += seg_counters[((size_t)q * n_counters + c) * B + b];
+    if (a.num_leaves > 0) {
+        for (int32_t j = 0, q = 0; q < a.NS; ++j) {
+            const int32_t src = a.chunk_src[(size_t)j * a.B + b];
+            const int64_t from = src >= 0 ? src : b;
+            const int32_t q_end = q + a.seg_per_chunk < a.NS ? q + a.seg_per_chunk : a.NS;
+            for (; q < q_end; ++q) v += a.seg_counters[((size_t)q * n_counters + c) * a.B + from];
+        }
+    }
     if (c < M) {
         model_num_good[(size_t)b * M + c] = (int32_t)v;
-        model_num_requests[(size_t)b * M + c] = model_hist[c];
+        model_num_requests[(size_t)b * M + c] = a.model_hist[c];
     } else if (c < M + G) {
         group_num_requests[(size_t)b * G + (c - M)] = (int32_t)v;
     } else {
@@ -316,24 +372,33 @@ __global__ void sum_counters_kernel(int32_t B, int32_t M, int32_t G, int32_t NS,
 }
 
 // Combines the leaf sums in numpy's pairing order and totals the good
-// requests (controller.py:401-402 consumes both).  One thread per candidate;
-// leaf sums are fetched eight at a time so that the loads overlap.
-__global__ void finalize_kernel(int32_t B, int32_t M, int32_t num_leaves,
-                                const uint8_t *leaf_merges, const double *leaf_sums,
+// requests (controller.py:401-402 consumes both).  One thread per scored
+// candidate; leaf sums are fetched eight at a time so that the loads overlap.
+__global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
                                 const int32_t *model_num_good, int64_t *good_total,
-                                double *latency_sum, uint32_t *status)
+                                double *latency_sum)
 {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= B) return;
+    if (b >= a.Bs) return;
+    const int32_t num_leaves = a.num_leaves;
     double stack[kMaxSumDepth];
     int sp = 0;
+    int32_t j = -1, chunk_end = 0;       // leaves [.., chunk_end) belong to chunk j
+    int64_t from = b;
     for (int32_t base = 0; base < num_leaves; base += 8) {
         double v[8];
         uint8_t mg[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int32_t leaf = base + u < num_leaves ? base + u : num_leaves - 1;
-            v[u] = leaf_sums[(size_t)leaf * B + b];
+            while (leaf >= chunk_end) {
+                if (!a.chunk_src) { chunk_end = num_leaves; break; }   // one run per candidate
+                ++j;
+                const int32_t src = a.chunk_src[(size_t)j * a.B + b];
+                from = src >= 0 ? src : b;
+                chunk_end = seg_leaf(a, (j + 1) * a.seg_per_chunk);
+            }
+            v[u] = a.leaf_sums[(size_t)leaf * a.B + from];
             mg[u] = leaf_merges[leaf];
         }
 #pragma unroll
@@ -347,10 +412,10 @@ __global__ void finalize_kernel(int32_t B, int32_t M, int32_t num_leaves,
             }
         }
     }
-    if (sp > kMaxSumDepth) status[b] |= MMS_STATUS_BAD_INDEX;
+    if (sp > kMaxSumDepth) a.status[b] |= MMS_STATUS_BAD_INDEX;
     latency_sum[b] = (num_leaves > 0) ? stack[0] : 0.0;
     int64_t total = 0;
-    for (int m = 0; m < M; ++m) total += model_num_good[(size_t)b * M + m];
+    for (int m = 0; m < a.M; ++m) total += model_num_good[(size_t)b * a.M + m];
     good_total[b] = total;
 }
 

@@ -21,6 +21,9 @@ struct KernelArgs {
     const int32_t *model_hist;    // [M + 1]; last entry = unsorted/non-finite positions
     // placements
     int32_t B, M, G, P, T, S, C;
+    int32_t Bs;                   // candidates with outputs; [Bs, B) are mirrors
+    const int32_t *partner;       // [B] or null
+    const uint32_t *mirror_swap;  // [B][2] or null
     const uint16_t *model_off;
     const uint32_t *model_rep;
     const uint32_t *group_info;
@@ -45,6 +48,8 @@ struct KernelArgs {
     uint32_t *work_count;         // [rounds]
     uint32_t *work_items;         // [B * K]: chunk * B + candidate; bit 31 = continue a repair
     int32_t *repair_from;         // [K][B]: segment a capped repair of chunk j stopped at, or -1
+    int32_t *chunk_src;           // [K][B]: whose run of chunk j counts for candidate b (its own
+                                  //         or a mirror's); -1 = its own
     int32_t repair_cap;           // segments a repair may run per round
     int32_t round;
     // outputs
@@ -72,6 +77,29 @@ __device__ inline int32_t seg_leaf(const KernelArgs &a, int32_t q)
     if (q <= 0) return 0;
     if (q >= a.NS) return a.num_leaves;
     return leaf_lower_bound(a.leaf_start, a.num_leaves, (int64_t)q * a.seg_len);
+}
+
+// The mirrors of scored candidate b are candidates [first, end): returns
+// first and sets end (first == end: none).
+__device__ inline int64_t mirrors_of(const KernelArgs &a, int64_t b, int64_t &end)
+{
+    end = 0;
+    if (!a.partner || a.Bs == a.B) return 0;
+    const int64_t first = a.partner[b];
+    if (first < a.Bs || first >= a.B) return 0;
+    int64_t m = first;
+    while (m < a.B && a.partner[m] == b) ++m;
+    end = m;
+    return first;
+}
+
+// Row of the status output candidate b reports to: its own, or for a mirror
+// the row of the candidate it mirrors (outputs have Bs rows).
+__device__ inline int64_t status_row(const KernelArgs &a, int64_t b)
+{
+    if (b < a.Bs) return b;
+    const int32_t p = a.partner ? a.partner[b] : 0;
+    return (p >= 0 && p < a.Bs) ? p : 0;
 }
 
 // True when the trace can be cut (sorted, finite arrival times).
@@ -158,7 +186,8 @@ template <bool kFull, bool kGroupGood, bool kLegacy>
 __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint32_t counters,
                                     int n_counters, int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
-                                    uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0)
+                                    uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0,
+                                    uint64_t swap_pairs = ~0ull)
 {
     double *fin_out = kFull ? a.finish + (size_t)b * a.N : nullptr;
     uint8_t *good_out = kFull ? a.good + (size_t)b * a.N : nullptr;
@@ -201,6 +230,23 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
             }
         }
         if (!record) {
+            // a mirror starts its chunk with interchangeable groups exchanged
+            for (int k = 0; k < 4 && swap_pairs != ~0ull; ++k) {
+                const uint32_t ga = (uint32_t)(swap_pairs >> (16 * k)) & 0xFFu;
+                const uint32_t gb = (uint32_t)(swap_pairs >> (16 * k + 8)) & 0xFFu;
+                if (ga >= (uint32_t)a.G || gb >= (uint32_t)a.G) continue;
+                const uint32_t ia = a.group_info[(size_t)b * a.G + ga];
+                const uint32_t ib = a.group_info[(size_t)b * a.G + gb];
+                const uint32_t ns = (ia >> 8) & 0xFFu;
+                if (ns != ((ib >> 8) & 0xFFu)) continue;
+                for (uint32_t t = 0; t < ns; ++t) {
+                    const uint32_t sa = ln.clk + ((ia & 0xFFu) + t) * kLanes;
+                    const uint32_t sb = ln.clk + ((ib & 0xFFu) + t) * kLanes;
+                    const double va = SM_F64(sa);
+                    SM_F64(sa) = SM_F64(sb);
+                    SM_F64(sb) = va;
+                }
+            }
             if (!repair && snapshots)   // the state this speculative chunk starts from
                 for (int t = 0; t < a.T; ++t)
                     a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);

@@ -9,7 +9,8 @@ only; all compute goes through the C ABI in libmms_sim.so.
 """
 import ctypes
 import operator
-from itertools import chain
+from itertools import chain, permutations, product
+from math import factorial
 from typing import List, Sequence
 
 import numpy as np
@@ -168,17 +169,145 @@ class EncodedBatch:
     """Host arrays of a placement batch in the layout of mms_placements."""
 
     def __init__(self, B, M, G, P, T, S, C, model_off, model_rep, group_info, num_groups,
-                 num_replicas):
+                 num_replicas, twins=None):
         self.B, self.M, self.G, self.P, self.T, self.S, self.C = B, M, G, P, T, S, C
         self.model_off = model_off        # u16[B][M+1]
         self.model_rep = model_rep        # u32[B][P]
         self.group_info = group_info      # u32[B][G]
         self.num_groups = num_groups      # i64[B]
         self.num_replicas = num_replicas  # i64[B]: sum of len(group_models)
+        # (candidate index, [[group ids of one class of interchangeable groups], ...])
+        # for every placement that has such groups, see twin_groups()
+        self.twins = twins
+
+    def with_mirrors(self):
+        """The tables with mirror candidates appended for every placement
+        that has interchangeable groups (see "Mirrors" in include/mms_sim.h),
+        one per way of permuting them: (model_off, model_rep, group_info,
+        partner i32[B'], mirror_swap u32[B'][2]) or None when no placement
+        has any."""
+        if not self.twins:
+            return None
+        owners, swaps, first = [], [], []
+        at = self.B
+        has = []
+        for b, classes in self.twins:
+            words = mirror_swaps(classes)
+            if not words:
+                continue
+            has.append(b)
+            first.append(at)
+            at += len(words)
+            owners.extend([b] * len(words))
+            swaps.extend(words)
+        if not has:
+            return None
+        owners = np.asarray(owners, np.int64)
+        partner = np.full(at, -1, np.int32)
+        partner[has] = first
+        partner[self.B:] = owners
+        swap = np.full((at, 2), NO_SWAP, np.uint32)
+        swap[self.B:] = np.asarray(swaps, np.uint64).view(np.uint32).reshape(-1, 2)
+        return (np.concatenate((self.model_off, self.model_off[owners])),
+                np.concatenate((self.model_rep, self.model_rep[owners])),
+                np.concatenate((self.group_info, self.group_info[owners])), partner, swap)
 
     @property
     def nbytes(self):
         return self.model_off.nbytes + self.model_rep.nbytes + self.group_info.nbytes
+
+
+NO_SWAP = np.uint32(0xFFFFFFFF)
+_MODEL_KEYS = {}
+
+
+MAX_MIRRORS = 15          # per placement
+_PERM_CACHE = {}
+
+
+def _perm_swaps(sizes):
+    """Every non-identity way of permuting classes of the given sizes among
+    themselves, each as a list of exchanges (i, j) of positions in the
+    concatenated classes, at most four per permutation."""
+    if sizes not in _PERM_CACHE:
+        offsets = np.concatenate(([0], np.cumsum(sizes)))[:-1]
+        per_class = []
+        for off, n in zip(offsets, sizes):
+            options = []
+            for perm in permutations(range(n)):
+                # exchanges that turn the identity arrangement into `perm`
+                cur, ex = list(range(n)), []
+                for i in range(n):
+                    if cur[i] != perm[i]:
+                        k = cur.index(perm[i])
+                        cur[i], cur[k] = cur[k], cur[i]
+                        ex.append((int(off) + i, int(off) + k))
+                options.append(ex)
+            per_class.append(options)
+        out = []
+        for combo in product(*per_class):
+            ex = [e for part in combo for e in part]
+            if ex and len(ex) <= 4:
+                out.append(ex)
+        _PERM_CACHE[sizes] = out
+    return _PERM_CACHE[sizes]
+
+
+def mirror_swaps(classes):
+    """64-bit exchange lists (see mirror_swap in include/mms_sim.h) of the
+    mirrors for one placement whose interchangeable groups are `classes`: one
+    per permutation, or none at all when there are more than MAX_MIRRORS
+    (covering only some would cost throughput without removing the serial
+    repairs of the rest)."""
+    sizes = tuple(len(c) for c in classes)
+    count = 1
+    for n in sizes:
+        count *= factorial(n) if n < 5 else MAX_MIRRORS + 2
+    if count - 1 > MAX_MIRRORS:
+        return []
+    groups = [g for c in classes for g in c]
+    words = []
+    for ex in _perm_swaps(sizes):
+        w = 0xFFFFFFFFFFFFFFFF
+        for k, (i, j) in enumerate(ex):
+            w &= ~(0xFFFF << (16 * k))
+            w |= (groups[i] | (groups[j] << 8)) << (16 * k)
+        words.append(w)
+    return words
+
+
+def twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model):
+    """Classes of groups of one placement with the same parallel config and
+    the same set of models (flat arrays as in encode_placements).  Such groups
+    are interchangeable: which of them is ahead after a stretch of the trace
+    depends on history long past, and a speculative chunk may come out with
+    their roles permuted.  Returns [(placement index, [[group ids], ...])] for
+    the placements that have any.  The sets are compared through a 64-bit sum
+    of random per-model keys; a collision could only cost speed, never
+    exactness."""
+    tot_groups = len(grp_b)
+    if tot_groups < 2 or len(placed_model) == 0:
+        return []
+    if M not in _MODEL_KEYS:
+        _MODEL_KEYS[M] = np.random.RandomState(20240229).randint(
+            1, 2 ** 62, size=max(M, 1), dtype=np.int64).astype(np.uint64)
+    with np.errstate(over="ignore"):
+        csum = np.concatenate((np.zeros(1, np.uint64),
+                               np.cumsum(_MODEL_KEYS[M][placed_model], dtype=np.uint64)))
+        ends = np.cumsum(n_in_group)
+        key = (csum[ends] - csum[ends - n_in_group]) * np.uint64(0x9E3779B97F4A7C15) \
+            + cfg_col.astype(np.uint64) * np.uint64(0xC2B2AE3D27D4EB4F) + n_in_group.astype(np.uint64)
+    order = np.lexsort((grp_g, key, grp_b))
+    b_s, k_s, n_s, g_s = grp_b[order], key[order], n_in_group[order], grp_g[order]
+    same = (b_s[1:] == b_s[:-1]) & (k_s[1:] == k_s[:-1]) & (n_s[1:] > 0)
+    if not same.any():
+        return []
+    # runs of `same`: a class is the group before the run plus the run
+    edges = np.flatnonzero(np.diff(np.concatenate(([0], same.view(np.int8), [0]))))
+    out = {}
+    for lo, hi in zip(edges[0::2].tolist(), edges[1::2].tolist()):
+        out.setdefault(int(b_s[lo]), []).append(g_s[lo:hi + 1].tolist())
+    return sorted(out.items())
 
 
 def encode_placements(placements: Sequence, table: LatencyTable, num_models: int) -> EncodedBatch:
@@ -246,8 +375,9 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     group_info = np.zeros((B, max(G, 1)), np.uint32)
     group_info[grp_b, grp_g] = (slot_first | (cfg_pp << 8) | (contested << 16)).astype(np.uint32)
 
+    twins = twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model)
     return EncodedBatch(B, M, max(G, 1), max(P, 1), max(T, 1), S, C, model_off, model_rep,
-                        group_info, n_groups, placed_per_b.astype(np.int64))
+                        group_info, n_groups, placed_per_b.astype(np.int64), twins)
 
 
 class BatchResult:
@@ -266,9 +396,12 @@ def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_seg
 
 
 def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
-            latency, latency_stride, flags, want_group_good, pinned=False, options=None):
+            latency, latency_stride, flags, want_group_good, pinned=False, options=None,
+            num_scored=None, partner=None, mirror_swap=None):
     """Uploads the tables, runs mms_sim_mixed on the current stream, downloads
-    the results.  Returns (BatchResult, h2d_bytes, d2h_bytes)."""
+    the results.  Returns (BatchResult, h2d_bytes, d2h_bytes).  With
+    num_scored < B the candidates behind the first num_scored are mirrors
+    (partner, mirror_swap as in mms_placements) and get no results."""
     _require_cuda()
     L = nat.lib()
     dev = trace.device
@@ -283,8 +416,14 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         d_info = _to_device(group_info, dev, pinned)
         d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev, pinned)
         h2d = model_off.nbytes + model_rep.nbytes + group_info.nbytes
-        cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), _ptr(d_info),
-                               _ptr(d_lat), int(latency_stride))
+        Bs = B if num_scored is None else int(num_scored)
+        d_partner = d_swap = None
+        if Bs != B:
+            d_partner, d_swap = _to_device(partner, dev, pinned), _to_device(mirror_swap, dev, pinned)
+            h2d += partner.nbytes + mirror_swap.nbytes
+        cands = nat.Placements(B, M, G, P, T, S, C, Bs if Bs != B else 0, _ptr(d_off), _ptr(d_rep),
+                               _ptr(d_info), _ptr(d_lat), int(latency_stride), _ptr(d_partner),
+                               _ptr(d_swap))
         need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts), flags)
         if need == 0 and B > 0:
             raise NotImplementedError("placement batch outside the kernel limits "
@@ -311,14 +450,14 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
                              _ptr(trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
                              ctypes.byref(out), flags, _stream_ptr())
         nat.check(rc, "mms_sim_mixed")
-        res.model_num_requests = o_mreq.cpu().numpy()[:, :M]
-        res.model_num_good = o_mgood.cpu().numpy()[:, :M]
-        res.group_num_requests = o_greq.cpu().numpy()
-        res.group_num_good = o_ggood.cpu().numpy() if want_group_good else None
-        res.good_total = o_total.cpu().numpy()
-        res.latency_sum = o_lsum.cpu().numpy()
+        res.model_num_requests = o_mreq[:Bs].cpu().numpy()[:, :M]
+        res.model_num_good = o_mgood[:Bs].cpu().numpy()[:, :M]
+        res.group_num_requests = o_greq[:Bs].cpu().numpy()
+        res.group_num_good = o_ggood[:Bs].cpu().numpy() if want_group_good else None
+        res.good_total = o_total[:Bs].cpu().numpy()
+        res.latency_sum = o_lsum[:Bs].cpu().numpy()
         res.status = o_status.cpu().numpy().astype(np.uint32)
-        res.resimulated = o_redo.cpu().numpy()
+        res.resimulated = o_redo[:Bs].cpu().numpy()
         res.finish = o_fin.cpu().numpy()[:, :N] if full else None
         res.good = o_good.cpu().numpy()[:, :N].astype(bool) if full else None
         d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
@@ -334,10 +473,18 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
 
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
-              per_request=False, group_good=False, pinned=False, options=None):
+              per_request=False, group_good=False, pinned=False, options=None, mirrors=True):
     """Simulates every placement of `enc` against `trace`
-    (simulate_requests_mixed, controller.py:561-628)."""
+    (simulate_requests_mixed, controller.py:561-628).  `mirrors`: placements
+    with interchangeable groups get a mirror candidate (a speed-up of the
+    time-parallel execution; results are the same with and without)."""
     flags = nat.FLAG_PER_REQUEST if per_request else 0
+    ext = None if per_request or not mirrors else enc.with_mirrors()
+    if ext is not None:
+        off, rep, info, partner, swap = ext
+        return _launch(trace, len(partner), enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, off, rep,
+                       info, table.device(trace.device), 0, flags, group_good, pinned, options,
+                       enc.B, partner, swap)
     return _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
                    enc.model_off, enc.model_rep, enc.group_info,
                    table.device(trace.device), 0, flags, group_good, pinned, options)

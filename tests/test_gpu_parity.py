@@ -301,3 +301,66 @@ def test_twin_groups_keep_exact_counters(loaded, chunk, run_in):
         assert np.array_equal(res.group_num_requests[b, :len(greq)], greq), b
         assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood), b
         assert res.latency_sum[b] == float(np.add.reduce(fin - arr))
+
+
+@pytest.mark.parametrize("chunk,run_in,rounds,cap", [
+    (0, 0, 0, 0), (4096, 512, 0, 0), (2048, 16, 2, 1), (4096, 2048, 1, 0), (8192, 1, 16, 2)])
+def test_mirror_candidates_change_nothing_but_speed(loaded, chunk, run_in, rounds, cap):
+    """Placements with interchangeable groups get a mirror candidate whose
+    speculative chunks start with those groups exchanged; a chunk is taken
+    from whichever run continues the chain.  Every reduced output must equal
+    the run without mirrors and the checker, for any cut of the trace."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement, PlacementEvaluator
+    from mms_b200.profiling import ParallelConfig
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=24, duration=1500.0, num_models=8,
+                                      num_devices=16, total_rate=40.0, cv=3.0, placement_seed=4)
+    c1, c2, c4 = (ParallelConfig(1, 1, p) for p in (1, 2, 4))
+    sols = list(case.placements) + [
+        ModelPlacement([c1] * 8 + [c2] * 4, [[0, 3]] * 4 + [[1, 4]] * 4 + [[2, 5, 6]] * 2 + [[7, 2]] * 2),
+        ModelPlacement([c2] * 8, [[0, 1, 3, 4, 6, 7]] * 2 + [[2, 5]] * 2 + [[0, 1]] * 2 + [[3, 4], [6, 7]]),
+        ModelPlacement([c4, c4, c2, c2, c1, c1, c1, c1],
+                       [[2, 5, 0], [2, 5, 0], [1, 3], [1, 3], [4], [4], [6, 7], [7, 6]]),
+        ModelPlacement([c1] * 16, [[0]] * 3 + [[1]] * 3 + [[3, 4]] * 5 + [[6, 7, 0]] * 5),
+        ModelPlacement([c2, c2, c4, c4, c4], [[0, 1, 2], [0, 1, 2], [3, 4, 5, 6, 7], [5], [5]]),
+    ]
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            options=engine.sim_options(chunk, run_in, rounds, cap))
+    enc = engine.encode_placements(sols, ev.table, len(ev.model_names))
+    ext = enc.with_mirrors()
+    assert ext is not None and len(ext[3]) >= enc.B + 4      # most hand-made ones get mirrors
+    with_m, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True, options=ev.options)
+    without, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True, options=ev.options,
+                                     mirrors=False)
+    for name in ("model_num_requests", "model_num_good", "group_num_requests", "group_num_good",
+                 "good_total", "latency_sum"):
+        a, b = getattr(with_m, name), getattr(without, name)
+        assert a.shape == b.shape and a.tobytes() == b.tobytes(), name
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    for b in range(len(sols) - 5, len(sols)):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(sols[b], profs, mids, slos, arr)
+        assert np.array_equal(with_m.model_num_good[b], mgood), b
+        assert np.array_equal(with_m.group_num_requests[b, :len(greq)], greq), b
+        assert np.array_equal(with_m.group_num_good[b, :len(ggood)], ggood), b
+        assert with_m.latency_sum[b] == float(np.add.reduce(fin - arr))
+
+
+def test_mirrors_are_refused_with_per_request_outputs(loaded):
+    """Per-request outputs come from one run per candidate: the library
+    rejects the combination instead of returning rows from two runs."""
+    import ctypes
+    from mms_b200 import _native as nat
+    fake = ctypes.c_void_p(256)             # the size query reads no table
+    cands = nat.Placements(4, 2, 1, 1, 1, 1, 1, 3, None, None, None, None, 0, fake, fake)
+    opts = nat.SimOptions(0, 0, 0, 0)
+    L = nat.lib()
+    assert L.mms_sim_workspace_bytes(100000, ctypes.byref(cands), ctypes.byref(opts), 0) > 0
+    assert L.mms_sim_workspace_bytes(100000, ctypes.byref(cands), ctypes.byref(opts),
+                                     nat.FLAG_PER_REQUEST) == 0
+    cands.partner = None                    # mirrors without a partner list
+    assert L.mms_sim_workspace_bytes(100000, ctypes.byref(cands), ctypes.byref(opts), 0) == 0

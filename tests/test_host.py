@@ -142,3 +142,61 @@ def test_group_lists_match_reference_tables():
             col = int(gcfg[b, g]) >> 16
             for m in want:
                 assert table.host[m, col, :ns[g], :].tobytes() == lat[m, g, :ns[g], :].tobytes()
+
+
+def test_twin_group_detection_matches_a_plain_search():
+    """Interchangeable groups (same parallel config, same set of models) are
+    found through hashed model sets; compare with a dictionary of sets.  Every
+    permutation of them gets a mirror candidate."""
+    from math import factorial
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement
+    from mms_b200.profiling import ParallelConfig
+    case = cases.candidate_batch_case(num_candidates=600, duration=5.0, placement_seed=2)
+    c1, c2 = ParallelConfig(1, 1, 1), ParallelConfig(1, 1, 2)
+    sols = list(case.placements) + [
+        ModelPlacement([c1] * 6 + [c2] * 2, [[0, 3], [3, 0], [1], [1], [1], [], [2, 5], [5]]),
+        ModelPlacement([c1, c2], [[0], [0]]),
+        ModelPlacement([c1, c1], [[], []]),
+        ModelPlacement([c1] * 7, [[4]] * 5 + [[2], [2]])]
+    table = engine.LatencyTable([d.profiling_result for d in case.model_datas])
+    enc = engine.encode_placements(sols, table, len(case.model_datas))
+    found = dict(enc.twins)
+    expect_mirrors = 0
+    for b, p in enumerate(sols):
+        classes = {}
+        for g, (c, ms) in enumerate(zip(p.group_configs, p.group_models)):
+            if len(ms):
+                classes.setdefault((c, tuple(sorted(ms))), []).append(g)
+        want = sorted(v for v in classes.values() if len(v) >= 2)
+        assert sorted(found.get(b, [])) == want, b
+        perms = int(np.prod([factorial(len(v)) for v in want])) if want else 1
+        expect_mirrors += perms - 1 if perms - 1 <= engine.MAX_MIRRORS else 0
+    assert len(found) >= 4
+    assert sorted(found[len(sols) - 4]) == [[0, 1], [2, 3, 4]]
+    off, rep, info, partner, swap = enc.with_mirrors()
+    assert len(partner) == enc.B + expect_mirrors
+    owners = partner[enc.B:]
+    assert np.all(np.diff(owners) >= 0)                      # mirrors of one placement are adjacent
+    assert len(sols) - 1 not in owners                       # 5! * 2 permutations: none at all
+    assert np.count_nonzero(owners == len(sols) - 4) == 2 * 6 - 1
+    for b in np.unique(owners):
+        assert partner[b] == enc.B + np.flatnonzero(owners == b)[0]
+    assert np.all(partner[:enc.B][np.setdiff1d(np.arange(enc.B), owners)] == -1)
+    assert np.array_equal(rep[enc.B:], enc.model_rep[owners])
+    assert np.all(swap[:enc.B] == engine.NO_SWAP)
+    # the exchanges of one placement's mirrors produce distinct arrangements of its groups
+    b = len(sols) - 4
+    seen = set()
+    for w in swap[enc.B:][owners == b].astype(np.uint64):
+        word = int(w[0]) | (int(w[1]) << 32)
+        arr = list(range(8))
+        for k in range(4):
+            i, j = (word >> (16 * k)) & 0xFF, (word >> (16 * k + 8)) & 0xFF
+            if i != 0xFF:
+                arr[i], arr[j] = arr[j], arr[i]
+        assert arr != list(range(8))
+        for cls in ([0, 1], [2, 3, 4]):
+            assert sorted(arr[g] for g in cls) == cls
+        seen.add(tuple(arr))
+    assert len(seen) == 11

@@ -42,7 +42,7 @@ struct Geometry {
     int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
-        off_repair_from, off_rows, off_chunk_src;
+        off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
     size_t total;
 };
 
@@ -139,7 +139,9 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
     g->off_repair_from = off; off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
-    g->off_chunk_src = off;   off += align256(sizeof(int32_t) * (size_t)K * B);
+    g->off_seg_src = off;     off += align256(sizeof(int32_t) * (size_t)NS * B);
+    g->off_compat = off;      off += align256(sizeof(uint16_t) * (size_t)K * B);
+    g->off_seg_leaf = off;    off += align256(sizeof(int32_t) * (size_t)(NS + 1));
     g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
     g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
     g->total = off;
@@ -149,6 +151,8 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
 template <bool kFull, bool kGroupGood, bool kLegacy>
 static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 {
+    seg_leaf_kernel<<<(unsigned)((ka.NS + 128) / 128), 128, 0, st>>>(ka);
+    MMS_CUDA(cudaGetLastError());
     const int64_t cells = (int64_t)ka.B * ka.M;
     if (cells > 0) {
         build_rows_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka);
@@ -167,10 +171,12 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
                                       (int)g.smem_repair));
         MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)g.smem_repair));
-        const int64_t bounds = (int64_t)ka.Bs * (ka.K - 1);
+        const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
         for (int r = 0; r < g.rounds; ++r) {
             ka.round = r;
-            resolve_kernel<<<(unsigned)((ka.Bs + 31) / 32), 32, 0, st>>>(ka);
+            validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(ka);
+            MMS_CUDA(cudaGetLastError());
+            resolve_kernel<<<(unsigned)((ka.Bs + 63) / 64), 64, 0, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
             // sized for the worst case; blocks past the work list return at once
             repair_k<<<(unsigned)((bounds + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
@@ -285,7 +291,9 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);
     ka.work_items = (uint32_t *)(scratch + g.off_work_items);
     ka.repair_from = (int32_t *)(scratch + g.off_repair_from);
-    ka.chunk_src = (int32_t *)(scratch + g.off_chunk_src);
+    ka.seg_src = (int32_t *)(scratch + g.off_seg_src);
+    ka.compat = (uint16_t *)(scratch + g.off_compat);
+    ka.seg_first_leaf = (int32_t *)(scratch + g.off_seg_leaf);
     ka.repair_cap = g.repair_cap;
     ka.seg_end = (double *)(scratch + g.off_seg_end);
     ka.chunk_start = (double *)(scratch + g.off_chunk_start);
@@ -296,7 +304,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)ka.Bs, st));
     MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kMaxRepairRounds + 1), st));
     MMS_CUDA(cudaMemsetAsync(ka.repair_from, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
-    MMS_CUDA(cudaMemsetAsync(ka.chunk_src, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
+    MMS_CUDA(cudaMemsetAsync(ka.seg_src, 0xFF, sizeof(int32_t) * (size_t)ka.NS * B, st));
     if (out->resimulated)
         MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)ka.Bs, st));
     const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;

@@ -178,13 +178,52 @@ sim_stream_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[status_row(a, b)], ln.status);
 }
 
-// One thread per scored candidate: follows the chain of chunks.  Chunk j is
-// taken from the first run of it (the candidate's own, then its mirrors')
-// whose start state continues the state the chosen run of chunk j-1 ended in
-// (states_equivalent: equal futures, provably).  Where none does, the true
-// state is copied into the candidate's own chunk and the chunk goes on the
-// work list.  Behind a listed chunk the walk goes on with the old data; the
-// next round (or the chain kernel) sees the repaired one.
+// First leaf of every segment, once per call.
+__global__ void seg_leaf_kernel(const KernelArgs a)
+{
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    if (q > a.NS) return;
+    a.seg_first_leaf[q] = q == 0 ? 0 : q == a.NS ? a.num_leaves
+        : leaf_lower_bound(a.leaf_start, a.num_leaves, (int64_t)q * a.seg_len);
+}
+
+// One thread per (array u, chunk j >= 1), u a scored candidate or a mirror:
+// which stored runs of chunk j start from a state that continues the state
+// array u holds at the end of chunk j-1 (states_equivalent: equal futures,
+// provably)?  Bit 0: the array of the candidate itself, bit 1 + i: its i-th
+// mirror.
+__global__ void validate_kernel(const KernelArgs a)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (!can_chunk(a) || t >= (int64_t)a.B * (a.K - 1)) return;
+    const int32_t j = (int32_t)(t / a.B) + 1;
+    const int64_t u = t % a.B;
+    const int64_t b = status_row(a, u);                // the scored candidate u belongs to
+    if (u >= a.Bs && (j == 1 || a.partner[u] != b)) return;   // a mirror has no chunk 0
+    int64_t m_end;
+    const int64_t m_first = mirrors_of(a, b, m_end);
+    const int32_t q_prev = j * a.seg_per_chunk - 1;
+    const double tau = a.arrivals[a.leaf_start[seg_leaf(a, q_prev + 1)]];
+    const size_t B = (size_t)a.B;
+    const double *X = a.seg_end + (size_t)q_prev * a.T * B + u;
+    uint8_t stale[MMS_MAX_GROUPS];
+    uint32_t mask = 0;
+    for (int64_t r = 0; r <= m_end - m_first && r < 16; ++r) {
+        const double *Y = a.chunk_start + (size_t)j * a.T * B + (r == 0 ? b : m_first + r - 1);
+        if (states_equivalent(a, b, [&](uint32_t s) { return X[s * B]; },
+                              [&](uint32_t s) { return Y[s * B]; }, tau,
+                              [&](int w) -> uint8_t & { return stale[w]; }))
+            mask |= 1u << r;
+    }
+    a.compat[(size_t)j * B + u] = (uint16_t)mask;
+}
+
+// One thread per scored candidate: follows the chain of chunks through the
+// masks of validate_kernel.  A chunk keeps the run selected for it when that
+// one continues the chunk before it; else it is taken from the first mirror
+// that does; else the true state is copied into the candidate's own array and
+// the chunk goes on the work list.  Behind a listed chunk the walk goes on
+// with the old data; the next round (or the chain kernel) sees the new one.
 __global__ void resolve_kernel(const KernelArgs a)
 {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -192,40 +231,33 @@ __global__ void resolve_kernel(const KernelArgs a)
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
     const size_t B = (size_t)a.B;
-    uint8_t stale[MMS_MAX_GROUPS];
     int32_t redone = 0;
-    int64_t prev = b;                                 // whose run of chunk j-1 counts
     for (int32_t j = 1; j < a.K; ++j) {
-        const int32_t q_prev = j * a.seg_per_chunk - 1;
-        const double tau = a.arrivals[a.leaf_start[seg_leaf(a, q_prev + 1)]];
-        const double *X = a.seg_end + (size_t)q_prev * a.T * B + prev;
-        int64_t src = -1;
-        for (int64_t r = 0; r <= m_end - m_first; ++r) {
-            const int64_t v = r == 0 ? b : m_first + r - 1;
-            const double *Y = a.chunk_start + (size_t)j * a.T * B + v;
-            if (states_equivalent(a, b, [&](uint32_t s) { return X[s * B]; },
-                                  [&](uint32_t s) { return Y[s * B]; }, tau,
-                                  [&](int w) -> uint8_t & { return stale[w]; })) {
-                src = v;
-                break;
-            }
-        }
-        if (src == b) {
-            if (a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair of this chunk goes on
+        const int32_t q0 = j * a.seg_per_chunk;
+        const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
+        const int32_t e = a.seg_src[(size_t)(q0 - 1) * B + b];     // whose end of chunk j-1 counts
+        const int32_t s0 = a.seg_src[(size_t)q0 * B + b];          // whose start of chunk j
+        const uint32_t mask = a.compat[(size_t)j * B + (e < 0 ? b : e)];
+        const uint32_t bit = s0 < 0 ? 0u : (uint32_t)(s0 - m_first + 1);
+        if (bit < 16 && ((mask >> bit) & 1u)) {
+            if (s0 < 0 && a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair goes on
                 const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
                 a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
             }
-        } else if (src < 0) {
+        } else if (mask >> 1) {
+            const int32_t v = (int32_t)m_first + (__ffs((int)(mask >> 1)) - 1);
+            for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * B + b] = v;
+            a.repair_from[(size_t)j * B + b] = -1;
+        } else {
+            const double *X = a.seg_end + (size_t)(q0 - 1) * a.T * B + (e < 0 ? b : e);
             double *Y = a.chunk_start + (size_t)j * a.T * B + b;
             for (int s = 0; s < a.T; ++s) Y[s * B] = X[s * B];
             a.repair_from[(size_t)j * B + b] = -1;         // the whole chunk is redone
+            a.seg_src[(size_t)q0 * B + b] = -1;
             const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
             a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
             ++redone;
-            src = b;
         }
-        a.chunk_src[(size_t)j * B + b] = src == b ? -1 : (int32_t)src;
-        prev = src;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
 }
@@ -260,17 +292,19 @@ sim_repair_kernel(const KernelArgs a)
     Pipe p;
     init_pipe(a, p);
     const int32_t first = a.leaf_start[seg_leaf(a, q_begin)];
+    int64_t m_end;
+    const int64_t m_first = mirrors_of(a, b, m_end);
     a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy>(
         a, ln, p, counters, n_counters, b, j, first, true, true, old_state, stale_buf, q_begin,
-        a.repair_cap);
+        a.repair_cap, ~0ull, m_first, m_end);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
-// One thread per scored candidate: walks the chunk boundaries in order, takes
-// each chunk from the run (own or mirror's) that continues the chunk before
-// it, and repairs in place, in the candidate's own arrays, what neither
-// continues.  After it, every chunk that counts was simulated from a state
-// equivalent to the true one.
+// One thread per scored candidate: walks the chunk boundaries in order.  A
+// chunk keeps the run selected for it when that one continues the chunk
+// before it, else takes the first mirror's run that does, else is repaired in
+// place in the candidate's own array.  After it, every segment that counts
+// was simulated from a state equivalent to the true one.
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __global__ void __launch_bounds__(kLanes, 1)
 sim_chain_kernel(const KernelArgs a)
@@ -290,51 +324,49 @@ sim_chain_kernel(const KernelArgs a)
     Pipe p;
     init_pipe(a, p);
     int32_t redone = 0;
-    int64_t prev = b;                                 // whose run of chunk j-1 counts
     for (int32_t j = 1; j < a.K; ++j) {
-        const int32_t q_prev = j * a.seg_per_chunk - 1;
-        const int64_t first = a.leaf_start[seg_leaf(a, q_prev + 1)];
+        const int32_t q0 = j * a.seg_per_chunk;
+        const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
+        const int64_t first = a.leaf_start[seg_leaf(a, q0)];
         const double tau = a.arrivals[first];
-        for (int t = 0; t < a.T; ++t) {
-            SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)q_prev * a.T + t) * a.B + prev];
-            SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + b];
-        }
-        auto continues = [&]() {
+        const int32_t e = a.seg_src[(size_t)(q0 - 1) * a.B + b];
+        const int32_t s0 = a.seg_src[(size_t)q0 * a.B + b];
+        for (int t = 0; t < a.T; ++t)
+            SM_F64(ln.clk + t * kLanes) =
+                a.seg_end[((size_t)(q0 - 1) * a.T + t) * a.B + (e < 0 ? b : e)];
+        auto continues = [&](int64_t v) {
+            for (int t = 0; t < a.T; ++t)
+                SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + v];
             return states_equivalent(
                 a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
                 [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
                 [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
         };
-        int32_t q_begin = j * a.seg_per_chunk;
+        int32_t q_begin = q0;
         int32_t begin = (int32_t)first;
-        a.chunk_src[(size_t)j * a.B + b] = -1;
-        prev = b;
-        if (continues()) {
+        if (continues(s0 < 0 ? b : s0)) {
             // the chunk continues its predecessor; finish a repair a round left capped
-            q_begin = a.repair_from[(size_t)j * a.B + b];
+            q_begin = s0 < 0 ? a.repair_from[(size_t)j * a.B + b] : -1;
             if (q_begin < 0) continue;
             begin = a.leaf_start[seg_leaf(a, q_begin)];
             for (int t = 0; t < a.T; ++t)
                 SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)(q_begin - 1) * a.T + t) * a.B + b];
         } else {
-            bool found = false;
-            for (int64_t m = m_first; m < m_end && !found; ++m) {
-                for (int t = 0; t < a.T; ++t)
-                    SM_F64(old_state + t * kLanes) = a.chunk_start[((size_t)j * a.T + t) * a.B + m];
-                if (continues()) {
-                    a.chunk_src[(size_t)j * a.B + b] = (int32_t)m;
-                    prev = m;
-                    found = true;
-                }
+            int64_t found = -1;
+            for (int64_t m = m_first; m < m_end && found < 0; ++m)
+                if (m != s0 && continues(m)) found = m;
+            if (found >= 0) {
+                for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * a.B + b] = (int32_t)found;
+                continue;
             }
-            if (found) continue;
             for (int t = 0; t < a.T; ++t)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
         }
         ++redone;
         for (int c = 0; c < n_counters; ++c) SM_U32(counters + c * kLanes) = 0;
         run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, begin, true,
-                                              true, old_state, stale_buf, q_begin, 0);
+                                              true, old_state, stale_buf, q_begin, 0, ~0ull,
+                                              m_first, m_end);
         a.repair_from[(size_t)j * a.B + b] = -1;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
@@ -354,11 +386,9 @@ __global__ void sum_counters_kernel(const KernelArgs a, int32_t n_counters,
     const int32_t M = a.M, G = a.G;
     uint32_t v = 0;
     if (a.num_leaves > 0) {
-        for (int32_t j = 0, q = 0; q < a.NS; ++j) {
-            const int32_t src = a.chunk_src[(size_t)j * a.B + b];
-            const int64_t from = src >= 0 ? src : b;
-            const int32_t q_end = q + a.seg_per_chunk < a.NS ? q + a.seg_per_chunk : a.NS;
-            for (; q < q_end; ++q) v += a.seg_counters[((size_t)q * n_counters + c) * a.B + from];
+        for (int32_t q = 0; q < a.NS; ++q) {
+            const int32_t src = a.seg_src[(size_t)q * a.B + b];
+            v += a.seg_counters[((size_t)q * n_counters + c) * a.B + (src >= 0 ? src : b)];
         }
     }
     if (c < M) {
@@ -374,6 +404,7 @@ __global__ void sum_counters_kernel(const KernelArgs a, int32_t n_counters,
 // Combines the leaf sums in numpy's pairing order and totals the good
 // requests (controller.py:401-402 consumes both).  One thread per scored
 // candidate; leaf sums are fetched eight at a time so that the loads overlap.
+// With seg_src == nullptr every leaf sum is the candidate's own.
 __global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
                                 const int32_t *model_num_good, int64_t *good_total,
                                 double *latency_sum)
@@ -383,7 +414,7 @@ __global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
     const int32_t num_leaves = a.num_leaves;
     double stack[kMaxSumDepth];
     int sp = 0;
-    int32_t j = -1, chunk_end = 0;       // leaves [.., chunk_end) belong to chunk j
+    int32_t q = -1, seg_stop = 0;        // leaves [.., seg_stop) belong to segment q
     int64_t from = b;
     for (int32_t base = 0; base < num_leaves; base += 8) {
         double v[8];
@@ -391,12 +422,12 @@ __global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int32_t leaf = base + u < num_leaves ? base + u : num_leaves - 1;
-            while (leaf >= chunk_end) {
-                if (!a.chunk_src) { chunk_end = num_leaves; break; }   // one run per candidate
-                ++j;
-                const int32_t src = a.chunk_src[(size_t)j * a.B + b];
+            while (leaf >= seg_stop) {
+                if (!a.seg_src) { seg_stop = num_leaves; break; }
+                ++q;
+                const int32_t src = a.seg_src[(size_t)q * a.B + b];
                 from = src >= 0 ? src : b;
-                chunk_end = seg_leaf(a, (j + 1) * a.seg_per_chunk);
+                seg_stop = seg_leaf(a, q + 1);
             }
             v[u] = a.leaf_sums[(size_t)leaf * a.B + from];
             mg[u] = leaf_merges[leaf];

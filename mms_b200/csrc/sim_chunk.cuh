@@ -48,8 +48,12 @@ struct KernelArgs {
     uint32_t *work_count;         // [rounds]
     uint32_t *work_items;         // [B * K]: chunk * B + candidate; bit 31 = continue a repair
     int32_t *repair_from;         // [K][B]: segment a capped repair of chunk j stopped at, or -1
-    int32_t *chunk_src;           // [K][B]: whose run of chunk j counts for candidate b (its own
-                                  //         or a mirror's); -1 = its own
+    int32_t *seg_src;             // [NS][B]: whose run of segment q counts for candidate b (its
+                                  //          own or one of its mirrors'); -1 = its own
+    uint16_t *compat;             // [K][B]: for run u of chunk j-1, the runs of chunk j whose
+                                  //         start continues u's end (bit 0: the candidate's own
+                                  //         array, bit 1 + i: its i-th mirror)
+    int32_t *seg_first_leaf;      // [NS + 1]: first leaf of each segment
     int32_t repair_cap;           // segments a repair may run per round
     int32_t round;
     // outputs
@@ -76,7 +80,7 @@ __device__ inline int32_t seg_leaf(const KernelArgs &a, int32_t q)
 {
     if (q <= 0) return 0;
     if (q >= a.NS) return a.num_leaves;
-    return leaf_lower_bound(a.leaf_start, a.num_leaves, (int64_t)q * a.seg_len);
+    return a.seg_first_leaf[q];
 }
 
 // The mirrors of scored candidate b are candidates [first, end): returns
@@ -174,9 +178,11 @@ __device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, in
 //   speculative (repair == false): the clock vector after the run-in is
 //       stored as the chunk's start state, and every segment's end state.
 //   repair: the lane's clocks already hold the true state at `first`.  After
-//       each segment the new state is compared with the one stored by the
-//       previous run of that segment; once they are equivalent the rest of
-//       the chunk is known to be right already and the lane stops.  A repair
+//       each segment the new state is compared with the states stored runs
+//       had at that point (the run selected for the segment so far, and the
+//       mirrors [m_first, m_end) of the candidate); once it is equivalent to
+//       one, the rest of the chunk is taken from that run (seg_src) and the
+//       lane stops.  The segments a repair runs become the candidate's own.  A repair
 //       may start at a later segment q_begin of the chunk (its clocks then
 //       hold the state after segment q_begin - 1) and may be capped at `cap`
 //       segments (0 = no cap).
@@ -187,7 +193,8 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
                                     int n_counters, int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
                                     uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0,
-                                    uint64_t swap_pairs = ~0ull)
+                                    uint64_t swap_pairs = ~0ull, int64_t m_first = 0,
+                                    int64_t m_end = 0)
 {
     double *fin_out = kFull ? a.finish + (size_t)b * a.N : nullptr;
     uint8_t *good_out = kFull ? a.good + (size_t)b * a.N : nullptr;
@@ -255,20 +262,39 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
             if (leaf + 1 == seg_stop) {             // segment q is complete
                 ++done;
                 flush_counters(a, counters, n_counters, q, b);
+                // A repair stops when its state is equivalent to the state some
+                // stored run had at this point: the run currently selected for
+                // this segment, or a mirror's.  The rest of the chunk is then
+                // taken from that run.
                 bool settled = false;
-                if (repair && snapshots) {
-                    const double tau = a.arrivals[span_end < a.N ? span_end : a.N - 1];
-                    for (int t = 0; t < a.T; ++t)
-                        SM_F64(old_state + t * kLanes) = a.seg_end[((size_t)q * a.T + t) * a.B + b];
-                    settled = span_end < a.N && states_equivalent(
-                        a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
-                        [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
-                        [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
+                int64_t settle_src = -1;
+                if (repair && snapshots && span_end < a.N) {
+                    const double tau = a.arrivals[span_end];
+                    const int32_t cur = a.seg_src[(size_t)q * a.B + b];
+                    for (int64_t r = 0; r <= m_end - m_first && !settled; ++r) {
+                        const int64_t v = r == 0 ? (cur < 0 ? b : cur) : m_first + r - 1;
+                        if (r > 0 && v == cur) continue;
+                        for (int t = 0; t < a.T; ++t)
+                            SM_F64(old_state + t * kLanes) =
+                                a.seg_end[((size_t)q * a.T + t) * a.B + v];
+                        settled = states_equivalent(
+                            a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
+                            [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
+                            [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
+                        if (settled && r > 0) settle_src = v;
+                    }
                 }
-                if (settled) return -1;
-                if (snapshots)
+                if (snapshots) {
                     for (int t = 0; t < a.T; ++t)
                         a.seg_end[((size_t)q * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
+                    if (repair) a.seg_src[(size_t)q * a.B + b] = -1;
+                }
+                if (settled) {
+                    if (settle_src >= 0)
+                        for (int32_t r = q + 1; r < q1; ++r)
+                            a.seg_src[(size_t)r * a.B + b] = (int32_t)settle_src;
+                    return -1;
+                }
                 if (++q >= q1) return -1;
                 if (cap > 0 && done >= cap) return q;
                 seg_stop = seg_leaf(a, q + 1);

@@ -38,7 +38,7 @@ extern "C" {
 #define MMS_MAX_SLOTS 256         /* sum of pipeline stages over a candidate     */
 #define MMS_MAX_PLACED 65535      /* (group, model) pairs per candidate          */
 #define MMS_MAX_STAGES 255        /* stages of one group                         */
-#define MMS_MAX_COLUMNS 255       /* columns of the latency table                */
+#define MMS_MAX_COLUMNS 254       /* columns of the latency table                */
 
 /* status[b] bits */
 #define MMS_STATUS_OK 0u

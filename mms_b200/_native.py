@@ -21,7 +21,7 @@ MAX_GROUPS = 255
 MAX_SLOTS = 256
 MAX_PLACED = 65535
 MAX_STAGES = 255
-MAX_COLUMNS = 255
+MAX_COLUMNS = 254
 
 STATUS_HEAP_OVERFLOW = 1
 STATUS_QUEUE_LEFT = 2

@@ -39,7 +39,8 @@ static int32_t plan_leaves(int64_t n)
 }
 
 struct Geometry {
-    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap;
+    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap,
+        block_warps;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
         off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
@@ -80,9 +81,19 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         (void)cudaGetLastError();
         sm_count = 148;
     }
-    int64_t per_sm = (int64_t)(233472 / (L0.total + 1024));
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 32) per_sm = 32;
+    // Warps per block: blocks share the latency table among their warps, so the
+    // size that fits the most warps on an SM (233472 bytes, 1024 reserved per
+    // block; 232448 at most in one block) wins, the smaller one on a tie.
+    int64_t per_sm = 1;
+    int block_warps = 1;
+    for (int w = 1; w <= kMaxBlockWarps; ++w) {
+        const size_t bytes = L0.warp0 + (size_t)w * L0.warp_bytes;
+        if (bytes > 232448) break;
+        int64_t warps = (int64_t)(233472 / (bytes + 1024)) * w;
+        if (warps > kMaxWarpsPerSm) warps = kMaxWarpsPerSm;
+        if (warps > per_sm) { per_sm = warps; block_warps = w; }
+    }
+    g->block_warps = block_warps;
     const int64_t resident_slots = (int64_t)sm_count * per_sm;
     int64_t chunk = opts ? opts->chunk_requests : 0;
     int64_t warm = opts ? opts->warmup_requests : 0;
@@ -95,12 +106,13 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     } else if (chunk > 0) {
         spc = (chunk + seg / 2) / seg;
     } else {
-        // Chunks are the units of parallel work: as many as fill just under two
-        // waves of the resident blocks (slots = SMs x blocks per SM at this
-        // kernel's shared-memory use), but never chunks shorter than 4
-        // segments.  More chunks mean more boundaries to validate and repair.
+        // Chunks are the units of parallel work: as many as fill nine tenths
+        // of ONE wave of the resident warps (SMs x warps per SM at this
+        // kernel's shared-memory use; a second wave would pay the run-in
+        // twice), but never chunks shorter than 4 segments.  More chunks mean
+        // more boundaries to validate and repair.
         int64_t Kmax = NS / 4 > 0 ? NS / 4 : 1;
-        int64_t K = B > 0 ? (19 * resident_slots * kLanes) / (10 * B) : 1;
+        int64_t K = B > 0 ? (9 * resident_slots * kLanes) / (10 * B) : 1;
         if (K > Kmax) K = Kmax;
         if (K < 1) K = 1;
         spc = (NS + K - 1) / K;
@@ -127,13 +139,14 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     const SmemLayout L = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
                                      c->max_stages, group_good, g->lat_smem_elems);
     g->n_counters = L.n_counters;
-    g->smem_stream = L.total;
+    g->smem_stream = L.warp0 + (size_t)g->block_warps * L.warp_bytes;
     g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
     g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
 
     size_t off = 0;
-    g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)B * c->num_models + 256);
+    g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
+                                               (c->num_models + 1) + 256);
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
     g->off_counters = off;    off += align256(sizeof(uint32_t) * (size_t)NS * L.n_counters * B);
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
@@ -153,7 +166,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 {
     seg_leaf_kernel<<<(unsigned)((ka.NS + 128) / 128), 128, 0, st>>>(ka);
     MMS_CUDA(cudaGetLastError());
-    const int64_t cells = (int64_t)ka.B * ka.M;
+    const int64_t cells = (int64_t)ka.B * (ka.M + 1);
     if (cells > 0) {
         build_rows_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka);
         MMS_CUDA(cudaGetLastError());
@@ -161,8 +174,10 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
     auto stream_k = sim_stream_kernel<kFull, kGroupGood, kLegacy>;
     MMS_CUDA(cudaFuncSetAttribute(stream_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)g.smem_stream));
+    const int64_t per_block = (int64_t)kLanes * g.block_warps;
     const int64_t streams = (int64_t)ka.B * ka.K;
-    stream_k<<<(unsigned)((streams + kLanes - 1) / kLanes), kLanes, g.smem_stream, st>>>(ka);
+    stream_k<<<(unsigned)((streams + per_block - 1) / per_block), (unsigned)per_block,
+               g.smem_stream, st>>>(ka);
     MMS_CUDA(cudaGetLastError());
     if (ka.K > 1) {
         auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy>;
@@ -281,7 +296,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.model_off = cands->model_off; ka.model_rep = cands->model_rep;
     ka.group_info = cands->group_info; ka.latency = cands->latency;
     ka.latency_stride = cands->latency_stride;
-    ka.lat_smem_elems = g.lat_smem_elems;
+    ka.lat_smem_elems = g.lat_smem_elems; ka.block_warps = g.block_warps;
     ka.K = g.K; ka.NS = g.NS; ka.seg_len = g.seg_len; ka.seg_per_chunk = g.seg_per_chunk;
     ka.warmup = g.warmup;
     ka.num_leaves = plan->num_leaves; ka.leaf_start = plan->leaf_start;

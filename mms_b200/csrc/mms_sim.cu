@@ -51,78 +51,81 @@ constexpr int kMaxRepairRounds = 16;
 constexpr int kDefaultRepairRounds = 3;
 constexpr int kDefaultRepairSegments = -1;   // no cap: measured best on the benchmark shape
 
-// One thread per (candidate, model): checks the model's replica list and
-// writes its 32-byte row (see Lane::rows).  A list with a bad index is
-// reported in the status word and emptied.
+// One thread per (candidate, model or the extra empty row): checks the model's
+// replica list and writes its 16-byte row (see Lane::rows).  A list with a bad
+// index is reported in the status word and emptied.
 __global__ void build_rows_kernel(const KernelArgs a)
 {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (int64_t)a.B * a.M) return;
-    const int64_t b = t / a.M;
-    const int m = (int)(t % a.M);
-    uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
-    uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
-    bool bad = lo > hi || hi > (uint32_t)a.P;
-    uint32_t e[4] = {1u << 16, 1u << 16, 1u << 16, 1u << 16};   // group 0, slot 0, one stage
-    if (!bad) {
-        for (uint32_t r = lo; r < hi; ++r) {
-            const uint32_t ent = a.model_rep[(size_t)b * a.P + r];
-            const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
-            if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
-                ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
-                bad = true;
-            else if (r - lo < 4)
-                e[r - lo] = rep_to_last(ent);
+    if (t >= (int64_t)a.B * (a.M + 1)) return;
+    const int64_t b = t / (a.M + 1);
+    const int m = (int)(t % (a.M + 1));
+    uint32_t e[4] = {kNoReplica, kNoReplica, kNoReplica, kNoReplica};
+    if (m < a.M) {
+        const uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
+        const uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
+        bool bad = lo > hi || hi > (uint32_t)a.P;
+        if (!bad) {
+            for (uint32_t r = lo; r < hi; ++r) {
+                const uint32_t ent = a.model_rep[(size_t)b * a.P + r];
+                const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
+                if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
+                    ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
+                    bad = true;
+                else if (r - lo < 4)
+                    e[r - lo] = rep_to_last(ent);
+            }
+            if (hi - lo > 4) e[3] = kMoreReplicas;
+        }
+        if (bad) {
+            atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
+            for (int k = 0; k < 4; ++k) e[k] = kNoReplica;
         }
     }
-    if (bad) {
-        atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
-        lo = hi = 0;
-        for (int k = 0; k < 4; ++k) e[k] = 1u << 16;
-    }
-    uint4 *row = reinterpret_cast<uint4 *>(a.rep_rows) + (size_t)t * 2;
-    row[0] = make_uint4(e[0], e[1], e[2], e[3]);
-    row[1] = make_uint4(hi - lo, lo, 0u, 0u);
+    reinterpret_cast<uint4 *>(a.rep_rows)[row_index(a, b, m)] = make_uint4(e[0], e[1], e[2], e[3]);
 }
 
 // This lane's view of candidate b: offsets of its shared-memory state (clocks
 // and counters zeroed) and pointers to its tables in global memory.
 template <bool kGroupGood>
 __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint32_t &counters,
-                                  int &n_counters)
+                                  int &n_counters, int warp = 0)
 {
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
+    const size_t base = L.warp0 + (size_t)warp * L.warp_bytes;
     Lane ln;
-    ln.clk = (uint32_t)(L.clocks / sizeof(double)) + lane;
-    ln.tmp = (uint32_t)(L.stage_tmp / sizeof(double)) + lane;
+    ln.clk = (uint32_t)((base + L.clocks) / sizeof(double)) + lane;
+    ln.tmp = (uint32_t)((base + L.stage_tmp) / sizeof(double)) + lane;
     ln.lat_sm = (uint32_t)(L.latency / sizeof(float));
-    counters = (uint32_t)(L.counters / sizeof(uint32_t)) + lane;
+    counters = (uint32_t)((base + L.counters) / sizeof(uint16_t)) + lane;
     n_counters = L.n_counters;
     ln.model_good = counters;
     ln.group_req = counters + (uint32_t)a.M * kLanes;
     ln.group_good = counters + (uint32_t)(a.M + a.G) * kLanes;
-    ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + (size_t)b * a.M * 2;
+    ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + row_index(a, b, 0);
     ln.rep_raw = a.model_rep + (size_t)b * a.P;
+    ln.rep_off = a.model_off + (size_t)b * (a.M + 1);
     ln.lat_gl = a.latency + (size_t)b * a.latency_stride;
     ln.lat_on_chip = a.lat_smem_elems != 0;
     ln.M = a.M; ln.C = a.C; ln.S = a.S;
     ln.status = 0;
     for (int t = 0; t < a.T + kClockPad; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
-    for (int c = 0; c < n_counters; ++c) SM_U32(counters + c * kLanes) = 0;
+    for (int c = 0; c < n_counters; ++c) SM_U16(counters + c * kLanes) = 0;
     return ln;
 }
 
 // The batch's shared latency table goes on chip (f32; widened to f64, exactly,
-// when it is used).
-__device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout &L, int lane)
+// when it is used), loaded by all threads of the block: call it before any
+// thread returns.
+__device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout &L)
 {
     if (a.lat_smem_elems) {
         const uint32_t base = (uint32_t)(L.latency / sizeof(float));
         const int real = a.M * a.C * a.S;
-        for (int i = lane; i < a.lat_smem_elems; i += kLanes)
+        for (int i = threadIdx.x; i < a.lat_smem_elems; i += blockDim.x)
             SM_F32(base + i) = i < real ? __ldg(a.latency + i) : 0.0f;
     }
-    __syncwarp();
+    __syncthreads();
 }
 
 __device__ inline void init_pipe(const KernelArgs &a, Pipe &p)
@@ -140,15 +143,16 @@ __device__ inline void repair_scratch(const KernelArgs &a, const SmemLayout &L, 
     stale_buf = (uint32_t)(L.total + sizeof(double) * (size_t)a.T * kLanes) + lane;
 }
 
+// Blocks of block_warps warps (they share the latency table and nothing else).
 template <bool kFull, bool kGroupGood, bool kLegacy>
-__global__ void __launch_bounds__(kLanes, 1)
+__global__ void __launch_bounds__(kLanes * kMaxBlockWarps, 1)
 sim_stream_kernel(const KernelArgs a)
 {
-    const int lane = threadIdx.x;
-    stage_latency_table(a, smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems),
-                        lane);
+    const int lane = threadIdx.x & (kLanes - 1);
+    const int warp = threadIdx.x / kLanes;
+    stage_latency_table(a, smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems));
     const bool chunked = can_chunk(a);
-    const int64_t stream = (int64_t)blockIdx.x * kLanes + lane;
+    const int64_t stream = ((int64_t)blockIdx.x * a.block_warps + warp) * kLanes + lane;
     if (stream >= (int64_t)a.B * a.K) return;   // lanes never wait for each other below
     const int32_t j = (int32_t)(stream / a.B);
     const int64_t b = stream % a.B;
@@ -161,7 +165,7 @@ sim_stream_kernel(const KernelArgs a)
                               : ~0ull;
 
     uint32_t counters; int n_counters;
-    Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
+    Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters, warp);
     Pipe p;
     init_pipe(a, p);
     // not chunked: one chunk holding every segment, plain sequential simulation
@@ -271,7 +275,7 @@ sim_repair_kernel(const KernelArgs a)
     const uint32_t count = a.work_count[a.round];
     if ((uint64_t)blockIdx.x * kLanes >= count) return;
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
-    stage_latency_table(a, L, lane);
+    stage_latency_table(a, L);
     const uint32_t w = blockIdx.x * kLanes + lane;
     if (w >= count) return;
     const uint32_t item = a.work_items[w] & 0x7FFFFFFFu;
@@ -311,7 +315,7 @@ sim_chain_kernel(const KernelArgs a)
 {
     const int lane = threadIdx.x;
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
-    stage_latency_table(a, L, lane);
+    stage_latency_table(a, L);
     const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
     if (b >= a.Bs || !can_chunk(a) || a.N == 0) return;
     int64_t m_end;
@@ -363,7 +367,7 @@ sim_chain_kernel(const KernelArgs a)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
         }
         ++redone;
-        for (int c = 0; c < n_counters; ++c) SM_U32(counters + c * kLanes) = 0;
+        for (int c = 0; c < n_counters; ++c) SM_U16(counters + c * kLanes) = 0;
         run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, begin, true,
                                               true, old_state, stale_buf, q_begin, 0, ~0ull,
                                               m_first, m_end);

@@ -30,6 +30,7 @@ struct KernelArgs {
     const float *latency;
     int64_t latency_stride;
     int32_t lat_smem_elems;
+    int32_t block_warps;          // warps per block of the stream kernel
     // geometry
     int32_t K;                    // chunks
     int32_t NS;                   // segments
@@ -40,7 +41,8 @@ struct KernelArgs {
     int32_t num_leaves;
     const int32_t *leaf_start;
     // scratch
-    uint32_t *rep_rows;           // [B][M][8]: replica rows built from model_off/model_rep
+    uint32_t *rep_rows;           // [ceil(B/32)][M + 1][32][4]: replica rows built from
+                                  //   model_off/model_rep, see row_index()
     double *leaf_sums;            // [num_leaves][B]
     double *seg_end;              // [NS][T][B]   clock vector after each segment
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from
@@ -81,6 +83,13 @@ __device__ inline int32_t seg_leaf(const KernelArgs &a, int32_t q)
     if (q <= 0) return 0;
     if (q >= a.NS) return a.num_leaves;
     return a.seg_first_leaf[q];
+}
+
+// Where the replica row of (candidate b, model m) is, in 16-byte units: the
+// rows of 32 consecutive candidates for one model are contiguous.
+__device__ inline size_t row_index(const KernelArgs &a, int64_t b, int m)
+{
+    return ((size_t)(b / kLanes) * (a.M + 1) + m) * kLanes + (size_t)(b % kLanes);
 }
 
 // The mirrors of scored candidate b are candidates [first, end): returns
@@ -163,8 +172,8 @@ __device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, in
                                       int32_t q, int64_t b)
 {
     for (int c = 0; c < n_counters; ++c) {
-        a.seg_counters[((size_t)q * n_counters + c) * a.B + b] = SM_U32(counters + c * kLanes);
-        SM_U32(counters + c * kLanes) = 0;
+        a.seg_counters[((size_t)q * n_counters + c) * a.B + b] = SM_U16(counters + c * kLanes);
+        SM_U16(counters + c * kLanes) = 0;
     }
 }
 

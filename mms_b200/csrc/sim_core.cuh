@@ -5,8 +5,8 @@
 // sim_step below).  Mutable state (stage clocks, counters) lives in shared
 // memory as [entry][lane], so lane-private accesses fall on distinct banks;
 // shared memory is what limits the number of resident warps, so the
-// read-only replica lists stay in global memory (one 32-byte row per model,
-// fetched a whole request ahead, served by L1/L2).  Everything is addressed by
+// read-only replica lists stay in global memory (one 16-byte row per model,
+// fetched two requests ahead, served by L2).  Everything is addressed by
 // 32-bit element offsets into the block's one dynamic shared array, which
 // keeps the accesses plain LDS/STS with immediate offsets.  The dependent
 // chain per request is kept short: trace values are fetched two requests
@@ -24,9 +24,11 @@ namespace mms {
 
 constexpr double kInf = 1e100;          // alpa_serve/util.py:23
 constexpr double kOverhead = 0.011;     // controller.py:575
-constexpr int kLanes = 32;              // streams per block (one warp)
+constexpr int kLanes = 32;              // streams per warp
+constexpr int kMaxBlockWarps = 10;      // warps of a stream-kernel block
+constexpr int kMaxWarpsPerSm = 12;      // the stream kernel's registers allow that many
 constexpr int kClockPad = 8;            // readable slots past the last clock
-constexpr int kRowWords = 8;            // u32 words of a model's replica row
+constexpr int kRowWords = 4;            // u32 words of a model's replica row
 
 extern __shared__ __align__(16) unsigned char smem[];
 
@@ -42,25 +44,34 @@ __device__ __forceinline__ uint32_t rep_last(uint32_t e) { return (e >> 8) & 0xF
 __device__ __forceinline__ uint32_t rep_stages(uint32_t e) { return (e >> 16) & 0xFFu; }
 __device__ __forceinline__ uint32_t rep_column(uint32_t e) { return e >> 24; }
 
+// Shared memory of a block: the latency table shared by all its warps, then
+// one region per warp with that warp's 32 lane-private states.
 struct SmemLayout {
-    size_t clocks, stage_tmp, latency, counters, total;
+    size_t latency;                      // from the start of the array
+    size_t warp0, warp_bytes;            // first warp's region; size of a region
+    size_t clocks, stage_tmp, counters;  // inside a warp's region
+    size_t total;                        // bytes of a one-warp block
     int n_counters, tmp_stages;
 };
 
 // lat_elems: entries of the shared f32 latency table kept on chip (0 = read
-// it from global memory).
+// it from global memory).  Counters are 16 bits wide: they are flushed to
+// global memory after every segment, and a segment has fewer than 2048
+// requests.
 __host__ __device__ inline SmemLayout smem_layout(int M, int G, int /*P*/, int T, int S,
                                                   bool group_good, int lat_elems)
 {
     SmemLayout L;
+    L.latency = 0;
+    L.warp0 = (sizeof(float) * (size_t)((lat_elems + 3) & ~3) + 15) & ~(size_t)15;
     size_t off = 0;
     L.clocks = off;     off += sizeof(double) * (size_t)(T + kClockPad) * kLanes;
     L.tmp_stages = S > 8 ? S - 8 : 0;
     L.stage_tmp = off;  off += sizeof(double) * (size_t)L.tmp_stages * kLanes;
-    L.latency = off;    off += sizeof(float) * (size_t)((lat_elems + 3) & ~3);
     L.n_counters = M + G + (group_good ? G : 0);
-    L.counters = off;   off += sizeof(uint32_t) * (size_t)L.n_counters * kLanes;
-    L.total = (off + 15) & ~(size_t)15;
+    L.counters = off;   off += sizeof(uint16_t) * (size_t)L.n_counters * kLanes;
+    L.warp_bytes = (off + 15) & ~(size_t)15;
+    L.total = L.warp0 + L.warp_bytes;
     return L;
 }
 
@@ -70,27 +81,37 @@ struct Lane {
     uint32_t clk;             // f64 index of clock slot 0
     uint32_t tmp;             // f64 index, stages beyond the 8th of a deep pipeline
     uint32_t lat_sm;          // f32 index of the on-chip latency table
-    uint32_t model_good;      // u32 index, [M]
-    uint32_t group_req;       // u32 index, [G]
-    uint32_t group_good;      // u32 index, [G]
-    const uint4 *rows;        // [M][2] replica rows of this candidate (global memory):
-                              //   words 0-3 the first four replicas, word 4 their number,
-                              //   word 5 the model's offset into the caller's model_rep
+    uint32_t model_good;      // u16 index, [M]
+    uint32_t group_req;       // u16 index, [G]
+    uint32_t group_good;      // u16 index, [G]
+    const uint4 *rows;        // [M + 1] replica rows of this candidate (global memory,
+                              //   kLanes apart: the rows of 32 consecutive candidates for one
+                              //   model are contiguous, so a warp fetches them coalesced): the
+                              //   model's first four replicas, kNoReplica where it has fewer;
+                              //   a model with more than four has kMoreReplicas in word 3
+                              //   (the full list is then read from the caller's tables);
+                              //   row M is empty (unknown models)
     const uint32_t *rep_raw;  // the caller's model_rep row of this candidate
+    const uint16_t *rep_off;  // the caller's model_off row of this candidate
     const float *lat_gl;      // this candidate's table in global memory
     bool lat_on_chip;
     int32_t M, C, S;
     uint32_t status;
 };
 
-// Requests in flight.  Request i is ready to execute (its replica row is in
-// registers).  While it executes, the row of request i+1 is loaded (an L1
-// hit: it was prefetched into L1 one step earlier), the row of request i+2
-// is prefetched into L1 and the trace values of request i+3 are fetched.
-// Nothing fetched ahead depends on simulator state.
+// Row words that are not replicas.  Both address clock slot 0 / one stage /
+// latency column 0, so that the branch-free step can load through them.
+constexpr uint32_t kNoReplica = 0xFF010000u;
+constexpr uint32_t kMoreReplicas = 0xFE010000u;
+
+// Requests in flight.  Request i is ready to execute: its replica row is in
+// registers, and so is the row of request i+1.  While i executes, the row of
+// request i+2 and the trace values of request i+3 are fetched, so every
+// global load has a whole step or more to arrive.  Nothing fetched ahead
+// depends on simulator state.
 struct Pipe {
-    double ts; float slo; int32_t m; uint32_t lo, n, e0, e1, e2, e3;
-    double ts1; float slo1; int32_t m1;
+    double ts; float slo; int32_t m; uint4 r;
+    double ts1; float slo1; int32_t m1; uint4 r1;
     double ts2; float slo2; int32_t m2;
     const double *arrivals; const int32_t *model_ids; const float *slos;
     int32_t last;             // highest readable request index
@@ -102,17 +123,9 @@ __device__ __forceinline__ int32_t clean_model(Lane &ln, int32_t m)
     return m;
 }
 
-__device__ __forceinline__ void fetch_row(const Lane &ln, int32_t m, uint4 &x, uint4 &y)
+__device__ __forceinline__ uint4 fetch_row(const Lane &ln, int32_t m)
 {
-    const uint32_t mm = m < 0 ? 0u : (uint32_t)m;
-    x = __ldg(ln.rows + 2 * mm);
-    y = __ldg(ln.rows + 2 * mm + 1);
-}
-
-__device__ __forceinline__ void prefetch_row(const Lane &ln, int32_t m)
-{
-    const uint32_t mm = m < 0 ? 0u : (uint32_t)m;
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(ln.rows + 2 * mm));
+    return __ldg(ln.rows + (m < 0 ? ln.M : m) * kLanes);
 }
 
 // Fills the pipe so that request `i` is ready to execute.
@@ -127,11 +140,8 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
     p.m1 = clean_model(ln, __ldg(p.model_ids + i1));
     p.ts2 = __ldg(p.arrivals + i2); p.slo2 = __ldg(p.slos + i2);
     p.m2 = clean_model(ln, __ldg(p.model_ids + i2));
-    uint4 x, y;
-    fetch_row(ln, p.m, x, y);
-    p.e0 = x.x; p.e1 = x.y; p.e2 = x.z; p.e3 = x.w;
-    p.n = p.m < 0 ? 0u : y.x; p.lo = y.y;
-    prefetch_row(ln, p.m1);
+    p.r = fetch_row(ln, p.m);
+    p.r1 = fetch_row(ln, p.m1);
 }
 
 // max of two times.  Times are never NaN (arrivals are checked to be finite,
@@ -145,14 +155,15 @@ __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
     return (e & 0xFFFF00FFu) | (((first + ns - 1) & 0xFFu) << 8);
 }
 
-
 // Executes request `i` (controller.py:579-622, or :519-555 with kLegacy) and
 // advances the pipe.  Returns finish - arrival, which is 0.0 for a dropped
 // request (the reference stores finish = arrival for those).
 //   record  update counters and per-request outputs (off during run-in)
-// The step is large; callers keep a single call site per kernel so that the
-// hot loop stays inside the instruction cache.
-
+// The common path has no divergent branch: a lane whose candidate has no
+// replica of the model, or drops the request, runs the same instructions on
+// harmless addresses and its stores are predicated off.  The step is large;
+// callers keep a single call site per kernel so that the hot loop stays
+// inside the instruction cache.
 template <bool kFull, bool kGroupGood, bool kLegacy>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)
@@ -160,132 +171,128 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     const double ts = p.ts;
     const float slo_f = p.slo;
     const int32_t m = p.m;
-    const uint32_t n = p.n, lo = p.lo, e0 = p.e0, e1 = p.e1, e2 = p.e2, e3 = p.e3;
+    const uint32_t e0 = p.r.x, e1 = p.r.y, e2 = p.r.z, e3 = p.r.w;
 
     // ---- state-independent fetches for the requests behind this one -------
-    uint4 x1, y1;
-    fetch_row(ln, p.m1, x1, y1);
-    prefetch_row(ln, p.m2);
+    const uint4 r2 = fetch_row(ln, p.m2);
     const int32_t i3 = i + 3 < p.last ? i + 3 : p.last;
     const double ts3 = __ldg(p.arrivals + i3);
     const float slo3 = __ldg(p.slos + i3);
     const int32_t m3raw = __ldg(p.model_ids + i3);
 
     // ---- :589-598 replica whose last-stage clock is strictly smallest ------
-    double fin = ts;
-    bool ok = false;
-    if (n > 0) {
-        const double c0 = SM_F64(ln.clk + rep_last(e0) * kLanes);
-        const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
-        const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
-        const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
-        double best = kInf;
-        uint32_t pick = 0;
-        bool found = false;
-        if (c0 < best) { best = c0; pick = e0; found = true; }
-        if (n > 1 && c1 < best) { best = c1; pick = e1; found = true; }
-        if (n > 2 && c2 < best) { best = c2; pick = e2; found = true; }
-        if (n > 3 && c3 < best) { best = c3; pick = e3; found = true; }
-        for (uint32_t r = 4; r < n; ++r) {
-            const uint32_t e = rep_to_last(__ldg(ln.rep_raw + lo + r));
+    const double c0 = SM_F64(ln.clk + rep_last(e0) * kLanes);
+    const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
+    const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
+    const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
+    double best = kInf;
+    uint32_t pick = 0x00010000u;          // group 0, slot 0, one stage, column 0
+    if (e0 < kMoreReplicas && c0 < best) { best = c0; pick = e0; }
+    if (e1 < kMoreReplicas && c1 < best) { best = c1; pick = e1; }
+    if (e2 < kMoreReplicas && c2 < best) { best = c2; pick = e2; }
+    if (e3 < kMoreReplicas && c3 < best) { best = c3; pick = e3; }
+    if (e3 == kMoreReplicas) {            // rare: the whole list, from the caller's tables
+        const uint32_t lo = ln.rep_off[m], hi = ln.rep_off[m + 1];
+        best = kInf;
+        pick = 0x00010000u;
+        for (uint32_t r = lo; r < hi; ++r) {
+            const uint32_t e = rep_to_last(__ldg(ln.rep_raw + r));
             const double c = SM_F64(ln.clk + rep_last(e) * kLanes);
-            if (c < best) { best = c; pick = e; found = true; }
+            if (c < best) { best = c; pick = e; }
         }
-        if (found) {
-            const uint32_t g = rep_group(pick);
-            const uint32_t ns = kLegacy ? 1u : rep_stages(pick);
-            const uint32_t ck = ln.clk + (rep_last(pick) + 1 - ns) * kLanes;   // first slot
-            const uint32_t row = ((uint32_t)m * ln.C + rep_column(pick)) * ln.S;
-            double f;
-            double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
-            (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
-            // all stage clocks and latencies are fetched at once; the max/add
-            // chain then runs in registers
-            const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
-                         k3 = SM_F64(ck + 3 * kLanes), k4 = SM_F64(ck + 4 * kLanes),
-                         k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
-                         k7 = SM_F64(ck + 7 * kLanes);
-            double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
-            if (ln.lat_on_chip) {
-                // rows are padded so that 8 entries are always readable
-                const uint32_t lr = ln.lat_sm + row;
-                l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
-                l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
-                l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
-                l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
-            } else {
-                const float *lat = ln.lat_gl + row;
-                const int sm = ln.S - 1;   // clamp reads to the table row
-                l0 = (double)__ldg(lat); l1 = (double)__ldg(lat + (1 < sm ? 1 : sm));
-                if (ns > 2) {
-                    l2 = (double)__ldg(lat + (2 < sm ? 2 : sm));
-                    l3 = (double)__ldg(lat + (3 < sm ? 3 : sm));
-                    l4 = (double)__ldg(lat + (4 < sm ? 4 : sm));
-                    l5 = (double)__ldg(lat + (5 < sm ? 5 : sm));
-                    l6 = (double)__ldg(lat + (6 < sm ? 6 : sm));
-                    l7 = (double)__ldg(lat + (7 < sm ? 7 : sm));
-                }
-            }
-            if (kLegacy) {
-                // :543-544 one clock per group; latency row = {sum, max}
-                const double start = tmax(k0, ts);
-                f = start + l0 + kOverhead;
-                t0 = start + l1;
-            } else {
-                // :605-610, written without branches: stages past the group's
-                // last one are computed and thrown away
-                t0 = tmax(ts, k0) + l0;
-                t1 = tmax(t0, k1) + l1;
-                double t = ns > 1 ? t1 : t0;
-                t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
-                t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
-                t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
-                t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
-                t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
-                t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
-                if (ns > 8) {
-                    for (uint32_t k = 8; k < ns; ++k) {
-                        const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
-                                                         : (double)__ldg(ln.lat_gl + row + k);
-                        t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
-                        SM_F64(ln.tmp + (k - 8) * kLanes) = t;
-                    }
-                }
-                f = t + kOverhead;                               // :610
-            }
-            if (record) SM_U32(ln.group_req + g * kLanes) += 1u;   // :611
-            const bool accept = f - ts <= (double)slo_f;         // :613-619
-            if (accept) {
-                fin = f;
-                ok = true;
-                SM_F64(ck) = t0;
-                if (ns > 1) SM_F64(ck + kLanes) = t1;
-                if (ns > 2) SM_F64(ck + 2 * kLanes) = t2;
-                if (ns > 3) SM_F64(ck + 3 * kLanes) = t3;
-                if (ns > 4) SM_F64(ck + 4 * kLanes) = t4;
-                if (ns > 5) SM_F64(ck + 5 * kLanes) = t5;
-                if (ns > 6) SM_F64(ck + 6 * kLanes) = t6;
-                if (ns > 7) SM_F64(ck + 7 * kLanes) = t7;
-                if (ns > 8)
-                    for (uint32_t k = 8; k < ns; ++k)
-                        SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
-                if (record) {
-                    SM_U32(ln.model_good + (uint32_t)m * kLanes) += 1u;
-                    if (kGroupGood) SM_U32(ln.group_good + g * kLanes) += 1u;
-                }
+    }
+    const bool found = best < kInf;
+
+    const uint32_t g = rep_group(pick);
+    const uint32_t ns = kLegacy ? 1u : rep_stages(pick);
+    const uint32_t ck = ln.clk + (rep_last(pick) + 1 - ns) * kLanes;   // first slot
+    const uint32_t row = ((uint32_t)(m < 0 ? 0 : m) * ln.C + rep_column(pick)) * ln.S;
+    double f;
+    double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
+    (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
+    // all stage clocks and latencies are fetched at once; the max/add chain
+    // then runs in registers
+    const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
+                 k3 = SM_F64(ck + 3 * kLanes), k4 = SM_F64(ck + 4 * kLanes),
+                 k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
+                 k7 = SM_F64(ck + 7 * kLanes);
+    double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
+    if (ln.lat_on_chip) {
+        // rows are padded so that 8 entries are always readable
+        const uint32_t lr = ln.lat_sm + row;
+        l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
+        l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
+        l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
+        l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
+    } else {
+        const float *lat = ln.lat_gl + row;
+        const int sm = ln.S - 1;   // clamp reads to the table row
+        l0 = (double)__ldg(lat); l1 = (double)__ldg(lat + (1 < sm ? 1 : sm));
+        if (ns > 2) {
+            l2 = (double)__ldg(lat + (2 < sm ? 2 : sm));
+            l3 = (double)__ldg(lat + (3 < sm ? 3 : sm));
+            l4 = (double)__ldg(lat + (4 < sm ? 4 : sm));
+            l5 = (double)__ldg(lat + (5 < sm ? 5 : sm));
+            l6 = (double)__ldg(lat + (6 < sm ? 6 : sm));
+            l7 = (double)__ldg(lat + (7 < sm ? 7 : sm));
+        }
+    }
+    if (kLegacy) {
+        // :543-544 one clock per group; latency row = {sum, max}
+        const double start = tmax(k0, ts);
+        f = start + l0 + kOverhead;
+        t0 = start + l1;
+    } else {
+        // :605-610, written without branches: stages past the group's last one
+        // are computed and thrown away
+        t0 = tmax(ts, k0) + l0;
+        t1 = tmax(t0, k1) + l1;
+        double t = ns > 1 ? t1 : t0;
+        t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
+        t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
+        t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
+        t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
+        t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
+        t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
+        if (ns > 8) {
+            for (uint32_t k = 8; k < ns; ++k) {
+                const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
+                                                 : (double)__ldg(ln.lat_gl + row + k);
+                t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
+                SM_F64(ln.tmp + (k - 8) * kLanes) = t;
             }
         }
+        f = t + kOverhead;                               // :610
+    }
+    const bool accept = found && (f - ts <= (double)slo_f);   // :613-619
+    const double fin = accept ? f : ts;
+    if (accept) {
+        SM_F64(ck) = t0;
+        if (ns > 1) SM_F64(ck + kLanes) = t1;
+        if (ns > 2) SM_F64(ck + 2 * kLanes) = t2;
+        if (ns > 3) SM_F64(ck + 3 * kLanes) = t3;
+        if (ns > 4) SM_F64(ck + 4 * kLanes) = t4;
+        if (ns > 5) SM_F64(ck + 5 * kLanes) = t5;
+        if (ns > 6) SM_F64(ck + 6 * kLanes) = t6;
+        if (ns > 7) SM_F64(ck + 7 * kLanes) = t7;
+        if (ns > 8)
+            for (uint32_t k = 8; k < ns; ++k)
+                SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
+    }
+    if (record) {
+        // :611, :617-618; lanes that did not dispatch or accept add 0 to harmless slots
+        SM_U16(ln.group_req + g * kLanes) += found ? 1u : 0u;
+        SM_U16(ln.model_good + (uint32_t)(m < 0 ? 0 : m) * kLanes) += accept ? 1u : 0u;
+        if (kGroupGood) SM_U16(ln.group_good + g * kLanes) += accept ? 1u : 0u;
     }
     if (kFull && record) {
         finish_out[i] = fin;
-        good_out[i] = ok ? 1 : 0;
+        good_out[i] = accept ? 1 : 0;
     }
 
     // ---- advance the pipe ---------------------------------------------------
-    p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1;
-    p.e0 = x1.x; p.e1 = x1.y; p.e2 = x1.z; p.e3 = x1.w;
-    p.n = p.m1 < 0 ? 0u : y1.x; p.lo = y1.y;
-    p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2;
+    p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1; p.r = p.r1;
+    p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2; p.r1 = r2;
     p.ts2 = ts3; p.slo2 = slo3; p.m2 = clean_model(ln, m3raw);
     return fin - ts;
 }

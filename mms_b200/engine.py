@@ -160,8 +160,13 @@ class LatencyTable:
         return self._host
 
     def device(self, dev):
+        """The table on `dev`; uploaded on the current stream when it changed,
+        and any stream that asks for it waits for that upload."""
         if self._device is None or self._device.device != dev:
             self._device = _to_device(self._host, dev)
+            self._ready = torch.cuda.Event()
+            self._ready.record(torch.cuda.current_stream(dev))
+        torch.cuda.current_stream(dev).wait_event(self._ready)
         return self._device
 
 
@@ -297,9 +302,12 @@ def twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model):
         ends = np.cumsum(n_in_group)
         key = (csum[ends] - csum[ends - n_in_group]) * np.uint64(0x9E3779B97F4A7C15) \
             + cfg_col.astype(np.uint64) * np.uint64(0xC2B2AE3D27D4EB4F) + n_in_group.astype(np.uint64)
-    order = np.lexsort((grp_g, key, grp_b))
-    b_s, k_s, n_s, g_s = grp_b[order], key[order], n_in_group[order], grp_g[order]
-    same = (b_s[1:] == b_s[:-1]) & (k_s[1:] == k_s[:-1]) & (n_s[1:] > 0)
+    # one sort key: placement, then 40 bits of the hash; the sort is stable, so the
+    # groups of a class stay in ascending group id
+    comb = (grp_b.astype(np.uint64) << np.uint64(40)) | (key >> np.uint64(24))
+    order = np.argsort(comb, kind="stable")
+    c_s, n_s, g_s, b_s = comb[order], n_in_group[order], grp_g[order], grp_b[order]
+    same = (c_s[1:] == c_s[:-1]) & (n_s[1:] > 0)
     if not same.any():
         return []
     # runs of `same`: a class is the group before the run plus the run
@@ -386,6 +394,36 @@ class BatchResult:
                  "group_num_good", "good_total", "latency_sum", "status", "finish", "good",
                  "resimulated")
 
+    @staticmethod
+    def concatenate(parts):
+        """Results of consecutive sub-batches as one (per-request outputs are
+        not carried); group columns are padded to the widest part."""
+        res = BatchResult()
+        G = max(p.group_num_requests.shape[1] for p in parts)
+
+        def wide(a):
+            return np.pad(a, ((0, 0), (0, G - a.shape[1])))
+        res.model_num_requests = np.concatenate([p.model_num_requests for p in parts])
+        res.model_num_good = np.concatenate([p.model_num_good for p in parts])
+        res.group_num_requests = np.concatenate([wide(p.group_num_requests) for p in parts])
+        res.group_num_good = (np.concatenate([wide(p.group_num_good) for p in parts])
+                              if parts[0].group_num_good is not None else None)
+        for name in ("good_total", "latency_sum", "status", "resimulated"):
+            setattr(res, name, np.concatenate([getattr(p, name) for p in parts]))
+        res.finish = res.good = None
+        return res
+
+
+class BatchSummary:
+    """What callers read from an encoded batch after evaluation, for a batch
+    that was encoded and launched in several parts."""
+
+    def __init__(self, encs):
+        self.parts = encs
+        self.B = sum(e.B for e in encs)
+        self.num_groups = np.concatenate([e.num_groups for e in encs])
+        self.num_replicas = np.concatenate([e.num_replicas for e in encs])
+
 
 def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_segments=0):
     """How the trace is cut for time-parallel execution (mms_sim_options):
@@ -395,21 +433,26 @@ def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_seg
                           int(repair_segments))
 
 
-def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+class _Pending:
+    """A submitted launch: device tensors and what collect() needs."""
+    __slots__ = ("keep", "out", "B", "Bs", "M", "N", "full", "want_group_good", "h2d", "stream")
+
+
+def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
             latency, latency_stride, flags, want_group_good, pinned=False, options=None,
-            num_scored=None, partner=None, mirror_swap=None):
-    """Uploads the tables, runs mms_sim_mixed on the current stream, downloads
-    the results.  Returns (BatchResult, h2d_bytes, d2h_bytes).  With
-    num_scored < B the candidates behind the first num_scored are mirrors
-    (partner, mirror_swap as in mms_placements) and get no results."""
+            num_scored=None, partner=None, mirror_swap=None) -> _Pending:
+    """Uploads the tables and enqueues mms_sim_mixed on the current stream;
+    nothing waits for the GPU.  With num_scored < B the candidates behind the
+    first num_scored are mirrors (partner, mirror_swap as in mms_placements)
+    and get no results."""
     _require_cuda()
     L = nat.lib()
     dev = trace.device
     N = trace.num_requests
-    res = BatchResult()
     opts = options if options is not None else sim_options()
     if not want_group_good:
         flags |= nat.FLAG_NO_GROUP_GOOD
+    job = _Pending()
     with torch.cuda.device(dev):
         d_off = _to_device(model_off, dev, pinned)
         d_rep = _to_device(model_rep, dev, pinned)
@@ -431,17 +474,18 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         ws = nat.Workspace(_ptr(ws_t), need)
         i32 = dict(dtype=torch.int32, device=dev)
-        o_mreq = torch.empty((B, max(M, 1)), **i32)
-        o_mgood = torch.empty((B, max(M, 1)), **i32)
-        o_greq = torch.empty((B, G), **i32)
-        o_ggood = torch.empty((B, G), **i32) if want_group_good else None
-        o_total = torch.empty(B, dtype=torch.int64, device=dev)
-        o_lsum = torch.empty(B, dtype=torch.float64, device=dev)
-        o_status = torch.zeros(B, dtype=torch.int32, device=dev)
-        o_redo = torch.zeros(B, dtype=torch.int32, device=dev)
+        rows = max(Bs, 1)
+        o_mreq = torch.empty((rows, max(M, 1)), **i32)
+        o_mgood = torch.empty((rows, max(M, 1)), **i32)
+        o_greq = torch.empty((rows, G), **i32)
+        o_ggood = torch.empty((rows, G), **i32) if want_group_good else None
+        o_total = torch.empty(rows, dtype=torch.int64, device=dev)
+        o_lsum = torch.empty(rows, dtype=torch.float64, device=dev)
+        o_status = torch.zeros(rows, dtype=torch.int32, device=dev)
+        o_redo = torch.zeros(rows, dtype=torch.int32, device=dev)
         full = bool(flags & nat.FLAG_PER_REQUEST)
-        o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev) if full else None
-        o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev) if full else None
+        o_fin = torch.empty((rows, max(N, 1)), dtype=torch.float64, device=dev) if full else None
+        o_good = torch.empty((rows, max(N, 1)), dtype=torch.uint8, device=dev) if full else None
         out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood),
                           _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good),
                           _ptr(o_redo))
@@ -450,26 +494,65 @@ def _launch(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
                              _ptr(trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
                              ctypes.byref(out), flags, _stream_ptr())
         nat.check(rc, "mms_sim_mixed")
+        job.stream = torch.cuda.current_stream()
+    job.keep = (d_off, d_rep, d_info, d_lat, d_partner, d_swap, ws_t)
+    job.out = (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good)
+    job.B, job.Bs, job.M, job.N, job.full = B, Bs, M, N, full
+    job.want_group_good, job.h2d = want_group_good, h2d
+    return job
+
+
+def _collect(job: _Pending):
+    """Waits for a submitted launch and downloads its results.  Returns
+    (BatchResult, h2d_bytes, d2h_bytes)."""
+    (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good) = job.out
+    Bs, M, N, full = job.Bs, job.M, job.N, job.full
+    res = BatchResult()
+    with torch.cuda.stream(job.stream):
         res.model_num_requests = o_mreq[:Bs].cpu().numpy()[:, :M]
         res.model_num_good = o_mgood[:Bs].cpu().numpy()[:, :M]
         res.group_num_requests = o_greq[:Bs].cpu().numpy()
-        res.group_num_good = o_ggood[:Bs].cpu().numpy() if want_group_good else None
+        res.group_num_good = o_ggood[:Bs].cpu().numpy() if job.want_group_good else None
         res.good_total = o_total[:Bs].cpu().numpy()
         res.latency_sum = o_lsum[:Bs].cpu().numpy()
-        res.status = o_status.cpu().numpy().astype(np.uint32)
+        res.status = o_status[:Bs].cpu().numpy().astype(np.uint32)
         res.resimulated = o_redo[:Bs].cpu().numpy()
-        res.finish = o_fin.cpu().numpy()[:, :N] if full else None
-        res.good = o_good.cpu().numpy()[:, :N].astype(bool) if full else None
-        d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
-                                     res.group_num_requests, res.good_total, res.latency_sum,
-                                     res.status))
-        if full:
-            d2h += res.finish.nbytes + res.good.nbytes
+        res.finish = o_fin[:Bs].cpu().numpy()[:, :N] if full else None
+        res.good = o_good[:Bs].cpu().numpy()[:, :N].astype(bool) if full else None
+    d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
+                                 res.group_num_requests, res.good_total, res.latency_sum,
+                                 res.status))
+    if full:
+        d2h += res.finish.nbytes + res.good.nbytes
+    job.keep = job.out = None
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         raise RuntimeError(f"simulator kernel reported status {int(res.status[bad])} "
                            f"for candidate {bad} (bad table index or capacity overflow)")
-    return res, h2d, d2h
+    return res, job.h2d, d2h
+
+
+def _launch(*args, **kwargs):
+    """_submit + _collect: uploads the tables, runs mms_sim_mixed on the current
+    stream, downloads the results.  Returns (BatchResult, h2d_bytes, d2h_bytes)."""
+    return _collect(_submit(*args, **kwargs))
+
+
+def submit_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable, group_good=False,
+                 pinned=False, options=None, mirrors=True) -> _Pending:
+    """run_batch without waiting: returns a handle for collect_batch."""
+    ext = enc.with_mirrors() if mirrors else None
+    if ext is not None:
+        off, rep, info, partner, swap = ext
+        return _submit(trace, len(partner), enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, off, rep,
+                       info, table.device(trace.device), 0, 0, group_good, pinned, options,
+                       enc.B, partner, swap)
+    return _submit(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
+                   enc.model_off, enc.model_rep, enc.group_info,
+                   table.device(trace.device), 0, 0, group_good, pinned, options)
+
+
+collect_batch = _collect
 
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
@@ -478,16 +561,12 @@ def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
     (simulate_requests_mixed, controller.py:561-628).  `mirrors`: placements
     with interchangeable groups get a mirror candidate (a speed-up of the
     time-parallel execution; results are the same with and without)."""
-    flags = nat.FLAG_PER_REQUEST if per_request else 0
-    ext = None if per_request or not mirrors else enc.with_mirrors()
-    if ext is not None:
-        off, rep, info, partner, swap = ext
-        return _launch(trace, len(partner), enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, off, rep,
-                       info, table.device(trace.device), 0, flags, group_good, pinned, options,
-                       enc.B, partner, swap)
+    if not per_request:
+        return _collect(submit_batch(trace, enc, table, group_good, pinned, options, mirrors))
     return _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
                    enc.model_off, enc.model_rep, enc.group_info,
-                   table.device(trace.device), 0, flags, group_good, pinned, options)
+                   table.device(trace.device), 0, nat.FLAG_PER_REQUEST, group_good, pinned,
+                   options)
 
 
 def encode_dense(m_id2g_id, num_stages, num_models):

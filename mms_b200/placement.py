@@ -127,19 +127,51 @@ class PlacementEvaluator:
                                         len(self.model_names), device=device)
         self.table = engine.LatencyTable(self.prof_ress)
         self.options = options          # engine.sim_options(...) or None
+        self.pipeline_parts = 4         # a long list is encoded and launched in parts
+        self.pipeline_min_part = 768    # placements per part, at least
+        self._streams = []
         self.last_resimulated = None
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
 
     # -- the batched core ---------------------------------------------------
     def evaluate(self, sols: Sequence[ModelPlacement], pinned=False):
-        """One launch for the whole list; returns (EncodedBatch, BatchResult)."""
-        enc = engine.encode_placements(sols, self.table, len(self.model_names))
-        res, h2d, d2h = engine.run_batch(self.trace, enc, self.table, pinned=pinned,
-                                         options=self.options)
-        self.last_h2d_bytes, self.last_d2h_bytes = h2d, d2h
+        """Scores the whole list; returns (batch, BatchResult) where `batch`
+        has B, num_groups and num_replicas.  A long list goes to the GPU in up
+        to `pipeline_parts` parts, each on a stream of its own, so that the
+        host encodes the next part while the GPU simulates the previous ones."""
+        n = len(sols)
+        parts = max(1, min(self.pipeline_parts, n // self.pipeline_min_part))
+        if parts == 1:
+            enc = engine.encode_placements(sols, self.table, len(self.model_names))
+            res, h2d, d2h = engine.run_batch(self.trace, enc, self.table, pinned=pinned,
+                                             options=self.options)
+            self.last_h2d_bytes, self.last_d2h_bytes = h2d, d2h
+            self.last_resimulated = res.resimulated
+            return enc, res
+        import torch
+        dev = self.trace.device
+        while len(self._streams) < parts:
+            self._streams.append(torch.cuda.Stream(device=dev))
+        main = torch.cuda.current_stream(dev)
+        bounds = [n * k // parts for k in range(parts + 1)]
+        encs, jobs = [], []
+        for k in range(parts):
+            enc = engine.encode_placements(sols[bounds[k]:bounds[k + 1]], self.table,
+                                           len(self.model_names))
+            self._streams[k].wait_stream(main)           # the trace was uploaded there
+            with torch.cuda.stream(self._streams[k]):
+                jobs.append(engine.submit_batch(self.trace, enc, self.table, pinned=pinned,
+                                                options=self.options))
+            encs.append(enc)
+        done = [engine.collect_batch(job) for job in jobs]
+        for k in range(parts):
+            main.wait_stream(self._streams[k])
+        res = engine.BatchResult.concatenate([d[0] for d in done])
+        self.last_h2d_bytes = sum(d[1] for d in done)
+        self.last_d2h_bytes = sum(d[2] for d in done)
         self.last_resimulated = res.resimulated
-        return enc, res
+        return engine.BatchSummary(encs), res
 
     def scores_from(self, enc, res) -> List[float]:
         """goodput - latency_mean/10000 + num_replicas/1e6 (base_policy.py:225-226)

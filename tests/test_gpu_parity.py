@@ -364,3 +364,24 @@ def test_mirrors_are_refused_with_per_request_outputs(loaded):
                                      nat.FLAG_PER_REQUEST) == 0
     cands.partner = None                    # mirrors without a partner list
     assert L.mms_sim_workspace_bytes(100000, ctypes.byref(cands), ctypes.byref(opts), 0) == 0
+
+
+def test_pipelined_evaluation_equals_one_launch(loaded):
+    """A long candidate list is encoded and launched in parts on separate
+    streams; scores and counters equal those of one launch."""
+    from mms_b200 import cases
+    from mms_b200.placement import PlacementEvaluator
+    case = cases.candidate_batch_case(num_candidates=1700, duration=200.0, placement_seed=3)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload)
+    ev.pipeline_min_part = 400
+    enc4, res4 = ev.evaluate(case.placements)
+    assert len(enc4.parts) == 4 and enc4.B == 1700
+    scores4 = ev.scores_from(enc4, res4)
+    ev.pipeline_parts = 1
+    enc1, res1 = ev.evaluate(case.placements)
+    assert scores4 == ev.scores_from(enc1, res1)
+    G = res1.group_num_requests.shape[1]
+    assert np.array_equal(res4.model_num_good, res1.model_num_good)
+    assert np.array_equal(res4.group_num_requests[:, :G], res1.group_num_requests)
+    assert np.array_equal(enc4.num_groups, enc1.num_groups)
+    assert ev.get_scores(case.placements[:5]) == scores4[:5]

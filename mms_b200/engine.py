@@ -435,7 +435,31 @@ def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_seg
 
 class _Pending:
     """A submitted launch: device tensors and what collect() needs."""
-    __slots__ = ("keep", "out", "B", "Bs", "M", "N", "full", "want_group_good", "h2d", "stream")
+    __slots__ = ("keep", "out", "B", "Bs", "M", "N", "full", "want_group_good", "h2d", "stream",
+                 "scratch")
+
+
+# Scratch buffers of finished launches, per device, kept for the next ones: a
+# search scores batch after batch of slowly changing size, and a fresh
+# cudaMalloc for each would cost more than the kernels.  A buffer is handed to
+# one launch at a time (taken in _submit, returned in _collect).
+_SCRATCH_POOL = {}
+
+
+def _take_scratch(dev, need):
+    pool = _SCRATCH_POOL.setdefault(dev, [])
+    fits = [k for k, t in enumerate(pool) if t.numel() >= need]
+    if fits:
+        return pool.pop(min(fits, key=lambda k: pool[k].numel()))
+    if pool:                       # grow instead of hoarding: drop the largest idle one
+        pool.pop(max(range(len(pool)), key=lambda k: pool[k].numel()))
+    return torch.empty(max(int(need * 1.25), 1 << 20), dtype=torch.uint8, device=dev)
+
+
+def _return_scratch(dev, t):
+    pool = _SCRATCH_POOL.setdefault(dev, [])
+    if len(pool) < 8:
+        pool.append(t)
 
 
 def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
@@ -471,7 +495,7 @@ def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         if need == 0 and B > 0:
             raise NotImplementedError("placement batch outside the kernel limits "
                                       "(see MMS_MAX_* in include/mms_sim.h)")
-        ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        ws_t = _take_scratch(dev, max(need, 256))
         ws = nat.Workspace(_ptr(ws_t), need)
         i32 = dict(dtype=torch.int32, device=dev)
         rows = max(Bs, 1)
@@ -495,7 +519,8 @@ def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
                              ctypes.byref(out), flags, _stream_ptr())
         nat.check(rc, "mms_sim_mixed")
         job.stream = torch.cuda.current_stream()
-    job.keep = (d_off, d_rep, d_info, d_lat, d_partner, d_swap, ws_t)
+    job.keep = (d_off, d_rep, d_info, d_lat, d_partner, d_swap)
+    job.scratch = ws_t
     job.out = (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good)
     job.B, job.Bs, job.M, job.N, job.full = B, Bs, M, N, full
     job.want_group_good, job.h2d = want_group_good, h2d
@@ -525,6 +550,8 @@ def _collect(job: _Pending):
     if full:
         d2h += res.finish.nbytes + res.good.nbytes
     job.keep = job.out = None
+    _return_scratch(job.scratch.device, job.scratch)   # every kernel that used it has finished
+    job.scratch = None
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         raise RuntimeError(f"simulator kernel reported status {int(res.status[bad])} "

@@ -105,8 +105,16 @@ def _expand(sol, weight, num_models, mem_budget, visited):
     the budget (strictly, base_policy.py:450) and were not seen before."""
     out = []
     group_mem = _group_mem(sol, weight)
+    seen = set()
     for g in range(len(sol.group_configs)):
         c = sol.group_configs[g]
+        # A later group with the same config and models yields, model by model,
+        # placements whose group_models were just produced by the earlier one:
+        # the `visited` test below would drop every one of them.
+        kind = (c, tuple(sol.group_models[g]))
+        if kind in seen:
+            continue
+        seen.add(kind)
         for m in range(num_models):
             if weight[c][m] + group_mem[g] < mem_budget and m not in sol.group_models[g]:
                 nxt = sol.add_model(g, m).normalize()

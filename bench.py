@@ -29,7 +29,7 @@ NUM_CANDIDATES = 4096
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one sim_stream_kernel launch (the dominant
 # kernel) on the default workload, from profiles/launch_list_candidates4096_3600s.md
-STREAM_KERNEL_DRAM_BYTES = 14732288 + 596909312
+STREAM_KERNEL_DRAM_BYTES = 52787456 + 684382464
 
 
 def parse_args():
@@ -268,6 +268,7 @@ def run_b200(args):
         step()
     barrier()
     times = []
+    nat.check(L.mms_profile_begin(), "mms_profile_begin")     # events around the stream kernel
     with ClockSampler(local) as clk:
         for _ in range(args.steps):
             flush.zero_()
@@ -278,6 +279,9 @@ def run_b200(args):
             e1.synchronize()
             times.append(e0.elapsed_time(e1))
     barrier()
+    k_launches, k_ms = ctypes.c_int32(0), ctypes.c_float(0.0)
+    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms)), "mms_profile_end")
+    stream_kernel_ms = k_ms.value / max(k_launches.value, 1)
     total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
@@ -308,8 +312,10 @@ def run_b200(args):
     greedy = greedy_step_timing(args, dev) if (rank == 0 and args.greedy_steps > 0) else None
     if rank == 0:
         peak, which = hbm_peak()
-        kern_s = (np.mean(times) * 1e-3)
-        achieved = B * N * BYTES_PER_UNIT / kern_s / 1e9
+        # the dominant kernel (sim_stream_kernel), timed by CUDA events on its own stream
+        # inside the timed steps; the whole call (all kernels) is reported beside it
+        achieved = B * N * BYTES_PER_UNIT / (stream_kernel_ms * 1e-3) / 1e9
+        call_achieved = B * N * BYTES_PER_UNIT / (np.mean(times) * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -325,12 +331,17 @@ def run_b200(args):
                          "traffic": (STREAM_KERNEL_DRAM_BYTES
                                      if (B, args.duration) == (NUM_CANDIDATES, 3600.0) else None),
                          "traffic_unit": "bytes per sim_stream_kernel launch (ncu, DRAM read+write)",
+                         "kernel": "sim_stream_kernel", "kernel_ms": stream_kernel_ms,
+                         "kernel_launches_timed": int(k_launches.value),
+                         "whole_call": {"achieved": call_achieved, "frac": call_achieved / peak,
+                                        "ms": float(np.mean(times))},
                          "peak_source": which, "bytes_per_unit": BYTES_PER_UNIT,
                          "algorithmic_bytes_per_launch": B * N * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
-            # rows, stream, (validate, resolve, repair) per round, chain, counters, finalize
-            "gpu_launches": (5 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps,
+            # segment leaves, rows, stream, (validate, resolve, repair) per round, chain,
+            # counters, finalize
+            "gpu_launches": (6 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps,
             "mirror_candidates_per_gpu": Bt - B,
             "chunks_resimulated_per_candidate": float(redo.float().mean().item()),
             "chunks_resimulated_hist": np.bincount(redo.cpu().numpy()).tolist(),

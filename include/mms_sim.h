@@ -168,6 +168,16 @@ int mms_abi_version(void);
 /* Text of the last failing CUDA call on this thread ("" if none). */
 const char *mms_last_error(void);
 
+/* Timing of the dominant kernel, for benchmarks (nothing in the reference
+ * corresponds).  After mms_profile_begin(), every mms_sim_mixed call of this
+ * process brackets its sim_stream_kernel launch with two CUDA events on the
+ * caller's stream (up to 256 launches; later ones are not recorded).
+ * mms_profile_end() stops recording, waits for the recorded events and
+ * returns the number of launches and their total duration.  Off by default;
+ * events are created on first use, on the device current then. */
+int mms_profile_begin(void);
+int mms_profile_end(int32_t *launches, float *total_ms);
+
 /* Summation plan (host side; replaces nothing in the reference — it restates
  * numpy's reduction order, reached from controller.py:402). */
 int32_t mms_sum_plan_leaves(int64_t num_requests);

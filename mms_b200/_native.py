@@ -38,6 +38,7 @@ EXPORTS = (
     "mms_abi_version", "mms_last_error", "mms_sum_plan_leaves", "mms_sum_plan_fill",
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
     "mms_sim_mixed_static", "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
+    "mms_profile_begin", "mms_profile_end",
 )
 
 _vp = ctypes.c_void_p
@@ -105,6 +106,9 @@ def lib():
     L.mms_sum_plan_fill.argtypes = [ctypes.c_int64, _vp, _vp]
     L.mms_trace_model_histogram.restype = ctypes.c_int
     L.mms_trace_model_histogram.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
+    L.mms_profile_begin.restype = ctypes.c_int
+    L.mms_profile_end.restype = ctypes.c_int
+    L.mms_profile_end.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float)]
     L.mms_sim_workspace_bytes.restype = ctypes.c_size_t
     L.mms_sim_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
                                           ctypes.POINTER(SimOptions), ctypes.c_uint32]

@@ -161,6 +161,13 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     return MMS_OK;
 }
 
+// Events around the stream kernel, see mms_profile_begin().
+constexpr int kProfileSlots = 256;
+static cudaEvent_t g_prof_ev[2 * kProfileSlots];
+static int g_prof_created = 0;      // events exist
+static int g_prof_on = 0;
+static int g_prof_count = 0;
+
 template <bool kFull, bool kGroupGood, bool kLegacy>
 static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 {
@@ -176,9 +183,12 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
                                   (int)g.smem_stream));
     const int64_t per_block = (int64_t)kLanes * g.block_warps;
     const int64_t streams = (int64_t)ka.B * ka.K;
+    const bool timed = g_prof_on && g_prof_count < kProfileSlots;
+    if (timed) MMS_CUDA(cudaEventRecord(g_prof_ev[2 * g_prof_count], st));
     stream_k<<<(unsigned)((streams + per_block - 1) / per_block), (unsigned)per_block,
                g.smem_stream, st>>>(ka);
     MMS_CUDA(cudaGetLastError());
+    if (timed) MMS_CUDA(cudaEventRecord(g_prof_ev[2 * g_prof_count++ + 1], st));
     if (ka.K > 1) {
         auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy>;
         auto chain_k = sim_chain_kernel<kFull, kGroupGood, kLegacy>;
@@ -210,6 +220,35 @@ extern "C" {
 int mms_abi_version(void) { return 4; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
+
+int mms_profile_begin(void)
+{
+    using namespace mms;
+    if (!g_prof_created) {
+        for (int i = 0; i < 2 * kProfileSlots; ++i) MMS_CUDA(cudaEventCreate(&g_prof_ev[i]));
+        g_prof_created = 1;
+    }
+    g_prof_count = 0;
+    g_prof_on = 1;
+    return MMS_OK;
+}
+
+int mms_profile_end(int32_t *launches, float *total_ms)
+{
+    using namespace mms;
+    g_prof_on = 0;
+    float total = 0.0f;
+    for (int i = 0; i < g_prof_count; ++i) {
+        float ms = 0.0f;
+        MMS_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
+        MMS_CUDA(cudaEventElapsedTime(&ms, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
+        total += ms;
+    }
+    if (launches) *launches = g_prof_count;
+    if (total_ms) *total_ms = total;
+    g_prof_count = 0;
+    return MMS_OK;
+}
 
 int32_t mms_sum_plan_leaves(int64_t num_requests)
 {

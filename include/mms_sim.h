@@ -59,6 +59,19 @@ typedef struct {
     const double *arrivals;        /* f64[N]                                     */
     const int32_t *model_ids;      /* i32[N]; -1 = model not registered          */
     const float *slos;             /* f32[N]                                     */
+    int64_t num_traces;            /* 0 or 1: one trace, shared by all candidates.
+                                      T > 1: T traces of N requests each, stored
+                                      request-major (element i of trace t at
+                                      [i * T + t], so that 32 candidates read
+                                      consecutive addresses); candidate b is
+                                      simulated on trace b (mms_sim_mixed only;
+                                      num_scored <= T).  Traces of different
+                                      lengths are padded at the end with
+                                      requests of model -1 that repeat the last
+                                      arrival time: such a request changes no
+                                      clock and no counter, only latency_sum is
+                                      then the pairwise sum over the padded
+                                      length.                                    */
 } mms_trace;
 
 /* B candidate placements, the tables of controller.py:418-476 in a compact
@@ -189,6 +202,8 @@ int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start /*host*/,
  * last entry counts positions where the arrival times are not finite or
  * decrease — the time-parallel path needs it to be 0 and the kernels fall
  * back to one chunk per candidate when it is not. */
+/* With T > 1 traces: hist is i32[T][M+1] followed by ONE more entry, the
+ * total of the bad positions of all traces; pass the whole array as model_hist. */
 int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models,
                               int32_t *hist, void *stream);
 

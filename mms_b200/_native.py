@@ -46,7 +46,7 @@ _vp = ctypes.c_void_p
 
 class Trace(ctypes.Structure):
     _fields_ = [("num_requests", ctypes.c_int64), ("arrivals", _vp), ("model_ids", _vp),
-                ("slos", _vp)]
+                ("slos", _vp), ("num_traces", ctypes.c_int64)]
 
 
 class Placements(ctypes.Structure):

@@ -217,7 +217,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 
 extern "C" {
 
-int mms_abi_version(void) { return 4; }
+int mms_abi_version(void) { return 5; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 
@@ -269,8 +269,27 @@ int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start, uint8_t *leaf_m
 int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models, int32_t *hist,
                               void *stream)
 {
-    if (!trace || !hist || num_models < 0 || trace->num_requests < 0) return MMS_ERR_ARG;
+    if (!trace || !hist || num_models < 0 || trace->num_requests < 0 || trace->num_traces < 0)
+        return MMS_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    if (trace->num_traces > 1) {
+        const int64_t T = trace->num_traces;
+        if (T > 0x7FFFFFFF) return MMS_ERR_UNSUPPORTED;
+        const size_t cells = (size_t)T * (num_models + 1) + 1;
+        MMS_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * cells, st));
+        if (trace->num_requests == 0) return MMS_OK;
+        if (!trace->model_ids || !trace->arrivals) return MMS_ERR_ARG;
+        const size_t smem = sizeof(int32_t) * 32 * ((size_t)num_models + 1);
+        if (smem > 48 * 1024) return MMS_ERR_UNSUPPORTED;
+        const dim3 block(32, 8);
+        int64_t slices = (trace->num_requests + 8 * 256 - 1) / (8 * 256);
+        if (slices > 64) slices = 64;
+        const dim3 grid((unsigned)((T + 31) / 32), (unsigned)slices);
+        mms::histogram_traces_kernel<<<grid, block, smem, st>>>(
+            trace->arrivals, trace->model_ids, trace->num_requests, (int32_t)T, num_models, hist);
+        MMS_CUDA(cudaGetLastError());
+        return MMS_OK;
+    }
     MMS_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * ((size_t)num_models + 1), st));
     if (trace->num_requests == 0) return MMS_OK;
     if (!trace->model_ids || !trace->arrivals) return MMS_ERR_ARG;
@@ -314,6 +333,10 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
         !out->good_total || !out->latency_sum || !out->status || !model_hist)
         return MMS_ERR_ARG;
     if (N > 0 && (!trace->arrivals || !trace->model_ids || !trace->slos)) return MMS_ERR_ARG;
+    if (trace->num_traces < 0 || trace->num_traces > 0x7FFFFFFF) return MMS_ERR_ARG;
+    if (trace->num_traces > 1 &&
+        (cands->num_scored ? cands->num_scored : cands->num_candidates) > trace->num_traces)
+        return MMS_ERR_ARG;                 // every scored candidate needs a trace of its own
     if (!cands->model_off || !cands->group_info || !cands->model_rep || !cands->latency)
         return MMS_ERR_ARG;
     const bool full = (flags & MMS_FLAG_PER_REQUEST) != 0;
@@ -328,6 +351,10 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     memset(&ka, 0, sizeof(ka));
     ka.arrivals = trace->arrivals; ka.model_ids = trace->model_ids; ka.slos = trace->slos;
     ka.N = N; ka.model_hist = model_hist;
+    ka.trace_pitch = trace->num_traces > 1 ? (int32_t)trace->num_traces : 1;
+    ka.unsorted = trace->num_traces > 1
+                      ? model_hist + (size_t)trace->num_traces * (cands->num_models + 1)
+                      : model_hist + cands->num_models;
     ka.B = B; ka.Bs = cands->num_scored ? cands->num_scored : B;
     ka.partner = cands->partner; ka.mirror_swap = cands->mirror_swap;
     ka.M = cands->num_models; ka.G = cands->max_groups; ka.P = cands->max_placed;
@@ -476,6 +503,7 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
         cands->max_placed > MMS_MAX_PLACED || cands->max_stages > MMS_MAX_STAGES ||
         cands->num_columns > MMS_MAX_COLUMNS)
         return MMS_ERR_UNSUPPORTED;
+    if (trace->num_traces > 1) return MMS_ERR_UNSUPPORTED;   // one shared trace only
     const int NB = batching->num_batch_sizes;
     if (NB < 1 || NB > 8 || batching->batch_sizes[0] != 1) return MMS_ERR_ARG;
     if (B == 0) return MMS_OK;

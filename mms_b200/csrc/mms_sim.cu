@@ -128,9 +128,11 @@ __device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout
     __syncthreads();
 }
 
-__device__ inline void init_pipe(const KernelArgs &a, Pipe &p)
+__device__ inline void init_pipe(const KernelArgs &a, Pipe &p, int64_t b)
 {
-    p.arrivals = a.arrivals; p.model_ids = a.model_ids; p.slos = a.slos;
+    const size_t base = trace_base(a, b);
+    p.arrivals = a.arrivals + base; p.model_ids = a.model_ids + base; p.slos = a.slos + base;
+    p.pitch = (uint32_t)a.trace_pitch;
     p.last = (int32_t)(a.N - 1);
 }
 
@@ -167,7 +169,7 @@ sim_stream_kernel(const KernelArgs a)
     uint32_t counters; int n_counters;
     Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters, warp);
     Pipe p;
-    init_pipe(a, p);
+    init_pipe(a, p, b);
     // not chunked: one chunk holding every segment, plain sequential simulation
     KernelArgs ka = a;
     int32_t begin = 0;
@@ -207,7 +209,7 @@ __global__ void validate_kernel(const KernelArgs a)
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
     const int32_t q_prev = j * a.seg_per_chunk - 1;
-    const double tau = a.arrivals[a.leaf_start[seg_leaf(a, q_prev + 1)]];
+    const double tau = arrival_at(a, b, a.leaf_start[seg_leaf(a, q_prev + 1)]);
     const size_t B = (size_t)a.B;
     const double *X = a.seg_end + (size_t)q_prev * a.T * B + u;
     uint8_t stale[MMS_MAX_GROUPS];
@@ -294,7 +296,7 @@ sim_repair_kernel(const KernelArgs a)
                                : a.chunk_start + (size_t)j * a.T * a.B;
     for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * kLanes) = src[(size_t)t * a.B + b];
     Pipe p;
-    init_pipe(a, p);
+    init_pipe(a, p, b);
     const int32_t first = a.leaf_start[seg_leaf(a, q_begin)];
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
@@ -326,13 +328,13 @@ sim_chain_kernel(const KernelArgs a)
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
     Pipe p;
-    init_pipe(a, p);
+    init_pipe(a, p, b);
     int32_t redone = 0;
     for (int32_t j = 1; j < a.K; ++j) {
         const int32_t q0 = j * a.seg_per_chunk;
         const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
         const int64_t first = a.leaf_start[seg_leaf(a, q0)];
-        const double tau = a.arrivals[first];
+        const double tau = arrival_at(a, b, first);
         const int32_t e = a.seg_src[(size_t)(q0 - 1) * a.B + b];
         const int32_t s0 = a.seg_src[(size_t)q0 * a.B + b];
         for (int t = 0; t < a.T; ++t)
@@ -397,7 +399,8 @@ __global__ void sum_counters_kernel(const KernelArgs a, int32_t n_counters,
     }
     if (c < M) {
         model_num_good[(size_t)b * M + c] = (int32_t)v;
-        model_num_requests[(size_t)b * M + c] = a.model_hist[c];
+        model_num_requests[(size_t)b * M + c] =
+            a.model_hist[(a.trace_pitch > 1 ? (size_t)b * (M + 1) : 0) + c];
     } else if (c < M + G) {
         group_num_requests[(size_t)b * G + (c - M)] = (int32_t)v;
     } else {
@@ -473,6 +476,37 @@ __global__ void histogram_kernel(const double *arrivals, const int32_t *model_id
     __syncthreads();
     for (int m = threadIdx.x; m <= M; m += blockDim.x)
         if (local[m]) atomicAdd(&hist[m], local[m]);
+}
+
+// The same for T traces stored request-major ([N][T]): hist[t][M + 1], and the
+// total of the bad positions of all traces in hist[T * (M + 1)].  A block
+// covers 32 traces (threadIdx.x) and a slice of the requests (blockIdx.y).
+__global__ void histogram_traces_kernel(const double *arrivals, const int32_t *model_ids, int64_t N,
+                                        int32_t T, int32_t M, int32_t *hist)
+{
+    extern __shared__ int32_t local[];      // [32][M + 1]
+    const int lane = threadIdx.x, row = threadIdx.y;
+    for (int k = row * 32 + lane; k < 32 * (M + 1); k += 32 * blockDim.y) local[k] = 0;
+    __syncthreads();
+    const int64_t t = (int64_t)blockIdx.x * 32 + lane;
+    const int64_t step = (int64_t)gridDim.y * blockDim.y;
+    if (t < T) {
+        for (int64_t i = (int64_t)blockIdx.y * blockDim.y + row; i < N; i += step) {
+            const int32_t m = model_ids[(size_t)i * T + t];
+            if (m >= 0 && m < M) atomicAdd(&local[lane * (M + 1) + m], 1);
+            const double x = arrivals[(size_t)i * T + t];
+            const bool bad = !(x - x == 0.0) || (i > 0 && !(arrivals[(size_t)(i - 1) * T + t] <= x));
+            if (bad) atomicAdd(&local[lane * (M + 1) + M], 1);
+        }
+    }
+    __syncthreads();
+    for (int k = row * 32 + lane; k < 32 * (M + 1); k += 32 * blockDim.y) {
+        const int64_t tt = (int64_t)blockIdx.x * 32 + k / (M + 1);
+        if (local[k] && tt < T) {
+            atomicAdd(&hist[tt * (M + 1) + k % (M + 1)], local[k]);
+            if (k % (M + 1) == M) atomicAdd(&hist[(size_t)T * (M + 1)], local[k]);
+        }
+    }
 }
 
 }  // namespace mms

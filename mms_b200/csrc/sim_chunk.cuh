@@ -18,7 +18,10 @@ struct KernelArgs {
     const int32_t *model_ids;
     const float *slos;
     int64_t N;
-    const int32_t *model_hist;    // [M + 1]; last entry = unsorted/non-finite positions
+    int32_t trace_pitch;          // 1: one trace for all candidates; T > 1: T traces stored
+                                  //   request-major ([N][T]), candidate b simulates trace b
+    const int32_t *model_hist;    // [M + 1] request counts per model ([T][M + 1] with T traces)
+    const int32_t *unsorted;      // number of unsorted / non-finite positions in the trace(s)
     // placements
     int32_t B, M, G, P, T, S, C;
     int32_t Bs;                   // candidates with outputs; [Bs, B) are mirrors
@@ -118,7 +121,20 @@ __device__ inline int64_t status_row(const KernelArgs &a, int64_t b)
 // True when the trace can be cut (sorted, finite arrival times).
 __device__ inline bool can_chunk(const KernelArgs &a)
 {
-    return a.K > 1 && a.model_hist[a.M] == 0;
+    return a.K > 1 && *a.unsorted == 0;
+}
+
+// Offset of request 0 of the trace candidate b simulates (a mirror: the trace
+// of the candidate it mirrors).
+__device__ inline size_t trace_base(const KernelArgs &a, int64_t b)
+{
+    return a.trace_pitch > 1 ? (size_t)status_row(a, b) : 0;
+}
+
+// Arrival time of request i in candidate b's trace.
+__device__ inline double arrival_at(const KernelArgs &a, int64_t b, int64_t i)
+{
+    return a.arrivals[(size_t)i * a.trace_pitch + trace_base(a, b)];
 }
 
 // Two clock vectors X and Y, taken at a point where every later arrival is
@@ -278,7 +294,7 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
                 bool settled = false;
                 int64_t settle_src = -1;
                 if (repair && snapshots && span_end < a.N) {
-                    const double tau = a.arrivals[span_end];
+                    const double tau = arrival_at(a, b, span_end);
                     const int32_t cur = a.seg_src[(size_t)q * a.B + b];
                     for (int64_t r = 0; r <= m_end - m_first && !settled; ++r) {
                         const int64_t v = r == 0 ? (cur < 0 ? b : cur) : m_first + r - 1;

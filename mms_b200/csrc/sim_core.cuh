@@ -113,7 +113,8 @@ struct Pipe {
     double ts; float slo; int32_t m; uint4 r;
     double ts1; float slo1; int32_t m1; uint4 r1;
     double ts2; float slo2; int32_t m2;
-    const double *arrivals; const int32_t *model_ids; const float *slos;
+    const double *arrivals; const int32_t *model_ids; const float *slos;   // request 0 of this lane's trace
+    uint32_t pitch;           // elements between consecutive requests of the trace
     int32_t last;             // highest readable request index
 };
 
@@ -134,12 +135,13 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
     const int32_t i0 = i < p.last ? i : p.last;
     const int32_t i1 = i + 1 < p.last ? i + 1 : p.last;
     const int32_t i2 = i + 2 < p.last ? i + 2 : p.last;
-    p.ts = __ldg(p.arrivals + i0); p.slo = __ldg(p.slos + i0);
-    p.m = clean_model(ln, __ldg(p.model_ids + i0));
-    p.ts1 = __ldg(p.arrivals + i1); p.slo1 = __ldg(p.slos + i1);
-    p.m1 = clean_model(ln, __ldg(p.model_ids + i1));
-    p.ts2 = __ldg(p.arrivals + i2); p.slo2 = __ldg(p.slos + i2);
-    p.m2 = clean_model(ln, __ldg(p.model_ids + i2));
+    const size_t o0 = (size_t)i0 * p.pitch, o1 = (size_t)i1 * p.pitch, o2 = (size_t)i2 * p.pitch;
+    p.ts = __ldg(p.arrivals + o0); p.slo = __ldg(p.slos + o0);
+    p.m = clean_model(ln, __ldg(p.model_ids + o0));
+    p.ts1 = __ldg(p.arrivals + o1); p.slo1 = __ldg(p.slos + o1);
+    p.m1 = clean_model(ln, __ldg(p.model_ids + o1));
+    p.ts2 = __ldg(p.arrivals + o2); p.slo2 = __ldg(p.slos + o2);
+    p.m2 = clean_model(ln, __ldg(p.model_ids + o2));
     p.r = fetch_row(ln, p.m);
     p.r1 = fetch_row(ln, p.m1);
 }
@@ -175,7 +177,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
 
     // ---- state-independent fetches for the requests behind this one -------
     const uint4 r2 = fetch_row(ln, p.m2);
-    const int32_t i3 = i + 3 < p.last ? i + 3 : p.last;
+    const size_t i3 = (size_t)(i + 3 < p.last ? i + 3 : p.last) * p.pitch;
     const double ts3 = __ldg(p.arrivals + i3);
     const float slo3 = __ldg(p.slos + i3);
     const int32_t m3raw = __ldg(p.model_ids + i3);

@@ -105,6 +105,67 @@ class DeviceTrace:
         return nat.SumPlan(self.num_leaves, 0, _ptr(self.leaf_start), _ptr(self.leaf_merges))
 
 
+class DeviceTraceBatch:
+    """T request traces resident on one GPU for runs in which every candidate
+    has a trace of its own (one placement scored on many traces).  The traces
+    are stored request-major ([N][T]: the 32 candidates of a warp read
+    consecutive addresses) and padded to the longest one with requests of
+    model -1 at the last arrival time, which change no clock and no counter.
+    Duck-type compatible with DeviceTrace where launches are concerned."""
+
+    def __init__(self, arrivals: Sequence, model_ids: Sequence, slos: Sequence, num_models: int,
+                 device=None):
+        _require_cuda()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        T = len(arrivals)
+        if T == 0 or not (len(model_ids) == len(slos) == T):
+            raise ValueError("need one (arrivals, model_ids, slos) triple per trace")
+        self.lengths = np.fromiter((len(a) for a in arrivals), np.int64, T)
+        N = int(self.lengths.max())
+        self.num_traces, self.num_requests, self.num_models = T, N, int(num_models)
+        arr = np.zeros((N, T), np.float64)
+        mid = np.full((N, T), -1, np.int32)
+        slo = np.zeros((N, T), np.float32)
+        for t in range(T):
+            n = int(self.lengths[t])
+            if not (len(model_ids[t]) == len(slos[t]) == n):
+                raise ValueError(f"trace {t}: arrays differ in length")
+            arr[:n, t], mid[:n, t], slo[:n, t] = arrivals[t], model_ids[t], slos[t]
+            if n:
+                arr[n:, t] = arrivals[t][n - 1]
+        self.h2d_bytes = arr.nbytes + mid.nbytes + slo.nbytes
+        L = nat.lib()
+        with torch.cuda.device(self.device):
+            self.arrivals = _to_device(arr, self.device)
+            self.model_ids = _to_device(mid, self.device)
+            self.slos = _to_device(slo, self.device)
+            n_leaves = L.mms_sum_plan_leaves(N)
+            if n_leaves < 0:
+                nat.check(n_leaves, "mms_sum_plan_leaves")
+            leaf_start = np.zeros(n_leaves + 1, np.int32)
+            leaf_merges = np.zeros(max(n_leaves, 1), np.uint8)
+            nat.check(L.mms_sum_plan_fill(N, leaf_start.ctypes.data, leaf_merges.ctypes.data),
+                      "mms_sum_plan_fill")
+            self.num_leaves = n_leaves
+            self.leaf_start = _to_device(leaf_start, self.device)
+            self.leaf_merges = _to_device(leaf_merges, self.device)
+            # [T][M + 1] counts, then the total of unsorted positions (T == 1: plain [M + 1])
+            cells = T * (self.num_models + 1) + (1 if T > 1 else 0)
+            self.model_hist = torch.zeros(cells, dtype=torch.int32, device=self.device)
+            tr = self.c_trace()
+            nat.check(L.mms_trace_model_histogram(ctypes.byref(tr), self.num_models,
+                                                  _ptr(self.model_hist), _stream_ptr()),
+                      "mms_trace_model_histogram")
+
+    def c_trace(self):
+        return nat.Trace(self.num_requests, _ptr(self.arrivals), _ptr(self.model_ids),
+                         _ptr(self.slos), self.num_traces)
+
+    def c_plan(self):
+        return nat.SumPlan(self.num_leaves, 0, _ptr(self.leaf_start), _ptr(self.leaf_merges))
+
+
 class LatencyTable:
     """stage latency per (model, parallel config, stage) in f32, with the
     0.9 %-per-stage penalty of controller.py:467-476 folded in.  Column c is
@@ -184,6 +245,16 @@ class EncodedBatch:
         # (candidate index, [[group ids of one class of interchangeable groups], ...])
         # for every placement that has such groups, see twin_groups()
         self.twins = twins
+
+    def repeat(self, count: int):
+        """This batch `count` times over (placement 0 .. B-1, then again ...):
+        the tables of one placement for `count` traces."""
+        B = self.B
+        twins = [(b + k * B, classes) for k in range(count) for b, classes in (self.twins or [])]
+        return EncodedBatch(B * count, self.M, self.G, self.P, self.T, self.S, self.C,
+                            np.tile(self.model_off, (count, 1)), np.tile(self.model_rep, (count, 1)),
+                            np.tile(self.group_info, (count, 1)), np.tile(self.num_groups, count),
+                            np.tile(self.num_replicas, count), twins)
 
     def with_mirrors(self):
         """The tables with mirror candidates appended for every placement

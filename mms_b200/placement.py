@@ -14,7 +14,7 @@ import numpy as np
 from . import engine
 from .profiling import ParallelConfig, ProfilingResult  # noqa: F401 (re-exported)
 from .simulator import fast_stats, workload_arrays
-from .workload import GammaProcess, Workload
+from .workload import GammaProcess, Workload, eps
 
 inf = 1e100      # alpa_serve/util.py:23
 
@@ -204,4 +204,45 @@ class PlacementEvaluator:
                                res.group_num_requests[b, :g])
             out.append((stats.goodput, [x.goodput for x in stats.per_model_stats],
                         stats.group_num_requests, stats))
+        return out
+
+
+class TraceSweep:
+    """One placement scored on many traces — the robustness sweeps that call
+    `approximate_one_case(..., fast_stats=True)` once per trace
+    (alpa_serve/simulator/controller.py:308-407) — with the traces as the
+    batch: `batch` of them are uploaded side by side and simulated in one
+    launch, every GPU thread running the placement on a trace of its own."""
+
+    def __init__(self, model_datas, cluster_env, placement: ModelPlacement, device=None,
+                 options=None, batch: int = 256):
+        self.model_datas = model_datas
+        self.cluster_env = cluster_env
+        self.placement = placement
+        self.model_names = tuple(d.name for d in model_datas)
+        self.table = engine.LatencyTable(tuple(d.profiling_result for d in model_datas))
+        self.enc = engine.encode_placements([placement], self.table, len(self.model_names))
+        self.device = device
+        self.options = options
+        self.batch = int(batch)
+
+    def evaluate(self, workloads: Sequence[Workload]):
+        """Per trace: (goodput, per-model goodput, group_num_requests), with
+        goodput = np.mean(good) and per-model goodput = good / (requests + eps)
+        as in fast_stats (controller.py:393-403)."""
+        out = []
+        M = len(self.model_names)
+        for lo in range(0, len(workloads), self.batch):
+            part = workloads[lo:lo + self.batch]
+            arrays = [workload_arrays(w, self.model_names) for w in part]
+            traces = engine.DeviceTraceBatch([w.arrivals for w in part], [a[0] for a in arrays],
+                                             [a[1] for a in arrays], M, device=self.device)
+            res, _, _ = engine.run_batch(traces, self.enc.repeat(len(part)), self.table,
+                                         options=self.options)
+            g = int(self.enc.num_groups[0])
+            for t in range(len(part)):
+                n = int(traces.lengths[t])
+                goodput = float(res.good_total[t]) / n if n else 0.0
+                per_model = res.model_num_good[t] / (res.model_num_requests[t] + eps)
+                out.append((goodput, per_model, tuple(res.group_num_requests[t, :g])))
         return out

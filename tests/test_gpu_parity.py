@@ -385,3 +385,41 @@ def test_pipelined_evaluation_equals_one_launch(loaded):
     assert np.array_equal(res4.group_num_requests[:, :G], res1.group_num_requests)
     assert np.array_equal(enc4.num_groups, enc1.num_groups)
     assert ev.get_scores(case.placements[:5]) == scores4[:5]
+
+
+def test_trace_sweep_one_placement_many_traces(loaded):
+    """Every candidate simulates a trace of its own (request-major trace
+    batch, shorter traces padded): goodput, per-model counts and group
+    counts of each trace equal the checker's on that trace alone."""
+    from mms_b200 import cases
+    from mms_b200.placement import ModelPlacement, TraceSweep
+    from mms_b200.profiling import ParallelConfig
+    from mms_b200.simulator import workload_arrays
+    from mms_b200.workload import eps
+    from oracle import tables
+    base = cases.candidate_batch_case(num_candidates=3, duration=10.0, num_models=8,
+                                      num_devices=16, total_rate=30.0)
+    datas = base.model_datas
+    c1, c2, c4 = (ParallelConfig(1, 1, p) for p in (1, 2, 4))
+    placements = [base.placements[1],
+                  ModelPlacement([c4, c4, c2, c2, c1, c1, c1, c1],
+                                 [[2, 5, 0], [2, 5, 0], [1, 3], [1, 3], [4], [4], [6, 7], [7, 6]])]
+    workloads = []
+    for t in range(37):                                   # not a multiple of 32
+        scale, cv = (0.5, 1.0, 2.0, 4.0)[t % 4], (1.0, 2.0, 4.0, 8.0)[(t // 4) % 4]
+        scaled = [type(d)(d.name, d.slo, d.rate * scale, cv, d.profiling_result) for d in datas]
+        workloads.append(cases.merged_gamma_trace(scaled, 500.0 / scale ** 0.5, base_seed=100 * t))
+    names = [d.name for d in datas]
+    profs = [d.profiling_result for d in datas]
+    lengths = {len(w.arrivals) for w in workloads}
+    assert len(lengths) > 10 and max(lengths) > 2 * 8192       # ragged, and long enough to be cut
+    for p in placements:
+        got = TraceSweep(datas, base.cluster_env, p, batch=32).evaluate(workloads)
+        assert len(got) == len(workloads)
+        for t, w in enumerate(workloads):
+            mids, slos = workload_arrays(w, names)
+            fin, good, mreq, mgood, greq, _ = tables.one_placement(p, profs, mids, slos, w.arrivals)
+            goodput, per_model, group_req = got[t]
+            assert goodput == np.mean(good), t
+            assert np.array_equal(per_model, mgood / (mreq + eps)), t
+            assert np.array_equal(np.array(group_req), greq), t

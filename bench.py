@@ -48,6 +48,10 @@ def parse_args():
     ap.add_argument("--rounds", type=int, default=0, help="validate+repair rounds (0 auto)")
     ap.add_argument("--repair-segments", type=int, default=0,
                     help="segments a repair runs per round (0 auto, <0 no cap)")
+    ap.add_argument("--workload", default="candidates", choices=["candidates", "sweep"],
+                    help="candidates: 4096 placements x one trace (the headline); sweep: one "
+                         "placement x many traces (robustness sweep)")
+    ap.add_argument("--traces", type=int, default=256, help="sweep: traces per GPU")
     ap.add_argument("--no-mirrors", action="store_true",
                     help="no mirror candidates for placements with interchangeable groups")
     return ap.parse_args()
@@ -396,10 +400,171 @@ def greedy_step_timing(args, dev):
             "includes": "host expansion and dedup, encoding, H2D, kernels, D2H, top-1 per partition"}
 
 
+def run_sweep(args):
+    """One placement x many traces per GPU (trace t of rank r is global trace
+    r * traces + t); same metric, 1 unit = 1 trace x 1 request."""
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+    from mms_b200 import _native as nat
+    from mms_b200 import cases, engine
+    from mms_b200.placement import TraceSweep
+    from mms_b200.simulator import workload_arrays
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    duration = args.duration if args.duration != 3600.0 else 720.0
+    case = cases.sweep_case(duration=duration)
+    T = args.traces
+    workloads = [case.trace(rank * T + t) for t in range(T)]
+    sweep = TraceSweep(case.model_datas, case.cluster_env, case.placement, device=dev, batch=T,
+                       options=engine.sim_options(args.chunk, args.run_in, args.rounds,
+                                                  args.repair_segments))
+    names = sweep.model_names
+    arrays = [workload_arrays(w, names) for w in workloads]
+    units = int(sum(len(w.arrivals) for w in workloads))
+    L = nat.lib()
+
+    # ---- device-resident arm ----
+    traces = engine.DeviceTraceBatch([w.arrivals for w in workloads], [a[0] for a in arrays],
+                                     [a[1] for a in arrays], len(names), device=dev)
+    enc = sweep.enc.repeat(T)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    jobs = []
+
+    def step():
+        job = engine.submit_batch(traces, enc, sweep.table, options=sweep.options)
+        jobs.append(job)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def drain():
+        out = None
+        while jobs:
+            out = engine.collect_batch(jobs.pop())[0]
+        return out
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+        drain()
+    barrier()
+    times = []
+    nat.check(L.mms_profile_begin(), "mms_profile_begin")
+    with ClockSampler(local) as clk:
+        for _ in range(args.steps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()                      # tables are uploaded inside (a few hundred KB)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+            res = drain()
+    barrier()
+    k_launches, k_ms = ctypes.c_int32(0), ctypes.c_float(0.0)
+    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms)), "mms_profile_end")
+    stream_kernel_ms = k_ms.value / max(k_launches.value, 1)
+    total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    all_units = torch.tensor([units], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(all_units)
+    all_units = float(all_units.item())
+    value = all_units * args.steps / (total_ms * 1e-3)
+
+    # ---- end-to-end arm: host traces in, goodputs out (and the tallies combined) ----
+    e2e_times = []
+    for i in range(3):
+        barrier()
+        t0 = time.perf_counter()
+        got = sweep.evaluate(workloads)
+        tally = torch.zeros(16, 2, dtype=torch.float64, device=dev)   # per cell: sum, count
+        for t, g in enumerate(got):
+            cell = (rank * T + t) % 16
+            tally[cell, 0] += g[0]
+            tally[cell, 1] += 1
+        if world > 1:
+            dist.all_reduce(tally)
+        torch.cuda.synchronize()
+        if i >= 1:
+            e2e_times.append(time.perf_counter() - t0)
+    e2e_t = torch.tensor([float(np.mean(e2e_times))], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    e2e_value = all_units / float(e2e_t.item())
+    goodputs = np.array([g[0] for g in got])
+    assert np.array_equal(goodputs, res.good_total / traces.lengths), "resident and e2e arms differ"
+
+    if rank == 0:
+        peak, which = hbm_peak()
+        achieved = units * BYTES_PER_UNIT / (stream_kernel_ms * 1e-3) / 1e9
+        call_achieved = units * BYTES_PER_UNIT / (np.mean(times) * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+            "config": {"workload": f"trace-sweep: one 64-device placement of 32 models x {T} traces "
+                                   f"per GPU ({duration:.0f} s Gamma traces, 16 cells of rate scale "
+                                   "{0.5,1,2,4} x CV {1,2,4,8}, 278 req/s at scale 1)",
+                       "traces_per_gpu": T, "requests_per_gpu": units,
+                       "padded_requests_per_trace": traces.num_requests,
+                       "parallelism": f"traces sharded over {world} GPU(s)",
+                       "l2": "256 MiB buffer written between timed steps"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "kernel": "sim_stream_kernel", "kernel_ms": stream_kernel_ms,
+                         "kernel_launches_timed": int(k_launches.value),
+                         "whole_call": {"achieved": call_achieved, "frac": call_achieved / peak,
+                                        "ms": float(np.mean(times))},
+                         "peak_source": which, "bytes_per_unit": BYTES_PER_UNIT,
+                         "algorithmic_bytes_per_launch": units * BYTES_PER_UNIT},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(traces.h2d_bytes),
+                    "d2h_bytes_per_step": int(T * (2 * len(names) + enc.G + 4) * 4)},
+            "gpu_launches": (6 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps,
+            "chunks_resimulated_per_trace": float(np.mean(res.resimulated)),
+            "clocks": clk.summary(),
+            "goodput_mean_per_cell": [float(np.mean(goodputs[c::16])) for c in range(16)],
+        }
+        if not args.no_cpu_baseline:
+            from oracle import tables
+            profs = [d.profiling_result for d in case.model_datas]
+            t0 = time.perf_counter()
+            done = 0
+            for t in range(T):
+                tables.one_placement(case.placement, profs, arrays[t][0], arrays[t][1],
+                                     workloads[t].arrivals)
+                done += len(workloads[t].arrivals)
+                if time.perf_counter() - t0 > 10.0:
+                    break
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": done / dt, "unit": UNIT, "cores": 1, "kind": "port",
+                                    "sample": f"{done} requests of the first traces, {dt:.1f} s"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
     else:
         run_b200(args)
 

@@ -137,3 +137,38 @@ def greedy_search_case(slo_scale=5.0, num_models=56, num_devices=64, total_rate=
     datas = mixed_models(num_models, total_rate, cv, slo_scale, classes=SEARCH_CLASSES)
     env = ClusterEnv(num_devices, 13 * GB)
     return Case("greedy-search", datas, env, merged_gamma_trace(datas, duration, base_seed), [])
+
+
+SWEEP_RATE_SCALES = (0.5, 1.0, 2.0, 4.0)
+SWEEP_CVS = (1.0, 2.0, 4.0, 8.0)
+
+
+@dataclasses.dataclass
+class SweepCase:
+    model_datas: List[ModelData]
+    cluster_env: ClusterEnv
+    placement: ModelPlacement
+    duration: float
+    total_rate: float
+
+    def cell(self, t: int):
+        """(rate scale, CV) of trace t: 16 cells, trace t is in cell t mod 16."""
+        return SWEEP_RATE_SCALES[t % 4], SWEEP_CVS[(t // 4) % 4]
+
+    def trace(self, t: int) -> Workload:
+        """Trace t: base seed t, the rates of all models scaled and the CV set
+        as its cell says."""
+        scale, cv = self.cell(t)
+        scaled = [ModelData(d.name, d.slo, d.rate * scale, cv, d.profiling_result)
+                  for d in self.model_datas]
+        return merged_gamma_trace(scaled, self.duration, base_seed=t)
+
+
+def sweep_case(duration=3600.0, total_rate=278.0, placement_seed=0) -> SweepCase:
+    """Robustness sweep: ONE 64-device placement of the 32 models of
+    candidate_batch_case, scored on many traces; at rate scale 1 the models
+    share `total_rate` req/s (about a million requests per hour-long trace)."""
+    datas = mixed_models(32, total_rate, 1.0)
+    env = ClusterEnv(64, 13 * GB)
+    placement = random_placements(datas, 64, env.mem_budget, 1, placement_seed)[0]
+    return SweepCase(datas, env, placement, duration, total_rate)

@@ -88,6 +88,27 @@ class Batching(ctypes.Structure):
 _lib = None
 
 
+_host = False
+
+
+def host_lib():
+    """The host-side helper (csrc/encode_host.c) through ctypes.PyDLL, or None
+    when it has not been built; callers then do the same work in Python."""
+    global _host
+    if _host is False:
+        path = os.path.join(os.path.dirname(LIB_PATH), "libmms_host.so")
+        _host = None
+        if os.path.exists(path):
+            H = ctypes.PyDLL(path)
+            H.mms_host_scan.restype = ctypes.c_int
+            H.mms_host_scan.argtypes = [ctypes.py_object, _vp, _vp]
+            H.mms_host_flatten.restype = ctypes.c_int
+            H.mms_host_flatten.argtypes = [ctypes.py_object, _vp, _vp, _vp, ctypes.c_int64,
+                                           ctypes.c_int64]
+            _host = H
+    return _host
+
+
 def lib():
     """Loads the extension; raises if it has not been built."""
     global _lib

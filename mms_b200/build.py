@@ -25,6 +25,30 @@ NVCC_FLAGS = [
 ]
 
 
+HOST_LIB_PATH = os.path.join(PKG_DIR, "libmms_host.so")
+HOST_SOURCE = os.path.join(PKG_DIR, "csrc", "encode_host.c")
+
+
+def build_host(force=False):
+    """Compile the host-side helper (gcc, CPython headers): flattens placement
+    lists for the encoder.  Optional: without it the encoder walks the lists
+    in Python."""
+    import sysconfig
+    if (not force and os.path.exists(HOST_LIB_PATH)
+            and os.path.getmtime(HOST_LIB_PATH) >= os.path.getmtime(HOST_SOURCE)):
+        return HOST_LIB_PATH
+    include = sysconfig.get_paths()["include"]
+    if not os.path.exists(os.path.join(include, "Python.h")):
+        return None
+    cmd = [os.environ.get("CC", "gcc"), "-O2", "-shared", "-fPIC", "-I", include,
+           "-o", HOST_LIB_PATH, HOST_SOURCE]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout)
+        raise RuntimeError("gcc failed building libmms_host.so")
+    return HOST_LIB_PATH
+
+
 def _nvcc():
     cand = os.environ.get("NVCC") or "/usr/local/cuda/bin/nvcc"
     return cand if os.path.exists(cand) else "nvcc"
@@ -39,6 +63,7 @@ def is_stale():
 
 def build(force=False, verbose=False):
     """Compile the extension if it is missing or older than its sources."""
+    build_host(force)
     if not force and not is_stale():
         return LIB_PATH
     cmd = [_nvcc()] + NVCC_FLAGS + ["-I", os.path.join(REPO_DIR, "include")]

@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from . import _native as nat
+from .profiling import ParallelConfig
 
 inf = 1e100      # alpa_serve/util.py:23
 _PP = operator.itemgetter(2)     # pipeline degree of a ParallelConfig(dp, op, pp)
@@ -373,20 +374,65 @@ def twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model):
         ends = np.cumsum(n_in_group)
         key = (csum[ends] - csum[ends - n_in_group]) * np.uint64(0x9E3779B97F4A7C15) \
             + cfg_col.astype(np.uint64) * np.uint64(0xC2B2AE3D27D4EB4F) + n_in_group.astype(np.uint64)
-    # one sort key: placement, then 40 bits of the hash; the sort is stable, so the
-    # groups of a class stay in ascending group id
-    comb = (grp_b.astype(np.uint64) << np.uint64(40)) | (key >> np.uint64(24))
-    order = np.argsort(comb, kind="stable")
-    c_s, n_s, g_s, b_s = comb[order], n_in_group[order], grp_g[order], grp_b[order]
-    same = (c_s[1:] == c_s[:-1]) & (n_s[1:] > 0)
-    if not same.any():
-        return []
-    # runs of `same`: a class is the group before the run plus the run
-    edges = np.flatnonzero(np.diff(np.concatenate(([0], same.view(np.int8), [0]))))
-    out = {}
-    for lo, hi in zip(edges[0::2].tolist(), edges[1::2].tolist()):
-        out.setdefault(int(b_s[lo]), []).append(g_s[lo:hi + 1].tolist())
-    return sorted(out.items())
+    # keys as a [B][G] matrix (unused cells and empty groups get keys of their own: top bit
+    # set, which no hash has), each row sorted on its own: equal neighbours are a class
+    G = int(grp_g.max()) + 1
+    mat = (np.arange(B * G, dtype=np.uint64) | np.uint64(1 << 63)).reshape(B, G)
+    live = n_in_group > 0
+    mat[grp_b[live], grp_g[live]] = key[live] & np.uint64((1 << 63) - 1)
+    order = np.argsort(mat, axis=1)
+    srt = np.take_along_axis(mat, order, axis=1)
+    same = srt[:, 1:] == srt[:, :-1]
+    rows, cols = np.nonzero(same)                     # sorted by row, then column
+    lo_ids = order[rows, cols].tolist()
+    hi_ids = order[rows, cols + 1].tolist()
+    out = []
+    prev_b, prev_c = -1, -2
+    for b, c, g_lo, g_hi in zip(rows.tolist(), cols.tolist(), lo_ids, hi_ids):
+        if b != prev_b:
+            out.append((b, []))
+        if b == prev_b and c == prev_c + 1:
+            out[-1][1][-1].append(g_hi)                # the run of equal keys goes on
+        else:
+            out[-1][1].append([g_lo, g_hi])
+        prev_b, prev_c = b, c
+    for _, classes in out:
+        for cls in classes:
+            cls.sort()
+    return out
+
+
+def _flatten(placements):
+    """(groups per placement i64[B], configs i64[groups][3] = (dp, op, pp),
+    models per group i64[groups], the models of all groups i64[pairs]) in
+    placement order: by the C helper when it is built, else by passes over the
+    Python objects."""
+    B = len(placements)
+    H = nat.host_lib()
+    if H is not None and isinstance(placements, (list, tuple)):
+        n_groups = np.zeros(B, np.int64)
+        n_pairs = np.zeros(B, np.int64)
+        if H.mms_host_scan(placements, n_groups.ctypes.data, n_pairs.ctypes.data) != 0:
+            raise RuntimeError("mms_host_scan failed")       # a Python exception is normally set
+        tot_groups, tot_placed = int(n_groups.sum()), int(n_pairs.sum())
+        cfg = np.zeros((tot_groups, 3), np.int64)
+        n_in_group = np.zeros(tot_groups, np.int64)
+        placed_model = np.zeros(tot_placed, np.int64)
+        if H.mms_host_flatten(placements, cfg.ctypes.data, n_in_group.ctypes.data,
+                              placed_model.ctypes.data, tot_groups, tot_placed) != 0:
+            raise RuntimeError("mms_host_flatten failed")
+        return n_groups, cfg, n_in_group, placed_model
+    all_cfgs = list(chain.from_iterable(p.group_configs for p in placements))
+    all_groups = list(chain.from_iterable(p.group_models for p in placements))
+    n_groups = np.fromiter(map(len, (p.group_configs for p in placements)), np.int64, B)
+    tot_groups = len(all_cfgs)
+    if len(all_groups) != tot_groups:
+        raise ValueError("group_configs and group_models differ in length")
+    cfg = np.fromiter(chain.from_iterable(c[:3] for c in all_cfgs), np.int64,
+                      3 * tot_groups).reshape(tot_groups, 3)
+    n_in_group = np.fromiter(map(len, all_groups), np.int64, tot_groups)
+    placed_model = np.fromiter(chain.from_iterable(all_groups), np.int64, int(n_in_group.sum()))
+    return n_groups, cfg, n_in_group, placed_model
 
 
 def encode_placements(placements: Sequence, table: LatencyTable, num_models: int) -> EncodedBatch:
@@ -395,19 +441,17 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     '<' over groups in ascending id), so nothing is re-sorted."""
     B = len(placements)
     M = int(num_models)
-    # One C-level pass per field (itertools/map), no Python-level loop per group.
-    all_cfgs = list(chain.from_iterable(p.group_configs for p in placements))
-    all_groups = list(chain.from_iterable(p.group_models for p in placements))
-    n_groups = np.fromiter(map(len, (p.group_configs for p in placements)), np.int64, B)
-    tot_groups = len(all_cfgs)
-    if len(all_groups) != tot_groups:
-        raise ValueError("group_configs and group_models differ in length")
-    table.columns_for(dict.fromkeys(all_cfgs))
-    cfg_col = np.fromiter(map(table.column.__getitem__, all_cfgs), np.int64, tot_groups)
-    cfg_pp = np.fromiter(map(_PP, all_cfgs), np.int64, tot_groups)
-    n_in_group = np.fromiter(map(len, all_groups), np.int64, tot_groups)
-    tot_placed = int(n_in_group.sum())
-    placed_model = np.fromiter(chain.from_iterable(all_groups), np.int64, tot_placed)
+    n_groups, cfg, n_in_group, placed_model = _flatten(placements)
+    tot_groups, tot_placed = len(n_in_group), len(placed_model)
+    # distinct (dp, op, pp) rows -> columns of the latency table
+    cfg_key = (cfg[:, 0] << 40) | (cfg[:, 1] << 20) | cfg[:, 2]
+    uniq, inverse = np.unique(cfg_key, return_inverse=True)
+    uniq_cfgs = [ParallelConfig(int(k >> 40), int((k >> 20) & 0xFFFFF), int(k & 0xFFFFF))
+                 for k in uniq]
+    table.columns_for(uniq_cfgs)
+    cfg_col = np.fromiter(map(table.column.__getitem__, uniq_cfgs), np.int64,
+                          len(uniq_cfgs))[inverse] if tot_groups else np.zeros(0, np.int64)
+    cfg_pp = cfg[:, 2].copy()
     if tot_placed and (placed_model.min() < 0 or placed_model.max() >= M):
         raise IndexError("model id in group_models is out of range")
 
@@ -434,7 +478,7 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     pl_b = grp_b[pl_grp]
     pl_g = grp_g[pl_grp]
     # one composite key: by candidate, then model, then group id
-    order = np.argsort((pl_b * max(M, 1) + placed_model) * (G + 1) + pl_g, kind="stable")
+    order = np.argsort((pl_b * max(M, 1) + placed_model) * (G + 1) + pl_g)      # keys are unique
     pl_b, pl_g, pl_m, pl_grp = pl_b[order], pl_g[order], placed_model[order], pl_grp[order]
     placed_per_b = np.bincount(pl_b, minlength=B) if tot_placed else np.zeros(B, np.int64)
     P = int(placed_per_b.max()) if B else 0

@@ -4,6 +4,7 @@ import os
 import re
 
 import numpy as np
+import pytest
 
 from mms_b200 import _native as nat
 from mms_b200 import build as mms_build
@@ -200,3 +201,30 @@ def test_twin_group_detection_matches_a_plain_search():
             assert sorted(arr[g] for g in cls) == cls
         seen.add(tuple(arr))
     assert len(seen) == 11
+
+
+def test_c_flattening_equals_python_flattening():
+    """The host helper (csrc/encode_host.c) and the pure-Python passes give the
+    encoder the same arrays; bad input raises instead of being encoded."""
+    from mms_b200 import _native as nat
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement
+    from mms_b200.profiling import ParallelConfig
+    assert nat.host_lib() is not None, "libmms_host.so was not built"
+    case = cases.candidate_batch_case(num_candidates=300, duration=5.0, placement_seed=7)
+    sols = list(case.placements) + [ModelPlacement([], []),
+                                    ModelPlacement((ParallelConfig(1, 1, 2),), ((np.int64(3), 1),))]
+    fast = engine._flatten(sols)
+    saved, nat._host = nat._host, None
+    try:
+        slow = engine._flatten(sols)
+    finally:
+        nat._host = saved
+    for a, b in zip(fast, slow):
+        assert a.dtype == b.dtype and np.array_equal(a, b)
+    with pytest.raises(ValueError):
+        engine._flatten([ModelPlacement([ParallelConfig(1, 1, 1)], [[0], [1]])])
+    with pytest.raises(TypeError):
+        engine._flatten([ModelPlacement(["pp2"], [[0]])])
+    with pytest.raises(AttributeError):
+        engine._flatten([object()])

@@ -28,8 +28,9 @@ BYTES_PER_UNIT = 16          # f64 arrival + i32 model id + f32 slo, read once p
 NUM_CANDIDATES = 4096
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one sim_stream_kernel launch (the dominant
-# kernel) on the default workload, from profiles/launch_list_candidates4096_3600s.md
-STREAM_KERNEL_DRAM_BYTES = 52787456 + 684382464
+# kernel: the launch over the 3695 placements without mirror candidates) on the default
+# workload, from profiles/launch_list_candidates4096_3600s.md
+STREAM_KERNEL_DRAM_BYTES = 35223808 + 546196736
 
 
 def parse_args():
@@ -52,6 +53,8 @@ def parse_args():
                     help="candidates: 4096 placements x one trace (the headline); sweep: one "
                          "placement x many traces (robustness sweep)")
     ap.add_argument("--traces", type=int, default=256, help="sweep: traces per GPU")
+    ap.add_argument("--no-split", action="store_true",
+                    help="one launch per step even when some placements have mirror candidates")
     ap.add_argument("--no-mirrors", action="store_true",
                     help="no mirror candidates for placements with interchangeable groups")
     return ap.parse_args()
@@ -218,48 +221,31 @@ def run_b200(args):
     N, B = ev.trace.num_requests, len(case.placements)
     L = nat.lib()
 
-    # ---- device-resident arm: tables already in HBM, time the C-ABI call ----
+    # ---- device-resident arm: tables already in HBM, time the C-ABI call(s) ----
+    # B placements are scored; the ones with interchangeable groups bring mirror candidates
+    # and go into a launch of their own beside the rest (engine.ResidentBatch)
     enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
-    ext = None if args.no_mirrors else enc.with_mirrors()
-    h_off, h_rep, h_info = ext[:3] if ext else (enc.model_off, enc.model_rep, enc.group_info)
-    d_off = torch.from_numpy(h_off).to(dev)
-    d_rep = torch.from_numpy(h_rep).to(dev)
-    d_info = torch.from_numpy(h_info).to(dev)
-    d_partner = torch.from_numpy(ext[3]).to(dev) if ext else None
-    d_swap = torch.from_numpy(ext[4]).to(dev) if ext else None
-    d_lat = ev.table.device(dev)
-    P = engine._ptr
-    # B placements are scored; the ones with interchangeable groups bring a mirror each
-    Bt = len(h_off)
-    cands = nat.Placements(Bt, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, B if ext else 0,
-                           P(d_off), P(d_rep), P(d_info), P(d_lat), 0, P(d_partner), P(d_swap))
     opts = engine.sim_options(args.chunk, args.run_in, args.rounds, args.repair_segments)
-    need = L.mms_sim_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(opts),
-                                     nat.FLAG_NO_GROUP_GOOD)
-    ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
-    ws = nat.Workspace(P(ws_t), need)
-    i32 = dict(dtype=torch.int32, device=dev)
-    o = [torch.empty((B, enc.M), **i32), torch.empty((B, enc.M), **i32),
-         torch.empty((B, enc.G), **i32), torch.empty(B, dtype=torch.int64, device=dev),
-         torch.empty(B, dtype=torch.float64, device=dev), torch.zeros(B, **i32)]
-    redo = torch.zeros(B, **i32)
-    out = nat.Results(P(o[0]), P(o[1]), P(o[2]), None, P(o[3]), P(o[4]), P(o[5]), None, None,
-                      P(redo))
-    tr, plan = ev.trace.c_trace(), ev.trace.c_plan()
+    resident = engine.ResidentBatch(ev.trace, enc, ev.table, options=opts,
+                                    mirrors=not args.no_mirrors, split=not args.no_split)
+    n_mirrors = sum(job.B - job.Bs for job in resident.jobs)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB of L2
     best = torch.zeros(2, dtype=torch.float64, device=dev)
     gathered = torch.zeros(2 * world, dtype=torch.float64, device=dev)
+    part_index = [None if idx is None else torch.from_numpy(idx).to(dev)
+                  for idx, _, _ in resident.device_outputs()]
 
     def step():
-        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
-                             P(ev.trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
-                             ctypes.byref(out), nat.FLAG_NO_GROUP_GOOD, stream)
-        nat.check(rc, "mms_sim_mixed")
+        resident.launch()
         if world > 1:   # the search's argmax over all ranks' candidates
-            score = o[3].double() / N - o[4] / N / 10000
-            top = torch.max(score, dim=0)
-            best[0], best[1] = top.values, (top.indices + rank * B).double()
+            best[0] = -1e300
+            for pos, (_, good, lat_sum) in zip(part_index, resident.device_outputs()):
+                score = good.double() / N - lat_sum / N / 10000
+                top = torch.max(score, dim=0)
+                where = top.indices if pos is None else pos[top.indices]
+                better = top.values > best[0]
+                best[1] = torch.where(better, (where + rank * B).double(), best[1])
+                best[0] = torch.where(better, top.values, best[0])
             dist.all_gather_into_tensor(gathered, best)
 
     def barrier():
@@ -284,13 +270,22 @@ def run_b200(args):
             times.append(e0.elapsed_time(e1))
     barrier()
     k_launches, k_ms = ctypes.c_int32(0), ctypes.c_float(0.0)
-    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms)), "mms_profile_end")
-    stream_kernel_ms = k_ms.value / max(k_launches.value, 1)
+    each = np.zeros(256, np.float32)
+    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms), each.ctypes.data,
+                                len(each)), "mms_profile_end")
+    # the dominant kernel: the stream kernel of the step's largest launch (with a split step,
+    # launch 0 holds the placements with mirror candidates and launch 1 the rest)
+    per_step = len(resident.jobs)
+    big = int(np.argmax([job.Bs for job in resident.jobs]))
+    stream_kernel_ms = float(np.mean(each[big:k_launches.value:per_step]))
+    kernel_units = resident.jobs[big].Bs * N
     total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = float(total_ms.item())
-    assert int(o[5].abs().sum().item()) == 0, "kernel status words are not clean"
+    final, _ = resident.results()
+    assert not np.any(final.status), "kernel status words are not clean"
+    redo = final.resimulated
     units_per_step = B * N * world
     value = units_per_step * args.steps / (total_ms * 1e-3)
 
@@ -318,7 +313,7 @@ def run_b200(args):
         peak, which = hbm_peak()
         # the dominant kernel (sim_stream_kernel), timed by CUDA events on its own stream
         # inside the timed steps; the whole call (all kernels) is reported beside it
-        achieved = B * N * BYTES_PER_UNIT / (stream_kernel_ms * 1e-3) / 1e9
+        achieved = kernel_units * BYTES_PER_UNIT / (stream_kernel_ms * 1e-3) / 1e9
         call_achieved = B * N * BYTES_PER_UNIT / (np.mean(times) * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
@@ -333,22 +328,25 @@ def run_b200(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
                          "traffic": (STREAM_KERNEL_DRAM_BYTES
-                                     if (B, args.duration) == (NUM_CANDIDATES, 3600.0) else None),
+                                     if (B, args.duration, per_step) == (NUM_CANDIDATES, 3600.0, 2)
+                                     else None),
                          "traffic_unit": "bytes per sim_stream_kernel launch (ncu, DRAM read+write)",
                          "kernel": "sim_stream_kernel", "kernel_ms": stream_kernel_ms,
-                         "kernel_launches_timed": int(k_launches.value),
+                         "kernel_launches_timed": int(k_launches.value) // per_step,
                          "whole_call": {"achieved": call_achieved, "frac": call_achieved / peak,
                                         "ms": float(np.mean(times))},
                          "peak_source": which, "bytes_per_unit": BYTES_PER_UNIT,
-                         "algorithmic_bytes_per_launch": B * N * BYTES_PER_UNIT},
+                         "algorithmic_bytes_per_launch": kernel_units * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             # segment leaves, rows, stream, (validate, resolve, repair) per round, chain,
             # counters, finalize
-            "gpu_launches": (6 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps,
-            "mirror_candidates_per_gpu": Bt - B,
-            "chunks_resimulated_per_candidate": float(redo.float().mean().item()),
-            "chunks_resimulated_hist": np.bincount(redo.cpu().numpy()).tolist(),
+            "gpu_launches": ((6 + 3 * (args.rounds if args.rounds > 0 else 3)) * args.steps
+                             * len(resident.jobs)),
+            "mirror_candidates_per_gpu": int(n_mirrors),
+            "launches_per_step": len(resident.jobs),
+            "chunks_resimulated_per_candidate": float(np.mean(redo)),
+            "chunks_resimulated_hist": np.bincount(redo).tolist(),
             "clocks": clk.summary(),
             "best_score": float(np.max(scores)),
         }
@@ -474,7 +472,8 @@ def run_sweep(args):
             res = drain()
     barrier()
     k_launches, k_ms = ctypes.c_int32(0), ctypes.c_float(0.0)
-    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms)), "mms_profile_end")
+    nat.check(L.mms_profile_end(ctypes.byref(k_launches), ctypes.byref(k_ms), None, 0),
+              "mms_profile_end")
     stream_kernel_ms = k_ms.value / max(k_launches.value, 1)
     total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
     if world > 1:

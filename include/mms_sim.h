@@ -186,10 +186,12 @@ const char *mms_last_error(void);
  * process brackets its sim_stream_kernel launch with two CUDA events on the
  * caller's stream (up to 256 launches; later ones are not recorded).
  * mms_profile_end() stops recording, waits for the recorded events and
- * returns the number of launches and their total duration.  Off by default;
- * events are created on first use, on the device current then. */
+ * returns the number of launches, their total duration and (when each_ms is
+ * not NULL) the duration of each of the first `capacity` launches, in call
+ * order.  Off by default; events are created on first use, on the device
+ * current then. */
 int mms_profile_begin(void);
-int mms_profile_end(int32_t *launches, float *total_ms);
+int mms_profile_end(int32_t *launches, float *total_ms, float *each_ms, int32_t capacity);
 
 /* Summation plan (host side; replaces nothing in the reference — it restates
  * numpy's reduction order, reached from controller.py:402). */

@@ -129,7 +129,8 @@ def lib():
     L.mms_trace_model_histogram.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_profile_begin.restype = ctypes.c_int
     L.mms_profile_end.restype = ctypes.c_int
-    L.mms_profile_end.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float)]
+    L.mms_profile_end.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float),
+                                  _vp, ctypes.c_int32]
     L.mms_sim_workspace_bytes.restype = ctypes.c_size_t
     L.mms_sim_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
                                           ctypes.POINTER(SimOptions), ctypes.c_uint32]

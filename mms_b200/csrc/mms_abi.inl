@@ -233,7 +233,7 @@ int mms_profile_begin(void)
     return MMS_OK;
 }
 
-int mms_profile_end(int32_t *launches, float *total_ms)
+int mms_profile_end(int32_t *launches, float *total_ms, float *each_ms, int32_t capacity)
 {
     using namespace mms;
     g_prof_on = 0;
@@ -243,6 +243,7 @@ int mms_profile_end(int32_t *launches, float *total_ms)
         MMS_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
         MMS_CUDA(cudaEventElapsedTime(&ms, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
         total += ms;
+        if (each_ms && i < capacity) each_ms[i] = ms;
     }
     if (launches) *launches = g_prof_count;
     if (total_ms) *total_ms = total;

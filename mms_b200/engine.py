@@ -247,6 +247,16 @@ class EncodedBatch:
         # for every placement that has such groups, see twin_groups()
         self.twins = twins
 
+    def take(self, index):
+        """The sub-batch of the placements `index` (ascending)."""
+        index = np.asarray(index, np.int64)
+        new_id = np.full(self.B, -1, np.int64)
+        new_id[index] = np.arange(len(index))
+        twins = [(int(new_id[b]), classes) for b, classes in (self.twins or []) if new_id[b] >= 0]
+        return EncodedBatch(len(index), self.M, self.G, self.P, self.T, self.S, self.C,
+                            self.model_off[index], self.model_rep[index], self.group_info[index],
+                            self.num_groups[index], self.num_replicas[index], twins)
+
     def repeat(self, count: int):
         """This batch `count` times over (placement 0 .. B-1, then again ...):
         the tables of one placement for `count` traces."""
@@ -551,7 +561,7 @@ def sim_options(chunk_requests=0, warmup_requests=0, repair_rounds=0, repair_seg
 class _Pending:
     """A submitted launch: device tensors and what collect() needs."""
     __slots__ = ("keep", "out", "B", "Bs", "M", "N", "full", "want_group_good", "h2d", "stream",
-                 "scratch")
+                 "scratch", "call", "trace")
 
 
 # Scratch buffers of finished launches, per device, kept for the next ones: a
@@ -584,6 +594,31 @@ def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
     nothing waits for the GPU.  With num_scored < B the candidates behind the
     first num_scored are mirrors (partner, mirror_swap as in mms_placements)
     and get no results."""
+    job = _prepare(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info, latency,
+                   latency_stride, flags, want_group_good, pinned, options, num_scored, partner,
+                   mirror_swap)
+    _enqueue(job)
+    return job
+
+
+def _enqueue(job: _Pending):
+    """The C call of a prepared launch, on the current stream (again and
+    again, if the caller wishes: everything it reads stays on the device)."""
+    trace = job.trace
+    cands, opts, ws, out, flags = job.call
+    with torch.cuda.device(trace.device):
+        tr, plan = trace.c_trace(), trace.c_plan()
+        rc = nat.lib().mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
+                                     _ptr(trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
+                                     ctypes.byref(out), flags, _stream_ptr())
+        nat.check(rc, "mms_sim_mixed")
+        job.stream = torch.cuda.current_stream()
+
+
+def _prepare(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+             latency, latency_stride, flags, want_group_good, pinned=False, options=None,
+             num_scored=None, partner=None, mirror_swap=None) -> _Pending:
+    """Uploads the tables and allocates scratch and outputs of one launch."""
     _require_cuda()
     L = nat.lib()
     dev = trace.device
@@ -628,12 +663,9 @@ def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
         out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood),
                           _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good),
                           _ptr(o_redo))
-        tr, plan = trace.c_trace(), trace.c_plan()
-        rc = L.mms_sim_mixed(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(plan),
-                             _ptr(trace.model_hist), ctypes.byref(opts), ctypes.byref(ws),
-                             ctypes.byref(out), flags, _stream_ptr())
-        nat.check(rc, "mms_sim_mixed")
         job.stream = torch.cuda.current_stream()
+    job.call = (cands, opts, ws, out, flags)
+    job.trace = trace
     job.keep = (d_off, d_rep, d_info, d_lat, d_partner, d_swap)
     job.scratch = ws_t
     job.out = (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good)
@@ -642,9 +674,9 @@ def _submit(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group
     return job
 
 
-def _collect(job: _Pending):
-    """Waits for a submitted launch and downloads its results.  Returns
-    (BatchResult, h2d_bytes, d2h_bytes)."""
+def _download(job: _Pending):
+    """Waits for the launch and copies its results to the host.  Returns
+    (BatchResult, d2h_bytes)."""
     (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good) = job.out
     Bs, M, N, full = job.Bs, job.M, job.N, job.full
     res = BatchResult()
@@ -664,14 +696,38 @@ def _collect(job: _Pending):
                                  res.status))
     if full:
         d2h += res.finish.nbytes + res.good.nbytes
-    job.keep = job.out = None
-    _return_scratch(job.scratch.device, job.scratch)   # every kernel that used it has finished
-    job.scratch = None
+    return res, d2h
+
+
+def _release(job: _Pending):
+    """Hands the scratch buffer back; every kernel that used it has finished."""
+    job.keep = job.out = job.call = None
+    if job.scratch is not None:
+        _return_scratch(job.scratch.device, job.scratch)
+        job.scratch = None
+
+
+def _check_status(res):
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         raise RuntimeError(f"simulator kernel reported status {int(res.status[bad])} "
                            f"for candidate {bad} (bad table index or capacity overflow)")
-    return res, job.h2d, d2h
+
+
+def _collect(job):
+    """Waits for a submitted launch and downloads its results.  Returns
+    (BatchResult, h2d_bytes, d2h_bytes)."""
+    if isinstance(job, ResidentBatch):
+        res, d2h = job.results()
+        h2d = job.h2d_bytes
+        job.release()
+        _check_status(res)
+        return res, h2d, d2h
+    res, d2h = _download(job)
+    h2d = job.h2d
+    _release(job)
+    _check_status(res)
+    return res, h2d, d2h
 
 
 def _launch(*args, **kwargs):
@@ -680,31 +736,126 @@ def _launch(*args, **kwargs):
     return _collect(_submit(*args, **kwargs))
 
 
+SPLIT_MIN_EASY = 512      # placements without mirrors a batch must have to be split
+SPLIT_MIN_HARD = 32       # ... and placements with mirrors
+_SIDE_STREAMS = {}
+
+
+def _side_streams(main):
+    """Two side streams per calling stream, so that batches launched from
+    different streams do not queue up behind each other."""
+    key = (main.device, main.cuda_stream)
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = (torch.cuda.Stream(device=main.device),
+                              torch.cuda.Stream(device=main.device))
+    return _SIDE_STREAMS[key]
+
+
+class ResidentBatch:
+    """An encoded batch with its tables, scratch and outputs on the GPU, ready
+    to be launched (any number of times).
+
+    A batch whose placements partly have mirrors is launched as TWO calls of
+    mms_sim_mixed on two side streams: the placements with mirrors first, cut
+    into many short chunks, and the rest beside them.  The first finish their
+    speculative pass early, and their repair rounds — a few long, serial
+    re-simulations that leave the GPU almost idle — run while the rest are
+    still in theirs.  Results are the same as from one call."""
+
+    def __init__(self, trace, enc: EncodedBatch, table: LatencyTable, group_good=False,
+                 pinned=False, options=None, mirrors=True, split=True):
+        self.trace, self.enc = trace, enc
+        dev = trace.device
+        ext_owner = [b for b, cl in (enc.twins or []) if mirror_swaps(cl)] if mirrors else []
+        parts = [(None, enc)]
+        if (split and len(ext_owner) >= SPLIT_MIN_HARD
+                and enc.B - len(ext_owner) >= SPLIT_MIN_EASY):
+            hard = np.asarray(ext_owner, np.int64)
+            easy = np.setdiff1d(np.arange(enc.B), hard)
+            parts = [(hard, enc.take(hard)), (easy, enc.take(easy))]
+        self.index = [p[0] for p in parts]
+        self.jobs = []
+        self.h2d_bytes = 0
+        lat = table.device(dev)
+        for _, e in parts:
+            ext = e.with_mirrors() if mirrors else None
+            if ext is not None:
+                off, rep, info, partner, swap = ext
+                job = _prepare(trace, len(partner), e.M, e.G, e.P, e.T, e.S, e.C, off, rep, info,
+                               lat, 0, 0, group_good, pinned, options, e.B, partner, swap)
+            else:
+                job = _prepare(trace, e.B, e.M, e.G, e.P, e.T, e.S, e.C, e.model_off, e.model_rep,
+                               e.group_info, lat, 0, 0, group_good, pinned, options)
+            self.jobs.append(job)
+            self.h2d_bytes += job.h2d
+
+    def launch(self):
+        """Enqueues the call(s); stream-ordered with respect to the current
+        stream on both sides, nothing waits for the GPU."""
+        if len(self.jobs) == 1:
+            _enqueue(self.jobs[0])
+            return self
+        main = torch.cuda.current_stream(self.trace.device)
+        sides = _side_streams(main)
+        for job, side in zip(self.jobs, sides):
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                _enqueue(job)
+        for side in sides:
+            main.wait_stream(side)
+        for job in self.jobs:           # results are read in order behind the join
+            job.stream = main
+        return self
+
+    def device_outputs(self):
+        """[(candidate indices or None, good_total i64[.], latency_sum f64[.])] per call, on the
+        device."""
+        return [(idx, job.out[4][:job.Bs], job.out[5][:job.Bs])
+                for idx, job in zip(self.index, self.jobs)]
+
+    def results(self):
+        """Waits and downloads: (BatchResult in the order of the batch, d2h bytes)."""
+        done = [_download(job) for job in self.jobs]
+        d2h = sum(d[1] for d in done)
+        if len(done) == 1:
+            return done[0][0], d2h
+        res = BatchResult()
+        B = self.enc.B
+        for name in BatchResult.__slots__:
+            first = getattr(done[0][0], name)
+            if first is None:
+                setattr(res, name, None)
+                continue
+            whole = np.zeros((B,) + first.shape[1:], first.dtype)
+            for idx, (part, _) in zip(self.index, done):
+                whole[idx] = getattr(part, name)
+            setattr(res, name, whole)
+        return res, d2h
+
+    def release(self):
+        for job in self.jobs:
+            _release(job)
+
+
 def submit_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable, group_good=False,
-                 pinned=False, options=None, mirrors=True) -> _Pending:
+                 pinned=False, options=None, mirrors=True, split=True) -> ResidentBatch:
     """run_batch without waiting: returns a handle for collect_batch."""
-    ext = enc.with_mirrors() if mirrors else None
-    if ext is not None:
-        off, rep, info, partner, swap = ext
-        return _submit(trace, len(partner), enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, off, rep,
-                       info, table.device(trace.device), 0, 0, group_good, pinned, options,
-                       enc.B, partner, swap)
-    return _submit(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
-                   enc.model_off, enc.model_rep, enc.group_info,
-                   table.device(trace.device), 0, 0, group_good, pinned, options)
+    return ResidentBatch(trace, enc, table, group_good, pinned, options, mirrors, split).launch()
 
 
 collect_batch = _collect
 
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
-              per_request=False, group_good=False, pinned=False, options=None, mirrors=True):
+              per_request=False, group_good=False, pinned=False, options=None, mirrors=True,
+              split=True):
     """Simulates every placement of `enc` against `trace`
     (simulate_requests_mixed, controller.py:561-628).  `mirrors`: placements
     with interchangeable groups get a mirror candidate (a speed-up of the
     time-parallel execution; results are the same with and without)."""
     if not per_request:
-        return _collect(submit_batch(trace, enc, table, group_good, pinned, options, mirrors))
+        return _collect(submit_batch(trace, enc, table, group_good, pinned, options, mirrors,
+                                     split))
     return _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
                    enc.model_off, enc.model_rep, enc.group_info,
                    table.device(trace.device), 0, nat.FLAG_PER_REQUEST, group_good, pinned,

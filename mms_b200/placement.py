@@ -127,8 +127,9 @@ class PlacementEvaluator:
                                         len(self.model_names), device=device)
         self.table = engine.LatencyTable(self.prof_ress)
         self.options = options          # engine.sim_options(...) or None
-        self.pipeline_parts = 4         # a long list is encoded and launched in parts
+        self.pipeline_parts = 3         # a long list is encoded and launched in parts
         self.pipeline_min_part = 768    # placements per part, at least
+        self.pipeline_split = False     # parts overlap each other already
         self._streams = []
         self.last_resimulated = None
         self.last_h2d_bytes = 0
@@ -162,7 +163,7 @@ class PlacementEvaluator:
             self._streams[k].wait_stream(main)           # the trace was uploaded there
             with torch.cuda.stream(self._streams[k]):
                 jobs.append(engine.submit_batch(self.trace, enc, self.table, pinned=pinned,
-                                                options=self.options))
+                                                options=self.options, split=self.pipeline_split))
             encs.append(enc)
         done = [engine.collect_batch(job) for job in jobs]
         for k in range(parts):

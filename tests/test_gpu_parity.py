@@ -373,7 +373,7 @@ def test_pipelined_evaluation_equals_one_launch(loaded):
     from mms_b200.placement import PlacementEvaluator
     case = cases.candidate_batch_case(num_candidates=1700, duration=200.0, placement_seed=3)
     ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload)
-    ev.pipeline_min_part = 400
+    ev.pipeline_min_part, ev.pipeline_parts = 400, 4
     enc4, res4 = ev.evaluate(case.placements)
     assert len(enc4.parts) == 4 and enc4.B == 1700
     scores4 = ev.scores_from(enc4, res4)
@@ -423,3 +423,27 @@ def test_trace_sweep_one_placement_many_traces(loaded):
             assert goodput == np.mean(good), t
             assert np.array_equal(per_model, mgood / (mreq + eps)), t
             assert np.array_equal(np.array(group_req), greq), t
+
+
+def test_split_launch_equals_one_launch(loaded, monkeypatch):
+    """Placements with mirror candidates go into a launch of their own beside
+    the rest (two streams); every output equals the single launch's, in the
+    order of the batch."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import PlacementEvaluator
+    monkeypatch.setattr(engine, "SPLIT_MIN_HARD", 4)
+    monkeypatch.setattr(engine, "SPLIT_MIN_EASY", 16)
+    case = cases.candidate_batch_case(num_candidates=300, duration=400.0, placement_seed=11)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload)
+    enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
+    batch = engine.ResidentBatch(ev.trace, enc, ev.table, group_good=True)
+    assert len(batch.jobs) == 2 and len(batch.index[0]) >= 4
+    assert sorted(np.concatenate(batch.index).tolist()) == list(range(300))
+    first, _ = batch.launch().results()
+    again, _ = batch.launch().results()          # a resident batch can be launched repeatedly
+    batch.release()
+    one, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True, split=False)
+    for name in ("model_num_requests", "model_num_good", "group_num_requests", "group_num_good",
+                 "good_total", "latency_sum", "status"):
+        assert getattr(first, name).tobytes() == getattr(one, name).tobytes(), name
+        assert getattr(again, name).tobytes() == getattr(one, name).tobytes(), name

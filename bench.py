@@ -33,6 +33,29 @@ FALLBACK_HBM_GBS = 6650.0
 STREAM_KERNEL_DRAM_BYTES = 35223808 + 546196736
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Libraries write banners to stdout (NCCL prints its version on the first
+    collective): everything but the result line goes to stderr."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    """The ONE JSON line of the contract, on the real stdout."""
+    text = (json.dumps(line) + "\n").encode()
+    sys.stdout.flush()
+    if _REAL_STDOUT is None:
+        os.write(1, text)
+    else:
+        os.write(_REAL_STDOUT, text)
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,7 +205,7 @@ def run_reference(args):
     value = float(np.mean([r for r, _ in rates]))
     ms = float(np.mean([d for _, d in rates])) * 1e3
     sample = f"{per_step} of {args.candidates} candidates x {len(case.workload)} requests per step"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
@@ -193,7 +216,7 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })
 
 
 def run_b200(args):
@@ -358,7 +381,7 @@ def run_b200(args):
             line["cpu_baseline"] = {
                 "value": rate, "unit": UNIT, "cores": 1, "kind": "port",
                 "sample": f"{count} of {B} candidates x {N} requests, {dt:.1f} s"}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -553,13 +576,14 @@ def run_sweep(args):
             dt = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": done / dt, "unit": UNIT, "cores": 1, "kind": "port",
                                     "sample": f"{done} requests of the first traces, {dt:.1f} s"}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
     args = parse_args()
+    quiet_stdout()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "sweep":

@@ -546,13 +546,16 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
     a.model_num_requests = out->model_num_requests; a.model_num_good = out->model_num_good;
     a.group_num_requests = out->group_num_requests; a.group_num_good = out->group_num_good;
     a.status = out->status;
-    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H);
+    // one candidate per warp unless there are too many candidates for that to fill the GPU
+    // better than warps of 32 candidates do
+    a.lanes = B <= 16384 ? 1 : kLanes;
+    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H, a.lanes);
     if (L.total > 227 * 1024) return MMS_ERR_UNSUPPORTED;
 
     cudaStream_t st = (cudaStream_t)stream;
     MMS_CUDA(cudaFuncSetAttribute(sim_batching_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   (int)L.total));
-    sim_batching_kernel<<<(B + kLanes - 1) / kLanes, kLanes, L.total, st>>>(a);
+    sim_batching_kernel<<<(B + a.lanes - 1) / a.lanes, kLanes, L.total, st>>>(a);
     MMS_CUDA(cudaGetLastError());
     double *leaf_sums = (double *)ws->ptr;
     if (plan->num_leaves > 0) {

@@ -33,6 +33,8 @@ struct BatchArgs {
     const uint32_t *group_cfg;    // [B][G]   first slot | stages<<8 | column<<16
     const float *latency;         // [M][C][S][NB]
     int64_t latency_stride;
+    int32_t lanes;                // candidates interleaved in one block's shared memory: 32
+                                  //   (a warp of candidates) or 1 (one candidate per warp)
     double *finish;               // [B][N]
     uint8_t *good;                // [B][N]
     int32_t *model_num_requests;  // [B][M]
@@ -47,7 +49,7 @@ struct BatchSmem {
         model_off, group_off, group_mod, total;
 };
 
-__host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int H)
+__host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int H, int kLanes)
 {
     BatchSmem L;
     size_t off = 0;
@@ -68,6 +70,7 @@ __host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int 
 }
 
 // One candidate's state; every member is an element offset (lane included).
+// Entries are a.lanes elements apart.
 struct BLane {
     uint32_t clk, idle, heap_t, heap_g, qhead, qlen;
     uint32_t model_req, model_good, group_req, group_good;
@@ -90,55 +93,55 @@ __device__ inline void heap_push(const BatchArgs &a, BLane &ln, double t, uint32
     uint32_t i = ln.heap_n++;
     while (i > 0) {
         const uint32_t p = (i - 1) >> 1;
-        const double tp = SM_F64(ln.heap_t + p * kLanes);
-        const uint32_t gp = SM_U32(ln.heap_g + p * kLanes);
+        const double tp = SM_F64(ln.heap_t + p * a.lanes);
+        const uint32_t gp = SM_U32(ln.heap_g + p * a.lanes);
         if (!event_less(t, g, tp, gp)) break;
-        SM_F64(ln.heap_t + i * kLanes) = tp;
-        SM_U32(ln.heap_g + i * kLanes) = gp;
+        SM_F64(ln.heap_t + i * a.lanes) = tp;
+        SM_U32(ln.heap_g + i * a.lanes) = gp;
         i = p;
     }
-    SM_F64(ln.heap_t + i * kLanes) = t;
-    SM_U32(ln.heap_g + i * kLanes) = g;
+    SM_F64(ln.heap_t + i * a.lanes) = t;
+    SM_U32(ln.heap_g + i * a.lanes) = g;
 }
 
-__device__ inline void heap_pop(BLane &ln, double &t, uint32_t &g)
+__device__ inline void heap_pop(const BatchArgs &a, BLane &ln, double &t, uint32_t &g)
 {
     t = SM_F64(ln.heap_t);
     g = SM_U32(ln.heap_g);
     const uint32_t n = --ln.heap_n;
     if (n == 0) return;
-    const double te = SM_F64(ln.heap_t + n * kLanes);
-    const uint32_t ge = SM_U32(ln.heap_g + n * kLanes);
+    const double te = SM_F64(ln.heap_t + n * a.lanes);
+    const uint32_t ge = SM_U32(ln.heap_g + n * a.lanes);
     uint32_t i = 0;
     for (;;) {
         uint32_t c = 2 * i + 1;
         if (c >= n) break;
-        double tc = SM_F64(ln.heap_t + c * kLanes);
-        uint32_t gc = SM_U32(ln.heap_g + c * kLanes);
+        double tc = SM_F64(ln.heap_t + c * a.lanes);
+        uint32_t gc = SM_U32(ln.heap_g + c * a.lanes);
         if (c + 1 < n) {
-            const double tr = SM_F64(ln.heap_t + (c + 1) * kLanes);
-            const uint32_t gr = SM_U32(ln.heap_g + (c + 1) * kLanes);
+            const double tr = SM_F64(ln.heap_t + (c + 1) * a.lanes);
+            const uint32_t gr = SM_U32(ln.heap_g + (c + 1) * a.lanes);
             if (event_less(tr, gr, tc, gc)) { c += 1; tc = tr; gc = gr; }
         }
         if (!event_less(tc, gc, te, ge)) break;
-        SM_F64(ln.heap_t + i * kLanes) = tc;
-        SM_U32(ln.heap_g + i * kLanes) = gc;
+        SM_F64(ln.heap_t + i * a.lanes) = tc;
+        SM_U32(ln.heap_g + i * a.lanes) = gc;
         i = c;
     }
-    SM_F64(ln.heap_t + i * kLanes) = te;
-    SM_U32(ln.heap_g + i * kLanes) = ge;
+    SM_F64(ln.heap_t + i * a.lanes) = te;
+    SM_U32(ln.heap_g + i * a.lanes) = ge;
 }
 
 // select_model, :654-664: the group's model whose queue head arrived first.
 __device__ inline int32_t pick_model(const BatchArgs &a, const BLane &ln, uint32_t g)
 {
-    const uint32_t lo = SM_U16(ln.goff + g * kLanes), hi = SM_U16(ln.goff + (g + 1) * kLanes);
+    const uint32_t lo = SM_U16(ln.goff + g * a.lanes), hi = SM_U16(ln.goff + (g + 1) * a.lanes);
     double first = kInf;
     int32_t pick = -1;
     for (uint32_t e = lo; e < hi; ++e) {
-        const uint32_t m = SM_U16(ln.gmod + e * kLanes);
-        if ((int32_t)SM_U32(ln.qlen + m * kLanes) > 0) {
-            const double ts = a.arrivals[(int32_t)SM_U32(ln.qhead + m * kLanes)];
+        const uint32_t m = SM_U16(ln.gmod + e * a.lanes);
+        if ((int32_t)SM_U32(ln.qlen + m * a.lanes) > 0) {
+            const double ts = a.arrivals[(int32_t)SM_U32(ln.qhead + m * a.lanes)];
             if (ts < first) { first = ts; pick = (int32_t)m; }
         }
     }
@@ -153,15 +156,15 @@ __device__ inline bool meets_deadline(const BatchArgs &a, const BLane &ln, doubl
     const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
     double t = ts;
     for (uint32_t k = 0; k < ns; ++k)
-        t = fmax(SM_F64(ln.clk + (slot + k) * kLanes), t) + (double)__ldg(lat + (size_t)k * a.NB);
+        t = fmax(SM_F64(ln.clk + (slot + k) * a.lanes), t) + (double)__ldg(lat + (size_t)k * a.NB);
     return t + kOverhead <= deadline;
 }
 
 __device__ inline int32_t queue_pop(const BatchArgs &a, BLane &ln, uint32_t m)
 {
-    const int32_t r = (int32_t)SM_U32(ln.qhead + m * kLanes);
-    SM_U32(ln.qhead + m * kLanes) = (uint32_t)a.next_same[r];
-    SM_U32(ln.qlen + m * kLanes) -= 1;
+    const int32_t r = (int32_t)SM_U32(ln.qhead + m * a.lanes);
+    SM_U32(ln.qhead + m * a.lanes) = (uint32_t)a.next_same[r];
+    SM_U32(ln.qlen + m * a.lanes) -= 1;
     return r;
 }
 
@@ -171,17 +174,17 @@ __device__ inline int32_t queue_pop(const BatchArgs &a, BLane &ln, uint32_t m)
 __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int32_t m_in,
                                    uint32_t g)
 {
-    const uint32_t cfg = SM_U32(ln.gcfg + g * kLanes);
+    const uint32_t cfg = SM_U32(ln.gcfg + g * a.lanes);
     const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu, col = cfg >> 16;
     int32_t m = m_in;
     while (m >= 0) {
         // :677-686 drop queue heads that cannot make their deadline even alone
         int32_t head = -1;
-        while ((int32_t)SM_U32(ln.qlen + m * kLanes) > 0) {
+        while ((int32_t)SM_U32(ln.qlen + m * a.lanes) > 0) {
             const int32_t r = queue_pop(a, ln, m);
             const double dl = a.arrivals[r] + (double)a.slos[r];
             if (meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[0], dl)) { head = r; break; }
-            SM_U32(ln.group_req + g * kLanes) += 1;
+            SM_U32(ln.group_req + g * a.lanes) += 1;
             ln.finish[r] = a.arrivals[r];
             ln.good[r] = 0;
         }
@@ -190,7 +193,7 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
         const double deadline = a.arrivals[head] + (double)a.slos[head];
         int32_t bs = 1, bcol = a.batch_cols[0];
         for (int j = 1; j < a.NB; ++j) {
-            if (a.batch_sizes[j] - 1 > (int32_t)SM_U32(ln.qlen + m * kLanes)) break;
+            if (a.batch_sizes[j] - 1 > (int32_t)SM_U32(ln.qlen + m * a.lanes)) break;
             if (!meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[j], deadline)) break;
             bs = a.batch_sizes[j];
             bcol = a.batch_cols[j];
@@ -199,8 +202,8 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
         const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
         double t = ts + kOverhead, t_first = 0.0;
         for (uint32_t k = 0; k < ns; ++k) {
-            t = fmax(t, SM_F64(ln.clk + (slot + k) * kLanes)) + (double)__ldg(lat + (size_t)k * a.NB);
-            SM_F64(ln.clk + (slot + k) * kLanes) = t;   // each stage reads only its own clock
+            t = fmax(t, SM_F64(ln.clk + (slot + k) * a.lanes)) + (double)__ldg(lat + (size_t)k * a.NB);
+            SM_F64(ln.clk + (slot + k) * a.lanes) = t;   // each stage reads only its own clock
             if (k == 0) t_first = t;
         }
         ln.finish[head] = t;
@@ -211,11 +214,11 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
             ln.good[r] = 1;
         }
         // :727-732
-        SM_F64(ln.idle + g * kLanes) = t_first;
+        SM_F64(ln.idle + g * a.lanes) = t_first;
         heap_push(a, ln, t_first, g);
-        SM_U32(ln.group_req + g * kLanes) += (uint32_t)bs;
-        SM_U32(ln.group_good + g * kLanes) += (uint32_t)bs;
-        SM_U32(ln.model_good + m * kLanes) += (uint32_t)bs;
+        SM_U32(ln.group_req + g * a.lanes) += (uint32_t)bs;
+        SM_U32(ln.group_good + g * a.lanes) += (uint32_t)bs;
+        SM_U32(ln.model_good + m * a.lanes) += (uint32_t)bs;
         return;
     }
 }
@@ -223,10 +226,13 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
 __global__ void __launch_bounds__(kLanes, 1)
 sim_batching_kernel(const BatchArgs a)
 {
+    // lanes == 32: a warp of 32 candidates; lanes == 1: thread 0 of the block alone, so that
+    // the candidate's branches are not serialised against 31 others'
+    if ((int)threadIdx.x >= a.lanes) return;
     const int lane = threadIdx.x;
-    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
+    const int64_t b = (int64_t)blockIdx.x * a.lanes + lane;
     if (b >= a.B) return;
-    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H);
+    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H, a.lanes);
     BLane ln;
     ln.clk = (uint32_t)(L.clocks / 8) + lane;
     ln.idle = (uint32_t)(L.idle / 8) + lane;
@@ -235,9 +241,9 @@ sim_batching_kernel(const BatchArgs a)
     ln.qhead = (uint32_t)(L.qhead / 4) + lane;
     ln.qlen = (uint32_t)(L.qlen / 4) + lane;
     ln.model_req = (uint32_t)(L.counters / 4) + lane;
-    ln.model_good = ln.model_req + (uint32_t)a.M * kLanes;
-    ln.group_req = ln.model_good + (uint32_t)a.M * kLanes;
-    ln.group_good = ln.group_req + (uint32_t)a.G * kLanes;
+    ln.model_good = ln.model_req + (uint32_t)a.M * a.lanes;
+    ln.group_req = ln.model_good + (uint32_t)a.M * a.lanes;
+    ln.group_good = ln.group_req + (uint32_t)a.G * a.lanes;
     ln.mrep = (uint32_t)(L.model_rep / 4) + lane;
     ln.gcfg = (uint32_t)(L.group_cfg / 4) + lane;
     ln.moff = (uint32_t)(L.model_off / 2) + lane;
@@ -250,10 +256,10 @@ sim_batching_kernel(const BatchArgs a)
     ln.good = a.good + (size_t)b * a.N;
 
     // tables on chip, every index checked
-    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
-    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * kLanes) = 0.0;
-    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * kLanes) = 0; SM_U32(ln.qlen + m * kLanes) = 0; }
-    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * kLanes) = 0;
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = 0.0;
+    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = 0.0;
+    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * a.lanes) = 0; SM_U32(ln.qlen + m * a.lanes) = 0; }
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * a.lanes) = 0;
     for (int g = 0; g < a.G; ++g) {
         uint32_t cfg = a.group_cfg[(size_t)b * a.G + g];
         const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu;
@@ -261,35 +267,35 @@ sim_batching_kernel(const BatchArgs a)
             ln.status |= MMS_STATUS_BAD_INDEX;
             cfg = 0;
         }
-        SM_U32(ln.gcfg + g * kLanes) = cfg;
+        SM_U32(ln.gcfg + g * a.lanes) = cfg;
     }
     uint32_t prev = 0;
     for (int m = 0; m <= a.M; ++m) {
         uint32_t o = a.model_off[(size_t)b * (a.M + 1) + m];
         if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
-        SM_U16(ln.moff + m * kLanes) = (uint16_t)o;
+        SM_U16(ln.moff + m * a.lanes) = (uint16_t)o;
         prev = o;
     }
     for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
         uint32_t ent = e < prev ? a.model_rep[(size_t)b * a.P + e] : 0u;
         if (e < prev) {
             const uint32_t g = ent & 0xFFu;
-            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (SM_U32(ln.gcfg + g * kLanes) & 0xFFFFu))
+            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (SM_U32(ln.gcfg + g * a.lanes) & 0xFFFFu))
                 ln.status |= MMS_STATUS_BAD_INDEX;
         }
-        SM_U32(ln.mrep + e * kLanes) = ent;
+        SM_U32(ln.mrep + e * a.lanes) = ent;
     }
     prev = 0;
     for (int g = 0; g <= a.G; ++g) {
         uint32_t o = a.group_off[(size_t)b * (a.G + 1) + g];
         if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
-        SM_U16(ln.goff + g * kLanes) = (uint16_t)o;
+        SM_U16(ln.goff + g * a.lanes) = (uint16_t)o;
         prev = o;
     }
     for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
         uint32_t m = e < prev ? a.group_mod[(size_t)b * a.P + e] : 0u;
         if (m >= (uint32_t)a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = 0; }
-        SM_U16(ln.gmod + e * kLanes) = (uint16_t)m;
+        SM_U16(ln.gmod + e * a.lanes) = (uint16_t)m;
     }
 
     if (!(ln.status & MMS_STATUS_BAD_INDEX)) {
@@ -298,7 +304,7 @@ sim_batching_kernel(const BatchArgs a)
             // :739-744 groups whose first stage became free before this arrival
             while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
                 double te; uint32_t ge;
-                heap_pop(ln, te, ge);
+                heap_pop(a, ln, te, ge);
                 const int32_t pm = pick_model(a, ln, ge);
                 if (pm < 0) break;                     // the reference breaks here, not continues
                 serve_group(a, ln, te, pm, ge);
@@ -306,7 +312,7 @@ sim_batching_kernel(const BatchArgs a)
             int32_t m = a.model_ids[i];
             if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
             uint32_t lo = 0, hi = 0;
-            if (m >= 0) { lo = SM_U16(ln.moff + m * kLanes); hi = SM_U16(ln.moff + (m + 1) * kLanes); }
+            if (m >= 0) { lo = SM_U16(ln.moff + m * a.lanes); hi = SM_U16(ln.moff + (m + 1) * a.lanes); }
             if (lo == hi) {                            // :748-757 unknown model or no replica
                 ln.finish[i] = ts;
                 ln.good[i] = 0;
@@ -316,37 +322,37 @@ sim_batching_kernel(const BatchArgs a)
             uint32_t pick = 0;
             bool found = false;
             for (uint32_t e = lo; e < hi; ++e) {
-                const uint32_t ent = SM_U32(ln.mrep + e * kLanes);
+                const uint32_t ent = SM_U32(ln.mrep + e * a.lanes);
                 const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
-                const double c = SM_F64(ln.clk + last * kLanes);
+                const double c = SM_F64(ln.clk + last * a.lanes);
                 if (c < best) { best = c; pick = ent; found = true; }
             }
             // :772-773 the request joins its MODEL's queue
-            if ((int32_t)SM_U32(ln.qlen + m * kLanes) == 0) SM_U32(ln.qhead + m * kLanes) = (uint32_t)i;
-            SM_U32(ln.qlen + m * kLanes) += 1;
-            SM_U32(ln.model_req + m * kLanes) += 1;
+            if ((int32_t)SM_U32(ln.qlen + m * a.lanes) == 0) SM_U32(ln.qhead + m * a.lanes) = (uint32_t)i;
+            SM_U32(ln.qlen + m * a.lanes) += 1;
+            SM_U32(ln.model_req + m * a.lanes) += 1;
             const uint32_t g = pick & 0xFFu;
-            if (found && ts >= SM_F64(ln.idle + g * kLanes))   // :776-778
+            if (found && ts >= SM_F64(ln.idle + g * a.lanes))   // :776-778
                 serve_group(a, ln, ts, m, g);
         }
         // :781-787 drain
         while (ln.heap_n > 0) {
             double te; uint32_t ge;
-            heap_pop(ln, te, ge);
+            heap_pop(a, ln, te, ge);
             const int32_t pm = pick_model(a, ln, ge);
             if (pm < 0) continue;
             serve_group(a, ln, te, pm, ge);
         }
         for (int m = 0; m < a.M; ++m)                  // :789-790
-            if ((int32_t)SM_U32(ln.qlen + m * kLanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+            if ((int32_t)SM_U32(ln.qlen + m * a.lanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
     }
     for (int m = 0; m < a.M; ++m) {
-        a.model_num_requests[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_req + m * kLanes);
-        a.model_num_good[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_good + m * kLanes);
+        a.model_num_requests[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_req + m * a.lanes);
+        a.model_num_good[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_good + m * a.lanes);
     }
     for (int g = 0; g < a.G; ++g) {
-        a.group_num_requests[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_req + g * kLanes);
-        a.group_num_good[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_good + g * kLanes);
+        a.group_num_requests[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_req + g * a.lanes);
+        a.group_num_good[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_good + g * a.lanes);
     }
     a.status[b] = ln.status;
 }

@@ -921,9 +921,10 @@ def group_lists(model_off, model_rep, group_info, G):
 
 
 def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
-                    latency, latency_stride, batch_sizes, heap_capacity=0):
+                    latency, latency_stride, batch_sizes, heap_capacity=0, per_request=True):
     """simulate_requests_mixed_batching (controller.py:630-798) for every
-    candidate.  Always returns per-request outputs."""
+    candidate.  The kernel always writes per-request outputs (the latency sums
+    are formed from them); per_request=False does not download them."""
     _require_cuda()
     L = nat.lib()
     dev = trace.device
@@ -964,8 +965,8 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
         res.latency_sum = o_lsum.cpu().numpy()
         res.status = o_status.cpu().numpy().astype(np.uint32)
         res.resimulated = None
-        res.finish = o_fin.cpu().numpy()[:, :N]
-        res.good = o_good.cpu().numpy()[:, :N].astype(bool)
+        res.finish = o_fin.cpu().numpy()[:, :N] if per_request else None
+        res.good = o_good.cpu().numpy()[:, :N].astype(bool) if per_request else None
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         what = {nat.STATUS_HEAP_OVERFLOW: "event heap overflow (raise heap_capacity)",
@@ -978,11 +979,12 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
 
 
 def run_batch_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
-                       heap_capacity=0):
+                       heap_capacity=0, per_request=True):
     """Batching simulation of every placement of `enc`; `table` must have been
-    built with batch sizes."""
+    built with batch sizes.  per_request=False leaves the per-request outputs
+    (9 bytes per candidate and request) on the device."""
     if table.batch_sizes is None:
         raise ValueError("the latency table has no batch-size axis")
     return launch_batching(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, enc.model_off,
                            enc.model_rep, enc.group_info, table.device(trace.device), 0,
-                           table.batch_sizes, heap_capacity)
+                           table.batch_sizes, heap_capacity, per_request)

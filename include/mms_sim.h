@@ -121,7 +121,7 @@ typedef struct {
     int32_t max_placed;            /* P: row length of model_rep                 */
     int32_t max_slots;             /* T: clock slots per candidate (<= 256)      */
     int32_t max_stages;            /* S: last axis of latency                    */
-    int32_t num_columns;           /* C (<= 255)                                 */
+    int32_t num_columns;           /* C (<= 254)                                 */
     int32_t num_scored;            /* 0 = num_candidates (no mirrors)            */
     const uint16_t *model_off;
     const uint32_t *model_rep;
@@ -163,6 +163,7 @@ typedef struct {
     size_t bytes;
 } mms_workspace;
 
+/* Outputs.  B below is num_scored when the batch has mirror candidates. */
 typedef struct {
     int32_t *model_num_requests;   /* i32[B][M]                                  */
     int32_t *model_num_good;       /* i32[B][M]                                  */

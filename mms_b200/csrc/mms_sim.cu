@@ -15,21 +15,29 @@
 //                   request (run-in, nothing recorded), stores the clock
 //                   vector it has when the chunk proper begins and after
 //                   every segment, and records counters and latency sums.
-//   validate kernel one thread per chunk boundary: is the state the chunk was
-//                   started from EQUIVALENT to the state the previous chunk
-//                   ended in (states_equivalent: equal futures, provably)?
-//                   If not, the true state is copied in and the chunk goes on
-//                   a work list.
+//                   A MIRROR candidate (a copy of a candidate with
+//                   interchangeable groups) exchanges those groups' clocks
+//                   after the run-in: a second guess at the state.
+//   validate kernel one thread per stored run and chunk boundary: which
+//                   stored runs of the next chunk start from a state
+//                   EQUIVALENT to the one this run ended in
+//                   (states_equivalent: equal futures, provably)?
+//   resolve kernel  one thread per candidate follows the chain of chunks
+//                   through those answers; where no stored run continues
+//                   the chain, the true state is copied in and the chunk
+//                   goes on a work list.
 //   repair kernel   one thread per listed chunk re-simulates it from the true
 //                   state, segment by segment, until its state is equivalent
-//                   to what the previous run had at that point.
-//                   validate + repair run a few rounds (a repaired chunk can
-//                   end differently and invalidate its successor).
+//                   to what a stored run had at that point; the rest of the
+//                   chunk is taken from that run.
+//                   validate + resolve + repair run a few rounds (a repaired
+//                   chunk can end differently and invalidate its successor).
 //   chain kernel    one thread per candidate walks all boundaries in order
 //                   and repairs in place whatever the rounds left — it makes
 //                   the result exact whatever the chunking and the rounds.
 //   finalize        adds the per-segment counters and combines the per-leaf
-//                   latency sums in numpy's pairwise order.
+//                   latency sums of the selected runs in numpy's pairwise
+//                   order.
 //
 // The 32 lanes of a warp are 32 candidates on the same chunk (one broadcast
 // load per trace element) whenever the batch has 32 or more candidates.

@@ -9,8 +9,8 @@
 // fetched two requests ahead, served by L2).  Everything is addressed by
 // 32-bit element offsets into the block's one dynamic shared array, which
 // keeps the accesses plain LDS/STS with immediate offsets.  The dependent
-// chain per request is kept short: trace values are fetched two requests
-// ahead and the replica list one request ahead (neither depends on simulator
+// chain per request is kept short: trace values are fetched three requests
+// ahead and the replica row two requests ahead (neither depends on simulator
 // state), the clocks of up to 4 replicas and of up to 8 pipeline stages are
 // loaded together, and the max/add chain runs in registers.
 #pragma once

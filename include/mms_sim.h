@@ -285,7 +285,13 @@ typedef struct {
 int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_t *next_same,
                               void *stream);
 
-size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands);
+/* Scratch of mms_sim_batching (depends on the heap capacity in `batching`). */
+size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands,
+                                        const mms_batching *batching);
+
+/* The trace is cut in time like in mms_sim_mixed (speculative chunks, then an
+ * exact chain pass), so results do not depend on the cut; out->resimulated,
+ * when not NULL, gets the number of chunks the chain pass re-simulated. */
 
 int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
                      const mms_batching *batching, const int32_t *next_same,

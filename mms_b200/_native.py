@@ -146,7 +146,8 @@ def lib():
     L.mms_trace_next_same_model.restype = ctypes.c_int
     L.mms_trace_next_same_model.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_sim_batching_workspace_bytes.restype = ctypes.c_size_t
-    L.mms_sim_batching_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements)]
+    L.mms_sim_batching_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
+                                                   ctypes.POINTER(Batching)]
     L.mms_sim_batching.restype = ctypes.c_int
     L.mms_sim_batching.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
                                    ctypes.POINTER(Batching), _vp, ctypes.POINTER(SumPlan),

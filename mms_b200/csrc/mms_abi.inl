@@ -217,7 +217,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 
 extern "C" {
 
-int mms_abi_version(void) { return 5; }
+int mms_abi_version(void) { return 6; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 
@@ -480,11 +480,74 @@ int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_
     return MMS_OK;
 }
 
-size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands)
+}  // extern "C"
+
+namespace mms {
+
+struct BatchGeometry {
+    int32_t lanes, H, K, chunk_len, warmup;
+    size_t smem, off_leaf, off_start, off_end, off_counters, off_carry, off_flag, total;
+};
+
+// Chunking and scratch layout of one mms_sim_batching call.
+static int plan_batching(int64_t N, const mms_placements *c, const mms_batching *bt,
+                         BatchGeometry *g)
 {
-    if (!cands || num_requests < 0 || num_requests > 0x7FFFFFFF) return 0;
-    return mms::align256(sizeof(double) * (size_t)mms::plan_leaves(num_requests) *
-                         (size_t)cands->num_candidates + 8);
+    if (!c || !bt || N < 0 || N > 0x7FFFFFFF || c->num_candidates < 0) return MMS_ERR_ARG;
+    const int64_t B = c->num_candidates;
+    g->H = bt->heap_capacity > 0 ? bt->heap_capacity : 4 * c->max_groups + 16;
+    // one candidate per warp unless there are too many candidates for that to fill the GPU
+    // better than warps of 32 candidates do
+    g->lanes = B <= 16384 ? 1 : kLanes;
+    const BatchSmem L = batch_smem(c->num_models, c->max_groups, c->max_placed, c->max_slots,
+                                   g->H, g->lanes);
+    g->smem = L.total;
+    int sm_count = 148, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        sm_count = 148;
+    }
+    // Chunks: with one candidate per warp, as many as fill ONE wave of the resident blocks,
+    // none shorter than twice the run-in — and none at all when that leaves fewer than four:
+    // the kernels are issue-bound (one lane of each warp works), so a batch that fills a
+    // quarter of the GPU by itself gains less from cutting than the re-simulated chunks cost.
+    g->warmup = 2048;
+    int64_t K = 1;
+    if (g->lanes == 1 && B > 0 && N >= 4 * 4096) {
+        int64_t per_sm = (int64_t)(233472 / (L.total + 1024));
+        if (per_sm > kBatchBlocksPerSm) per_sm = kBatchBlocksPerSm;
+        if (per_sm < 1) per_sm = 1;
+        K = per_sm * sm_count / B;
+        if (K > N / 4096) K = N / 4096;
+        if (K < 4) K = 1;
+    }
+    const int64_t len = (N + K - 1) / (K > 0 ? K : 1);
+    g->chunk_len = (int32_t)(len > 0 ? len : 1);
+    g->K = (int32_t)(N > 0 ? (N + g->chunk_len - 1) / g->chunk_len : 1);
+    const size_t cells = (size_t)g->K * (size_t)(B > 0 ? B : 1);
+    const size_t sb = batch_state_bytes(c->num_models, c->max_groups, c->max_slots, g->H);
+    size_t off = 0;
+    g->off_leaf = off;     off += align256(sizeof(double) * (size_t)plan_leaves(N) * (size_t)B + 8);
+    g->off_flag = off;     off += 256;
+    g->off_counters = off; off += align256(sizeof(uint32_t) * cells * (2 * c->num_models + 2 * c->max_groups));
+    g->off_carry = off;    off += align256(cells * batch_carry_bytes());
+    g->off_start = off;    off += g->K > 1 ? align256(cells * sb) : 0;
+    g->off_end = off;      off += g->K > 1 ? align256(cells * sb) : 0;
+    g->total = off;
+    return MMS_OK;
+}
+
+}  // namespace mms
+
+extern "C" {
+
+size_t mms_sim_batching_workspace_bytes(int64_t num_requests, const mms_placements *cands,
+                                        const mms_batching *batching)
+{
+    mms::BatchGeometry g;
+    if (mms::plan_batching(num_requests, cands, batching, &g) != MMS_OK) return 0;
+    return g.total;
 }
 
 int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
@@ -519,7 +582,9 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
         return MMS_ERR_ARG;
     if (plan->num_leaves != plan_leaves(N)) return MMS_ERR_ARG;
     if (plan->num_leaves > 0 && (!plan->leaf_start || !plan->leaf_merges)) return MMS_ERR_ARG;
-    if (!ws->ptr || ws->bytes < mms_sim_batching_workspace_bytes(N, cands)) return MMS_ERR_ARG;
+    BatchGeometry geo;
+    if (plan_batching(N, cands, batching, &geo) != MMS_OK) return MMS_ERR_ARG;
+    if (!ws->ptr || ws->bytes < geo.total) return MMS_ERR_ARG;
 
     BatchArgs a;
     memset(&a, 0, sizeof(a));
@@ -527,7 +592,7 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
     a.next_same = next_same; a.N = N;
     a.B = B; a.M = cands->num_models; a.G = cands->max_groups; a.P = cands->max_placed;
     a.T = cands->max_slots; a.S = cands->max_stages; a.C = cands->num_columns; a.NB = NB;
-    a.H = batching->heap_capacity > 0 ? batching->heap_capacity : 4 * a.G + 16;
+    a.H = geo.H;
     for (int j = 0; j < NB; ++j) {
         const int32_t bs = batching->batch_sizes[j];
         if (bs < 1 || (bs & (bs - 1)) || (j > 0 && bs <= batching->batch_sizes[j - 1]))
@@ -546,18 +611,41 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
     a.model_num_requests = out->model_num_requests; a.model_num_good = out->model_num_good;
     a.group_num_requests = out->group_num_requests; a.group_num_good = out->group_num_good;
     a.status = out->status;
-    // one candidate per warp unless there are too many candidates for that to fill the GPU
-    // better than warps of 32 candidates do
-    a.lanes = B <= 16384 ? 1 : kLanes;
-    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H, a.lanes);
-    if (L.total > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    a.lanes = geo.lanes;
+    if (geo.smem > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    unsigned char *scratch = (unsigned char *)ws->ptr;
+    a.K = geo.K; a.chunk_len = geo.chunk_len; a.warmup = geo.warmup;
+    a.unsorted = (const int32_t *)(scratch + geo.off_flag);
+    a.chunk_counters = (uint32_t *)(scratch + geo.off_counters);
+    a.carry = scratch + geo.off_carry;
+    a.snap_start = scratch + geo.off_start;
+    a.snap_end = scratch + geo.off_end;
+    a.resimulated = out->resimulated;
 
     cudaStream_t st = (cudaStream_t)stream;
-    MMS_CUDA(cudaFuncSetAttribute(sim_batching_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)L.total));
-    sim_batching_kernel<<<(B + a.lanes - 1) / a.lanes, kLanes, L.total, st>>>(a);
+    MMS_CUDA(cudaMemsetAsync(scratch + geo.off_flag, 0, 256, st));
+    MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)B, st));
+    if (out->resimulated)
+        MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)B, st));
+    if (N > 0 && a.K > 1) {
+        unsorted_kernel<<<296, 256, 0, st>>>(trace->arrivals, N, (int32_t *)(scratch + geo.off_flag));
+        MMS_CUDA(cudaGetLastError());
+    }
+    MMS_CUDA(cudaFuncSetAttribute(batch_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)geo.smem));
+    MMS_CUDA(cudaFuncSetAttribute(batch_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)geo.smem));
+    const int64_t streams = (int64_t)B * a.K;
+    batch_stream_kernel<<<(unsigned)((streams + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
     MMS_CUDA(cudaGetLastError());
-    double *leaf_sums = (double *)ws->ptr;
+    if (a.K > 1) {
+        batch_chain_kernel<<<(unsigned)((B + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
+        MMS_CUDA(cudaGetLastError());
+    }
+    const int64_t sum_cells = (int64_t)B * (2 * a.M + 2 * a.G);
+    batch_sum_kernel<<<(unsigned)((sum_cells + 127) / 128), 128, 0, st>>>(a);
+    MMS_CUDA(cudaGetLastError());
+    double *leaf_sums = (double *)(scratch + geo.off_leaf);
     if (plan->num_leaves > 0) {
         const int64_t cells = (int64_t)B * plan->num_leaves;
         leaf_sums_from_finish_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(

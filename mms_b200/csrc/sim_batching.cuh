@@ -12,6 +12,17 @@
 // next_same[i] = next request with the model of request i; nothing is stored
 // per queued request.  The heap of (time, group) events, the queues and the
 // clocks are lane-private shared memory, [entry][lane].
+//
+// Like the unbatched path, the trace is cut into chunks that are simulated
+// speculatively at the same time (batch_stream_kernel: idle start, a run-in,
+// then the chunk) and stitched exactly afterwards (batch_chain_kernel: a
+// chunk is kept if the state it started from is equivalent to the state the
+// chunk before it ended in — batch_states_equivalent — and re-simulated from
+// the true state otherwise).  A request that is still queued at a chunk
+// boundary is served by the NEXT chunk's run; a speculative run does not
+// write the outputs of such carried requests itself (a wrong guess would
+// clobber what the chunk before it wrote) but lists them, and the chain
+// kernel applies the list when it accepts the chunk.
 #pragma once
 #include "sim_core.cuh"
 
@@ -42,7 +53,35 @@ struct BatchArgs {
     int32_t *group_num_requests;  // [B][G]
     int32_t *group_num_good;      // [B][G]
     uint32_t *status;             // [B]
+    // time-parallel execution
+    int32_t K;                    // chunks
+    int32_t chunk_len;            // arrivals per chunk (the last one takes the rest)
+    int32_t warmup;               // run-in arrivals of a speculative chunk
+    const int32_t *unsorted;      // != 0: arrival times not sorted / not finite -> one chunk
+    unsigned char *snap_start;    // [K][B][state_bytes]: state a speculative chunk started from
+    unsigned char *snap_end;      // [K][B][state_bytes]: state after the chunk's last arrival
+    uint32_t *chunk_counters;     // [K][B][2M + 2G]
+    unsigned char *carry;         // [K][B][carry_bytes]: outputs of carried requests
+    int32_t *resimulated;         // [B] or null: chunks the chain kernel re-simulated
 };
+
+constexpr int kMaxCarry = 120;    // carried requests a speculative chunk may list
+constexpr int kBatchBlocksPerSm = 16;   // register budget of the batching kernels: 128 per thread
+
+// Bytes of one saved state: clocks f64[T], idle f64[G], heap times f64[H],
+// heap groups u32[H], queue heads i32[M], queue lengths i32[M], heap size.
+__host__ __device__ inline size_t batch_state_bytes(int M, int G, int T, int H)
+{
+    return (8 * (size_t)(T + G + H) + 4 * (size_t)(H + 2 * M) + 8 + 15) & ~(size_t)15;
+}
+
+// Bytes of one carry list: count u32 (0xFFFFFFFF = overflowed), the status
+// word of the chunk's speculative run, pad, then kMaxCarry x (finish f64) and
+// kMaxCarry x (request i32 | good << 31).
+__host__ __device__ inline size_t batch_carry_bytes()
+{
+    return 16 + (size_t)kMaxCarry * 12 + 8;
+}
 
 struct BatchSmem {
     size_t clocks, idle, heap_t, qhead, qlen, heap_g, counters, model_rep, group_cfg,
@@ -79,7 +118,30 @@ struct BLane {
     const float *lat;
     double *finish;
     uint8_t *good;
+    // where outputs go: requests >= own_begin are written directly; older ones (carried over a
+    // chunk boundary) only when `direct`, else they are appended to the carry list
+    int32_t own_begin;
+    bool direct, record;
+    uint32_t carry_n;
+    double *carry_fin;
+    uint32_t *carry_req;
 };
+
+// Output of request r.
+__device__ inline void put(BLane &ln, int32_t r, double fin, bool good)
+{
+    if (!ln.record) return;
+    if (ln.direct || r >= ln.own_begin) {
+        ln.finish[r] = fin;
+        ln.good[r] = good ? 1 : 0;
+    } else if (ln.carry_n < (uint32_t)kMaxCarry) {
+        ln.carry_fin[ln.carry_n] = fin;
+        ln.carry_req[ln.carry_n] = (uint32_t)r | (good ? 0x80000000u : 0u);
+        ++ln.carry_n;
+    } else {
+        ln.carry_n = 0xFFFFFFFFu;          // too many: the chain kernel re-simulates the chunk
+    }
+}
 
 // (time, group) ordered like the Python tuples the reference pushes (:728).
 __device__ inline bool event_less(double ta, uint32_t ga, double tb, uint32_t gb)
@@ -185,8 +247,7 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
             const double dl = a.arrivals[r] + (double)a.slos[r];
             if (meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[0], dl)) { head = r; break; }
             SM_U32(ln.group_req + g * a.lanes) += 1;
-            ln.finish[r] = a.arrivals[r];
-            ln.good[r] = 0;
+            put(ln, r, a.arrivals[r], false);
         }
         if (head < 0) { m = pick_model(a, ln, g); continue; }      // :709-713
         // :693-702 grow the batch while the HEAD's deadline still holds
@@ -206,12 +267,10 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
             SM_F64(ln.clk + (slot + k) * a.lanes) = t;   // each stage reads only its own clock
             if (k == 0) t_first = t;
         }
-        ln.finish[head] = t;
-        ln.good[head] = 1;
+        put(ln, head, t, true);
         for (int32_t k = 1; k < bs; ++k) {
             const int32_t r = queue_pop(a, ln, m);
-            ln.finish[r] = t;
-            ln.good[r] = 1;
+            put(ln, r, t, true);
         }
         // :727-732
         SM_F64(ln.idle + g * a.lanes) = t_first;
@@ -223,17 +282,11 @@ __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int
     }
 }
 
-__global__ void __launch_bounds__(kLanes, 1)
-sim_batching_kernel(const BatchArgs a)
+// This lane's view of candidate b and the candidate's tables on chip, every
+// index checked (a bad one is reported in ln.status).
+__device__ inline void batch_setup(const BatchArgs &a, BLane &ln, int lane, int64_t b)
 {
-    // lanes == 32: a warp of 32 candidates; lanes == 1: thread 0 of the block alone, so that
-    // the candidate's branches are not serialised against 31 others'
-    if ((int)threadIdx.x >= a.lanes) return;
-    const int lane = threadIdx.x;
-    const int64_t b = (int64_t)blockIdx.x * a.lanes + lane;
-    if (b >= a.B) return;
     const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H, a.lanes);
-    BLane ln;
     ln.clk = (uint32_t)(L.clocks / 8) + lane;
     ln.idle = (uint32_t)(L.idle / 8) + lane;
     ln.heap_t = (uint32_t)(L.heap_t / 8) + lane;
@@ -254,12 +307,9 @@ sim_batching_kernel(const BatchArgs a)
     ln.lat = a.latency + (size_t)b * a.latency_stride;
     ln.finish = a.finish + (size_t)b * a.N;
     ln.good = a.good + (size_t)b * a.N;
+    ln.own_begin = 0; ln.direct = true; ln.record = true;
+    ln.carry_n = 0; ln.carry_fin = nullptr; ln.carry_req = nullptr;
 
-    // tables on chip, every index checked
-    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = 0.0;
-    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = 0.0;
-    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * a.lanes) = 0; SM_U32(ln.qlen + m * a.lanes) = 0; }
-    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * a.lanes) = 0;
     for (int g = 0; g < a.G; ++g) {
         uint32_t cfg = a.group_cfg[(size_t)b * a.G + g];
         const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu;
@@ -297,64 +347,331 @@ sim_batching_kernel(const BatchArgs a)
         if (m >= (uint32_t)a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = 0; }
         SM_U16(ln.gmod + e * a.lanes) = (uint16_t)m;
     }
+}
 
-    if (!(ln.status & MMS_STATUS_BAD_INDEX)) {
-        for (int64_t i = 0; i < a.N; ++i) {
-            const double ts = a.arrivals[i];
-            // :739-744 groups whose first stage became free before this arrival
-            while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
-                double te; uint32_t ge;
-                heap_pop(a, ln, te, ge);
-                const int32_t pm = pick_model(a, ln, ge);
-                if (pm < 0) break;                     // the reference breaks here, not continues
-                serve_group(a, ln, te, pm, ge);
-            }
-            int32_t m = a.model_ids[i];
-            if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
-            uint32_t lo = 0, hi = 0;
-            if (m >= 0) { lo = SM_U16(ln.moff + m * a.lanes); hi = SM_U16(ln.moff + (m + 1) * a.lanes); }
-            if (lo == hi) {                            // :748-757 unknown model or no replica
-                ln.finish[i] = ts;
-                ln.good[i] = 0;
-                continue;
-            }
-            double best = kInf;                        // :759-770
-            uint32_t pick = 0;
-            bool found = false;
-            for (uint32_t e = lo; e < hi; ++e) {
-                const uint32_t ent = SM_U32(ln.mrep + e * a.lanes);
-                const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
-                const double c = SM_F64(ln.clk + last * a.lanes);
-                if (c < best) { best = c; pick = ent; found = true; }
-            }
-            // :772-773 the request joins its MODEL's queue
-            if ((int32_t)SM_U32(ln.qlen + m * a.lanes) == 0) SM_U32(ln.qhead + m * a.lanes) = (uint32_t)i;
-            SM_U32(ln.qlen + m * a.lanes) += 1;
-            SM_U32(ln.model_req + m * a.lanes) += 1;
-            const uint32_t g = pick & 0xFFu;
-            if (found && ts >= SM_F64(ln.idle + g * a.lanes))   // :776-778
-                serve_group(a, ln, ts, m, g);
-        }
-        // :781-787 drain
-        while (ln.heap_n > 0) {
-            double te; uint32_t ge;
-            heap_pop(a, ln, te, ge);
-            const int32_t pm = pick_model(a, ln, ge);
-            if (pm < 0) continue;
-            serve_group(a, ln, te, pm, ge);
-        }
-        for (int m = 0; m < a.M; ++m)                  // :789-790
-            if ((int32_t)SM_U32(ln.qlen + m * a.lanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+__device__ inline void batch_zero_counters(const BatchArgs &a, BLane &ln)
+{
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * a.lanes) = 0;
+}
+
+// Idle clocks, empty queues, empty heap.
+__device__ inline void batch_zero_state(const BatchArgs &a, BLane &ln)
+{
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = 0.0;
+    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = 0.0;
+    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * a.lanes) = 0; SM_U32(ln.qlen + m * a.lanes) = 0; }
+    ln.heap_n = 0;
+}
+
+// Arrival i, :736-778.
+__device__ inline void batch_arrival(const BatchArgs &a, BLane &ln, int64_t i)
+{
+    const double ts = a.arrivals[i];
+    // :739-744 groups whose first stage became free before this arrival
+    while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
+        double te; uint32_t ge;
+        heap_pop(a, ln, te, ge);
+        const int32_t pm = pick_model(a, ln, ge);
+        if (pm < 0) break;                     // the reference breaks here, not continues
+        serve_group(a, ln, te, pm, ge);
+    }
+    int32_t m = a.model_ids[i];
+    if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
+    uint32_t lo = 0, hi = 0;
+    if (m >= 0) { lo = SM_U16(ln.moff + m * a.lanes); hi = SM_U16(ln.moff + (m + 1) * a.lanes); }
+    if (lo == hi) {                            // :748-757 unknown model or no replica
+        put(ln, (int32_t)i, ts, false);
+        return;
+    }
+    double best = kInf;                        // :759-770
+    uint32_t pick = 0;
+    bool found = false;
+    for (uint32_t e = lo; e < hi; ++e) {
+        const uint32_t ent = SM_U32(ln.mrep + e * a.lanes);
+        const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
+        const double c = SM_F64(ln.clk + last * a.lanes);
+        if (c < best) { best = c; pick = ent; found = true; }
+    }
+    // :772-773 the request joins its MODEL's queue
+    if ((int32_t)SM_U32(ln.qlen + m * a.lanes) == 0) SM_U32(ln.qhead + m * a.lanes) = (uint32_t)i;
+    SM_U32(ln.qlen + m * a.lanes) += 1;
+    SM_U32(ln.model_req + m * a.lanes) += 1;
+    const uint32_t g = pick & 0xFFu;
+    if (found && ts >= SM_F64(ln.idle + g * a.lanes))   // :776-778
+        serve_group(a, ln, ts, m, g);
+}
+
+// After the last arrival, :781-790.
+__device__ inline void batch_drain(const BatchArgs &a, BLane &ln)
+{
+    while (ln.heap_n > 0) {
+        double te; uint32_t ge;
+        heap_pop(a, ln, te, ge);
+        const int32_t pm = pick_model(a, ln, ge);
+        if (pm < 0) continue;
+        serve_group(a, ln, te, pm, ge);
+    }
+    for (int m = 0; m < a.M; ++m)
+        if ((int32_t)SM_U32(ln.qlen + m * a.lanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+}
+
+// A saved state, see batch_state_bytes.
+struct StateView {
+    double *clk, *idle, *heap_t;
+    uint32_t *heap_g;
+    int32_t *qhead, *qlen;
+    uint32_t *heap_n;
+};
+
+__device__ inline StateView state_view(const BatchArgs &a, unsigned char *p)
+{
+    StateView v;
+    v.clk = reinterpret_cast<double *>(p);
+    v.idle = v.clk + a.T;
+    v.heap_t = v.idle + a.G;
+    v.heap_g = reinterpret_cast<uint32_t *>(v.heap_t + a.H);
+    v.qhead = reinterpret_cast<int32_t *>(v.heap_g + a.H);
+    v.qlen = v.qhead + a.M;
+    v.heap_n = reinterpret_cast<uint32_t *>(v.qlen + a.M);
+    return v;
+}
+
+__device__ inline void state_save(const BatchArgs &a, const BLane &ln, unsigned char *p)
+{
+    const StateView v = state_view(a, p);
+    for (int t = 0; t < a.T; ++t) v.clk[t] = SM_F64(ln.clk + t * a.lanes);
+    for (int g = 0; g < a.G; ++g) v.idle[g] = SM_F64(ln.idle + g * a.lanes);
+    for (uint32_t h = 0; h < ln.heap_n; ++h) {
+        v.heap_t[h] = SM_F64(ln.heap_t + h * a.lanes);
+        v.heap_g[h] = SM_U32(ln.heap_g + h * a.lanes);
     }
     for (int m = 0; m < a.M; ++m) {
-        a.model_num_requests[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_req + m * a.lanes);
-        a.model_num_good[(size_t)b * a.M + m] = (int32_t)SM_U32(ln.model_good + m * a.lanes);
+        v.qhead[m] = (int32_t)SM_U32(ln.qhead + m * a.lanes);
+        v.qlen[m] = (int32_t)SM_U32(ln.qlen + m * a.lanes);
+    }
+    *v.heap_n = ln.heap_n;
+}
+
+__device__ inline void state_load(const BatchArgs &a, BLane &ln, unsigned char *p)
+{
+    const StateView v = state_view(a, p);
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = v.clk[t];
+    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = v.idle[g];
+    ln.heap_n = *v.heap_n;
+    for (uint32_t h = 0; h < ln.heap_n; ++h) {
+        SM_F64(ln.heap_t + h * a.lanes) = v.heap_t[h];
+        SM_U32(ln.heap_g + h * a.lanes) = v.heap_g[h];
+    }
+    for (int m = 0; m < a.M; ++m) {
+        SM_U32(ln.qhead + m * a.lanes) = (uint32_t)v.qhead[m];
+        SM_U32(ln.qlen + m * a.lanes) = (uint32_t)v.qlen[m];
+    }
+}
+
+// The state X on chip (true) and a saved state Y, both taken just before the
+// arrival at time tau, lead to identical futures when
+//  - every queue has the same length and, if not empty, the same head (a
+//    queue is a run of consecutive requests of its model);
+//  - the heaps hold the same events: compared as arrays, which is stricter
+//    than as sets (two runs that pushed and popped the same events in the
+//    same order have identical arrays);
+//  - a group's idle time is equal in both or <= tau in both (it is only
+//    compared with arrival times >= tau, :776);
+//  - every clock is equal in both or < theta in both, theta = the earlier of
+//    tau and the first pending event: a clock only ever enters max(clock, t)
+//    with t an arrival time or a pending event's time (:669, :719);
+//  - the last-stage clocks that differ (both < theta) of groups serving a
+//    replicated model are in the same order (ties included) relative to all
+//    such groups' last-stage clocks: dispatch compares them with '<' (:764).
+// Sufficient, not necessary: a failed check only costs a re-simulation.
+__device__ inline bool batch_states_equivalent(const BatchArgs &a, const BLane &ln,
+                                               unsigned char *saved, double tau)
+{
+    const StateView y = state_view(a, saved);
+    if (*y.heap_n != ln.heap_n) return false;
+    double theta = tau;
+    for (uint32_t h = 0; h < ln.heap_n; ++h) {
+        const double t = SM_F64(ln.heap_t + h * a.lanes);
+        if (t != y.heap_t[h] || SM_U32(ln.heap_g + h * a.lanes) != y.heap_g[h]) return false;
+        if (t < theta) theta = t;
+    }
+    for (int m = 0; m < a.M; ++m) {
+        const int32_t n = (int32_t)SM_U32(ln.qlen + m * a.lanes);
+        if (n != y.qlen[m]) return false;
+        if (n > 0 && (int32_t)SM_U32(ln.qhead + m * a.lanes) != y.qhead[m]) return false;
     }
     for (int g = 0; g < a.G; ++g) {
-        a.group_num_requests[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_req + g * a.lanes);
-        a.group_num_good[(size_t)b * a.G + g] = (int32_t)SM_U32(ln.group_good + g * a.lanes);
+        const double x = SM_F64(ln.idle + g * a.lanes), v = y.idle[g];
+        if (!(x == v || (x <= tau && v <= tau))) return false;
     }
-    a.status[b] = ln.status;
+    for (int t = 0; t < a.T; ++t) {
+        const double x = SM_F64(ln.clk + t * a.lanes), v = y.clk[t];
+        if (!(x == v || (x < theta && v < theta))) return false;
+    }
+    // order of differing last-stage clocks among groups that share a model
+    for (int m = 0; m < a.M; ++m) {
+        const uint32_t lo = SM_U16(ln.moff + m * a.lanes), hi = SM_U16(ln.moff + (m + 1) * a.lanes);
+        for (uint32_t e = lo; e + 1 < hi; ++e) {
+            const uint32_t eu = SM_U32(ln.mrep + e * a.lanes);
+            const uint32_t su = ((eu >> 8) & 0xFFu) + ((eu >> 16) & 0xFFu) - 1;
+            const double xu = SM_F64(ln.clk + su * a.lanes), yu = y.clk[su];
+            for (uint32_t f = e + 1; f < hi; ++f) {
+                const uint32_t ev = SM_U32(ln.mrep + f * a.lanes);
+                const uint32_t sv = ((ev >> 8) & 0xFFu) + ((ev >> 16) & 0xFFu) - 1;
+                const double xv = SM_F64(ln.clk + sv * a.lanes), yv = y.clk[sv];
+                if ((xu < xv) != (yu < yv) || (xu > xv) != (yu > yv)) return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ inline void counters_store(const BatchArgs &a, const BLane &ln, uint32_t *dst)
+{
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) dst[c] = SM_U32(ln.model_req + c * a.lanes);
+}
+
+// First arrival of chunk j (j == K: one past the last arrival).
+__device__ inline int64_t chunk_first(const BatchArgs &a, int32_t j)
+{
+    const int64_t at = (int64_t)j * a.chunk_len;
+    return j >= a.K || at > a.N ? a.N : at;
+}
+
+__device__ inline bool batch_can_chunk(const BatchArgs &a) { return a.K > 1 && *a.unsorted == 0; }
+
+// One thread per (candidate, chunk); with lanes == 1 thread 0 of the block
+// alone, so that a candidate's branches are not serialised against 31
+// others'.  Chunk 0 starts from the true (idle) state; the others start idle
+// `warmup` arrivals early and store the state they have at their first arrival.
+__global__ void __launch_bounds__(kLanes, kBatchBlocksPerSm)
+batch_stream_kernel(const BatchArgs a)
+{
+    if ((int)threadIdx.x >= a.lanes) return;
+    const int lane = threadIdx.x;
+    const int64_t stream = (int64_t)blockIdx.x * a.lanes + lane;
+    if (stream >= (int64_t)a.B * a.K) return;
+    const int32_t j = (int32_t)(stream / a.B);
+    const int64_t b = stream % a.B;
+    const bool chunked = batch_can_chunk(a);
+    if (!chunked && j > 0) return;
+    BLane ln;
+    batch_setup(a, ln, lane, b);
+    batch_zero_state(a, ln);
+    batch_zero_counters(a, ln);
+    const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
+    const size_t cell = (size_t)j * a.B + b;
+    const int64_t first = chunked ? chunk_first(a, j) : 0;
+    const int64_t end = chunked ? chunk_first(a, j + 1) : a.N;
+    if (!(ln.status & MMS_STATUS_BAD_INDEX)) {
+        if (j > 0) {
+            unsigned char *carry = a.carry + cell * batch_carry_bytes();
+            ln.carry_fin = reinterpret_cast<double *>(carry + 16);
+            ln.carry_req = reinterpret_cast<uint32_t *>(carry + 16 + (size_t)kMaxCarry * 8);
+            ln.own_begin = (int32_t)first;
+            ln.direct = false;
+            ln.record = false;
+            for (int64_t i = first - a.warmup > 0 ? first - a.warmup : 0; i < first; ++i)
+                batch_arrival(a, ln, i);
+            ln.record = true;
+            ln.status &= MMS_STATUS_BAD_INDEX;       // overflows of the run-in are not the chunk's
+            batch_zero_counters(a, ln);
+            state_save(a, ln, a.snap_start + cell * sb);
+        }
+        for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
+        if (end == a.N) batch_drain(a, ln);
+        if (chunked) state_save(a, ln, a.snap_end + cell * sb);
+    }
+    counters_store(a, ln, a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G));
+    if (chunked) {
+        // the chain kernel decides whether this run, and with it its status word, counts
+        uint32_t *hdr = reinterpret_cast<uint32_t *>(a.carry + cell * batch_carry_bytes());
+        hdr[0] = ln.carry_n;
+        hdr[1] = ln.status;
+    } else if (ln.status) {
+        atomicOr(&a.status[b], ln.status);
+    }
+}
+
+// One thread per candidate: walks the chunk boundaries in order; a chunk
+// whose start state is equivalent to the true state is kept (and the outputs
+// of the requests it carried over are written), any other is re-simulated
+// from the true state.
+__global__ void __launch_bounds__(kLanes, kBatchBlocksPerSm)
+batch_chain_kernel(const BatchArgs a)
+{
+    if ((int)threadIdx.x >= a.lanes) return;
+    const int lane = threadIdx.x;
+    const int64_t b = (int64_t)blockIdx.x * a.lanes + lane;
+    if (b >= a.B || !batch_can_chunk(a)) return;
+    BLane ln;
+    batch_setup(a, ln, lane, b);
+    if (ln.status & MMS_STATUS_BAD_INDEX) {             // bad tables: nothing was simulated
+        atomicOr(&a.status[b], ln.status);
+        return;
+    }
+    const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
+    const size_t n_counters = (size_t)(2 * a.M + 2 * a.G);
+    state_load(a, ln, a.snap_end + (size_t)b * sb);     // chunk 0 ran from the true state
+    uint32_t status = reinterpret_cast<const uint32_t *>(a.carry + (size_t)b * batch_carry_bytes())[1];
+    int32_t redone = 0;
+    for (int32_t j = 1; j < a.K; ++j) {
+        const size_t cell = (size_t)j * a.B + b;
+        const int64_t first = chunk_first(a, j), end = chunk_first(a, j + 1);
+        if (first >= a.N) break;
+        unsigned char *carry = a.carry + cell * batch_carry_bytes();
+        const uint32_t carried = reinterpret_cast<const uint32_t *>(carry)[0];
+        if (carried != 0xFFFFFFFFu &&
+            batch_states_equivalent(a, ln, a.snap_start + cell * sb, a.arrivals[first])) {
+            const double *fin = reinterpret_cast<const double *>(carry + 16);
+            const uint32_t *req = reinterpret_cast<const uint32_t *>(carry + 16 + (size_t)kMaxCarry * 8);
+            for (uint32_t k = 0; k < carried; ++k) {
+                ln.finish[req[k] & 0x7FFFFFFFu] = fin[k];
+                ln.good[req[k] & 0x7FFFFFFFu] = (uint8_t)(req[k] >> 31);
+            }
+            status |= reinterpret_cast<const uint32_t *>(carry)[1];
+            state_load(a, ln, a.snap_end + cell * sb);
+            continue;
+        }
+        ++redone;                          // the speculative run of chunk j is dropped, status and all
+        batch_zero_counters(a, ln);
+        ln.status = 0;
+        for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
+        if (end == a.N) batch_drain(a, ln);
+        counters_store(a, ln, a.chunk_counters + cell * n_counters);
+        status |= ln.status;
+    }
+    if (a.resimulated) a.resimulated[b] = redone;
+    if (status) atomicOr(&a.status[b], status);
+}
+
+// Adds the per-chunk counters: one thread per (counter, candidate).
+__global__ void batch_sum_kernel(const BatchArgs a)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int n_counters = 2 * a.M + 2 * a.G;
+    if (t >= (int64_t)a.B * n_counters) return;
+    const int c = (int)(t % n_counters);
+    const int64_t b = t / n_counters;
+    const int32_t chunks = batch_can_chunk(a) ? a.K : 1;
+    uint32_t v = 0;
+    for (int32_t j = 0; j < chunks; ++j) v += a.chunk_counters[((size_t)j * a.B + b) * n_counters + c];
+    if (c < a.M) a.model_num_requests[(size_t)b * a.M + c] = (int32_t)v;
+    else if (c < 2 * a.M) a.model_num_good[(size_t)b * a.M + (c - a.M)] = (int32_t)v;
+    else if (c < 2 * a.M + a.G) a.group_num_requests[(size_t)b * a.G + (c - 2 * a.M)] = (int32_t)v;
+    else a.group_num_good[(size_t)b * a.G + (c - 2 * a.M - a.G)] = (int32_t)v;
+}
+
+// Number of positions where the arrival times are not finite or go backwards.
+__global__ void unsorted_kernel(const double *arrivals, int64_t N, int32_t *count)
+{
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int32_t bad = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < N; i += stride) {
+        const double t = arrivals[i];
+        if (!(t - t == 0.0) || (i > 0 && !(arrivals[i - 1] <= t))) ++bad;
+    }
+    if (bad) atomicAdd(count, bad);
 }
 
 // next_same[i] = next request with request i's model, -1 if none; one thread

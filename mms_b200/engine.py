@@ -939,7 +939,7 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
                                _ptr(d_lat), int(latency_stride))
         bat = nat.Batching(_ptr(d_goff), _ptr(d_gmod), _ptr(d_gcfg), len(batch_sizes),
                            int(heap_capacity), (ctypes.c_int32 * 8)(*list(batch_sizes)))
-        need = L.mms_sim_batching_workspace_bytes(N, ctypes.byref(cands))
+        need = L.mms_sim_batching_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(bat))
         ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
         ws = nat.Workspace(_ptr(ws_t), need)
         i32 = dict(dtype=torch.int32, device=dev)
@@ -950,8 +950,9 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
         o_status = torch.zeros(B, **i32)
         o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev)
         o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev)
+        o_redo = torch.zeros(B, **i32)
         out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood), _ptr(o_total),
-                          _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good), None)
+                          _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good), _ptr(o_redo))
         tr, plan = trace.c_trace(), trace.c_plan()
         rc = L.mms_sim_batching(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(bat),
                                 _ptr(trace.next_same_model()), ctypes.byref(plan),
@@ -964,7 +965,7 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
         res.good_total = o_total.cpu().numpy()
         res.latency_sum = o_lsum.cpu().numpy()
         res.status = o_status.cpu().numpy().astype(np.uint32)
-        res.resimulated = None
+        res.resimulated = o_redo.cpu().numpy()
         res.finish = o_fin.cpu().numpy()[:, :N] if per_request else None
         res.good = o_good.cpu().numpy()[:, :N].astype(bool) if per_request else None
     if np.any(res.status):

@@ -261,6 +261,67 @@ def test_batching_against_cpu_checker_long(loaded):
         assert np.array_equal(res.model_num_requests[b], mreq)
         assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
         assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)
+        assert res.latency_sum[b] == float(np.add.reduce(fin - arr))
+        assert res.good_total[b] == np.count_nonzero(good)
+    assert res.resimulated is not None and res.resimulated.shape == (64,)
+
+
+@pytest.mark.parametrize("total_rate,cv", [(150.0, 4.0), (400.0, 1.0), (20.0, 8.0)])
+def test_batching_time_cut_under_load(loaded, total_rate, cv):
+    """The batching path is cut in time too.  Under overload requests queue
+    across chunk boundaries (their outputs travel through the carry lists or
+    the chunk is re-simulated); every per-request output must still equal the
+    checker's."""
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=40, duration=60000.0 / total_rate,
+                                      batching=True, placement_seed=6, total_rate=total_rate, cv=cv)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    assert len(arr) > 40000                               # long enough to be cut
+    trace = engine.DeviceTrace(arr, mids, slos, len(names))
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(names))
+    res = engine.run_batch_batching(trace, enc, table)
+    for b in range(0, 40, 3):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(
+            case.placements[b], profs, mids, slos, arr, batchsize_config=(1, 2, 4, 8))
+        assert res.finish[b].tobytes() == fin.tobytes(), b
+        assert np.array_equal(res.good[b], good)
+        assert np.array_equal(res.model_num_requests[b], mreq)
+        assert np.array_equal(res.model_num_good[b], mgood)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
+        assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)
+        assert res.latency_sum[b] == float(np.add.reduce(fin - arr))
+
+
+def test_batching_unsorted_trace_is_not_cut(loaded):
+    """Arrival times that go backwards: the batching path falls back to one
+    chunk and still equals the checker."""
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=6, duration=500.0, batching=True,
+                                      placement_seed=8)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals.copy()
+    arr[15000], arr[15001] = arr[15001], arr[15000] + 0.0     # one inversion
+    assert arr[15000] > arr[15001]
+    trace = engine.DeviceTrace(arr, mids, slos, len(names))
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(names))
+    res = engine.run_batch_batching(trace, enc, table)
+    for b in range(6):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(
+            case.placements[b], profs, mids, slos, arr, batchsize_config=(1, 2, 4, 8))
+        assert res.finish[b].tobytes() == fin.tobytes(), b
+        assert np.array_equal(res.good[b], good)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
 
 
 @pytest.mark.parametrize("chunk,run_in", [(2048, 256), (4096, 2048), (0, 0)])

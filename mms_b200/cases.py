@@ -172,3 +172,19 @@ def sweep_case(duration=3600.0, total_rate=278.0, placement_seed=0) -> SweepCase
     env = ClusterEnv(64, 13 * GB)
     placement = random_placements(datas, 64, env.mem_budget, 1, placement_seed)[0]
     return SweepCase(datas, env, placement, duration, total_rate)
+
+
+def replacement_case(duration=900.0, base_seed=3):
+    """A placement schedule (ModelPlacementWithReplacement, base_policy.py:58-68)
+    for approximate_one_case: 16 devices, 8 models, three placements of four
+    groups each that take over at 0 s, 300 s and 600 s.  Returns (model_datas,
+    cluster_env, workload, start_times, placements)."""
+    datas = mixed_models(8, 30.0, 3.0)
+    env = ClusterEnv(16, 13 * GB)
+    c2, c4, c8 = (ParallelConfig(1, 1, p) for p in (2, 4, 8))
+    placements = [
+        ModelPlacement([c4, c4, c4, c4], [[0, 3, 6], [1, 4, 7], [0, 3, 1], [4, 6, 7]]),
+        ModelPlacement([c8, c4, c2, c2], [[2, 5, 0, 1], [3, 4, 6, 7], [0, 3], [1, 6]]),
+        ModelPlacement([c4, c4, c4, c4], [[0, 1, 3], [4, 6, 7], [0, 1, 3], [4, 6, 7]]),
+    ]
+    return datas, env, merged_gamma_trace(datas, duration, base_seed), [0.0, 300.0, 600.0], placements

@@ -165,6 +165,38 @@ def main():
         arrivals_sha256=digest(rw.arrivals), finish=fins, good=goods,
         model_num_requests=mreq, model_num_good=mgood, group_num_requests=greq,
         group_num_good=ggood)
+    # ---- a placement schedule through approximate_one_case ---------------------------
+    from functools import partial
+    datas0, env0, w0, starts, pls0 = cases.replacement_case()
+    case = cases.Case("replacement", datas0, env0, w0, pls0)
+    datas, env, rw, pls = reference.to_reference_case(case)
+    schedule = ref.base_policy.ModelPlacementWithReplacement(list(starts), pls)
+
+    def register_models(controller):
+        for d in datas:
+            controller.register_model.remote(d.name, partial(object, d.profiling_result))
+
+    serving_case = ref.util.ServingCase(register_models, lambda start=0: rw,
+                                        lambda controller: schedule)
+    out = {}
+    for tag, fast in (("fast", True), ("full", False)):
+        stats, _ = C.approximate_one_case(serving_case, fast_stats=fast)
+        pm = stats.per_model_stats
+        out.update({
+            f"{tag}_goodput": stats.goodput, f"{tag}_latency_mean": stats.latency_mean,
+            f"{tag}_num_requests": stats.num_requests, f"{tag}_request_rate": stats.request_rate,
+            f"{tag}_group_num_requests": np.array(stats.group_num_requests, np.int64),
+            f"{tag}_model_num_requests": np.array([x.num_requests for x in pm], np.int64),
+            f"{tag}_model_goodput": np.array([x.goodput for x in pm], np.float64),
+            f"{tag}_model_throughput": np.array([x.throughput for x in pm], np.float64),
+            f"{tag}_model_latency_mean": np.array([x.latency_mean for x in pm], np.float64),
+            f"{tag}_model_latency_std": np.array([x.latency_std for x in pm], np.float64),
+            f"{tag}_model_latency_p90": np.array([x.latency_p90 for x in pm], np.float64),
+            f"{tag}_model_latency_p99": np.array([x.latency_p99 for x in pm], np.float64)})
+    np.savez_compressed(os.path.join(HERE, "case_replacement.npz"),
+                        arrivals_sha256=digest(rw.arrivals), num_requests_total=len(rw.arrivals),
+                        **out)
+
     # ---- whole searches: the placements the reference's policies arrive at ----------
     import json
     from mms_b200 import search_cases

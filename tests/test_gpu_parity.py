@@ -508,3 +508,36 @@ def test_split_launch_equals_one_launch(loaded, monkeypatch):
                  "good_total", "latency_sum", "status"):
         assert getattr(first, name).tobytes() == getattr(one, name).tobytes(), name
         assert getattr(again, name).tobytes() == getattr(one, name).tobytes(), name
+
+
+@pytest.mark.parametrize("fast", [True, False])
+def test_placement_schedule_through_approximate_one_case(loaded, golden, fast):
+    """approximate_one_case on a ModelPlacementWithReplacement, with the
+    reference's ServingCase closures: every field of the StatsResult equals
+    what the reference returned, for fast_stats and for compute_stats."""
+    from functools import partial
+    from mms_b200 import cases, simulator
+    from mms_b200.placement import ModelPlacementWithReplacement
+    g = golden("case_replacement")
+    datas, env, w, starts, pls = cases.replacement_case()
+    schedule = ModelPlacementWithReplacement(list(starts), pls)
+
+    def register_models(controller):
+        for d in datas:
+            controller.register_model.remote(d.name, partial(object, d.profiling_result))
+
+    case = (register_models, lambda start=0: w, lambda controller: schedule)
+    stats, placement = simulator.approximate_one_case(case, fast_stats=fast)
+    assert placement is schedule
+    tag = "fast" if fast else "full"
+    assert stats.goodput == float(g[f"{tag}_goodput"])
+    assert stats.latency_mean == float(g[f"{tag}_latency_mean"])
+    assert stats.num_requests == int(g[f"{tag}_num_requests"])
+    assert stats.request_rate == float(g[f"{tag}_request_rate"])
+    assert isinstance(stats.group_num_requests, tuple)
+    assert np.array_equal(np.array(stats.group_num_requests), g[f"{tag}_group_num_requests"])
+    pm = stats.per_model_stats
+    for field in ("num_requests", "goodput", "throughput", "latency_mean", "latency_std",
+                  "latency_p90", "latency_p99"):
+        got = np.array([getattr(x, field) for x in pm], np.float64)
+        assert np.array_equal(got, g[f"{tag}_model_{field}"].astype(np.float64)), field

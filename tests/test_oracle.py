@@ -121,3 +121,41 @@ def test_pairwise_sum_is_numpys_order(n):
     assert cpu.pairwise_sum(a) == float(np.add.reduce(a))
     if n:
         assert cpu.pairwise_sum(a) / n == float(np.mean(a))
+
+
+def test_placement_schedule_fast_stats(golden):
+    """approximate_one_case with a ModelPlacementWithReplacement
+    (controller.py:346-403): the trace is split at the first arrival later
+    than each change time, every part starts from idle clocks, counters add
+    up.  The checker, driven that way, reproduces the reference's StatsResult."""
+    g = golden("case_replacement")
+    datas, env, w, starts, pls = cases.replacement_case()
+    assert hashlib.sha256(np.ascontiguousarray(w.arrivals).tobytes()).hexdigest() == str(g["arrivals_sha256"])
+    names = [d.name for d in datas]
+    profs = [d.profiling_result for d in datas]
+    mids, slos = workload_arrays(w, names)
+    arr = w.arrivals
+    change = list(starts[1:]) + [np.inf]
+    bounds, pt = [0], 0
+    for i in range(len(arr)):
+        if arr[i] > change[pt]:
+            bounds.append(i)
+            pt += 1
+    bounds.append(len(arr))
+    parts = [tables.one_placement(pls[k], profs, mids[bounds[k]:bounds[k + 1]],
+                                  slos[bounds[k]:bounds[k + 1]], arr[bounds[k]:bounds[k + 1]])
+             for k in range(len(pls))]
+    finish = np.concatenate([p[0] for p in parts])
+    good = np.concatenate([p[1] for p in parts])
+    mreq = np.sum([p[2] for p in parts], axis=0)
+    mgood = np.sum([p[3] for p in parts], axis=0)
+    greq = np.sum([p[4] for p in parts], axis=0)
+    interval = arr[-1] - arr[0]
+    assert np.mean(good) == float(g["fast_goodput"])
+    assert np.mean(finish - arr) == float(g["fast_latency_mean"])
+    assert len(arr) == int(g["fast_num_requests"])
+    assert len(arr) / interval == float(g["fast_request_rate"])
+    assert np.array_equal(greq, g["fast_group_num_requests"])
+    assert np.array_equal(mreq, g["fast_model_num_requests"])
+    assert np.array_equal(mgood / (mreq + 1e-6), g["fast_model_goodput"])
+    assert np.array_equal(mreq / interval, g["fast_model_throughput"])

@@ -39,10 +39,10 @@ static int32_t plan_leaves(int64_t n)
 }
 
 struct Geometry {
-    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, n_counters, rounds, repair_cap,
+    int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, rounds, repair_cap,
         block_warps;
     size_t smem_stream, smem_repair;
-    size_t off_leaf, off_seg_end, off_chunk_start, off_counters, off_work_count, off_work_items,
+    size_t off_leaf, off_seg_end, off_chunk_start, off_decisions, off_work_count, off_work_items,
         off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
     size_t total;
 };
@@ -91,7 +91,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         if (bytes > 232448) break;
         int64_t warps = (int64_t)(233472 / (bytes + 1024)) * w;
         if (warps > kMaxWarpsPerSm) warps = kMaxWarpsPerSm;
-        if (warps > per_sm) { per_sm = warps; block_warps = w; }
+        if (warps >= per_sm) { per_sm = warps; block_warps = w; }
     }
     g->block_warps = block_warps;
     const int64_t resident_slots = (int64_t)sm_count * per_sm;
@@ -138,7 +138,6 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
                             ? (int32_t)lat_elems : 0;
     const SmemLayout L = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
                                      c->max_stages, group_good, g->lat_smem_elems);
-    g->n_counters = L.n_counters;
     g->smem_stream = L.warp0 + (size_t)g->block_warps * L.warp_bytes;
     g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
     g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
@@ -148,7 +147,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
                                                (c->num_models + 1) + 256);
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
-    g->off_counters = off;    off += align256(sizeof(uint32_t) * (size_t)NS * L.n_counters * B);
+    g->off_decisions = off;   off += align256((c->max_groups > 126 ? 2 : 1) * (size_t)(N > 0 ? N : 1) * B);
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
     g->off_repair_from = off; off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
@@ -369,7 +368,8 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.num_leaves = plan->num_leaves; ka.leaf_start = plan->leaf_start;
     ka.rep_rows = (uint32_t *)(scratch + g.off_rows);
     ka.leaf_sums = (double *)(scratch + g.off_leaf);
-    ka.seg_counters = (uint32_t *)(scratch + g.off_counters);
+    ka.decisions = scratch + g.off_decisions;
+    ka.dec_wide = cands->max_groups > 126;
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);
     ka.work_items = (uint32_t *)(scratch + g.off_work_items);
     ka.repair_from = (int32_t *)(scratch + g.off_repair_from);
@@ -403,12 +403,28 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     }
     if (rc) return rc;
 
-    const int threads = 128;
-    const int64_t cells = (int64_t)ka.Bs * g.n_counters;
-    sum_counters_kernel<<<(unsigned)((cells + threads - 1) / threads), threads, 0, st>>>(
-        ka, g.n_counters, out->model_num_requests, out->model_num_good, out->group_num_requests,
-        out->group_num_good);
+    // tally the recorded decisions of the selected runs
+    const size_t rows = (size_t)ka.Bs;
+    MMS_CUDA(cudaMemsetAsync(out->model_num_good, 0, sizeof(int32_t) * rows * ka.M, st));
+    MMS_CUDA(cudaMemsetAsync(out->group_num_requests, 0, sizeof(int32_t) * rows * ka.G, st));
+    if (gg) MMS_CUDA(cudaMemsetAsync(out->group_num_good, 0, sizeof(int32_t) * rows * ka.G, st));
+    const size_t hist_bytes = sizeof(uint16_t) * (size_t)(ka.M + 2 * ka.G) * kLanes;
+    if (hist_bytes > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    auto count_k = ka.dec_wide ? count_kernel<uint16_t> : count_kernel<uint8_t>;
+    MMS_CUDA(cudaFuncSetAttribute(count_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)hist_bytes));
+    int32_t seg_per_block = ka.NS / 96 > 0 ? ka.NS / 96 : 1;   // 16-bit counts: at most 32 segments
+    if (seg_per_block > 32) seg_per_block = 32;
+    const dim3 count_grid((unsigned)((ka.Bs + kLanes - 1) / kLanes),
+                          (unsigned)((ka.NS + seg_per_block - 1) / seg_per_block));
+    count_k<<<count_grid, kLanes, hist_bytes, st>>>(ka, seg_per_block, gg, out->model_num_good,
+                                                    out->group_num_requests, out->group_num_good);
     MMS_CUDA(cudaGetLastError());
+    if (ka.M > 0) {
+        const int64_t cells = (int64_t)ka.Bs * ka.M;
+        model_requests_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka, out->model_num_requests);
+        MMS_CUDA(cudaGetLastError());
+    }
     finalize_kernel<<<(ka.Bs + 31) / 32, 32, 0, st>>>(
         ka, plan->leaf_merges, out->model_num_good, out->good_total, out->latency_sum);
     MMS_CUDA(cudaGetLastError());

@@ -14,7 +14,7 @@
 //                   idle clocks a few thousand requests before its first
 //                   request (run-in, nothing recorded), stores the clock
 //                   vector it has when the chunk proper begins and after
-//                   every segment, and records counters and latency sums.
+//                   every segment, and records its decisions and latency sums.
 //                   A MIRROR candidate (a copy of a candidate with
 //                   interchangeable groups) exchanges those groups' clocks
 //                   after the run-in: a second guess at the state.
@@ -35,9 +35,9 @@
 //   chain kernel    one thread per candidate walks all boundaries in order
 //                   and repairs in place whatever the rounds left — it makes
 //                   the result exact whatever the chunking and the rounds.
-//   finalize        adds the per-segment counters and combines the per-leaf
-//                   latency sums of the selected runs in numpy's pairwise
-//                   order.
+//   count, finalize tally the recorded decisions of the selected runs into the
+//                   counters and combine the per-leaf latency sums in numpy's
+//                   pairwise order.
 //
 // The 32 lanes of a warp are 32 candidates on the same chunk (one broadcast
 // load per trace element) whenever the batch has 32 or more candidates.
@@ -94,10 +94,9 @@ __global__ void build_rows_kernel(const KernelArgs a)
 }
 
 // This lane's view of candidate b: offsets of its shared-memory state (clocks
-// and counters zeroed) and pointers to its tables in global memory.
+// zeroed) and pointers to its tables in global memory.
 template <bool kGroupGood>
-__device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint32_t &counters,
-                                  int &n_counters, int warp = 0)
+__device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int warp = 0)
 {
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
     const size_t base = L.warp0 + (size_t)warp * L.warp_bytes;
@@ -105,11 +104,10 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint
     ln.clk = (uint32_t)((base + L.clocks) / sizeof(double)) + lane;
     ln.tmp = (uint32_t)((base + L.stage_tmp) / sizeof(double)) + lane;
     ln.lat_sm = (uint32_t)(L.latency / sizeof(float));
-    counters = (uint32_t)((base + L.counters) / sizeof(uint16_t)) + lane;
-    n_counters = L.n_counters;
-    ln.model_good = counters;
-    ln.group_req = counters + (uint32_t)a.M * kLanes;
-    ln.group_good = counters + (uint32_t)(a.M + a.G) * kLanes;
+    ln.dec_wide = a.dec_wide;
+    ln.dec = a.dec_wide ? static_cast<void *>(static_cast<uint16_t *>(a.decisions) + b)
+                        : static_cast<void *>(static_cast<uint8_t *>(a.decisions) + b);
+    ln.dec_pitch = (uint32_t)a.B;
     ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + row_index(a, b, 0);
     ln.rep_raw = a.model_rep + (size_t)b * a.P;
     ln.rep_off = a.model_off + (size_t)b * (a.M + 1);
@@ -118,7 +116,6 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, uint
     ln.M = a.M; ln.C = a.C; ln.S = a.S;
     ln.status = 0;
     for (int t = 0; t < a.T + kClockPad; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
-    for (int c = 0; c < n_counters; ++c) SM_U16(counters + c * kLanes) = 0;
     return ln;
 }
 
@@ -174,8 +171,7 @@ sim_stream_kernel(const KernelArgs a)
                               ? ((uint64_t)a.mirror_swap[2 * b + 1] << 32) | a.mirror_swap[2 * b]
                               : ~0ull;
 
-    uint32_t counters; int n_counters;
-    Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters, warp);
+    Lane ln = setup_lane<kGroupGood>(a, b, lane, warp);
     Pipe p;
     init_pipe(a, p, b);
     // not chunked: one chunk holding every segment, plain sequential simulation
@@ -187,7 +183,7 @@ sim_stream_kernel(const KernelArgs a)
         const int32_t first = a.leaf_start[seg_leaf(a, j * a.seg_per_chunk)];
         begin = first - a.warmup > 0 ? first - a.warmup : 0;
     }
-    run_chunk<kFull, kGroupGood, kLegacy>(ka, ln, p, counters, n_counters, b, j, begin, false,
+    run_chunk<kFull, kGroupGood, kLegacy>(ka, ln, p, b, j, begin, false,
                                           chunked, 0, 0, -1, 0, swap);
     if (ln.status) atomicOr(&a.status[status_row(a, b)], ln.status);
 }
@@ -293,8 +289,7 @@ sim_repair_kernel(const KernelArgs a)
     const int32_t j = (int32_t)(item / (uint32_t)a.B);
     const int64_t b = item % (uint32_t)a.B;
 
-    uint32_t counters; int n_counters;
-    Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
+    Lane ln = setup_lane<kGroupGood>(a, b, lane);
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
     // start of the chunk from the copied-in true state, or where a capped
@@ -309,7 +304,7 @@ sim_repair_kernel(const KernelArgs a)
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
     a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy>(
-        a, ln, p, counters, n_counters, b, j, first, true, true, old_state, stale_buf, q_begin,
+        a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
         a.repair_cap, ~0ull, m_first, m_end);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
@@ -331,8 +326,7 @@ sim_chain_kernel(const KernelArgs a)
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
 
-    uint32_t counters; int n_counters;
-    Lane ln = setup_lane<kGroupGood>(a, b, lane, counters, n_counters);
+    Lane ln = setup_lane<kGroupGood>(a, b, lane);
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
     Pipe p;
@@ -377,8 +371,7 @@ sim_chain_kernel(const KernelArgs a)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
         }
         ++redone;
-        for (int c = 0; c < n_counters; ++c) SM_U16(counters + c * kLanes) = 0;
-        run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, counters, n_counters, b, j, begin, true,
+        run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, b, j, begin, true,
                                               true, old_state, stale_buf, q_begin, 0, ~0ull,
                                               m_first, m_end);
         a.repair_from[(size_t)j * a.B + b] = -1;
@@ -387,33 +380,72 @@ sim_chain_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
-// Adds the per-segment counters of the runs that count: one thread per
-// (counter, scored candidate).
-__global__ void sum_counters_kernel(const KernelArgs a, int32_t n_counters,
-                                    int32_t *model_num_requests, int32_t *model_num_good,
-                                    int32_t *group_num_requests, int32_t *group_num_good)
+// Tallies the recorded decisions of the runs that count (controller.py:587,
+// 611, 617-618).  A warp handles 32 consecutive scored candidates (one per
+// lane, so their decisions of one request are one 64-byte access) over a
+// range of at most 32 segments (fewer than 65 536 requests); each lane counts
+// in its own 16-bit shared-memory histogram [M + 2G][lane] and adds it to the
+// outputs, which must be zero on entry.
+template <typename Dec>
+__global__ void __launch_bounds__(kLanes)
+count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t *model_num_good,
+             int32_t *group_num_requests, int32_t *group_num_good)
 {
-    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (int64_t)a.Bs * n_counters) return;
-    const int c = (int)(t / a.Bs);
-    const int64_t b = t % a.Bs;
-    const int32_t M = a.M, G = a.G;
-    uint32_t v = 0;
-    if (a.num_leaves > 0) {
-        for (int32_t q = 0; q < a.NS; ++q) {
-            const int32_t src = a.seg_src[(size_t)q * a.B + b];
-            v += a.seg_counters[((size_t)q * n_counters + c) * a.B + (src >= 0 ? src : b)];
+    constexpr uint32_t kAccepted = 1u << (8 * sizeof(Dec) - 1);
+    extern __shared__ uint16_t hist[];
+    const int lane = threadIdx.x;
+    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
+    const int n_counters = a.M + 2 * a.G;
+    for (int c = 0; c < n_counters; ++c) hist[c * kLanes + lane] = 0;
+    if (b >= a.Bs || a.num_leaves == 0) return;
+    const size_t tb = trace_base(a, b);
+    const int32_t q0 = blockIdx.y * seg_per_block;
+    const int32_t q1 = q0 + seg_per_block < a.NS ? q0 + seg_per_block : a.NS;
+    for (int32_t q = q0; q < q1; ++q) {
+        const int32_t src = a.seg_src[(size_t)q * a.B + b];
+        const Dec *col = static_cast<const Dec *>(a.decisions) + (src >= 0 ? src : b);
+        const int32_t i1 = seg_leaf(a, q + 1) < a.num_leaves ? a.leaf_start[seg_leaf(a, q + 1)]
+                                                             : (int32_t)a.N;
+        // eight requests at a time, so that their loads are in flight together
+        for (int32_t i0 = a.leaf_start[seg_leaf(a, q)]; i0 < i1; i0 += 8) {
+            uint32_t d[8];
+            int32_t m[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int32_t i = i0 + u < i1 ? i0 + u : i1 - 1;
+                d[u] = col[(size_t)i * a.B];
+                m[u] = a.model_ids[(size_t)i * a.trace_pitch + tb];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (i0 + u >= i1 || d[u] == 0) continue;
+                const uint32_t g = (d[u] & (kAccepted - 1)) - 1;
+                hist[(a.M + g) * kLanes + lane] += 1;
+                if (d[u] & kAccepted) {
+                    hist[m[u] * kLanes + lane] += 1;
+                    hist[(a.M + a.G + g) * kLanes + lane] += 1;
+                }
+            }
         }
     }
-    if (c < M) {
-        model_num_good[(size_t)b * M + c] = (int32_t)v;
-        model_num_requests[(size_t)b * M + c] =
-            a.model_hist[(a.trace_pitch > 1 ? (size_t)b * (M + 1) : 0) + c];
-    } else if (c < M + G) {
-        group_num_requests[(size_t)b * G + (c - M)] = (int32_t)v;
-    } else {
-        group_num_good[(size_t)b * G + (c - M - G)] = (int32_t)v;
+    for (int m = 0; m < a.M; ++m)
+        if (hist[m * kLanes + lane]) atomicAdd(&model_num_good[(size_t)b * a.M + m], (int32_t)hist[m * kLanes + lane]);
+    for (int g = 0; g < a.G; ++g) {
+        const uint32_t r = hist[(a.M + g) * kLanes + lane], k = hist[(a.M + a.G + g) * kLanes + lane];
+        if (r) atomicAdd(&group_num_requests[(size_t)b * a.G + g], (int32_t)r);
+        if (group_good && k) atomicAdd(&group_num_good[(size_t)b * a.G + g], (int32_t)k);
     }
+}
+
+// model_num_requests (controller.py:587) does not depend on the placement:
+// one thread per (candidate, model) copies the trace's histogram.
+__global__ void model_requests_kernel(const KernelArgs a, int32_t *model_num_requests)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (int64_t)a.Bs * a.M) return;
+    const int64_t b = t / a.M;
+    const int m = (int)(t % a.M);
+    model_num_requests[t] = a.model_hist[(a.trace_pitch > 1 ? (size_t)b * (a.M + 1) : 0) + m];
 }
 
 // Combines the leaf sums in numpy's pairing order and totals the good

@@ -3,7 +3,7 @@
 // Geometry.  The trace is cut at leaf boundaries of numpy's pairwise sum into
 // SEGMENTS of about seg_len requests (the last one takes the remainder); a
 // CHUNK is seg_per_chunk consecutive segments.  Per (candidate, segment) the
-// kernels keep the clock vector at the segment's end and the counters of the
+// kernels keep the clock vector at the segment's end and the decisions of the
 // segment; per (candidate, chunk) the clock vector the chunk was started
 // from.  All of it is laid out [..][entry][candidate] so that the 32
 // candidates of a warp touch consecutive addresses.
@@ -49,7 +49,10 @@ struct KernelArgs {
     double *leaf_sums;            // [num_leaves][B]
     double *seg_end;              // [NS][T][B]   clock vector after each segment
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from
-    uint32_t *seg_counters;       // [NS][n_counters][B]
+    void *decisions;              // [N][B] u8 (up to 126 groups) or u16: per request 0 = not
+                                  //   dispatched, else (group + 1) | accepted << 7 (or << 15),
+                                  //   see count_kernel
+    bool dec_wide;
     uint32_t *work_count;         // [rounds]
     uint32_t *work_items;         // [B * K]: chunk * B + candidate; bit 31 = continue a repair
     int32_t *repair_from;         // [K][B]: segment a capped repair of chunk j stopped at, or -1
@@ -184,18 +187,9 @@ __device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X
     return true;
 }
 
-__device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, int n_counters,
-                                      int32_t q, int64_t b)
-{
-    for (int c = 0; c < n_counters; ++c) {
-        a.seg_counters[((size_t)q * n_counters + c) * a.B + b] = SM_U16(counters + c * kLanes);
-        SM_U16(counters + c * kLanes) = 0;
-    }
-}
-
 // Runs chunk j of candidate b on this lane: requests [begin, first) as run-in
 // (nothing recorded; `first` is the chunk's first request), then the chunk's
-// segments, recording counters, per-request outputs (kFull) and one latency
+// segments, recording decisions, per-request outputs (kFull) and one latency
 // sum per leaf.  Within a leaf the latency of request k goes to partial sum
 // k mod 8, as numpy's pairwise sum does: the eight partial sums rotate
 // through p0 so that the loop holds ONE copy of the step.
@@ -214,8 +208,8 @@ __device__ inline void flush_counters(const KernelArgs &a, uint32_t counters, in
 // Returns -1 when the chunk is finished (ran to its end, or settled), else
 // the segment at which the capped repair has to be continued.
 template <bool kFull, bool kGroupGood, bool kLegacy>
-__device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint32_t counters,
-                                    int n_counters, int64_t b, int32_t j, int32_t begin,
+__device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
+                                    int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
                                     uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0,
                                     uint64_t swap_pairs = ~0ull, int64_t m_first = 0,
@@ -286,7 +280,6 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p, uint
             a.leaf_sums[(size_t)leaf * a.B + b] = r;
             if (leaf + 1 == seg_stop) {             // segment q is complete
                 ++done;
-                flush_counters(a, counters, n_counters, q, b);
                 // A repair stops when its state is equivalent to the state some
                 // stored run had at this point: the run currently selected for
                 // this segment, or a mirror's.  The rest of the chunk is then

@@ -2,7 +2,7 @@
 //
 // One THREAD simulates one stream of requests for one candidate placement
 // (alpa_serve/simulator/controller.py:579-622 is the loop body restated in
-// sim_step below).  Mutable state (stage clocks, counters) lives in shared
+// sim_step below).  Mutable state (the stage clocks) lives in shared
 // memory as [entry][lane], so lane-private accesses fall on distinct banks;
 // shared memory is what limits the number of resident warps, so the
 // read-only replica lists stay in global memory (one 16-byte row per model,
@@ -25,7 +25,7 @@ namespace mms {
 constexpr double kInf = 1e100;          // alpa_serve/util.py:23
 constexpr double kOverhead = 0.011;     // controller.py:575
 constexpr int kLanes = 32;              // streams per warp
-constexpr int kMaxBlockWarps = 10;      // warps of a stream-kernel block
+constexpr int kMaxBlockWarps = 12;      // warps of a stream-kernel block
 constexpr int kMaxWarpsPerSm = 12;      // the stream kernel's registers allow that many
 constexpr int kClockPad = 8;            // readable slots past the last clock
 constexpr int kRowWords = 4;            // u32 words of a model's replica row
@@ -49,15 +49,14 @@ __device__ __forceinline__ uint32_t rep_column(uint32_t e) { return e >> 24; }
 struct SmemLayout {
     size_t latency;                      // from the start of the array
     size_t warp0, warp_bytes;            // first warp's region; size of a region
-    size_t clocks, stage_tmp, counters;  // inside a warp's region
+    size_t clocks, stage_tmp;            // inside a warp's region
     size_t total;                        // bytes of a one-warp block
-    int n_counters, tmp_stages;
+    int tmp_stages;
 };
 
 // lat_elems: entries of the shared f32 latency table kept on chip (0 = read
-// it from global memory).  Counters are 16 bits wide: they are flushed to
-// global memory after every segment, and a segment has fewer than 2048
-// requests.
+// it from global memory).  Counters are not kept on chip: the step records
+// its decision per request (see Lane::dec) and count_kernel tallies them.
 __host__ __device__ inline SmemLayout smem_layout(int M, int G, int /*P*/, int T, int S,
                                                   bool group_good, int lat_elems)
 {
@@ -68,8 +67,6 @@ __host__ __device__ inline SmemLayout smem_layout(int M, int G, int /*P*/, int T
     L.clocks = off;     off += sizeof(double) * (size_t)(T + kClockPad) * kLanes;
     L.tmp_stages = S > 8 ? S - 8 : 0;
     L.stage_tmp = off;  off += sizeof(double) * (size_t)L.tmp_stages * kLanes;
-    L.n_counters = M + G + (group_good ? G : 0);
-    L.counters = off;   off += sizeof(uint16_t) * (size_t)L.n_counters * kLanes;
     L.warp_bytes = (off + 15) & ~(size_t)15;
     L.total = L.warp0 + L.warp_bytes;
     return L;
@@ -81,9 +78,11 @@ struct Lane {
     uint32_t clk;             // f64 index of clock slot 0
     uint32_t tmp;             // f64 index, stages beyond the 8th of a deep pipeline
     uint32_t lat_sm;          // f32 index of the on-chip latency table
-    uint32_t model_good;      // u16 index, [M]
-    uint32_t group_req;       // u16 index, [G]
-    uint32_t group_good;      // u16 index, [G]
+    void *dec;                // this candidate's column of the decision array: per request
+                              //   0 = not dispatched, else (group + 1) | accepted << 7 in a
+                              //   byte (up to 126 groups), or | accepted << 15 in 16 bits
+    uint32_t dec_pitch;       // elements between consecutive requests in that array
+    bool dec_wide;            // 16-bit decisions
     const uint4 *rows;        // [M + 1] replica rows of this candidate (global memory,
                               //   kLanes apart: the rows of 32 consecutive candidates for one
                               //   model are contiguous, so a warp fetches them coalesced): the
@@ -160,7 +159,7 @@ __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
 // Executes request `i` (controller.py:579-622, or :519-555 with kLegacy) and
 // advances the pipe.  Returns finish - arrival, which is 0.0 for a dropped
 // request (the reference stores finish = arrival for those).
-//   record  update counters and per-request outputs (off during run-in)
+//   record  write the decision and the per-request outputs (off during run-in)
 // The common path has no divergent branch: a lane whose candidate has no
 // replica of the model, or drops the request, runs the same instructions on
 // harmless addresses and its stores are predicated off.  The step is large;
@@ -281,11 +280,14 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
             for (uint32_t k = 8; k < ns; ++k)
                 SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
     }
-    if (record) {
-        // :611, :617-618; lanes that did not dispatch or accept add 0 to harmless slots
-        SM_U16(ln.group_req + g * kLanes) += found ? 1u : 0u;
-        SM_U16(ln.model_good + (uint32_t)(m < 0 ? 0 : m) * kLanes) += accept ? 1u : 0u;
-        if (kGroupGood) SM_U16(ln.group_good + g * kLanes) += accept ? 1u : 0u;
+    if (record) {   // :611, :617-618 are tallied from this record by count_kernel
+        const size_t at = (size_t)i * ln.dec_pitch;
+        if (ln.dec_wide)
+            static_cast<uint16_t *>(ln.dec)[at] =
+                (uint16_t)(found ? (g + 1u) | (accept ? 0x8000u : 0u) : 0u);
+        else
+            static_cast<uint8_t *>(ln.dec)[at] =
+                (uint8_t)(found ? (g + 1u) | (accept ? 0x80u : 0u) : 0u);
     }
     if (kFull && record) {
         finish_out[i] = fin;

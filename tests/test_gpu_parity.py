@@ -541,3 +541,38 @@ def test_placement_schedule_through_approximate_one_case(loaded, golden, fast):
                   "latency_p90", "latency_p99"):
         got = np.array([getattr(x, field) for x in pm], np.float64)
         assert np.array_equal(got, g[f"{tag}_model_{field}"].astype(np.float64)), field
+
+
+def test_many_groups_use_wide_decision_records(loaded):
+    """More than 126 groups: the per-request decision records are 16 bits
+    wide; counters and outputs still equal the checker's."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement, PlacementEvaluator
+    from mms_b200.profiling import ParallelConfig
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    base = cases.candidate_batch_case(num_candidates=1, duration=400.0, num_models=8,
+                                      num_devices=16, total_rate=60.0)
+    rng = np.random.RandomState(5)
+    c1, c2 = ParallelConfig(1, 1, 1), ParallelConfig(1, 1, 2)
+    sols = []
+    for n_groups in (127, 150, 200):
+        configs = [c1 if rng.rand() < 0.9 else c2 for _ in range(n_groups)]
+        models = [sorted(rng.choice(8, size=rng.randint(1, 3), replace=False).tolist())
+                  for _ in range(n_groups)]
+        sols.append(ModelPlacement(configs, models))
+    ev = PlacementEvaluator(base.model_datas, base.cluster_env, base.workload)
+    enc = engine.encode_placements(sols, ev.table, len(ev.model_names))
+    assert enc.G == 200
+    res, _, _ = engine.run_batch(ev.trace, enc, ev.table, per_request=True, group_good=True)
+    names = [d.name for d in base.model_datas]
+    profs = [d.profiling_result for d in base.model_datas]
+    mids, slos = workload_arrays(base.workload, names)
+    arr = base.workload.arrivals
+    assert len(arr) > 2 * 8192
+    for b, p in enumerate(sols):
+        fin, good, mreq, mgood, greq, ggood = tables.one_placement(p, profs, mids, slos, arr)
+        assert res.finish[b].tobytes() == fin.tobytes(), b
+        assert np.array_equal(res.model_num_good[b], mgood)
+        assert np.array_equal(res.group_num_requests[b, :len(greq)], greq)
+        assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood)

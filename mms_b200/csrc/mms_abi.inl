@@ -109,13 +109,20 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         // Chunks are the units of parallel work: as many as fill nine tenths
         // of ONE wave of the resident warps (SMs x warps per SM at this
         // kernel's shared-memory use; a second wave would pay the run-in
-        // twice), but never chunks shorter than 4 segments.  More chunks mean
-        // more boundaries to validate and repair.
-        int64_t Kmax = NS / 4 > 0 ? NS / 4 : 1;
+        // twice), but never chunks shorter than 3 segments.  More chunks mean
+        // more boundaries to validate and repair.  The chunk length is rounded
+        // to the nearest number of segments when the chunks still fit the wave.
+        int64_t Kmax = NS / 3 > 0 ? NS / 3 : 1;
         int64_t K = B > 0 ? (9 * resident_slots * kLanes) / (10 * B) : 1;
         if (K > Kmax) K = Kmax;
         if (K < 1) K = 1;
         spc = (NS + K - 1) / K;
+        if (spc > 3 && B > 0) {
+            const int64_t shorter = spc - 1;
+            const int64_t more = (NS + shorter - 1) / shorter;
+            if (2 * NS < K * (2 * shorter + 1) && more * B <= resident_slots * kLanes)
+                spc = shorter;          // NS / K is nearer to the shorter length
+        }
     }
     if (spc < 1) spc = 1;
     if (spc > NS) spc = NS;

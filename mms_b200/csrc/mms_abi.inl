@@ -154,7 +154,8 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
                                                (c->num_models + 1) + 256);
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
-    g->off_decisions = off;   off += align256((c->max_groups > 126 ? 2 : 1) * (size_t)(N > 0 ? N : 1) * B);
+    g->off_decisions = off;   off += align256((c->max_groups > 126 ? 2 : 1) * (size_t)((N + 3) / 4 * 4 + 4) *
+                                               (size_t)((B + 31) / 32 * 32));
     g->off_work_count = off;  off += align256(sizeof(uint32_t) * (kMaxRepairRounds + 1));
     g->off_repair_from = off; off += align256(sizeof(int32_t) * (size_t)K * B);
     g->off_work_items = off;  off += align256(sizeof(uint32_t) * (size_t)K * B);
@@ -377,6 +378,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.leaf_sums = (double *)(scratch + g.off_leaf);
     ka.decisions = scratch + g.off_decisions;
     ka.dec_wide = cands->max_groups > 126;
+    ka.dec_pitch = ((int64_t)B + 31) / 32 * 32;
     ka.work_count = (uint32_t *)(scratch + g.off_work_count);
     ka.work_items = (uint32_t *)(scratch + g.off_work_items);
     ka.repair_from = (int32_t *)(scratch + g.off_repair_from);

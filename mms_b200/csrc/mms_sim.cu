@@ -105,9 +105,9 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
     ln.tmp = (uint32_t)((base + L.stage_tmp) / sizeof(double)) + lane;
     ln.lat_sm = (uint32_t)(L.latency / sizeof(float));
     ln.dec_wide = a.dec_wide;
-    ln.dec = a.dec_wide ? static_cast<void *>(static_cast<uint16_t *>(a.decisions) + b)
-                        : static_cast<void *>(static_cast<uint8_t *>(a.decisions) + b);
-    ln.dec_pitch = (uint32_t)a.B;
+    ln.dec = a.dec_wide ? static_cast<void *>(static_cast<uint16_t *>(a.decisions) + 4 * b)
+                        : static_cast<void *>(static_cast<uint8_t *>(a.decisions) + 4 * b);
+    ln.dec_pitch = (uint32_t)a.dec_pitch;
     ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + row_index(a, b, 0);
     ln.rep_raw = a.model_rep + (size_t)b * a.P;
     ln.rep_off = a.model_off + (size_t)b * (a.M + 1);
@@ -403,25 +403,34 @@ count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t
     const int32_t q1 = q0 + seg_per_block < a.NS ? q0 + seg_per_block : a.NS;
     for (int32_t q = q0; q < q1; ++q) {
         const int32_t src = a.seg_src[(size_t)q * a.B + b];
-        const Dec *col = static_cast<const Dec *>(a.decisions) + (src >= 0 ? src : b);
+        // four consecutive requests of a candidate are one aligned group of records
+        struct alignas(4 * sizeof(Dec)) Quad { Dec r[4]; };
+        const Quad *col = static_cast<const Quad *>(a.decisions) + (src >= 0 ? src : b);
+        const int32_t i_begin = a.leaf_start[seg_leaf(a, q)];
         const int32_t i1 = seg_leaf(a, q + 1) < a.num_leaves ? a.leaf_start[seg_leaf(a, q + 1)]
                                                              : (int32_t)a.N;
-        // eight requests at a time, so that their loads are in flight together
-        for (int32_t i0 = a.leaf_start[seg_leaf(a, q)]; i0 < i1; i0 += 8) {
-            uint32_t d[8];
+        // two groups (eight requests) at a time, so that their loads are in flight together;
+        // segments start at multiples of 8
+        for (int32_t i0 = i_begin; i0 < i1; i0 += 8) {
+            Quad d[2];
             int32_t m[8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int32_t i = i0 + 4 * u < i1 ? i0 + 4 * u : i0;
+                d[u] = col[(size_t)(i >> 2) * a.dec_pitch];
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int32_t i = i0 + u < i1 ? i0 + u : i1 - 1;
-                d[u] = col[(size_t)i * a.B];
                 m[u] = a.model_ids[(size_t)i * a.trace_pitch + tb];
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                if (i0 + u >= i1 || d[u] == 0) continue;
-                const uint32_t g = (d[u] & (kAccepted - 1)) - 1;
+                const uint32_t rec = d[u >> 2].r[u & 3];
+                if (i0 + u >= i1 || rec == 0) continue;
+                const uint32_t g = (rec & (kAccepted - 1)) - 1;
                 hist[(a.M + g) * kLanes + lane] += 1;
-                if (d[u] & kAccepted) {
+                if (rec & kAccepted) {
                     hist[m[u] * kLanes + lane] += 1;
                     hist[(a.M + a.G + g) * kLanes + lane] += 1;
                 }

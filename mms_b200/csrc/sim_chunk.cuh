@@ -49,7 +49,9 @@ struct KernelArgs {
     double *leaf_sums;            // [num_leaves][B]
     double *seg_end;              // [NS][T][B]   clock vector after each segment
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from
-    void *decisions;              // [N][B] u8 (up to 126 groups) or u16: per request 0 = not
+    int64_t dec_pitch;            // elements per request row of `decisions`: B rounded up to 32,
+                                  //   so that a warp's records of one request fill whole sectors
+    void *decisions;              // [ceil(N/4)][dec_pitch][4] u8 (up to 126 groups) or u16: 0 = not
                                   //   dispatched, else (group + 1) | accepted << 7 (or << 15),
                                   //   see count_kernel
     bool dec_wide;

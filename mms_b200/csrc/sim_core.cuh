@@ -78,7 +78,7 @@ struct Lane {
     uint32_t clk;             // f64 index of clock slot 0
     uint32_t tmp;             // f64 index, stages beyond the 8th of a deep pipeline
     uint32_t lat_sm;          // f32 index of the on-chip latency table
-    void *dec;                // this candidate's column of the decision array: per request
+    void *dec;                // element (request 0, this candidate) of the decision array: per request
                               //   0 = not dispatched, else (group + 1) | accepted << 7 in a
                               //   byte (up to 126 groups), or | accepted << 15 in 16 bits
     uint32_t dec_pitch;       // elements between consecutive requests in that array
@@ -281,7 +281,9 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
                 SM_F64(ck + k * kLanes) = SM_F64(ln.tmp + (k - 8) * kLanes);
     }
     if (record) {   // :611, :617-618 are tallied from this record by count_kernel
-        const size_t at = (size_t)i * ln.dec_pitch;
+        // four consecutive requests of a candidate sit side by side (count_kernel reads them
+        // with one load): element (i, b) is at ((i / 4) * pitch + b) * 4 + i % 4
+        const size_t at = ((size_t)(i >> 2) * ln.dec_pitch) * 4 + (size_t)(i & 3);
         if (ln.dec_wide)
             static_cast<uint16_t *>(ln.dec)[at] =
                 (uint16_t)(found ? (g + 1u) | (accept ? 0x8000u : 0u) : 0u);

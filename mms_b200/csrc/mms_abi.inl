@@ -110,19 +110,14 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         // of ONE wave of the resident warps (SMs x warps per SM at this
         // kernel's shared-memory use; a second wave would pay the run-in
         // twice), but never chunks shorter than 3 segments.  More chunks mean
-        // more boundaries to validate and repair.  The chunk length is rounded
-        // to the nearest number of segments when the chunks still fit the wave.
-        int64_t Kmax = NS / 3 > 0 ? NS / 3 : 1;
-        int64_t K = B > 0 ? (9 * resident_slots * kLanes) / (10 * B) : 1;
-        if (K > Kmax) K = Kmax;
-        if (K < 1) K = 1;
-        spc = (NS + K - 1) / K;
-        if (spc > 3 && B > 0) {
-            const int64_t shorter = spc - 1;
-            const int64_t more = (NS + shorter - 1) / shorter;
-            if (2 * NS < K * (2 * shorter + 1) && more * B <= resident_slots * kLanes)
-                spc = shorter;          // NS / K is nearer to the shorter length
-        }
+        // more boundaries to validate and repair.  The chunk length is that
+        // ideal rounded to the nearest number of segments, or the next longer
+        // one when the chunks would not fit the wave any more.
+        const int64_t lanes = resident_slots * kLanes;
+        spc = B > 0 ? (20 * NS * B + 9 * lanes) / (18 * lanes) : NS;      // round(NS / K_ideal)
+        if (spc < 3) spc = 3;
+        if (spc > NS) spc = NS;
+        if (B > 0 && ((NS + spc - 1) / spc) * B > lanes) spc += 1;
     }
     if (spc < 1) spc = 1;
     if (spc > NS) spc = NS;

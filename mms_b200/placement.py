@@ -127,7 +127,7 @@ class PlacementEvaluator:
                                         len(self.model_names), device=device)
         self.table = engine.LatencyTable(self.prof_ress)
         self.options = options          # engine.sim_options(...) or None
-        self.pipeline_parts = 3         # a long list is encoded and launched in parts
+        self.pipeline_parts = 4         # a long list is encoded and launched in parts
         self.pipeline_min_part = 768    # placements per part, at least
         self.pipeline_split = False     # parts overlap each other already
         self._streams = []

@@ -105,6 +105,13 @@ def host_lib():
             H.mms_host_flatten.restype = ctypes.c_int
             H.mms_host_flatten.argtypes = [ctypes.py_object, _vp, _vp, _vp, ctypes.c_int64,
                                            ctypes.c_int64]
+            H.mms_host_flatten_once.restype = ctypes.c_int
+            H.mms_host_flatten_once.argtypes = [ctypes.py_object] + [_vp] * 5 + [
+                ctypes.c_int64, ctypes.c_int64, _vp]
+            H.mms_host_configs.restype = ctypes.c_int64
+            H.mms_host_configs.argtypes = [_vp, ctypes.c_int64, _vp, ctypes.c_int64, _vp]
+            H.mms_host_encode.restype = ctypes.c_int
+            H.mms_host_encode.argtypes = [ctypes.c_int64] * 4 + [_vp] * 14
             _host = H
     return _host
 

@@ -1,16 +1,18 @@
-/* encode_host.c — flattens a list of placements for the numpy encoder.
+/* encode_host.c — flattens and encodes a list of placements.
  *
  * Host-side helper of mms_b200/engine.py::encode_placements, loaded with
  * ctypes.PyDLL (the GIL stays held; no module object, no numpy C API: the
  * caller passes pointers to arrays it allocated).  It replaces the
  * per-object passes over 10^5 Python objects (group configs, model lists)
- * that dominated the encoding time; everything after the flattening stays
- * vectorised numpy.  A placement is any object with `group_configs` (a
+ * and the dozen numpy passes behind them (sort by model, prefix sums,
+ * hashing of model sets) that dominated the encoding time: one walk over the
+ * objects, one walk over the flat arrays.  A placement is any object with `group_configs` (a
  * sequence of (dp, op, pp) tuples, e.g. ParallelConfig namedtuples) and
  * `group_models` (a sequence of sequences of ints) —
  * alpa_serve/placement_policy/base_policy.py:18-27.
  *
- * Every function returns 0, or -1 with a Python exception set.
+ * The functions that take Python objects return 0, or -1 with a Python
+ * exception set.
  */
 #define PY_SSIZE_T_CLEAN
 #include <Python.h>
@@ -138,4 +140,211 @@ int mms_host_flatten(PyObject *placements, int64_t *cfg, int64_t *n_in_group, in
     }
     Py_DECREF(seq);
     return rc;
+}
+
+/* One pass instead of scan + flatten, for callers that come with room to
+ * spare: fills n_groups[B], n_pairs[B] and the three flat arrays, totals[0] =
+ * groups, totals[1] = pairs.  Returns -2 (no exception set) when the arrays
+ * are too small; the caller then falls back to the two passes above. */
+int mms_host_flatten_once(PyObject *placements, int64_t *n_groups, int64_t *n_pairs, int64_t *cfg,
+                          int64_t *n_in_group, int64_t *placed_model, int64_t cap_groups,
+                          int64_t cap_pairs, int64_t *totals)
+{
+    if (intern_names()) return -1;
+    PyObject *seq = PySequence_Fast(placements, "placements must be a sequence");
+    if (!seq) return -1;
+    const Py_ssize_t B = PySequence_Fast_GET_SIZE(seq);
+    int rc = 0;
+    int64_t gi = 0, pi = 0;
+    for (Py_ssize_t b = 0; b < B && rc == 0; ++b) {
+        PyObject *p = PySequence_Fast_GET_ITEM(seq, b);
+        PyObject *cfgs = PyObject_GetAttr(p, g_str_configs);
+        PyObject *mods = cfgs ? PyObject_GetAttr(p, g_str_models) : NULL;
+        PyObject *cseq = mods ? PySequence_Fast(cfgs, "group_configs must be a sequence") : NULL;
+        PyObject *mseq = cseq ? PySequence_Fast(mods, "group_models must be a sequence") : NULL;
+        if (!mseq) {
+            rc = -1;
+        } else {
+            const Py_ssize_t G = PySequence_Fast_GET_SIZE(mseq);
+            const int64_t p_first = pi;
+            if (PySequence_Fast_GET_SIZE(cseq) != G) {
+                PyErr_SetString(PyExc_ValueError, "group_configs and group_models differ in length");
+                rc = -1;
+            } else if (gi + G > cap_groups) {
+                rc = -2;
+            }
+            for (Py_ssize_t g = 0; g < G && rc == 0; ++g) {
+                PyObject *c = PySequence_Fast_GET_ITEM(cseq, g);
+                if (!PyTuple_Check(c) || PyTuple_GET_SIZE(c) < 3) {
+                    PyErr_SetString(PyExc_TypeError, "a group config must be a (dp, op, pp) tuple");
+                    rc = -1;
+                    break;
+                }
+                for (int k = 0; k < 3 && rc == 0; ++k)
+                    rc = as_int64(PyTuple_GET_ITEM(c, k), &cfg[3 * gi + k]);
+                if (rc) break;
+                PyObject *ms = PySequence_Fast(PySequence_Fast_GET_ITEM(mseq, g),
+                                               "a group's models must be a sequence");
+                if (!ms) { rc = -1; break; }
+                const Py_ssize_t n = PySequence_Fast_GET_SIZE(ms);
+                if (pi + n > cap_pairs) rc = -2;
+                for (Py_ssize_t k = 0; k < n && rc == 0; ++k)
+                    rc = as_int64(PySequence_Fast_GET_ITEM(ms, k), &placed_model[pi++]);
+                Py_DECREF(ms);
+                n_in_group[gi++] = (int64_t)n;
+            }
+            n_groups[b] = (int64_t)G;
+            n_pairs[b] = pi - p_first;
+        }
+        Py_XDECREF(mseq);
+        Py_XDECREF(cseq);
+        Py_XDECREF(mods);
+        Py_XDECREF(cfgs);
+    }
+    Py_DECREF(seq);
+    totals[0] = gi;
+    totals[1] = pi;
+    return rc;
+}
+
+/* ---- plain C from here on: no Python objects ---- */
+
+/* Distinct (dp, op, pp) rows in order of first appearance: uniq[count][3],
+ * inverse[n] = index into uniq.  Returns the count, or -1 when there are more
+ * than cap. */
+int64_t mms_host_configs(const int64_t *cfg, int64_t n, int64_t *uniq, int64_t cap, int32_t *inverse)
+{
+    int64_t count = 0, last = -1;
+    for (int64_t i = 0; i < n; ++i) {
+        const int64_t *c = cfg + 3 * i;
+        int64_t hit = -1;
+        if (last >= 0 && uniq[3 * last] == c[0] && uniq[3 * last + 1] == c[1] && uniq[3 * last + 2] == c[2]) {
+            hit = last;
+        } else {
+            for (int64_t u = 0; u < count; ++u)
+                if (uniq[3 * u] == c[0] && uniq[3 * u + 1] == c[1] && uniq[3 * u + 2] == c[2]) { hit = u; break; }
+        }
+        if (hit < 0) {
+            if (count >= cap) return -1;
+            uniq[3 * count] = c[0]; uniq[3 * count + 1] = c[1]; uniq[3 * count + 2] = c[2];
+            hit = count++;
+        }
+        inverse[i] = (int32_t)hit;
+        last = hit;
+    }
+    return count;
+}
+
+static uint64_t mix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+/* The tables of mms_placements (include/mms_sim.h) from the flat arrays.
+ * Per placement b with groups g = 0 .. n_groups[b]-1 in the given order:
+ *   group_info[b][g] = first clock slot | stages << 8 | contested << 16
+ *   model_off[b][m] .. model_off[b][m+1]: the replicas of model m in model_rep,
+ *   ascending group id (dispatch ties go to the lowest group id,
+ *   alpa_serve/simulator/controller.py:590-598)
+ *   model_rep[b][k] = group | first clock slot << 8 | stages << 16 | column << 24
+ * slots[b] = clock slots used; twin_items[n][3] = (placement, class number
+ * inside the placement, group id) for every group that has the same column
+ * and the same set of models as another group of its placement, classes and
+ * groups ascending; *n_twin_items = n.  counts is scratch of M + 1 entries,
+ * mark of M.  Unused cells of the tables must come zeroed.
+ * Returns 0, or 1 when a model id is outside [0, M). */
+int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
+                    const int64_t *n_groups, const int64_t *cfg, const int32_t *cfg_index,
+                    const int64_t *column_of, const int64_t *n_in_group, const int64_t *placed_model,
+                    uint16_t *model_off, uint32_t *model_rep, uint32_t *group_info,
+                    int64_t *slots, int32_t *twin_items, int64_t *n_twin_items,
+                    int64_t *counts, int64_t *mark)
+{
+    int64_t gi = 0, pi = 0, n_items = 0;
+    for (int64_t m = 0; m < M; ++m) mark[m] = -1;
+    for (int64_t b = 0; b < B; ++b) {
+        const int64_t ng = n_groups[b];
+        const int64_t *nin = n_in_group + gi;
+        uint16_t *off = model_off + b * (M + 1);
+        uint32_t *rep = model_rep + b * P;
+        uint32_t *info = group_info + b * G;
+        /* replicas per model */
+        for (int64_t m = 0; m <= M; ++m) counts[m] = 0;
+        int64_t q = pi;
+        for (int64_t g = 0; g < ng; ++g)
+            for (int64_t k = 0; k < nin[g]; ++k) {
+                const int64_t m = placed_model[q++];
+                if (m < 0 || m >= M) return 1;
+                counts[m + 1]++;
+            }
+        int64_t run = 0;
+        off[0] = 0;
+        for (int64_t m = 0; m < M; ++m) {
+            const int64_t c = counts[m + 1];
+            counts[m + 1] = run;                      /* next free position of model m */
+            run += c;
+            off[m + 1] = (uint16_t)run;
+        }
+        /* groups in ascending id: positions inside a model's list come out ascending too */
+        int64_t slot = 0;
+        q = pi;
+        uint64_t key[256];
+        for (int64_t g = 0; g < ng; ++g) {
+            const int64_t pp = cfg[3 * (gi + g) + 2];
+            const int64_t col = column_of[cfg_index[gi + g]];
+            uint32_t contested = 0;
+            uint64_t h = 0;
+            for (int64_t k = 0; k < nin[g]; ++k) {
+                const int64_t m = placed_model[q++];
+                rep[counts[m + 1]++] = (uint32_t)(g | (slot << 8) | (pp << 16) | (col << 24));
+                if (off[m + 1] - off[m] > 1) contested = 1;
+                h += mix64((uint64_t)m);
+            }
+            info[g] = (uint32_t)(slot | (pp << 8) | ((int64_t)contested << 16));
+            if (g < 256) key[g] = h * 0x9E3779B97F4A7C15ull + (uint64_t)col * 0xC2B2AE3D27D4EB4Full + (uint64_t)nin[g];
+            slot += pp;
+        }
+        slots[b] = slot;
+        /* interchangeable groups: same column, same set of models (non-empty) */
+        if (ng <= 256) {
+            int64_t first_of[256];                     /* start of each group's models */
+            int64_t at = pi;
+            for (int64_t g = 0; g < ng; ++g) { first_of[g] = at; at += nin[g]; }
+            uint8_t done[256];
+            for (int64_t g = 0; g < ng; ++g) done[g] = 0;
+            int32_t cls = 0;
+            for (int64_t g = 0; g < ng; ++g) {
+                if (done[g] || nin[g] == 0) continue;
+                int marked = 0, found = 0;
+                for (int64_t h2 = g + 1; h2 < ng; ++h2) {
+                    if (done[h2] || key[h2] != key[g] || nin[h2] != nin[g]) continue;
+                    if (column_of[cfg_index[gi + h2]] != column_of[cfg_index[gi + g]]) continue;
+                    if (!marked) {
+                        for (int64_t k = 0; k < nin[g]; ++k) mark[placed_model[first_of[g] + k]] = gi + g;
+                        marked = 1;
+                    }
+                    int same = 1;
+                    for (int64_t k = 0; k < nin[h2] && same; ++k)
+                        same = mark[placed_model[first_of[h2] + k]] == gi + g;
+                    if (!same) continue;
+                    if (!found) {
+                        twin_items[3 * n_items] = (int32_t)b; twin_items[3 * n_items + 1] = cls;
+                        twin_items[3 * n_items + 2] = (int32_t)g; ++n_items;
+                        found = 1;
+                    }
+                    twin_items[3 * n_items] = (int32_t)b; twin_items[3 * n_items + 1] = cls;
+                    twin_items[3 * n_items + 2] = (int32_t)h2; ++n_items;
+                    done[h2] = 1;
+                }
+                if (found) ++cls;
+            }
+        }
+        pi = q;
+        gi += ng;
+    }
+    *n_twin_items = n_items;
+    return 0;
 }

@@ -422,8 +422,23 @@ def _flatten(placements):
     if H is not None and isinstance(placements, (list, tuple)):
         n_groups = np.zeros(B, np.int64)
         n_pairs = np.zeros(B, np.int64)
+        # one pass with room for 48 groups and 192 (group, model) pairs per placement ...
+        cap_g, cap_p = 48 * B + 64, 192 * B + 256
+        cfg = np.empty((cap_g, 3), np.int64)
+        n_in_group = np.empty(cap_g, np.int64)
+        placed_model = np.empty(cap_p, np.int64)
+        totals = np.zeros(2, np.int64)
+        rc = H.mms_host_flatten_once(placements, n_groups.ctypes.data, n_pairs.ctypes.data,
+                                     cfg.ctypes.data, n_in_group.ctypes.data,
+                                     placed_model.ctypes.data, cap_g, cap_p, totals.ctypes.data)
+        if rc == 0:
+            tg, tp = int(totals[0]), int(totals[1])
+            return n_groups, cfg[:tg], n_in_group[:tg], placed_model[:tp]
+        if rc != -2:
+            raise RuntimeError("mms_host_flatten_once failed")   # a Python exception is normally set
+        # ... else count first, then fill
         if H.mms_host_scan(placements, n_groups.ctypes.data, n_pairs.ctypes.data) != 0:
-            raise RuntimeError("mms_host_scan failed")       # a Python exception is normally set
+            raise RuntimeError("mms_host_scan failed")
         tot_groups, tot_placed = int(n_groups.sum()), int(n_pairs.sum())
         cfg = np.zeros((tot_groups, 3), np.int64)
         n_in_group = np.zeros(tot_groups, np.int64)
@@ -445,14 +460,84 @@ def _flatten(placements):
     return n_groups, cfg, n_in_group, placed_model
 
 
-def encode_placements(placements: Sequence, table: LatencyTable, num_models: int) -> EncodedBatch:
+def _too_large(G, T, S, C):
+    if G > nat.MAX_GROUPS or T > nat.MAX_SLOTS or S > nat.MAX_STAGES or C > nat.MAX_COLUMNS:
+        raise NotImplementedError(
+            f"placement too large for the kernels: {G} groups (max {nat.MAX_GROUPS}), "
+            f"{T} pipeline stages in total (max {nat.MAX_SLOTS}), {C} parallel configs "
+            f"(max {nat.MAX_COLUMNS})")
+
+
+def _encode_native(H, B, M, table, n_groups, cfg, n_in_group, placed_model) -> EncodedBatch:
+    """encode_placements behind the flattening, by csrc/encode_host.c."""
+    tot_groups = len(n_in_group)
+    cfg = np.ascontiguousarray(cfg)
+    uniq = np.zeros((nat.MAX_COLUMNS + 1, 3), np.int64)
+    cfg_index = np.zeros(max(tot_groups, 1), np.int32)
+    n_uniq = H.mms_host_configs(cfg.ctypes.data, tot_groups, uniq.ctypes.data, len(uniq),
+                                cfg_index.ctypes.data)
+    if n_uniq < 0:
+        raise NotImplementedError(f"more than {nat.MAX_COLUMNS} parallel configs in one batch")
+    # new columns are handed out in ascending (dp, op, pp)
+    found = [ParallelConfig(*map(int, row)) for row in uniq[:n_uniq]]
+    table.columns_for(sorted(found))
+    column_of = np.fromiter(map(table.column.__getitem__, found), np.int64, n_uniq)
+    G = int(n_groups.max()) if B else 0
+    S, C = int(table.max_stages), len(table.configs)
+    _too_large(G, 0, S, C)
+    # pairs per placement: the sums of n_in_group over each placement's groups
+    ends = np.cumsum(n_groups)
+    csum = np.concatenate(([0], np.cumsum(n_in_group)))
+    placed_per_b = csum[ends] - csum[ends - n_groups] if B else np.zeros(0, np.int64)
+    P = int(placed_per_b.max()) if B else 0
+    if P > nat.MAX_PLACED:
+        raise NotImplementedError(f"{P} (group, model) pairs in one placement (max {nat.MAX_PLACED})")
+    Gc, Pc = max(G, 1), max(P, 1)
+    model_off = np.zeros((B, M + 1), np.uint16)
+    model_rep = np.zeros((B, Pc), np.uint32)
+    group_info = np.zeros((B, Gc), np.uint32)
+    slots = np.zeros(max(B, 1), np.int64)
+    items = np.empty((max(tot_groups, 1), 3), np.int32)
+    n_items = np.zeros(1, np.int64)
+    counts = np.zeros(M + 1, np.int64)
+    mark = np.zeros(max(M, 1), np.int64)
+    n_groups = np.ascontiguousarray(n_groups, np.int64)
+    rc = H.mms_host_encode(B, M, Gc, Pc, n_groups.ctypes.data, cfg.ctypes.data,
+                           cfg_index.ctypes.data, column_of.ctypes.data, n_in_group.ctypes.data,
+                           placed_model.ctypes.data, model_off.ctypes.data, model_rep.ctypes.data,
+                           group_info.ctypes.data, slots.ctypes.data, items.ctypes.data,
+                           n_items.ctypes.data, counts.ctypes.data, mark.ctypes.data)
+    if rc == 1:
+        raise IndexError("model id in group_models is out of range")
+    T = int(slots[:B].max()) if B else 0
+    _too_large(G, T, S, C)
+    twins = []
+    prev_b, prev_c = -1, -1
+    for b, c, g in items[:int(n_items[0])].tolist():
+        if b != prev_b:
+            twins.append((b, []))
+            prev_c = -1
+        if c != prev_c:
+            twins[-1][1].append([])
+        twins[-1][1][-1].append(g)
+        prev_b, prev_c = b, c
+    return EncodedBatch(B, M, Gc, Pc, max(T, 1), S, C, model_off, model_rep, group_info,
+                        n_groups, placed_per_b.astype(np.int64), twins)
+
+
+def encode_placements(placements: Sequence, table: LatencyTable, num_models: int,
+                      native: bool = True) -> EncodedBatch:
     """List of ModelPlacement -> compact tables.  Each placement is taken as
     given: group order decides dispatch ties (controller.py:596 is a strict
-    '<' over groups in ascending id), so nothing is re-sorted."""
+    '<' over groups in ascending id), so nothing is re-sorted.  With the host
+    helper built (and `native`), one C pass makes the tables; else numpy does."""
     B = len(placements)
     M = int(num_models)
     n_groups, cfg, n_in_group, placed_model = _flatten(placements)
     tot_groups, tot_placed = len(n_in_group), len(placed_model)
+    H = nat.host_lib() if native else None
+    if H is not None:
+        return _encode_native(H, B, M, table, n_groups, cfg, n_in_group, placed_model)
     # distinct (dp, op, pp) rows -> columns of the latency table
     cfg_key = (cfg[:, 0] << 40) | (cfg[:, 1] << 20) | cfg[:, 2]
     uniq, inverse = np.unique(cfg_key, return_inverse=True)
@@ -477,11 +562,7 @@ def encode_placements(placements: Sequence, table: LatencyTable, num_models: int
     T = int(slots_per_b.max()) if B else 0
     S = int(table.max_stages)
     C = len(table.configs)
-    if G > nat.MAX_GROUPS or T > nat.MAX_SLOTS or S > nat.MAX_STAGES or C > nat.MAX_COLUMNS:
-        raise NotImplementedError(
-            f"placement too large for the kernels: {G} groups (max {nat.MAX_GROUPS}), "
-            f"{T} pipeline stages in total (max {nat.MAX_SLOTS}), {C} parallel configs "
-            f"(max {nat.MAX_COLUMNS})")
+    _too_large(G, T, S, C)
 
     # (candidate, model, group) triples, ordered by model then group inside b
     pl_grp = np.repeat(np.arange(tot_groups), n_in_group)           # flat group of each pair

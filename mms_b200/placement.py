@@ -127,9 +127,16 @@ class PlacementEvaluator:
                                         len(self.model_names), device=device)
         self.table = engine.LatencyTable(self.prof_ress)
         self.options = options          # engine.sim_options(...) or None
-        self.pipeline_parts = 4         # a long list is encoded and launched in parts
+        # A long list is encoded and launched in parts.  The first part only has
+        # to cover the host's work on the second, so it is the smaller one; more
+        # and smaller parts cost more on the GPU (shorter chunks, more run-in)
+        # than the encoding they hide.
+        self.pipeline_parts = 2
         self.pipeline_min_part = 768    # placements per part, at least
-        self.pipeline_split = False     # parts overlap each other already
+        self.pipeline_shares = (3, 5)   # relative sizes of the parts (None: equal)
+        # placements with mirror candidates as a launch of their own inside a
+        # part: one flag, or one per part
+        self.pipeline_split = True
         self._streams = []
         self.last_resimulated = None
         self.last_h2d_bytes = 0
@@ -138,9 +145,9 @@ class PlacementEvaluator:
     # -- the batched core ---------------------------------------------------
     def evaluate(self, sols: Sequence[ModelPlacement], pinned=False):
         """Scores the whole list; returns (batch, BatchResult) where `batch`
-        has B, num_groups and num_replicas.  A long list goes to the GPU in up
-        to `pipeline_parts` parts, each on a stream of its own, so that the
-        host encodes the next part while the GPU simulates the previous ones."""
+        has B, num_groups and num_replicas.  A long list goes to the GPU in
+        `pipeline_parts` parts, each on a stream of its own, so that the host
+        encodes the next part while the GPU simulates the previous ones."""
         n = len(sols)
         parts = max(1, min(self.pipeline_parts, n // self.pipeline_min_part))
         if parts == 1:
@@ -155,7 +162,17 @@ class PlacementEvaluator:
         while len(self._streams) < parts:
             self._streams.append(torch.cuda.Stream(device=dev))
         main = torch.cuda.current_stream(dev)
-        bounds = [n * k // parts for k in range(parts + 1)]
+        shares = self.pipeline_shares
+        if shares is None or len(shares) != parts:
+            shares = (1,) * parts
+        total, run, bounds = float(sum(shares)), 0.0, [0]
+        for share in shares:
+            run += share
+            bounds.append(min(n, int(round(n * run / total))))
+        bounds[-1] = n
+        split = self.pipeline_split
+        if isinstance(split, (bool, int)):
+            split = (bool(split),) * parts
         encs, jobs = [], []
         for k in range(parts):
             enc = engine.encode_placements(sols[bounds[k]:bounds[k + 1]], self.table,
@@ -163,7 +180,7 @@ class PlacementEvaluator:
             self._streams[k].wait_stream(main)           # the trace was uploaded there
             with torch.cuda.stream(self._streams[k]):
                 jobs.append(engine.submit_batch(self.trace, enc, self.table, pinned=pinned,
-                                                options=self.options, split=self.pipeline_split))
+                                                options=self.options, split=split[k]))
             encs.append(enc)
         done = [engine.collect_batch(job) for job in jobs]
         for k in range(parts):

@@ -446,6 +446,12 @@ def test_pipelined_evaluation_equals_one_launch(loaded):
     assert np.array_equal(res4.group_num_requests[:, :G], res1.group_num_requests)
     assert np.array_equal(enc4.num_groups, enc1.num_groups)
     assert ev.get_scores(case.placements[:5]) == scores4[:5]
+    # the defaults: two unequal parts, placements with mirrors launched apart inside each
+    ev2 = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload)
+    enc2, res2 = ev2.evaluate(case.placements)
+    assert [e.B for e in enc2.parts] == [638, 1062]
+    assert ev2.scores_from(enc2, res2) == scores4
+    assert np.array_equal(res2.model_num_good, res1.model_num_good)
 
 
 def test_trace_sweep_one_placement_many_traces(loaded):

@@ -228,3 +228,38 @@ def test_c_flattening_equals_python_flattening():
         engine._flatten([ModelPlacement(["pp2"], [[0]])])
     with pytest.raises(AttributeError):
         engine._flatten([object()])
+
+
+def test_c_encoder_equals_numpy_encoder():
+    """The tables and the classes of interchangeable groups from
+    csrc/encode_host.c equal those of the numpy encoder."""
+    from mms_b200 import _native as nat
+    from mms_b200 import cases, engine
+    from mms_b200.placement import ModelPlacement
+    from mms_b200.profiling import ParallelConfig
+    assert nat.host_lib() is not None, "libmms_host.so was not built"
+    case = cases.candidate_batch_case(num_candidates=700, duration=5.0, placement_seed=11)
+    c1, c2 = ParallelConfig(1, 1, 1), ParallelConfig(1, 1, 2)
+    sols = list(case.placements) + [
+        ModelPlacement([c1] * 6 + [c2] * 2, [[0, 3], [3, 0], [1], [1], [1], [], [2, 5], [5]]),
+        ModelPlacement([c1, c2], [[0], [0]]), ModelPlacement([], []),
+        ModelPlacement([c1, c1], [[], []]),
+        ModelPlacement([c2, c1, c2], [[7, 1, 2], [2], [2, 7, 1]])]
+    profs = [d.profiling_result for d in case.model_datas]
+    for batch in (sols, sols[-3:-2], []):
+        ta, tb = engine.LatencyTable(profs), engine.LatencyTable(profs)
+        a = engine.encode_placements(batch, ta, len(profs), native=True)
+        b = engine.encode_placements(batch, tb, len(profs), native=False)
+        assert ta.configs == tb.configs and ta.host.tobytes() == tb.host.tobytes()
+        for k in "B M G P T S C".split():
+            assert getattr(a, k) == getattr(b, k), k
+        for k in "model_off model_rep group_info num_groups num_replicas".split():
+            x, y = getattr(a, k), getattr(b, k)
+            assert x.dtype == y.dtype and x.shape == y.shape and np.array_equal(x, y), k
+        assert ({i: sorted(c) for i, c in a.twins} == {i: sorted(c) for i, c in b.twins})
+        assert [i for i, _ in a.twins] == sorted(i for i, _ in a.twins)
+    assert dict(a.twins) == {} and len(sols) - 1 in dict(
+        engine.encode_placements(sols, engine.LatencyTable(profs), len(profs)).twins)
+    with pytest.raises(IndexError):
+        engine.encode_placements([ModelPlacement([c1], [[len(profs)]])], engine.LatencyTable(profs),
+                                 len(profs))

@@ -93,7 +93,6 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
         if (warps > kMaxWarpsPerSm) warps = kMaxWarpsPerSm;
         if (warps >= per_sm) { per_sm = warps; block_warps = w; }
     }
-    g->block_warps = block_warps;
     const int64_t resident_slots = (int64_t)sm_count * per_sm;
     int64_t chunk = opts ? opts->chunk_requests : 0;
     int64_t warm = opts ? opts->warmup_requests : 0;
@@ -123,6 +122,17 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     if (spc > NS) spc = NS;
     const int64_t K = (NS + spc - 1) / spc;
     if (K * (B > 0 ? B : 1) >= 0x7FFFFFFFLL) return MMS_ERR_UNSUPPORTED;   // work-list encoding
+    // A launch that fills less than half of the GPU goes out in smaller
+    // blocks, one per SM: a warp that shares its SM with two others runs
+    // faster than one that shares it with eleven while most SMs stand idle.
+    // (A nearly full launch keeps the large blocks: the SMs they leave free
+    // serve the small kernels of a launch running beside it.)
+    const int64_t total_warps = ((B + kLanes - 1) / kLanes) * K;
+    if (2 * total_warps <= (int64_t)sm_count * block_warps) {
+        block_warps = (int)((total_warps + sm_count - 1) / sm_count);
+        if (block_warps < 1) block_warps = 1;
+    }
+    g->block_warps = block_warps;
     if (warm <= 0) warm = 2048;
     int rounds = opts ? opts->repair_rounds : 0;
     if (rounds <= 0) rounds = kDefaultRepairRounds;
@@ -146,7 +156,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
 
     size_t off = 0;
-    g->off_rows = off;        off += align256(sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
+    g->off_rows = off;        off += align256(2 * sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
                                                (c->num_models + 1) + 256);
     g->off_leaf = off;        off += align256(sizeof(double) * (size_t)plan_leaves(N) * B);
     g->off_decisions = off;   off += align256((c->max_groups > 126 ? 2 : 1) * (size_t)((N + 3) / 4 * 4 + 4) *

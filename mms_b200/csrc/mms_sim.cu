@@ -68,7 +68,8 @@ __global__ void build_rows_kernel(const KernelArgs a)
     if (t >= (int64_t)a.B * (a.M + 1)) return;
     const int64_t b = t / (a.M + 1);
     const int m = (int)(t % (a.M + 1));
-    uint32_t e[4] = {kNoReplica, kNoReplica, kNoReplica, kNoReplica};
+    uint32_t e[8] = {kNoReplica, kNoReplica, kNoReplica, kNoReplica,
+                     kNoReplica, kNoReplica, kNoReplica, kNoReplica};
     if (m < a.M) {
         const uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
         const uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
@@ -80,17 +81,19 @@ __global__ void build_rows_kernel(const KernelArgs a)
                 if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
                     ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
                     bad = true;
-                else if (r - lo < 4)
+                else if (r - lo < 8)
                     e[r - lo] = rep_to_last(ent);
             }
-            if (hi - lo > 4) e[3] = kMoreReplicas;
+            if (hi - lo > 8) e[7] = kMoreReplicas;
         }
         if (bad) {
             atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
-            for (int k = 0; k < 4; ++k) e[k] = kNoReplica;
+            for (int k = 0; k < 8; ++k) e[k] = kNoReplica;
         }
     }
-    reinterpret_cast<uint4 *>(a.rep_rows)[row_index(a, b, m)] = make_uint4(e[0], e[1], e[2], e[3]);
+    uint4 *rows = reinterpret_cast<uint4 *>(a.rep_rows);
+    rows[row_index(a, b, m)] = make_uint4(e[0], e[1], e[2], e[3]);
+    rows[row_plane(a) + row_index(a, b, m)] = make_uint4(e[4], e[5], e[6], e[7]);
 }
 
 // This lane's view of candidate b: offsets of its shared-memory state (clocks
@@ -109,6 +112,7 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
                         : static_cast<void *>(static_cast<uint8_t *>(a.decisions) + 4 * b);
     ln.dec_pitch = (uint32_t)a.dec_pitch;
     ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + row_index(a, b, 0);
+    ln.rows_b = ln.rows + row_plane(a);
     ln.rep_raw = a.model_rep + (size_t)b * a.P;
     ln.rep_off = a.model_off + (size_t)b * (a.M + 1);
     ln.lat_gl = a.latency + (size_t)b * a.latency_stride;
@@ -206,6 +210,8 @@ __global__ void validate_kernel(const KernelArgs a)
 {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (!can_chunk(a) || t >= (int64_t)a.B * (a.K - 1)) return;
+    // a round that repaired nothing left every state, and so every mask, as it was
+    if (a.round > 0 && a.work_count[a.round - 1] == 0) return;
     const int32_t j = (int32_t)(t / a.B) + 1;
     const int64_t u = t % a.B;
     const int64_t b = status_row(a, u);                // the scored candidate u belongs to
@@ -234,10 +240,15 @@ __global__ void validate_kernel(const KernelArgs a)
 // that does; else the true state is copied into the candidate's own array and
 // the chunk goes on the work list.  Behind a listed chunk the walk goes on
 // with the old data; the next round (or the chain kernel) sees the new one.
+// A candidate whose walk lists nothing is settled: every chunk continues the
+// one before it.  That is noted in row 0 of the masks (no boundary uses it)
+// and lets the chain kernel skip the candidate.
 __global__ void resolve_kernel(const KernelArgs a)
 {
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (!can_chunk(a) || b >= a.Bs) return;
+    if (a.round > 0 && a.work_count[a.round - 1] == 0) return;    // same masks, same answer
+    bool settled = true;
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
     const size_t B = (size_t)a.B;
@@ -253,6 +264,7 @@ __global__ void resolve_kernel(const KernelArgs a)
             if (s0 < 0 && a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair goes on
                 const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
                 a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+                settled = false;
             }
         } else if (mask >> 1) {
             const int32_t v = (int32_t)m_first + (__ffs((int)(mask >> 1)) - 1);
@@ -267,8 +279,10 @@ __global__ void resolve_kernel(const KernelArgs a)
             const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
             a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
             ++redone;
+            settled = false;
         }
     }
+    a.compat[b] = settled ? 1 : 0;
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
 }
 
@@ -323,6 +337,7 @@ sim_chain_kernel(const KernelArgs a)
     stage_latency_table(a, L);
     const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
     if (b >= a.Bs || !can_chunk(a) || a.N == 0) return;
+    if (a.compat[b]) return;             // settled by the last walk of resolve_kernel
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
 

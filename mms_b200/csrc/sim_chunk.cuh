@@ -44,8 +44,9 @@ struct KernelArgs {
     int32_t num_leaves;
     const int32_t *leaf_start;
     // scratch
-    uint32_t *rep_rows;           // [ceil(B/32)][M + 1][32][4]: replica rows built from
-                                  //   model_off/model_rep, see row_index()
+    uint32_t *rep_rows;           // [2][ceil(B/32)][M + 1][32][4]: replica rows built from
+                                  //   model_off/model_rep (first four replicas of each model,
+                                  //   then the next four), see row_index()
     double *leaf_sums;            // [num_leaves][B]
     double *seg_end;              // [NS][T][B]   clock vector after each segment
     double *chunk_start;          // [K][T][B]    clock vector each chunk started from
@@ -98,6 +99,12 @@ __device__ inline int32_t seg_leaf(const KernelArgs &a, int32_t q)
 __device__ inline size_t row_index(const KernelArgs &a, int64_t b, int m)
 {
     return ((size_t)(b / kLanes) * (a.M + 1) + m) * kLanes + (size_t)(b % kLanes);
+}
+
+// 16-byte units between a model's first and second replica row.
+__device__ inline size_t row_plane(const KernelArgs &a)
+{
+    return (size_t)((a.B + kLanes - 1) / kLanes) * (a.M + 1) * kLanes;
 }
 
 // The mirrors of scored candidate b are candidates [first, end): returns

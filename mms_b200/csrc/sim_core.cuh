@@ -5,8 +5,10 @@
 // sim_step below).  Mutable state (the stage clocks) lives in shared
 // memory as [entry][lane], so lane-private accesses fall on distinct banks;
 // shared memory is what limits the number of resident warps, so the
-// read-only replica lists stay in global memory (one 16-byte row per model,
-// fetched two requests ahead, served by L2).  Everything is addressed by
+// read-only replica lists stay in global memory (a 16-byte row per model with
+// its first four replicas, fetched two requests ahead, and a second one with
+// the next four, fetched one request ahead where the first is full; served by
+// L2).  Everything is addressed by
 // 32-bit element offsets into the block's one dynamic shared array, which
 // keeps the accesses plain LDS/STS with immediate offsets.  The dependent
 // chain per request is kept short: trace values are fetched three requests
@@ -87,9 +89,10 @@ struct Lane {
                               //   kLanes apart: the rows of 32 consecutive candidates for one
                               //   model are contiguous, so a warp fetches them coalesced): the
                               //   model's first four replicas, kNoReplica where it has fewer;
-                              //   a model with more than four has kMoreReplicas in word 3
-                              //   (the full list is then read from the caller's tables);
                               //   row M is empty (unknown models)
+    const uint4 *rows_b;      // the same for replicas five to eight; a model with more than
+                              //   eight has kMoreReplicas in word 3 of this row (the full list
+                              //   is then read from the caller's tables)
     const uint32_t *rep_raw;  // the caller's model_rep row of this candidate
     const uint16_t *rep_off;  // the caller's model_off row of this candidate
     const float *lat_gl;      // this candidate's table in global memory
@@ -106,10 +109,12 @@ constexpr uint32_t kMoreReplicas = 0xFE010000u;
 // Requests in flight.  Request i is ready to execute: its replica row is in
 // registers, and so is the row of request i+1.  While i executes, the row of
 // request i+2 and the trace values of request i+3 are fetched, so every
-// global load has a whole step or more to arrive.  Nothing fetched ahead
-// depends on simulator state.
+// global load has a whole step or more to arrive; so is the second row of
+// request i+1, by the lanes whose first row of it is full.  Nothing fetched
+// ahead depends on simulator state.
 struct Pipe {
     double ts; float slo; int32_t m; uint4 r;
+    uint4 rb;                 // replicas five to eight of request i (kNoReplica: none)
     double ts1; float slo1; int32_t m1; uint4 r1;
     double ts2; float slo2; int32_t m2;
     const double *arrivals; const int32_t *model_ids; const float *slos;   // request 0 of this lane's trace
@@ -128,6 +133,13 @@ __device__ __forceinline__ uint4 fetch_row(const Lane &ln, int32_t m)
     return __ldg(ln.rows + (m < 0 ? ln.M : m) * kLanes);
 }
 
+// The second row of model m, given its first: only a full first row has one.
+__device__ __forceinline__ uint4 fetch_row_b(const Lane &ln, int32_t m, const uint4 &first)
+{
+    if (first.w >= kMoreReplicas) return make_uint4(kNoReplica, kNoReplica, kNoReplica, kNoReplica);
+    return __ldg(ln.rows_b + (m < 0 ? ln.M : m) * kLanes);
+}
+
 // Fills the pipe so that request `i` is ready to execute.
 __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 {
@@ -143,6 +155,7 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
     p.m2 = clean_model(ln, __ldg(p.model_ids + o2));
     p.r = fetch_row(ln, p.m);
     p.r1 = fetch_row(ln, p.m1);
+    p.rb = fetch_row_b(ln, p.m, p.r);
 }
 
 // max of two times.  Times are never NaN (arrivals are checked to be finite,
@@ -176,6 +189,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
 
     // ---- state-independent fetches for the requests behind this one -------
     const uint4 r2 = fetch_row(ln, p.m2);
+    const uint4 rb1 = fetch_row_b(ln, p.m1, p.r1);
     const size_t i3 = (size_t)(i + 3 < p.last ? i + 3 : p.last) * p.pitch;
     const double ts3 = __ldg(p.arrivals + i3);
     const float slo3 = __ldg(p.slos + i3);
@@ -192,14 +206,25 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     if (e1 < kMoreReplicas && c1 < best) { best = c1; pick = e1; }
     if (e2 < kMoreReplicas && c2 < best) { best = c2; pick = e2; }
     if (e3 < kMoreReplicas && c3 < best) { best = c3; pick = e3; }
-    if (e3 == kMoreReplicas) {            // rare: the whole list, from the caller's tables
-        const uint32_t lo = ln.rep_off[m], hi = ln.rep_off[m + 1];
-        best = kInf;
-        pick = 0x00010000u;
-        for (uint32_t r = lo; r < hi; ++r) {
-            const uint32_t e = rep_to_last(__ldg(ln.rep_raw + r));
-            const double c = SM_F64(ln.clk + rep_last(e) * kLanes);
-            if (c < best) { best = c; pick = e; }
+    if (p.rb.x < kMoreReplicas) {         // five replicas or more: the second row
+        const uint32_t e4 = p.rb.x, e5 = p.rb.y, e6 = p.rb.z, e7 = p.rb.w;
+        const double c4 = SM_F64(ln.clk + rep_last(e4) * kLanes);
+        const double c5 = SM_F64(ln.clk + rep_last(e5) * kLanes);
+        const double c6 = SM_F64(ln.clk + rep_last(e6) * kLanes);
+        const double c7 = SM_F64(ln.clk + rep_last(e7) * kLanes);
+        if (c4 < best) { best = c4; pick = e4; }
+        if (e5 < kMoreReplicas && c5 < best) { best = c5; pick = e5; }
+        if (e6 < kMoreReplicas && c6 < best) { best = c6; pick = e6; }
+        if (e7 < kMoreReplicas && c7 < best) { best = c7; pick = e7; }
+        if (e7 == kMoreReplicas) {        // rare: the whole list, from the caller's tables
+            const uint32_t lo = ln.rep_off[m], hi = ln.rep_off[m + 1];
+            best = kInf;
+            pick = 0x00010000u;
+            for (uint32_t r = lo; r < hi; ++r) {
+                const uint32_t e = rep_to_last(__ldg(ln.rep_raw + r));
+                const double c = SM_F64(ln.clk + rep_last(e) * kLanes);
+                if (c < best) { best = c; pick = e; }
+            }
         }
     }
     const bool found = best < kInf;
@@ -297,7 +322,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     }
 
     // ---- advance the pipe ---------------------------------------------------
-    p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1; p.r = p.r1;
+    p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1; p.r = p.r1; p.rb = rb1;
     p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2; p.r1 = r2;
     p.ts2 = ts3; p.slo2 = slo3; p.m2 = clean_model(ln, m3raw);
     return fin - ts;

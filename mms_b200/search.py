@@ -11,6 +11,7 @@ simulator call each.
 """
 import math
 import time
+from bisect import bisect_left, bisect_right
 from typing import List, Sequence
 
 import numpy as np
@@ -100,23 +101,62 @@ def replica_placement_fast_greedy(init_sol, model_datas, cluster_env, workload, 
     return fast_greedy_lockstep([init_sol], model_datas, cluster_env, evaluator, verbose)[0]
 
 
+def _is_normalized(sol) -> bool:
+    """True when `sol` is what ModelPlacement.normalize() returns: tuples all
+    the way down, models ascending inside each group, groups ascending by
+    their model tuple."""
+    cfgs, models = sol.group_configs, sol.group_models
+    if type(cfgs) is not tuple or type(models) is not tuple:
+        return False
+    prev = None
+    for ms in models:
+        if type(ms) is not tuple or (prev is not None and ms < prev):
+            return False
+        if any(ms[i] > ms[i + 1] for i in range(len(ms) - 1)):
+            return False
+        prev = ms
+    return True
+
+
 def _expand(sol, weight, num_models, mem_budget, visited):
     """All placements one (group, model) addition away from `sol` that fit
-    the budget (strictly, base_policy.py:450) and were not seen before."""
+    the budget (strictly, base_policy.py:450) and were not seen before, each
+    normalized (base_policy.py:29-35).  A normalized `sol` — every placement a
+    search makes after its first step — is not re-sorted per addition: the new
+    model is inserted into its group's tuple, and the group into the sorted
+    rest, where the stable sort of normalize() would put it."""
     out = []
     group_mem = _group_mem(sol, weight)
     seen = set()
-    for g in range(len(sol.group_configs)):
-        c = sol.group_configs[g]
+    fast = _is_normalized(sol)
+    cfgs, models = sol.group_configs, sol.group_models
+    for g in range(len(cfgs)):
+        c = cfgs[g]
         # A later group with the same config and models yields, model by model,
         # placements whose group_models were just produced by the earlier one:
         # the `visited` test below would drop every one of them.
-        kind = (c, tuple(sol.group_models[g]))
+        kind = (c, tuple(models[g]))
         if kind in seen:
             continue
         seen.add(kind)
+        if fast:
+            mine = models[g]
+            rest_m, rest_c = models[:g] + models[g + 1:], cfgs[:g] + cfgs[g + 1:]
         for m in range(num_models):
-            if weight[c][m] + group_mem[g] < mem_budget and m not in sol.group_models[g]:
+            if weight[c][m] + group_mem[g] < mem_budget and m not in models[g]:
+                if fast:
+                    k = bisect_left(mine, m)
+                    grown = mine[:k] + (m,) + mine[k:]
+                    # groups with an equal tuple keep their order: those that stood before
+                    # group g stay before it
+                    lo = bisect_left(rest_m, grown)
+                    at = lo + max(0, min(bisect_right(rest_m, grown), g) - lo)
+                    new_models = rest_m[:at] + (grown,) + rest_m[at:]
+                    if new_models in visited:
+                        continue
+                    visited.add(new_models)
+                    out.append(ModelPlacement(rest_c[:at] + (c,) + rest_c[at:], new_models))
+                    continue
                 nxt = sol.add_model(g, m).normalize()
                 if nxt.group_models not in visited:
                     visited.add(nxt.group_models)

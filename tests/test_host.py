@@ -263,3 +263,38 @@ def test_c_encoder_equals_numpy_encoder():
     with pytest.raises(IndexError):
         engine.encode_placements([ModelPlacement([c1], [[len(profs)]])], engine.LatencyTable(profs),
                                  len(profs))
+
+
+def test_expansion_of_normalized_placements_equals_add_then_normalize():
+    """search._expand inserts into sorted tuples instead of re-sorting every
+    candidate; the placements equal add_model(g, m).normalize()
+    (base_policy.py:29-35,439-455), in the same order, ties between equal
+    groups included."""
+    import random
+    from mms_b200 import search
+    case = cases.greedy_search_case(duration=5.0)
+    M = len(case.model_datas)
+    budget = case.cluster_env.mem_budget
+    starts = search.ModelParallelismSearch(max_op=1).enumerate_group_configs_uneven(case.cluster_env)
+    rng = random.Random(5)
+    for sol in starts:
+        weight = search._weights(sol.group_configs, case.model_datas)
+        visited = set()
+        for step in range(10):
+            group_mem = search._group_mem(sol, weight)
+            want, seen = [], set(visited)
+            for g, c in enumerate(sol.group_configs):
+                for m in range(M):
+                    if weight[c][m] + group_mem[g] < budget and m not in sol.group_models[g]:
+                        nxt = sol.add_model(g, m).normalize()
+                        if nxt.group_models not in seen:
+                            seen.add(nxt.group_models)
+                            want.append(nxt)
+            got = search._expand(sol, weight, M, budget, visited)
+            assert step == 0 or search._is_normalized(sol)
+            assert [(tuple(p.group_configs), p.group_models) for p in got] == \
+                   [(tuple(p.group_configs), p.group_models) for p in want]
+            assert visited == seen
+            if not got:
+                break
+            sol = rng.choice(got)

@@ -422,6 +422,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     MMS_CUDA(cudaMemsetAsync(out->model_num_good, 0, sizeof(int32_t) * rows * ka.M, st));
     MMS_CUDA(cudaMemsetAsync(out->group_num_requests, 0, sizeof(int32_t) * rows * ka.G, st));
     if (gg) MMS_CUDA(cudaMemsetAsync(out->group_num_good, 0, sizeof(int32_t) * rows * ka.G, st));
+    MMS_CUDA(cudaMemsetAsync(out->good_total, 0, sizeof(int64_t) * rows, st));
     const size_t hist_bytes = sizeof(uint16_t) * (size_t)(ka.M + 2 * ka.G) * kLanes;
     if (hist_bytes > 227 * 1024) return MMS_ERR_UNSUPPORTED;
     auto count_k = ka.dec_wide ? count_kernel<uint16_t> : count_kernel<uint8_t>;
@@ -429,19 +430,19 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
                                   (int)hist_bytes));
     int32_t seg_per_block = ka.NS / 96 > 0 ? ka.NS / 96 : 1;   // 16-bit counts: at most 32 segments
     if (seg_per_block > 32) seg_per_block = 32;
+    // one more row of blocks (the first) forms the latency sums
     const dim3 count_grid((unsigned)((ka.Bs + kLanes - 1) / kLanes),
-                          (unsigned)((ka.NS + seg_per_block - 1) / seg_per_block));
+                          (unsigned)((ka.NS + seg_per_block - 1) / seg_per_block) + 1);
     count_k<<<count_grid, kLanes, hist_bytes, st>>>(ka, seg_per_block, gg, out->model_num_good,
-                                                    out->group_num_requests, out->group_num_good);
+                                                    out->group_num_requests, out->group_num_good,
+                                                    out->good_total, plan->leaf_merges,
+                                                    out->latency_sum);
     MMS_CUDA(cudaGetLastError());
     if (ka.M > 0) {
         const int64_t cells = (int64_t)ka.Bs * ka.M;
         model_requests_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka, out->model_num_requests);
         MMS_CUDA(cudaGetLastError());
     }
-    finalize_kernel<<<(ka.Bs + 31) / 32, 32, 0, st>>>(
-        ka, plan->leaf_merges, out->model_num_good, out->good_total, out->latency_sum);
-    MMS_CUDA(cudaGetLastError());
     return MMS_OK;
 }
 

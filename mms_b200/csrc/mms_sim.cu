@@ -56,7 +56,7 @@ namespace mms {
 constexpr int kMaxSumDepth = 48;        // pair-sum stack of the numpy order
 constexpr int kLatSmemBytes = 32 * 1024;
 constexpr int kMaxRepairRounds = 16;
-constexpr int kDefaultRepairRounds = 3;
+constexpr int kDefaultRepairRounds = 4;
 constexpr int kDefaultRepairSegments = -1;   // no cap: measured best on the benchmark shape
 
 // One thread per (candidate, model or the extra empty row): checks the model's
@@ -395,93 +395,13 @@ sim_chain_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
-// Tallies the recorded decisions of the runs that count (controller.py:587,
-// 611, 617-618).  A warp handles 32 consecutive scored candidates (one per
-// lane, so their decisions of one request are one 64-byte access) over a
-// range of at most 32 segments (fewer than 65 536 requests); each lane counts
-// in its own 16-bit shared-memory histogram [M + 2G][lane] and adds it to the
-// outputs, which must be zero on entry.
-template <typename Dec>
-__global__ void __launch_bounds__(kLanes)
-count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t *model_num_good,
-             int32_t *group_num_requests, int32_t *group_num_good)
+// Combines the leaf sums of candidate b in numpy's pairing order
+// (controller.py:402 consumes the mean).  Leaf sums are fetched eight at a
+// time so that the loads overlap.  With seg_src == nullptr every leaf sum is
+// the candidate's own.
+__device__ inline void sum_leaves(const KernelArgs &a, int64_t b, const uint8_t *leaf_merges,
+                                  double *latency_sum)
 {
-    constexpr uint32_t kAccepted = 1u << (8 * sizeof(Dec) - 1);
-    extern __shared__ uint16_t hist[];
-    const int lane = threadIdx.x;
-    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
-    const int n_counters = a.M + 2 * a.G;
-    for (int c = 0; c < n_counters; ++c) hist[c * kLanes + lane] = 0;
-    if (b >= a.Bs || a.num_leaves == 0) return;
-    const size_t tb = trace_base(a, b);
-    const int32_t q0 = blockIdx.y * seg_per_block;
-    const int32_t q1 = q0 + seg_per_block < a.NS ? q0 + seg_per_block : a.NS;
-    for (int32_t q = q0; q < q1; ++q) {
-        const int32_t src = a.seg_src[(size_t)q * a.B + b];
-        // four consecutive requests of a candidate are one aligned group of records
-        struct alignas(4 * sizeof(Dec)) Quad { Dec r[4]; };
-        const Quad *col = static_cast<const Quad *>(a.decisions) + (src >= 0 ? src : b);
-        const int32_t i_begin = a.leaf_start[seg_leaf(a, q)];
-        const int32_t i1 = seg_leaf(a, q + 1) < a.num_leaves ? a.leaf_start[seg_leaf(a, q + 1)]
-                                                             : (int32_t)a.N;
-        // two groups (eight requests) at a time, so that their loads are in flight together;
-        // segments start at multiples of 8
-        for (int32_t i0 = i_begin; i0 < i1; i0 += 8) {
-            Quad d[2];
-            int32_t m[8];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int32_t i = i0 + 4 * u < i1 ? i0 + 4 * u : i0;
-                d[u] = col[(size_t)(i >> 2) * a.dec_pitch];
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int32_t i = i0 + u < i1 ? i0 + u : i1 - 1;
-                m[u] = a.model_ids[(size_t)i * a.trace_pitch + tb];
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const uint32_t rec = d[u >> 2].r[u & 3];
-                if (i0 + u >= i1 || rec == 0) continue;
-                const uint32_t g = (rec & (kAccepted - 1)) - 1;
-                hist[(a.M + g) * kLanes + lane] += 1;
-                if (rec & kAccepted) {
-                    hist[m[u] * kLanes + lane] += 1;
-                    hist[(a.M + a.G + g) * kLanes + lane] += 1;
-                }
-            }
-        }
-    }
-    for (int m = 0; m < a.M; ++m)
-        if (hist[m * kLanes + lane]) atomicAdd(&model_num_good[(size_t)b * a.M + m], (int32_t)hist[m * kLanes + lane]);
-    for (int g = 0; g < a.G; ++g) {
-        const uint32_t r = hist[(a.M + g) * kLanes + lane], k = hist[(a.M + a.G + g) * kLanes + lane];
-        if (r) atomicAdd(&group_num_requests[(size_t)b * a.G + g], (int32_t)r);
-        if (group_good && k) atomicAdd(&group_num_good[(size_t)b * a.G + g], (int32_t)k);
-    }
-}
-
-// model_num_requests (controller.py:587) does not depend on the placement:
-// one thread per (candidate, model) copies the trace's histogram.
-__global__ void model_requests_kernel(const KernelArgs a, int32_t *model_num_requests)
-{
-    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (int64_t)a.Bs * a.M) return;
-    const int64_t b = t / a.M;
-    const int m = (int)(t % a.M);
-    model_num_requests[t] = a.model_hist[(a.trace_pitch > 1 ? (size_t)b * (a.M + 1) : 0) + m];
-}
-
-// Combines the leaf sums in numpy's pairing order and totals the good
-// requests (controller.py:401-402 consumes both).  One thread per scored
-// candidate; leaf sums are fetched eight at a time so that the loads overlap.
-// With seg_src == nullptr every leaf sum is the candidate's own.
-__global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
-                                const int32_t *model_num_good, int64_t *good_total,
-                                double *latency_sum)
-{
-    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= a.Bs) return;
     const int32_t num_leaves = a.num_leaves;
     double stack[kMaxSumDepth];
     int sp = 0;
@@ -514,11 +434,115 @@ __global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
             }
         }
     }
-    if (sp > kMaxSumDepth) a.status[b] |= MMS_STATUS_BAD_INDEX;
+    if (sp > kMaxSumDepth) atomicOr(&a.status[b], MMS_STATUS_BAD_INDEX);
     latency_sum[b] = (num_leaves > 0) ? stack[0] : 0.0;
+}
+
+// One thread per scored candidate: the latency sum, and the total of the good
+// requests (controller.py:401) from the per-model counts.
+__global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
+                                const int32_t *model_num_good, int64_t *good_total,
+                                double *latency_sum)
+{
+    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= a.Bs) return;
+    sum_leaves(a, b, leaf_merges, latency_sum);
     int64_t total = 0;
     for (int m = 0; m < a.M; ++m) total += model_num_good[(size_t)b * a.M + m];
     good_total[b] = total;
+}
+
+// Tallies the recorded decisions of the runs that count (controller.py:587,
+// 611, 617-618).  A warp handles 32 consecutive scored candidates (one per
+// lane, so their decisions of one request are one 64-byte access) over a
+// range of at most 32 segments (fewer than 65 536 requests); each lane counts
+// in its own 16-bit shared-memory histogram [M + 2G][lane] and adds it to the
+// outputs (good_total among them), which must be zero on entry.  One more row
+// of blocks (blockIdx.y == 0, so that it starts first) forms the candidates'
+// latency sums beside the tally: that walk is one dependent chain per
+// candidate and hides under it.
+template <typename Dec>
+__global__ void __launch_bounds__(kLanes)
+count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t *model_num_good,
+             int32_t *group_num_requests, int32_t *group_num_good, int64_t *good_total,
+             const uint8_t *leaf_merges, double *latency_sum)
+{
+    if (blockIdx.y == 0) {
+        const int64_t c = (int64_t)blockIdx.x * kLanes + threadIdx.x;
+        if (c < a.Bs) sum_leaves(a, c, leaf_merges, latency_sum);
+        return;
+    }
+    constexpr uint32_t kAccepted = 1u << (8 * sizeof(Dec) - 1);
+    extern __shared__ uint16_t hist[];
+    const int lane = threadIdx.x;
+    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
+    const int n_counters = a.M + 2 * a.G;
+    for (int c = 0; c < n_counters; ++c) hist[c * kLanes + lane] = 0;
+    if (b >= a.Bs || a.num_leaves == 0) return;
+    const size_t tb = trace_base(a, b);
+    const int32_t q0 = (blockIdx.y - 1) * seg_per_block;
+    const int32_t q1 = q0 + seg_per_block < a.NS ? q0 + seg_per_block : a.NS;
+    for (int32_t q = q0; q < q1; ++q) {
+        const int32_t src = a.seg_src[(size_t)q * a.B + b];
+        // four consecutive requests of a candidate are one aligned group of records
+        struct alignas(4 * sizeof(Dec)) Quad { Dec r[4]; };
+        const Quad *col = static_cast<const Quad *>(a.decisions) + (src >= 0 ? src : b);
+        const int32_t i_begin = a.leaf_start[seg_leaf(a, q)];
+        const int32_t i1 = seg_leaf(a, q + 1) < a.num_leaves ? a.leaf_start[seg_leaf(a, q + 1)]
+                                                             : (int32_t)a.N;
+        // four groups (sixteen requests) at a time, so that their loads are in flight
+        // together; segments start at multiples of 8
+        constexpr int kQuads = 4;
+        for (int32_t i0 = i_begin; i0 < i1; i0 += 4 * kQuads) {
+            Quad d[kQuads];
+            int32_t m[4 * kQuads];
+#pragma unroll
+            for (int u = 0; u < kQuads; ++u) {
+                const int32_t i = i0 + 4 * u < i1 ? i0 + 4 * u : i0;
+                d[u] = col[(size_t)(i >> 2) * a.dec_pitch];
+            }
+#pragma unroll
+            for (int u = 0; u < 4 * kQuads; ++u) {
+                const int32_t i = i0 + u < i1 ? i0 + u : i1 - 1;
+                m[u] = a.model_ids[(size_t)i * a.trace_pitch + tb];
+            }
+#pragma unroll
+            for (int u = 0; u < 4 * kQuads; ++u) {
+                const uint32_t rec = d[u >> 2].r[u & 3];
+                if (i0 + u >= i1 || rec == 0) continue;
+                const uint32_t g = (rec & (kAccepted - 1)) - 1;
+                hist[(a.M + g) * kLanes + lane] += 1;
+                if (rec & kAccepted) {
+                    hist[m[u] * kLanes + lane] += 1;
+                    hist[(a.M + a.G + g) * kLanes + lane] += 1;
+                }
+            }
+        }
+    }
+    uint32_t accepted = 0;
+    for (int m = 0; m < a.M; ++m)
+        if (hist[m * kLanes + lane]) {
+            atomicAdd(&model_num_good[(size_t)b * a.M + m], (int32_t)hist[m * kLanes + lane]);
+            accepted += hist[m * kLanes + lane];
+        }
+    if (accepted)
+        atomicAdd(reinterpret_cast<unsigned long long *>(good_total + b), (unsigned long long)accepted);
+    for (int g = 0; g < a.G; ++g) {
+        const uint32_t r = hist[(a.M + g) * kLanes + lane], k = hist[(a.M + a.G + g) * kLanes + lane];
+        if (r) atomicAdd(&group_num_requests[(size_t)b * a.G + g], (int32_t)r);
+        if (group_good && k) atomicAdd(&group_num_good[(size_t)b * a.G + g], (int32_t)k);
+    }
+}
+
+// model_num_requests (controller.py:587) does not depend on the placement:
+// one thread per (candidate, model) copies the trace's histogram.
+__global__ void model_requests_kernel(const KernelArgs a, int32_t *model_num_requests)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (int64_t)a.Bs * a.M) return;
+    const int64_t b = t / a.M;
+    const int m = (int)(t % a.M);
+    model_num_requests[t] = a.model_hist[(a.trace_pitch > 1 ? (size_t)b * (a.M + 1) : 0) + m];
 }
 
 // Per-model request counts, plus the number of positions where the arrival

@@ -30,7 +30,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one sim_stream_kernel launch (the dominant
 # kernel: the launch over the 3695 placements without mirror candidates) on the default
 # workload, from profiles/launch_list_candidates4096_3600s.md
-STREAM_KERNEL_DRAM_BYTES = 175129088 + 1164066304
+STREAM_KERNEL_DRAM_BYTES = 39151616 + 1057084928
 
 
 _REAL_STDOUT = None
@@ -258,8 +258,11 @@ def run_b200(args):
     part_index = [None if idx is None else torch.from_numpy(idx).to(dev)
                   for idx, _, _ in resident.device_outputs()]
 
+    own_done = torch.cuda.Event(enable_timing=True)     # this rank's kernels, before the exchange
+
     def step():
         resident.launch()
+        own_done.record()
         if world > 1:   # the search's argmax over all ranks' candidates
             best[0] = -1e300
             for pos, (_, good, lat_sum) in zip(part_index, resident.device_outputs()):
@@ -280,7 +283,7 @@ def run_b200(args):
         flush.zero_()
         step()
     barrier()
-    times = []
+    times, own_times = [], []
     nat.check(L.mms_profile_begin(), "mms_profile_begin")     # events around the stream kernel
     with ClockSampler(local) as clk:
         for _ in range(args.steps):
@@ -291,6 +294,7 @@ def run_b200(args):
             e1.record()
             e1.synchronize()
             times.append(e0.elapsed_time(e1))
+            own_times.append(e0.elapsed_time(own_done))
     barrier()
     k_launches, k_ms = ctypes.c_int32(0), ctypes.c_float(0.0)
     each = np.zeros(256, np.float32)
@@ -306,6 +310,12 @@ def run_b200(args):
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     total_ms = float(total_ms.item())
+    by_rank = torch.tensor([float(np.mean(own_times))], dtype=torch.float64, device=dev)
+    if world > 1:
+        all_ranks = torch.zeros(world, dtype=torch.float64, device=dev)
+        dist.all_gather_into_tensor(all_ranks, by_rank)
+        by_rank = all_ranks
+    by_rank = [round(float(x), 3) for x in by_rank.tolist()]
     final, _ = resident.results()
     assert not np.any(final.status), "kernel status words are not clean"
     redo = final.resimulated
@@ -368,6 +378,8 @@ def run_b200(args):
                              * len(resident.jobs)),
             "mirror_candidates_per_gpu": int(n_mirrors),
             "launches_per_step": len(resident.jobs),
+            # each rank's own kernels per step, before the exchange of the best score
+            "kernel_ms_per_step_by_rank": by_rank,
             "chunks_resimulated_per_candidate": float(np.mean(redo)),
             "chunks_resimulated_hist": np.bincount(redo).tolist(),
             "clocks": clk.summary(),

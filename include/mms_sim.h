@@ -51,6 +51,11 @@ extern "C" {
 #define MMS_FLAG_LEGACY_CLOCK 2u  /* one clock per group: controller.py:506-558  */
 #define MMS_FLAG_NO_GROUP_GOOD 4u /* group_num_good is not wanted (not written);
                                      pass the same flags to the workspace query  */
+#define MMS_FLAG_CROWDED 8u       /* a hint, results do not depend on it: another
+                                     launch is expected to fill most of the GPU
+                                     while this one repairs its chunks, so its
+                                     repairs stay packed 32 to a warp unless only
+                                     a handful are left                          */
 
 /* The request trace: what controller.py:323-339 caches per Workload
  * (model_ids, slos) plus Workload.arrivals (simulator/workload.py:272). */

@@ -30,6 +30,7 @@ STATUS_BAD_INDEX = 4
 FLAG_PER_REQUEST = 1
 FLAG_LEGACY_CLOCK = 2
 FLAG_NO_GROUP_GOOD = 4
+FLAG_CROWDED = 8
 
 STATIC_SCRATCH_BYTES = 32 << 20
 

@@ -40,7 +40,7 @@ static int32_t plan_leaves(int64_t n)
 
 struct Geometry {
     int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, rounds, repair_cap,
-        block_warps;
+        block_warps, narrow_limit;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_decisions, off_work_count, off_work_items,
         off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
@@ -154,6 +154,13 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
     g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    // one-chunk-per-warp repairs: as many as are resident at once (12 warps of
+    // this register use per SM, or what shared memory admits)
+    int64_t narrow_per_sm = 233472 / (int64_t)(g->smem_repair + 1024);
+    if (narrow_per_sm > 12) narrow_per_sm = 12;
+    g->narrow_limit = (int32_t)(narrow_per_sm * sm_count);
+    // beside a launch that holds most SMs for itself, what is left over takes few blocks
+    if ((flags & MMS_FLAG_CROWDED) && g->narrow_limit > 48) g->narrow_limit = 48;
 
     size_t off = 0;
     g->off_rows = off;        off += align256(2 * sizeof(uint32_t) * kRowWords * (size_t)((B + kLanes - 1) / kLanes * kLanes) *
@@ -202,11 +209,17 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
     MMS_CUDA(cudaGetLastError());
     if (timed) MMS_CUDA(cudaEventRecord(g_prof_ev[2 * g_prof_count++ + 1], st));
     if (ka.K > 1) {
-        auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy>;
-        auto chain_k = sim_chain_kernel<kFull, kGroupGood, kLegacy>;
+        auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy, false>;
+        auto chain_k = sim_chain_kernel<kFull, kGroupGood, kLegacy, false>;
+        auto repair_narrow_k = sim_repair_kernel<kFull, kGroupGood, kLegacy, true>;
+        auto chain_narrow_k = sim_chain_kernel<kFull, kGroupGood, kLegacy, true>;
         MMS_CUDA(cudaFuncSetAttribute(repair_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)g.smem_repair));
         MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)g.smem_repair));
+        MMS_CUDA(cudaFuncSetAttribute(repair_narrow_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)g.smem_repair));
+        MMS_CUDA(cudaFuncSetAttribute(chain_narrow_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       (int)g.smem_repair));
         const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
         for (int r = 0; r < g.rounds; ++r) {
@@ -218,8 +231,16 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
             // sized for the worst case; blocks past the work list return at once
             repair_k<<<(unsigned)((bounds + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
+            // the same list one chunk to a warp, when it is short (see sim_repair_kernel)
+            const int64_t narrow = bounds < ka.narrow_limit ? bounds : ka.narrow_limit;
+            if (narrow > 0) {
+                repair_narrow_k<<<(unsigned)narrow, kLanes, g.smem_repair, st>>>(ka);
+                MMS_CUDA(cudaGetLastError());
+            }
         }
         chain_k<<<(unsigned)((ka.Bs + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
+        MMS_CUDA(cudaGetLastError());
+        chain_narrow_k<<<(unsigned)ka.Bs, kLanes, g.smem_repair, st>>>(ka);
         MMS_CUDA(cudaGetLastError());
     }
     return MMS_OK;
@@ -332,7 +353,8 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
 {
     using namespace mms;
     if (!trace || !cands || !plan || !ws || !out) return MMS_ERR_ARG;
-    if (flags & ~(MMS_FLAG_PER_REQUEST | MMS_FLAG_LEGACY_CLOCK | MMS_FLAG_NO_GROUP_GOOD))
+    if (flags & ~(MMS_FLAG_PER_REQUEST | MMS_FLAG_LEGACY_CLOCK | MMS_FLAG_NO_GROUP_GOOD |
+                  MMS_FLAG_CROWDED))
         return MMS_ERR_ARG;
     const int64_t N = trace->num_requests;
     const bool gg = !(flags & MMS_FLAG_NO_GROUP_GOOD);
@@ -391,6 +413,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.compat = (uint16_t *)(scratch + g.off_compat);
     ka.seg_first_leaf = (int32_t *)(scratch + g.off_seg_leaf);
     ka.repair_cap = g.repair_cap;
+    ka.narrow_limit = g.narrow_limit;
     ka.seg_end = (double *)(scratch + g.off_seg_end);
     ka.chunk_start = (double *)(scratch + g.off_chunk_start);
     ka.status = out->status;

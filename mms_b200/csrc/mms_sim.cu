@@ -212,6 +212,7 @@ __global__ void validate_kernel(const KernelArgs a)
     if (!can_chunk(a) || t >= (int64_t)a.B * (a.K - 1)) return;
     // a round that repaired nothing left every state, and so every mask, as it was
     if (a.round > 0 && a.work_count[a.round - 1] == 0) return;
+    if (t == 0) a.work_count[kMaxRepairRounds] = 0;   // resolve_kernel counts the unsettled there
     const int32_t j = (int32_t)(t / a.B) + 1;
     const int64_t u = t % a.B;
     const int64_t b = status_row(a, u);                // the scored candidate u belongs to
@@ -283,20 +284,29 @@ __global__ void resolve_kernel(const KernelArgs a)
         }
     }
     a.compat[b] = settled ? 1 : 0;
+    if (!settled) atomicAdd(&a.work_count[kMaxRepairRounds], 1u);
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
 }
 
-// One thread per chunk on the work list of this round.
-template <bool kFull, bool kGroupGood, bool kLegacy>
+// One thread per chunk on the work list of this round.  A long list is
+// worked 32 chunks to a warp (kNarrow false).  A short one — the late rounds,
+// where what is left is a few long dependent repairs and the GPU is otherwise
+// idle — one chunk to a warp, with the step that branches (kNarrow): the
+// duration of a round is that of its longest repair, and a lone lane gets
+// through a request in about half the instructions.  Both kernels are
+// launched every round; the one whose turn it is not returns at once.
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow>
 __global__ void __launch_bounds__(kLanes, 1)
 sim_repair_kernel(const KernelArgs a)
 {
-    const int lane = threadIdx.x;
+    const int lane = kNarrow ? 0 : threadIdx.x;
     const uint32_t count = a.work_count[a.round];
-    if ((uint64_t)blockIdx.x * kLanes >= count) return;
+    if ((count <= (uint32_t)a.narrow_limit) != kNarrow) return;
+    if ((uint64_t)blockIdx.x * (kNarrow ? 1 : kLanes) >= count) return;
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
     stage_latency_table(a, L);
-    const uint32_t w = blockIdx.x * kLanes + lane;
+    if (kNarrow && threadIdx.x != 0) return;
+    const uint32_t w = kNarrow ? blockIdx.x : blockIdx.x * kLanes + lane;
     if (w >= count) return;
     const uint32_t item = a.work_items[w] & 0x7FFFFFFFu;
     const bool resume = (a.work_items[w] >> 31) != 0;
@@ -317,7 +327,7 @@ sim_repair_kernel(const KernelArgs a)
     const int32_t first = a.leaf_start[seg_leaf(a, q_begin)];
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
-    a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy>(
+    a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(
         a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
         a.repair_cap, ~0ull, m_first, m_end);
     if (ln.status) atomicOr(&a.status[b], ln.status);
@@ -327,16 +337,22 @@ sim_repair_kernel(const KernelArgs a)
 // chunk keeps the run selected for it when that one continues the chunk
 // before it, else takes the first mirror's run that does, else is repaired in
 // place in the candidate's own array.  After it, every segment that counts
-// was simulated from a state equivalent to the true one.
-template <bool kFull, bool kGroupGood, bool kLegacy>
+// was simulated from a state equivalent to the true one.  Like the repairs, it
+// comes in two forms, 32 candidates to a warp or (kNarrow, when few are left
+// unsettled) one.
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow>
 __global__ void __launch_bounds__(kLanes, 1)
 sim_chain_kernel(const KernelArgs a)
 {
-    const int lane = threadIdx.x;
+    const int lane = kNarrow ? 0 : threadIdx.x;
+    if (!can_chunk(a) || a.N == 0) return;
+    if ((a.work_count[kMaxRepairRounds] <= (uint32_t)a.narrow_limit) != kNarrow) return;
+    if (kNarrow && a.compat[blockIdx.x]) return;          // whole block: nothing to stage for
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
     stage_latency_table(a, L);
-    const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
-    if (b >= a.Bs || !can_chunk(a) || a.N == 0) return;
+    if (kNarrow && threadIdx.x != 0) return;
+    const int64_t b = kNarrow ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kLanes + lane;
+    if (b >= a.Bs) return;
     if (a.compat[b]) return;             // settled by the last walk of resolve_kernel
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
@@ -386,9 +402,9 @@ sim_chain_kernel(const KernelArgs a)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
         }
         ++redone;
-        run_chunk<kFull, kGroupGood, kLegacy>(a, ln, p, b, j, begin, true,
-                                              true, old_state, stale_buf, q_begin, 0, ~0ull,
-                                              m_first, m_end);
+        run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(a, ln, p, b, j, begin, true, true,
+                                                       old_state, stale_buf, q_begin, 0, ~0ull,
+                                                       m_first, m_end);
         a.repair_from[(size_t)j * a.B + b] = -1;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);

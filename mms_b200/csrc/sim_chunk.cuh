@@ -65,6 +65,8 @@ struct KernelArgs {
                                   //         start continues u's end (bit 0: the candidate's own
                                   //         array, bit 1 + i: its i-th mirror)
     int32_t *seg_first_leaf;      // [NS + 1]: first leaf of each segment
+    int32_t narrow_limit;         // repairs of at most this many chunks (or candidates) run one
+                                  //   per warp, see sim_repair_kernel
     int32_t repair_cap;           // segments a repair may run per round
     int32_t round;
     // outputs
@@ -216,7 +218,7 @@ __device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X
 //       segments (0 = no cap).
 // Returns -1 when the chunk is finished (ran to its end, or settled), else
 // the segment at which the capped repair has to be continued.
-template <bool kFull, bool kGroupGood, bool kLegacy>
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false>
 __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                                     int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
@@ -248,8 +250,8 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
         double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
         double r = 0.0;
         for (; i < span_end; ++i) {
-            const double d = sim_step<kFull, kGroupGood, kLegacy>(ln, p, i, record, fin_out,
-                                                                  good_out);
+            const double d = sim_step<kFull, kGroupGood, kLegacy, kNarrow>(ln, p, i, record,
+                                                                           fin_out, good_out);
             if (i < body_end) {
                 SM_F64(ring + (uint32_t)(i & 7) * kLanes) = d;
                 if ((i & 7) == 7) {

@@ -178,7 +178,10 @@ __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
 // harmless addresses and its stores are predicated off.  The step is large;
 // callers keep a single call site per kernel so that the hot loop stays
 // inside the instruction cache.
-template <bool kFull, bool kGroupGood, bool kLegacy>
+//   kNarrow  for a warp in which ONE lane works (the serial repairs): real
+//            branches, so that only the replicas and the stages that exist are
+//            touched — about half the instructions, and no other lane to hold up.
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)
 {
@@ -196,16 +199,37 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     const int32_t m3raw = __ldg(p.model_ids + i3);
 
     // ---- :589-598 replica whose last-stage clock is strictly smallest ------
-    const double c0 = SM_F64(ln.clk + rep_last(e0) * kLanes);
-    const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
-    const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
-    const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
     double best = kInf;
     uint32_t pick = 0x00010000u;          // group 0, slot 0, one stage, column 0
-    if (e0 < kMoreReplicas && c0 < best) { best = c0; pick = e0; }
-    if (e1 < kMoreReplicas && c1 < best) { best = c1; pick = e1; }
-    if (e2 < kMoreReplicas && c2 < best) { best = c2; pick = e2; }
-    if (e3 < kMoreReplicas && c3 < best) { best = c3; pick = e3; }
+    if constexpr (kNarrow) {
+        // a row is filled from word 0 on
+        if (e0 < kMoreReplicas) {
+            best = SM_F64(ln.clk + rep_last(e0) * kLanes);
+            pick = e0;
+            if (!(best < kInf)) { best = kInf; pick = 0x00010000u; }
+            if (e1 < kMoreReplicas) {
+                const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
+                if (c1 < best) { best = c1; pick = e1; }
+                if (e2 < kMoreReplicas) {
+                    const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
+                    if (c2 < best) { best = c2; pick = e2; }
+                    if (e3 < kMoreReplicas) {
+                        const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
+                        if (c3 < best) { best = c3; pick = e3; }
+                    }
+                }
+            }
+        }
+    } else {
+        const double c0 = SM_F64(ln.clk + rep_last(e0) * kLanes);
+        const double c1 = SM_F64(ln.clk + rep_last(e1) * kLanes);
+        const double c2 = SM_F64(ln.clk + rep_last(e2) * kLanes);
+        const double c3 = SM_F64(ln.clk + rep_last(e3) * kLanes);
+        if (e0 < kMoreReplicas && c0 < best) { best = c0; pick = e0; }
+        if (e1 < kMoreReplicas && c1 < best) { best = c1; pick = e1; }
+        if (e2 < kMoreReplicas && c2 < best) { best = c2; pick = e2; }
+        if (e3 < kMoreReplicas && c3 < best) { best = c3; pick = e3; }
+    }
     if (p.rb.x < kMoreReplicas) {         // five replicas or more: the second row
         const uint32_t e4 = p.rb.x, e5 = p.rb.y, e6 = p.rb.z, e7 = p.rb.w;
         const double c4 = SM_F64(ln.clk + rep_last(e4) * kLanes);
@@ -236,59 +260,95 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     double f;
     double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
     (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
-    // all stage clocks and latencies are fetched at once; the max/add chain
-    // then runs in registers
-    const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
-                 k3 = SM_F64(ck + 3 * kLanes), k4 = SM_F64(ck + 4 * kLanes),
-                 k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
-                 k7 = SM_F64(ck + 7 * kLanes);
-    double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
-    if (ln.lat_on_chip) {
-        // rows are padded so that 8 entries are always readable
-        const uint32_t lr = ln.lat_sm + row;
-        l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
-        l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
-        l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
-        l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
-    } else {
-        const float *lat = ln.lat_gl + row;
-        const int sm = ln.S - 1;   // clamp reads to the table row
-        l0 = (double)__ldg(lat); l1 = (double)__ldg(lat + (1 < sm ? 1 : sm));
-        if (ns > 2) {
-            l2 = (double)__ldg(lat + (2 < sm ? 2 : sm));
-            l3 = (double)__ldg(lat + (3 < sm ? 3 : sm));
-            l4 = (double)__ldg(lat + (4 < sm ? 4 : sm));
-            l5 = (double)__ldg(lat + (5 < sm ? 5 : sm));
-            l6 = (double)__ldg(lat + (6 < sm ? 6 : sm));
-            l7 = (double)__ldg(lat + (7 < sm ? 7 : sm));
-        }
-    }
-    if (kLegacy) {
-        // :543-544 one clock per group; latency row = {sum, max}
-        const double start = tmax(k0, ts);
-        f = start + l0 + kOverhead;
-        t0 = start + l1;
-    } else {
-        // :605-610, written without branches: stages past the group's last one
-        // are computed and thrown away
-        t0 = tmax(ts, k0) + l0;
-        t1 = tmax(t0, k1) + l1;
-        double t = ns > 1 ? t1 : t0;
-        t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
-        t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
-        t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
-        t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
-        t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
-        t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
-        if (ns > 8) {
-            for (uint32_t k = 8; k < ns; ++k) {
-                const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
-                                                 : (double)__ldg(ln.lat_gl + row + k);
-                t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
-                SM_F64(ln.tmp + (k - 8) * kLanes) = t;
+    if constexpr (kNarrow && !kLegacy) {
+        // :605-610 stage by stage, as far as the group has stages
+        auto lat = [&](uint32_t k) {
+            return ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
+                                  : (double)__ldg(ln.lat_gl + row + k);
+        };
+        t0 = tmax(ts, SM_F64(ck)) + lat(0);
+        double t = t0;
+        if (ns > 1) {
+            t1 = tmax(t0, SM_F64(ck + kLanes)) + lat(1); t = t1;
+            if (ns > 2) {
+                t2 = tmax(t1, SM_F64(ck + 2 * kLanes)) + lat(2); t = t2;
+                if (ns > 3) {
+                    t3 = tmax(t2, SM_F64(ck + 3 * kLanes)) + lat(3); t = t3;
+                    if (ns > 4) {
+                        t4 = tmax(t3, SM_F64(ck + 4 * kLanes)) + lat(4); t = t4;
+                        if (ns > 5) {
+                            t5 = tmax(t4, SM_F64(ck + 5 * kLanes)) + lat(5); t = t5;
+                            if (ns > 6) {
+                                t6 = tmax(t5, SM_F64(ck + 6 * kLanes)) + lat(6); t = t6;
+                                if (ns > 7) {
+                                    t7 = tmax(t6, SM_F64(ck + 7 * kLanes)) + lat(7); t = t7;
+                                    for (uint32_t k = 8; k < ns; ++k) {
+                                        t = tmax(t, SM_F64(ck + k * kLanes)) + lat(k);
+                                        SM_F64(ln.tmp + (k - 8) * kLanes) = t;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
             }
         }
         f = t + kOverhead;                               // :610
+    } else {
+        // all stage clocks and latencies are fetched at once; the max/add chain
+        // then runs in registers
+        const double k0 = SM_F64(ck), k1 = SM_F64(ck + kLanes), k2 = SM_F64(ck + 2 * kLanes),
+                     k3 = SM_F64(ck + 3 * kLanes), k4 = SM_F64(ck + 4 * kLanes),
+                     k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
+                     k7 = SM_F64(ck + 7 * kLanes);
+        double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
+        if (ln.lat_on_chip) {
+            // rows are padded so that 8 entries are always readable
+            const uint32_t lr = ln.lat_sm + row;
+            l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
+            l2 = (double)SM_F32(lr + 2); l3 = (double)SM_F32(lr + 3);
+            l4 = (double)SM_F32(lr + 4); l5 = (double)SM_F32(lr + 5);
+            l6 = (double)SM_F32(lr + 6); l7 = (double)SM_F32(lr + 7);
+        } else {
+            const float *lat = ln.lat_gl + row;
+            const int sm = ln.S - 1;   // clamp reads to the table row
+            l0 = (double)__ldg(lat); l1 = (double)__ldg(lat + (1 < sm ? 1 : sm));
+            if (ns > 2) {
+                l2 = (double)__ldg(lat + (2 < sm ? 2 : sm));
+                l3 = (double)__ldg(lat + (3 < sm ? 3 : sm));
+                l4 = (double)__ldg(lat + (4 < sm ? 4 : sm));
+                l5 = (double)__ldg(lat + (5 < sm ? 5 : sm));
+                l6 = (double)__ldg(lat + (6 < sm ? 6 : sm));
+                l7 = (double)__ldg(lat + (7 < sm ? 7 : sm));
+            }
+        }
+        if (kLegacy) {
+            // :543-544 one clock per group; latency row = {sum, max}
+            const double start = tmax(k0, ts);
+            f = start + l0 + kOverhead;
+            t0 = start + l1;
+        } else {
+            // :605-610, written without branches: stages past the group's last one
+            // are computed and thrown away
+            t0 = tmax(ts, k0) + l0;
+            t1 = tmax(t0, k1) + l1;
+            double t = ns > 1 ? t1 : t0;
+            t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
+            t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
+            t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
+            t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
+            t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
+            t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
+            if (ns > 8) {
+                for (uint32_t k = 8; k < ns; ++k) {
+                    const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
+                                                     : (double)__ldg(ln.lat_gl + row + k);
+                    t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
+                    SM_F64(ln.tmp + (k - 8) * kLanes) = t;
+                }
+            }
+            f = t + kOverhead;                               // :610
+        }
     }
     const bool accept = found && (f - ts <= (double)slo_f);   // :613-619
     const double fin = accept ? f : ts;

@@ -844,7 +844,9 @@ class ResidentBatch:
     still in theirs.  Results are the same as from one call."""
 
     def __init__(self, trace, enc: EncodedBatch, table: LatencyTable, group_good=False,
-                 pinned=False, options=None, mirrors=True, split=True):
+                 pinned=False, options=None, mirrors=True, split=True, crowded=False):
+        """crowded: other launches will be filling the GPU while this batch
+        repairs its chunks (a pipelined part that is not the last)."""
         self.trace, self.enc = trace, enc
         dev = trace.device
         ext_owner = [b for b, cl in (enc.twins or []) if mirror_swaps(cl)] if mirrors else []
@@ -858,15 +860,17 @@ class ResidentBatch:
         self.jobs = []
         self.h2d_bytes = 0
         lat = table.device(dev)
-        for _, e in parts:
+        for k, (_, e) in enumerate(parts):
+            # the first of two calls repairs while the second one fills the GPU
+            flags = nat.FLAG_CROWDED if (crowded or k + 1 < len(parts)) else 0
             ext = e.with_mirrors() if mirrors else None
             if ext is not None:
                 off, rep, info, partner, swap = ext
                 job = _prepare(trace, len(partner), e.M, e.G, e.P, e.T, e.S, e.C, off, rep, info,
-                               lat, 0, 0, group_good, pinned, options, e.B, partner, swap)
+                               lat, 0, flags, group_good, pinned, options, e.B, partner, swap)
             else:
                 job = _prepare(trace, e.B, e.M, e.G, e.P, e.T, e.S, e.C, e.model_off, e.model_rep,
-                               e.group_info, lat, 0, 0, group_good, pinned, options)
+                               e.group_info, lat, 0, flags, group_good, pinned, options)
             self.jobs.append(job)
             self.h2d_bytes += job.h2d
 
@@ -919,9 +923,11 @@ class ResidentBatch:
 
 
 def submit_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable, group_good=False,
-                 pinned=False, options=None, mirrors=True, split=True) -> ResidentBatch:
+                 pinned=False, options=None, mirrors=True, split=True,
+                 crowded=False) -> ResidentBatch:
     """run_batch without waiting: returns a handle for collect_batch."""
-    return ResidentBatch(trace, enc, table, group_good, pinned, options, mirrors, split).launch()
+    return ResidentBatch(trace, enc, table, group_good, pinned, options, mirrors, split,
+                         crowded).launch()
 
 
 collect_batch = _collect

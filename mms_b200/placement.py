@@ -180,7 +180,8 @@ class PlacementEvaluator:
             self._streams[k].wait_stream(main)           # the trace was uploaded there
             with torch.cuda.stream(self._streams[k]):
                 jobs.append(engine.submit_batch(self.trace, enc, self.table, pinned=pinned,
-                                                options=self.options, split=split[k]))
+                                                options=self.options, split=split[k],
+                                                crowded=k + 1 < parts))
             encs.append(enc)
         done = [engine.collect_batch(job) for job in jobs]
         for k in range(parts):

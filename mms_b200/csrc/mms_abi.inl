@@ -250,7 +250,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 
 extern "C" {
 
-int mms_abi_version(void) { return 6; }
+int mms_abi_version(void) { return 7; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 
@@ -446,7 +446,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     MMS_CUDA(cudaMemsetAsync(out->group_num_requests, 0, sizeof(int32_t) * rows * ka.G, st));
     if (gg) MMS_CUDA(cudaMemsetAsync(out->group_num_good, 0, sizeof(int32_t) * rows * ka.G, st));
     MMS_CUDA(cudaMemsetAsync(out->good_total, 0, sizeof(int64_t) * rows, st));
-    const size_t hist_bytes = sizeof(uint16_t) * (size_t)(ka.M + 2 * ka.G) * kLanes;
+    const size_t hist_bytes = sizeof(uint32_t) * (size_t)(ka.G + (ka.M + 1) / 2) * kLanes;
     if (hist_bytes > 227 * 1024) return MMS_ERR_UNSUPPORTED;
     auto count_k = ka.dec_wide ? count_kernel<uint16_t> : count_kernel<uint8_t>;
     MMS_CUDA(cudaFuncSetAttribute(count_k, cudaFuncAttributeMaxDynamicSharedMemorySize,

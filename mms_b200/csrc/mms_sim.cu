@@ -472,7 +472,7 @@ __global__ void finalize_kernel(const KernelArgs a, const uint8_t *leaf_merges,
 // 611, 617-618).  A warp handles 32 consecutive scored candidates (one per
 // lane, so their decisions of one request are one 64-byte access) over a
 // range of at most 32 segments (fewer than 65 536 requests); each lane counts
-// in its own 16-bit shared-memory histogram [M + 2G][lane] and adds it to the
+// in its own 16-bit shared-memory histograms and adds them to the
 // outputs (good_total among them), which must be zero on entry.  One more row
 // of blocks (blockIdx.y == 0, so that it starts first) forms the candidates'
 // latency sums beside the tally: that walk is one dependent chain per
@@ -488,12 +488,20 @@ count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t
         if (c < a.Bs) sum_leaves(a, c, leaf_merges, latency_sum);
         return;
     }
-    constexpr uint32_t kAccepted = 1u << (8 * sizeof(Dec) - 1);
-    extern __shared__ uint16_t hist[];
+    constexpr int kAcceptedBit = 8 * sizeof(Dec) - 1;
+    constexpr uint32_t kAccepted = 1u << kAcceptedBit;
+    // per lane: a 32-bit word per group (requests in the low half, good ones in
+    // the high half: one update per record) at [group][lane], and 16-bit counts
+    // of good requests per model at [model / 2][lane][model % 2] — every lane
+    // stays in a bank of its own whatever it counts
+    extern __shared__ uint32_t hist[];
+    uint32_t *grp = hist;
+    uint16_t *mod = reinterpret_cast<uint16_t *>(hist + (size_t)a.G * kLanes);
     const int lane = threadIdx.x;
     const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
-    const int n_counters = a.M + 2 * a.G;
-    for (int c = 0; c < n_counters; ++c) hist[c * kLanes + lane] = 0;
+    for (int g = 0; g < a.G; ++g) grp[g * kLanes + lane] = 0;
+    for (int h = 0; h < (a.M + 1) / 2; ++h)
+        reinterpret_cast<uint32_t *>(mod)[h * kLanes + lane] = 0;
     if (b >= a.Bs || a.num_leaves == 0) return;
     const size_t tb = trace_base(a, b);
     const int32_t q0 = (blockIdx.y - 1) * seg_per_block;
@@ -522,29 +530,31 @@ count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t
                 const int32_t i = i0 + u < i1 ? i0 + u : i1 - 1;
                 m[u] = a.model_ids[(size_t)i * a.trace_pitch + tb];
             }
+            const int32_t valid = i1 - i0;
 #pragma unroll
             for (int u = 0; u < 4 * kQuads; ++u) {
                 const uint32_t rec = d[u >> 2].r[u & 3];
-                if (i0 + u >= i1 || rec == 0) continue;
+                if (u >= valid || rec == 0) continue;
                 const uint32_t g = (rec & (kAccepted - 1)) - 1;
-                hist[(a.M + g) * kLanes + lane] += 1;
-                if (rec & kAccepted) {
-                    hist[m[u] * kLanes + lane] += 1;
-                    hist[(a.M + a.G + g) * kLanes + lane] += 1;
-                }
+                const uint32_t accepted = rec >> kAcceptedBit;
+                grp[g * kLanes + lane] += 1u + (accepted << 16);
+                if (accepted)
+                    mod[(((uint32_t)m[u] >> 1) * kLanes + lane) * 2 + (m[u] & 1)] += 1;
             }
         }
     }
     uint32_t accepted = 0;
-    for (int m = 0; m < a.M; ++m)
-        if (hist[m * kLanes + lane]) {
-            atomicAdd(&model_num_good[(size_t)b * a.M + m], (int32_t)hist[m * kLanes + lane]);
-            accepted += hist[m * kLanes + lane];
+    for (int m = 0; m < a.M; ++m) {
+        const uint32_t k = mod[((m >> 1) * kLanes + lane) * 2 + (m & 1)];
+        if (k) {
+            atomicAdd(&model_num_good[(size_t)b * a.M + m], (int32_t)k);
+            accepted += k;
         }
+    }
     if (accepted)
         atomicAdd(reinterpret_cast<unsigned long long *>(good_total + b), (unsigned long long)accepted);
     for (int g = 0; g < a.G; ++g) {
-        const uint32_t r = hist[(a.M + g) * kLanes + lane], k = hist[(a.M + a.G + g) * kLanes + lane];
+        const uint32_t r = grp[g * kLanes + lane] & 0xFFFFu, k = grp[g * kLanes + lane] >> 16;
         if (r) atomicAdd(&group_num_requests[(size_t)b * a.G + g], (int32_t)r);
         if (group_good && k) atomicAdd(&group_num_good[(size_t)b * a.G + g], (int32_t)k);
     }

@@ -135,8 +135,9 @@ class PlacementEvaluator:
         self.pipeline_min_part = 768    # placements per part, at least
         self.pipeline_shares = (3, 5)   # relative sizes of the parts (None: equal)
         # placements with mirror candidates as a launch of their own inside a
-        # part: one flag, or one per part
-        self.pipeline_split = True
+        # part: one flag, or one per part.  Only the last part needs it: the
+        # serial repairs of an earlier part run beside the parts behind it anyway.
+        self.pipeline_split = (False, True)
         self._streams = []
         self.last_resimulated = None
         self.last_h2d_bytes = 0
@@ -173,6 +174,8 @@ class PlacementEvaluator:
         split = self.pipeline_split
         if isinstance(split, (bool, int)):
             split = (bool(split),) * parts
+        elif len(split) != parts:
+            split = (False,) * (parts - 1) + (True,)
         encs, jobs = [], []
         for k in range(parts):
             enc = engine.encode_placements(sols[bounds[k]:bounds[k + 1]], self.table,

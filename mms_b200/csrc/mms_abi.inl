@@ -40,7 +40,7 @@ static int32_t plan_leaves(int64_t n)
 
 struct Geometry {
     int32_t K, NS, seg_len, seg_per_chunk, warmup, lat_smem_elems, rounds, repair_cap,
-        block_warps, narrow_limit;
+        block_warps, narrow_limit, lat_f64;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_decisions, off_work_count, off_work_items,
         off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
@@ -86,12 +86,29 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     // block; 232448 at most in one block) wins, the smaller one on a tie.
     int64_t per_sm = 1;
     int block_warps = 1;
-    for (int w = 1; w <= kMaxBlockWarps; ++w) {
-        const size_t bytes = L0.warp0 + (size_t)w * L0.warp_bytes;
-        if (bytes > 232448) break;
-        int64_t warps = (int64_t)(233472 / (bytes + 1024)) * w;
-        if (warps > kMaxWarpsPerSm) warps = kMaxWarpsPerSm;
-        if (warps >= per_sm) { per_sm = warps; block_warps = w; }
+    auto fit = [&](const SmemLayout &L, int64_t &best_per_sm, int &best_w) {
+        best_per_sm = 1;
+        best_w = 1;
+        for (int w = 1; w <= kMaxBlockWarps; ++w) {
+            const size_t bytes = L.warp0 + (size_t)w * L.warp_bytes;
+            if (bytes > 232448) break;
+            int64_t warps = (int64_t)(233472 / (bytes + 1024)) * w;
+            if (warps > kMaxWarpsPerSm) warps = kMaxWarpsPerSm;
+            if (warps >= best_per_sm) { best_per_sm = warps; best_w = w; }
+        }
+    };
+    fit(L0, per_sm, block_warps);
+    // The table goes on chip as doubles (no conversion per use) when that costs
+    // no resident warp.
+    g->lat_f64 = 0;
+    if (lat_on_chip0) {
+        const SmemLayout L64 = smem_layout(c->num_models, c->max_groups, c->max_placed,
+                                           c->max_slots, c->max_stages, group_good, lat_on_chip0,
+                                           true);
+        int64_t per_sm64;
+        int block_warps64;
+        fit(L64, per_sm64, block_warps64);
+        if (per_sm64 >= per_sm) { g->lat_f64 = 1; block_warps = block_warps64; }
     }
     const int64_t resident_slots = (int64_t)sm_count * per_sm;
     int64_t chunk = opts ? opts->chunk_requests : 0;
@@ -149,7 +166,8 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->lat_smem_elems = (c->latency_stride == 0 && lat_elems * sizeof(float) <= (size_t)kLatSmemBytes)
                             ? (int32_t)lat_elems : 0;
     const SmemLayout L = smem_layout(c->num_models, c->max_groups, c->max_placed, c->max_slots,
-                                     c->max_stages, group_good, g->lat_smem_elems);
+                                     c->max_stages, group_good, g->lat_smem_elems,
+                                     g->lat_smem_elems != 0 && g->lat_f64 != 0);
     g->smem_stream = L.warp0 + (size_t)g->block_warps * L.warp_bytes;
     g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
     g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
@@ -398,6 +416,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.group_info = cands->group_info; ka.latency = cands->latency;
     ka.latency_stride = cands->latency_stride;
     ka.lat_smem_elems = g.lat_smem_elems; ka.block_warps = g.block_warps;
+    ka.lat_f64 = g.lat_smem_elems != 0 ? g.lat_f64 : 0;
     ka.K = g.K; ka.NS = g.NS; ka.seg_len = g.seg_len; ka.seg_per_chunk = g.seg_per_chunk;
     ka.warmup = g.warmup;
     ka.num_leaves = plan->num_leaves; ka.leaf_start = plan->leaf_start;

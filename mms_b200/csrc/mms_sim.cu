@@ -101,7 +101,7 @@ __global__ void build_rows_kernel(const KernelArgs a)
 template <bool kGroupGood>
 __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int warp = 0)
 {
-    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
+    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0);
     const size_t base = L.warp0 + (size_t)warp * L.warp_bytes;
     Lane ln;
     ln.clk = (uint32_t)((base + L.clocks) / sizeof(double)) + lane;
@@ -117,6 +117,7 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
     ln.rep_off = a.model_off + (size_t)b * (a.M + 1);
     ln.lat_gl = a.latency + (size_t)b * a.latency_stride;
     ln.lat_on_chip = a.lat_smem_elems != 0;
+    ln.lat_f64 = a.lat_f64 != 0;
     ln.M = a.M; ln.C = a.C; ln.S = a.S;
     ln.status = 0;
     for (int t = 0; t < a.T + kClockPad; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
@@ -129,10 +130,16 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
 __device__ inline void stage_latency_table(const KernelArgs &a, const SmemLayout &L)
 {
     if (a.lat_smem_elems) {
-        const uint32_t base = (uint32_t)(L.latency / sizeof(float));
         const int real = a.M * a.C * a.S;
-        for (int i = threadIdx.x; i < a.lat_smem_elems; i += blockDim.x)
-            SM_F32(base + i) = i < real ? __ldg(a.latency + i) : 0.0f;
+        if (a.lat_f64) {        // widened once here instead of at every use
+            const uint32_t base = (uint32_t)(L.latency / sizeof(double));
+            for (int i = threadIdx.x; i < a.lat_smem_elems; i += blockDim.x)
+                SM_F64(base + i) = i < real ? (double)__ldg(a.latency + i) : 0.0;
+        } else {
+            const uint32_t base = (uint32_t)(L.latency / sizeof(float));
+            for (int i = threadIdx.x; i < a.lat_smem_elems; i += blockDim.x)
+                SM_F32(base + i) = i < real ? __ldg(a.latency + i) : 0.0f;
+        }
     }
     __syncthreads();
 }
@@ -161,7 +168,7 @@ sim_stream_kernel(const KernelArgs a)
 {
     const int lane = threadIdx.x & (kLanes - 1);
     const int warp = threadIdx.x / kLanes;
-    stage_latency_table(a, smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems));
+    stage_latency_table(a, smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0));
     const bool chunked = can_chunk(a);
     const int64_t stream = ((int64_t)blockIdx.x * a.block_warps + warp) * kLanes + lane;
     if (stream >= (int64_t)a.B * a.K) return;   // lanes never wait for each other below
@@ -303,7 +310,7 @@ sim_repair_kernel(const KernelArgs a)
     const uint32_t count = a.work_count[a.round];
     if ((count <= (uint32_t)a.narrow_limit) != kNarrow) return;
     if ((uint64_t)blockIdx.x * (kNarrow ? 1 : kLanes) >= count) return;
-    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
+    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0);
     stage_latency_table(a, L);
     if (kNarrow && threadIdx.x != 0) return;
     const uint32_t w = kNarrow ? blockIdx.x : blockIdx.x * kLanes + lane;
@@ -348,7 +355,7 @@ sim_chain_kernel(const KernelArgs a)
     if (!can_chunk(a) || a.N == 0) return;
     if ((a.work_count[kMaxRepairRounds] <= (uint32_t)a.narrow_limit) != kNarrow) return;
     if (kNarrow && a.compat[blockIdx.x]) return;          // whole block: nothing to stage for
-    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems);
+    const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0);
     stage_latency_table(a, L);
     if (kNarrow && threadIdx.x != 0) return;
     const int64_t b = kNarrow ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kLanes + lane;

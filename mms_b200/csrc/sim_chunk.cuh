@@ -33,6 +33,7 @@ struct KernelArgs {
     const float *latency;
     int64_t latency_stride;
     int32_t lat_smem_elems;
+    int32_t lat_f64;              // the on-chip latency table holds doubles (the f32 values widened)
     int32_t block_warps;          // warps per block of the stream kernel
     // geometry
     int32_t K;                    // chunks

@@ -56,15 +56,17 @@ struct SmemLayout {
     int tmp_stages;
 };
 
-// lat_elems: entries of the shared f32 latency table kept on chip (0 = read
-// it from global memory).  Counters are not kept on chip: the step records
+// lat_elems: entries of the shared latency table kept on chip (0 = read it
+// from global memory), as f32 or, with lat_f64, widened to f64.  Counters are not kept on chip: the step records
 // its decision per request (see Lane::dec) and count_kernel tallies them.
 __host__ __device__ inline SmemLayout smem_layout(int M, int G, int /*P*/, int T, int S,
-                                                  bool group_good, int lat_elems)
+                                                  bool group_good, int lat_elems,
+                                                  bool lat_f64 = false)
 {
     SmemLayout L;
     L.latency = 0;
-    L.warp0 = (sizeof(float) * (size_t)((lat_elems + 3) & ~3) + 15) & ~(size_t)15;
+    L.warp0 = ((lat_f64 ? sizeof(double) : sizeof(float)) * (size_t)((lat_elems + 3) & ~3) + 15) &
+              ~(size_t)15;
     size_t off = 0;
     L.clocks = off;     off += sizeof(double) * (size_t)(T + kClockPad) * kLanes;
     L.tmp_stages = S > 8 ? S - 8 : 0;
@@ -97,6 +99,7 @@ struct Lane {
     const uint16_t *rep_off;  // the caller's model_off row of this candidate
     const float *lat_gl;      // this candidate's table in global memory
     bool lat_on_chip;
+    bool lat_f64;             // on chip as doubles
     int32_t M, C, S;
     uint32_t status;
 };
@@ -161,6 +164,13 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
 // max of two times.  Times are never NaN (arrivals are checked to be finite,
 // latencies are finite or +inf), so one compare and a select do.
 __device__ __forceinline__ double tmax(double a, double b) { return a > b ? a : b; }
+
+// Latency table entry `at` (model, column, stage flattened), widened.
+__device__ __forceinline__ double lat_at(const Lane &ln, uint32_t at)
+{
+    if (!ln.lat_on_chip) return (double)__ldg(ln.lat_gl + at);
+    return ln.lat_f64 ? SM_F64(ln.lat_sm + at) : (double)SM_F32(ln.lat_sm + at);
+}
 
 // Replica entry as the caller gives it (first clock slot) -> with the LAST slot.
 __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
@@ -262,10 +272,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
     if constexpr (kNarrow && !kLegacy) {
         // :605-610 stage by stage, as far as the group has stages
-        auto lat = [&](uint32_t k) {
-            return ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
-                                  : (double)__ldg(ln.lat_gl + row + k);
-        };
+        auto lat = [&](uint32_t k) { return lat_at(ln, row + k); };
         t0 = tmax(ts, SM_F64(ck)) + lat(0);
         double t = t0;
         if (ns > 1) {
@@ -302,7 +309,11 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
                      k5 = SM_F64(ck + 5 * kLanes), k6 = SM_F64(ck + 6 * kLanes),
                      k7 = SM_F64(ck + 7 * kLanes);
         double l0, l1, l2 = 0, l3 = 0, l4 = 0, l5 = 0, l6 = 0, l7 = 0;
-        if (ln.lat_on_chip) {
+        if (ln.lat_on_chip && ln.lat_f64) {
+            const uint32_t lr = ln.lat_sm + row;
+            l0 = SM_F64(lr); l1 = SM_F64(lr + 1); l2 = SM_F64(lr + 2); l3 = SM_F64(lr + 3);
+            l4 = SM_F64(lr + 4); l5 = SM_F64(lr + 5); l6 = SM_F64(lr + 6); l7 = SM_F64(lr + 7);
+        } else if (ln.lat_on_chip) {
             // rows are padded so that 8 entries are always readable
             const uint32_t lr = ln.lat_sm + row;
             l0 = (double)SM_F32(lr); l1 = (double)SM_F32(lr + 1);
@@ -341,8 +352,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
             t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
             if (ns > 8) {
                 for (uint32_t k = 8; k < ns; ++k) {
-                    const double lk = ln.lat_on_chip ? (double)SM_F32(ln.lat_sm + row + k)
-                                                     : (double)__ldg(ln.lat_gl + row + k);
+                    const double lk = lat_at(ln, row + k);
                     t = tmax(t, SM_F64(ck + k * kLanes)) + lk;
                     SM_F64(ln.tmp + (k - 8) * kLanes) = t;
                 }

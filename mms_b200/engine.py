@@ -935,18 +935,20 @@ collect_batch = _collect
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
               per_request=False, group_good=False, pinned=False, options=None, mirrors=True,
-              split=True):
+              split=True, crowded=False):
     """Simulates every placement of `enc` against `trace`
     (simulate_requests_mixed, controller.py:561-628).  `mirrors`: placements
     with interchangeable groups get a mirror candidate (a speed-up of the
-    time-parallel execution; results are the same with and without)."""
+    time-parallel execution; results are the same with and without).
+    `crowded`: the MMS_FLAG_CROWDED hint (results are the same)."""
     if not per_request:
         return _collect(submit_batch(trace, enc, table, group_good, pinned, options, mirrors,
-                                     split))
+                                     split, crowded))
     return _launch(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
                    enc.model_off, enc.model_rep, enc.group_info,
-                   table.device(trace.device), 0, nat.FLAG_PER_REQUEST, group_good, pinned,
-                   options)
+                   table.device(trace.device), 0,
+                   nat.FLAG_PER_REQUEST | (nat.FLAG_CROWDED if crowded else 0), group_good,
+                   pinned, options)
 
 
 def encode_dense(m_id2g_id, num_stages, num_models):

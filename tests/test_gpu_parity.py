@@ -134,13 +134,17 @@ def test_short_and_ragged_traces(loaded, n):
         assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("chunk,run_in,rounds,cap", [
-    (-1, 0, 0, 0), (1024, 2048, 0, 0), (4096, 1, 0, 0), (2048, 64, 2, 1), (8192, 2048, 6, 2),
-    (8192, 16, 1, 1), (0, 0, 0, 0), (0, 0, 16, 3)])
-def test_results_do_not_depend_on_chunking(loaded, chunk, run_in, rounds, cap):
+@pytest.mark.parametrize("chunk,run_in,rounds,cap,crowded", [
+    (-1, 0, 0, 0, False), (1024, 2048, 0, 0, False), (4096, 1, 0, 0, False),
+    (2048, 64, 2, 1, False), (8192, 2048, 6, 2, False), (8192, 16, 1, 1, False),
+    (0, 0, 0, 0, False), (0, 0, 16, 3, False),
+    # with the hint, more than 48 failing chunks are repaired 32 to a warp
+    (4096, 1, 0, 0, True), (2048, 64, 2, 1, True), (3072, 8, 16, 0, True)])
+def test_results_do_not_depend_on_chunking(loaded, chunk, run_in, rounds, cap, crowded):
     """Speculative chunks are kept only when provably equivalent, so any cut of
     the trace — even a run-in of one request, which makes nearly every chunk
-    wrong and re-simulated — gives the sequential results bit for bit."""
+    wrong and re-simulated — gives the sequential results bit for bit, whether
+    the repairs run one chunk to a warp or 32."""
     from mms_b200 import cases, engine
     from mms_b200.placement import PlacementEvaluator
     from mms_b200.simulator import workload_arrays
@@ -150,13 +154,13 @@ def test_results_do_not_depend_on_chunking(loaded, chunk, run_in, rounds, cap):
                             options=engine.sim_options(chunk, run_in, rounds, cap))
     enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
     res, _, _ = engine.run_batch(ev.trace, enc, ev.table, per_request=True, group_good=True,
-                                 options=ev.options)
+                                 options=ev.options, crowded=crowded)
     names = [d.name for d in case.model_datas]
     profs = [d.profiling_result for d in case.model_datas]
     mids, slos = workload_arrays(case.workload, names)
     arr = case.workload.arrivals
     if chunk == 4096:
-        assert res.resimulated.sum() > 0        # the repair path really ran
+        assert res.resimulated.sum() > (48 if crowded else 0)   # the repair path really ran
     for b, p in enumerate(case.placements):
         fin, good, mreq, mgood, greq, ggood = tables.one_placement(p, profs, mids, slos, arr)
         assert res.finish[b].tobytes() == fin.tobytes(), (b, chunk)

@@ -112,7 +112,7 @@ def host_lib():
             H.mms_host_configs.restype = ctypes.c_int64
             H.mms_host_configs.argtypes = [_vp, ctypes.c_int64, _vp, ctypes.c_int64, _vp]
             H.mms_host_encode.restype = ctypes.c_int
-            H.mms_host_encode.argtypes = [ctypes.c_int64] * 4 + [_vp] * 14
+            H.mms_host_encode.argtypes = [ctypes.c_int64] * 4 + [_vp] * 14 + [ctypes.c_int64]
             _host = H
     return _host
 

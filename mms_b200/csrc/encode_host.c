@@ -253,7 +253,10 @@ static uint64_t mix64(uint64_t x)
  * slots[b] = clock slots used; twin_items[n][3] = (placement, class number
  * inside the placement, group id) for every group that has the same column
  * and the same set of models as another group of its placement, classes and
- * groups ascending; *n_twin_items = n.  counts is scratch of M + 1 entries,
+ * groups ascending; *n_twin_items = n.  A placement whose classes can be
+ * permuted in more than max_perms ways (the product of the factorials of
+ * their sizes) is left out: it gets no mirror candidates anyway, and early in
+ * a search nearly every placement is one.  counts is scratch of M + 1 entries,
  * mark of M.  Unused cells of the tables must come zeroed.
  * Returns 0, or 1 when a model id is outside [0, M). */
 int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
@@ -261,7 +264,7 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
                     const int64_t *column_of, const int64_t *n_in_group, const int64_t *placed_model,
                     uint16_t *model_off, uint32_t *model_rep, uint32_t *group_info,
                     int64_t *slots, int32_t *twin_items, int64_t *n_twin_items,
-                    int64_t *counts, int64_t *mark)
+                    int64_t *counts, int64_t *mark, int64_t max_perms)
 {
     int64_t gi = 0, pi = 0, n_items = 0;
     for (int64_t m = 0; m < M; ++m) mark[m] = -1;
@@ -316,6 +319,8 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
             uint8_t done[256];
             for (int64_t g = 0; g < ng; ++g) done[g] = 0;
             int32_t cls = 0;
+            const int64_t first_item = n_items;
+            int64_t perms = 1;
             for (int64_t g = 0; g < ng; ++g) {
                 if (done[g] || nin[g] == 0) continue;
                 int marked = 0, found = 0;
@@ -339,8 +344,16 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
                     twin_items[3 * n_items + 2] = (int32_t)h2; ++n_items;
                     done[h2] = 1;
                 }
-                if (found) ++cls;
+                if (found) {
+                    int64_t size = 0;
+                    for (int64_t k = n_items - 1; k >= first_item && twin_items[3 * k + 1] == cls; --k)
+                        ++size;
+                    for (int64_t k = 2; k <= size && perms <= max_perms; ++k) perms *= k;
+                    ++cls;
+                }
+                if (perms > max_perms) break;
             }
+            if (perms > max_perms) n_items = first_item;
         }
         pi = q;
         gi += ng;

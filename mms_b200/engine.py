@@ -363,13 +363,21 @@ def mirror_swaps(classes):
     return words
 
 
+def _arrangements(classes) -> int:
+    count = 1
+    for cls in classes:
+        count *= factorial(len(cls)) if len(cls) < 5 else MAX_MIRRORS + 2
+    return count
+
+
 def twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model):
     """Classes of groups of one placement with the same parallel config and
     the same set of models (flat arrays as in encode_placements).  Such groups
     are interchangeable: which of them is ahead after a stretch of the trace
     depends on history long past, and a speculative chunk may come out with
     their roles permuted.  Returns [(placement index, [[group ids], ...])] for
-    the placements that have any.  The sets are compared through a 64-bit sum
+    the placements that have any and at most MAX_MIRRORS + 1 ways of arranging
+    them.  The sets are compared through a 64-bit sum
     of random per-model keys; a collision could only cost speed, never
     exactness."""
     tot_groups = len(grp_b)
@@ -409,7 +417,8 @@ def twin_groups(B, M, grp_b, grp_g, cfg_col, n_in_group, placed_model):
     for _, classes in out:
         for cls in classes:
             cls.sort()
-    return out
+    # placements with more arrangements than get mirrors are of no use to anyone
+    return [(b, classes) for b, classes in out if _arrangements(classes) <= MAX_MIRRORS + 1]
 
 
 def _flatten(placements):
@@ -422,8 +431,9 @@ def _flatten(placements):
     if H is not None and isinstance(placements, (list, tuple)):
         n_groups = np.zeros(B, np.int64)
         n_pairs = np.zeros(B, np.int64)
-        # one pass with room for 48 groups and 192 (group, model) pairs per placement ...
-        cap_g, cap_p = 48 * B + 64, 192 * B + 256
+        # one pass with room for 96 groups and 256 (group, model) pairs per placement
+        # (untouched room costs nothing) ...
+        cap_g, cap_p = 96 * B + 64, 256 * B + 256
         cfg = np.empty((cap_g, 3), np.int64)
         n_in_group = np.empty(cap_g, np.int64)
         placed_model = np.empty(cap_p, np.int64)
@@ -506,7 +516,8 @@ def _encode_native(H, B, M, table, n_groups, cfg, n_in_group, placed_model) -> E
                            cfg_index.ctypes.data, column_of.ctypes.data, n_in_group.ctypes.data,
                            placed_model.ctypes.data, model_off.ctypes.data, model_rep.ctypes.data,
                            group_info.ctypes.data, slots.ctypes.data, items.ctypes.data,
-                           n_items.ctypes.data, counts.ctypes.data, mark.ctypes.data)
+                           n_items.ctypes.data, counts.ctypes.data, mark.ctypes.data,
+                           MAX_MIRRORS + 1)
     if rc == 1:
         raise IndexError("model id in group_models is out of range")
     T = int(slots[:B].max()) if B else 0

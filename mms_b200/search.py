@@ -9,6 +9,7 @@ the simulator is called: independent searches advance in LOCKSTEP so that
 every step scores all their candidates in one GPU launch instead of one
 simulator call each.
 """
+import gc
 import math
 import time
 from bisect import bisect_left, bisect_right
@@ -180,6 +181,21 @@ def beam_search_lockstep(init_sols: Sequence[ModelPlacement], model_datas, clust
     best_sol = list(init_sols)
     visited = [set() for _ in range(n)]
     active = list(range(n))
+    # The search keeps tens of thousands of small tuples alive (the visited
+    # sets); a full collection walking them costs tens of milliseconds, more
+    # than a layer, and finds nothing: none of these objects form cycles.
+    gc_was_on = gc.isenabled()
+    gc.disable()
+    try:
+        return _beam_layers(active, beams, best_score, best_sol, visited, weights, num_models,
+                            mem_budget, evaluator, beam_size, verbose, on_layer)
+    finally:
+        if gc_was_on:
+            gc.enable()
+
+
+def _beam_layers(active, beams, best_score, best_sol, visited, weights, num_models, mem_budget,
+                 evaluator, beam_size, verbose, on_layer):
     while active:
         tic = time.time()
         layers, owner = [], []

@@ -170,9 +170,11 @@ def test_twin_group_detection_matches_a_plain_search():
             if len(ms):
                 classes.setdefault((c, tuple(sorted(ms))), []).append(g)
         want = sorted(v for v in classes.values() if len(v) >= 2)
-        assert sorted(found.get(b, [])) == want, b
         perms = int(np.prod([factorial(len(v)) for v in want])) if want else 1
-        expect_mirrors += perms - 1 if perms - 1 <= engine.MAX_MIRRORS else 0
+        if perms - 1 > engine.MAX_MIRRORS:
+            want = []                                # too many arrangements: not reported
+        assert sorted(found.get(b, [])) == want, b
+        expect_mirrors += perms - 1 if want else 0
     assert len(found) >= 4
     assert sorted(found[len(sols) - 4]) == [[0, 1], [2, 3, 4]]
     off, rep, info, partner, swap = enc.with_mirrors()

@@ -244,7 +244,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
             ka.round = r;
             validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
-            resolve_kernel<<<(unsigned)((ka.Bs + 63) / 64), 64, 0, st>>>(ka);
+            resolve_kernel<<<(unsigned)((ka.Bs + 3) / 4), 4 * kLanes, 0, st>>>(ka);
             MMS_CUDA(cudaGetLastError());
             // sized for the worst case; blocks past the work list return at once
             repair_k<<<(unsigned)((bounds + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);

@@ -242,7 +242,7 @@ __global__ void validate_kernel(const KernelArgs a)
     a.compat[(size_t)j * B + u] = (uint16_t)mask;
 }
 
-// One thread per scored candidate: follows the chain of chunks through the
+// One warp per scored candidate: follows the chain of chunks through the
 // masks of validate_kernel.  A chunk keeps the run selected for it when that
 // one continues the chunk before it; else it is taken from the first mirror
 // that does; else the true state is copied into the candidate's own array and
@@ -253,7 +253,9 @@ __global__ void validate_kernel(const KernelArgs a)
 // and lets the chain kernel skip the candidate.
 __global__ void resolve_kernel(const KernelArgs a)
 {
-    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // a warp per candidate: lane 0 walks, all lanes copy a state when one is to be copied
+    const int lane = threadIdx.x & (kLanes - 1);
+    const int64_t b = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / kLanes;
     if (!can_chunk(a) || b >= a.Bs) return;
     if (a.round > 0 && a.work_count[a.round - 1] == 0) return;    // same masks, same answer
     bool settled = true;
@@ -264,32 +266,40 @@ __global__ void resolve_kernel(const KernelArgs a)
     for (int32_t j = 1; j < a.K; ++j) {
         const int32_t q0 = j * a.seg_per_chunk;
         const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;
-        const int32_t e = a.seg_src[(size_t)(q0 - 1) * B + b];     // whose end of chunk j-1 counts
-        const int32_t s0 = a.seg_src[(size_t)q0 * B + b];          // whose start of chunk j
-        const uint32_t mask = a.compat[(size_t)j * B + (e < 0 ? b : e)];
-        const uint32_t bit = s0 < 0 ? 0u : (uint32_t)(s0 - m_first + 1);
-        if (bit < 16 && ((mask >> bit) & 1u)) {
-            if (s0 < 0 && a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair goes on
+        int64_t copy_from = -1;          // candidate whose end state becomes chunk j's start
+        if (lane == 0) {
+            const int32_t e = a.seg_src[(size_t)(q0 - 1) * B + b];     // whose end of chunk j-1 counts
+            const int32_t s0 = a.seg_src[(size_t)q0 * B + b];          // whose start of chunk j
+            const uint32_t mask = a.compat[(size_t)j * B + (e < 0 ? b : e)];
+            const uint32_t bit = s0 < 0 ? 0u : (uint32_t)(s0 - m_first + 1);
+            if (bit < 16 && ((mask >> bit) & 1u)) {
+                if (s0 < 0 && a.repair_from[(size_t)j * B + b] >= 0) {   // a capped repair goes on
+                    const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
+                    a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+                    settled = false;
+                }
+            } else if (mask >> 1) {
+                const int32_t v = (int32_t)m_first + (__ffs((int)(mask >> 1)) - 1);
+                for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * B + b] = v;
+                a.repair_from[(size_t)j * B + b] = -1;
+            } else {
+                copy_from = e < 0 ? b : e;
+                a.repair_from[(size_t)j * B + b] = -1;         // the whole chunk is redone
+                a.seg_src[(size_t)q0 * B + b] = -1;
                 const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
-                a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
+                a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
+                ++redone;
                 settled = false;
             }
-        } else if (mask >> 1) {
-            const int32_t v = (int32_t)m_first + (__ffs((int)(mask >> 1)) - 1);
-            for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * B + b] = v;
-            a.repair_from[(size_t)j * B + b] = -1;
-        } else {
-            const double *X = a.seg_end + (size_t)(q0 - 1) * a.T * B + (e < 0 ? b : e);
+        }
+        copy_from = __shfl_sync(0xFFFFFFFFu, copy_from, 0);
+        if (copy_from >= 0) {
+            const double *X = a.seg_end + (size_t)(q0 - 1) * a.T * B + copy_from;
             double *Y = a.chunk_start + (size_t)j * a.T * B + b;
-            for (int s = 0; s < a.T; ++s) Y[s * B] = X[s * B];
-            a.repair_from[(size_t)j * B + b] = -1;         // the whole chunk is redone
-            a.seg_src[(size_t)q0 * B + b] = -1;
-            const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
-            a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
-            ++redone;
-            settled = false;
+            for (int s = lane; s < a.T; s += kLanes) Y[s * B] = X[s * B];
         }
     }
+    if (lane != 0) return;
     a.compat[b] = settled ? 1 : 0;
     if (!settled) atomicAdd(&a.work_count[kMaxRepairRounds], 1u);
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);

@@ -372,9 +372,9 @@ def run_b200(args):
                          "algorithmic_bytes_per_launch": kernel_units * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
-            # segment leaves, rows, stream, (validate, resolve, repair) per round, chain,
-            # count, requests per model, finalize
-            "gpu_launches": ((7 + 3 * (args.rounds if args.rounds > 0 else 4)) * args.steps
+            # segment leaves, rows, stream, (validate, resolve, two forms of repair) per
+            # round, two forms of chain, count, requests per model
+            "gpu_launches": ((7 + 4 * (args.rounds if args.rounds > 0 else 4)) * args.steps
                              * len(resident.jobs)),
             "mirror_candidates_per_gpu": int(n_mirrors),
             "launches_per_step": len(resident.jobs),
@@ -569,7 +569,7 @@ def run_sweep(args):
                          "algorithmic_bytes_per_launch": units * BYTES_PER_UNIT},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(traces.h2d_bytes),
                     "d2h_bytes_per_step": int(T * (2 * len(names) + enc.G + 4) * 4)},
-            "gpu_launches": (7 + 3 * (args.rounds if args.rounds > 0 else 4)) * args.steps,
+            "gpu_launches": (7 + 4 * (args.rounds if args.rounds > 0 else 4)) * args.steps,
             "chunks_resimulated_per_trace": float(np.mean(res.resimulated)),
             "clocks": clk.summary(),
             "goodput_mean_per_cell": [float(np.mean(goodputs[c::16])) for c in range(16)],

@@ -76,6 +76,8 @@ def parse_args():
                     help="candidates: 4096 placements x one trace (the headline); sweep: one "
                          "placement x many traces (robustness sweep)")
     ap.add_argument("--traces", type=int, default=256, help="sweep: traces per GPU")
+    ap.add_argument("--placement-seed", type=int, default=-1,
+                    help="seed of the candidate list (default: the rank)")
     ap.add_argument("--no-split", action="store_true",
                     help="one launch per step even when some placements have mirror candidates")
     ap.add_argument("--no-mirrors", action="store_true",
@@ -238,7 +240,7 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
 
     # every rank scores its own 4096 candidates (weak scaling) on the same trace
-    case = build_case(args, placement_seed=rank)
+    case = build_case(args, placement_seed=rank if args.placement_seed < 0 else args.placement_seed)
     ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload, device=dev,
                             options=engine.sim_options(args.chunk, args.run_in, args.rounds, args.repair_segments))
     N, B = ev.trace.num_requests, len(case.placements)

@@ -113,7 +113,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     const int64_t resident_slots = (int64_t)sm_count * per_sm;
     int64_t chunk = opts ? opts->chunk_requests : 0;
     int64_t warm = opts ? opts->warmup_requests : 0;
-    // segments: the unit of state snapshots, counter flushes and repairs
+    // segments: the unit of state snapshots and repairs
     const int64_t seg = 1024;
     const int64_t NS = N / seg > 0 ? N / seg : 1;
     int64_t spc;                                   // segments per chunk

@@ -22,22 +22,24 @@
 //                   stored runs of the next chunk start from a state
 //                   EQUIVALENT to the one this run ended in
 //                   (states_equivalent: equal futures, provably)?
-//   resolve kernel  one thread per candidate follows the chain of chunks
+//   resolve kernel  one warp per candidate follows the chain of chunks
 //                   through those answers; where no stored run continues
 //                   the chain, the true state is copied in and the chunk
 //                   goes on a work list.
 //   repair kernel   one thread per listed chunk re-simulates it from the true
 //                   state, segment by segment, until its state is equivalent
 //                   to what a stored run had at that point; the rest of the
-//                   chunk is taken from that run.
+//                   chunk is taken from that run.  32 chunks to a warp, or,
+//                   for a short list, one (with a step that branches).
 //                   validate + resolve + repair run a few rounds (a repaired
 //                   chunk can end differently and invalidate its successor).
-//   chain kernel    one thread per candidate walks all boundaries in order
-//                   and repairs in place whatever the rounds left — it makes
-//                   the result exact whatever the chunking and the rounds.
-//   count, finalize tally the recorded decisions of the selected runs into the
-//                   counters and combine the per-leaf latency sums in numpy's
-//                   pairwise order.
+//   chain kernel    one thread per candidate that is still unsettled walks
+//                   all boundaries in order and repairs in place whatever the
+//                   rounds left — it makes the result exact whatever the
+//                   chunking and the rounds.
+//   count kernel    tallies the recorded decisions of the selected runs into
+//                   the counters and combines the per-leaf latency sums in
+//                   numpy's pairwise order.
 //
 // The 32 lanes of a warp are 32 candidates on the same chunk (one broadcast
 // load per trace element) whenever the batch has 32 or more candidates.

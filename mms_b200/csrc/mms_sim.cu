@@ -312,7 +312,7 @@ __global__ void resolve_kernel(const KernelArgs a)
 // where what is left is a few long dependent repairs and the GPU is otherwise
 // idle — one chunk to a warp, with the step that branches (kNarrow): the
 // duration of a round is that of its longest repair, and a lone lane gets
-// through a request in about half the instructions.  Both kernels are
+// through a request in a quarter fewer instructions.  Both kernels are
 // launched every round; the one whose turn it is not returns at once.
 template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow>
 __global__ void __launch_bounds__(kLanes, 1)

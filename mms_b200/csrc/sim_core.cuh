@@ -190,7 +190,7 @@ __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
 // inside the instruction cache.
 //   kNarrow  for a warp in which ONE lane works (the serial repairs): real
 //            branches, so that only the replicas and the stages that exist are
-//            touched — about half the instructions, and no other lane to hold up.
+//            touched — about a quarter fewer instructions, and no other lane to hold up.
 template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)

@@ -343,7 +343,7 @@ def run_b200(args):
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     e2e_value = units_per_step / float(e2e_t.item())
 
-    greedy = greedy_step_timing(args, dev) if (rank == 0 and args.greedy_steps > 0) else None
+    greedy = greedy_step_timing(args, dev) if (world == 1 and args.greedy_steps > 0) else None
     if rank == 0:
         peak, which = hbm_peak()
         # the dominant kernel (sim_stream_kernel), timed by CUDA events on its own stream
@@ -389,7 +389,7 @@ def run_b200(args):
         }
         if greedy:
             line["greedy_step"] = greedy
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:      # single-GPU runs only
             count = min(B, 3072)       # about 10 s of one host core
             rate, dt = cpu_port_rate(case, count, 1)
             line["cpu_baseline"] = {
@@ -576,7 +576,7 @@ def run_sweep(args):
             "clocks": clk.summary(),
             "goodput_mean_per_cell": [float(np.mean(goodputs[c::16])) for c in range(16)],
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             from oracle import tables
             profs = [d.profiling_result for d in case.model_datas]
             t0 = time.perf_counter()

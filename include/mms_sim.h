@@ -90,8 +90,12 @@ typedef struct {
  *                          slot, 16-23 its stages (pp), 24-31 its column in
  *                          the latency table
  *  group_info u32[B][G]    bits 0-7 first clock slot, 8-15 stages (0 = row
- *                          padding), bit 16 set when the group serves a
- *                          model that has more than one replica
+ *                          padding).  Bit 16 ("serves a model that has more
+ *                          than one replica") may be set by the caller but is
+ *                          not relied on: the library derives it from
+ *                          model_off / model_rep on the device, and checks
+ *                          slot + stages <= T (MMS_STATUS_BAD_INDEX, the
+ *                          group is then treated as padding)
  *  latency    f32[M][C][S] seconds per stage, already rounded to f32 the way
  *                          controller.py:467-476 does; column = parallel
  *                          config.  With latency_stride != 0 candidate b
@@ -187,17 +191,23 @@ int mms_abi_version(void);
 /* Text of the last failing CUDA call on this thread ("" if none). */
 const char *mms_last_error(void);
 
-/* Timing of the dominant kernel, for benchmarks (nothing in the reference
- * corresponds).  After mms_profile_begin(), every mms_sim_mixed call of this
- * process brackets its sim_stream_kernel launch with two CUDA events on the
- * caller's stream (up to 256 launches; later ones are not recorded).
- * mms_profile_end() stops recording, waits for the recorded events and
- * returns the number of launches, their total duration and (when each_ms is
- * not NULL) the duration of each of the first `capacity` launches, in call
- * order.  Off by default; events are created on first use, on the device
- * current then. */
+/* Timing of the dominant kernels, for benchmarks (nothing in the reference
+ * corresponds).  After mms_profile_begin(), every mms_sim_mixed and
+ * mms_sim_batching call of this process brackets the launches named below
+ * with two CUDA events on the caller's stream (up to 2048 spans; later ones
+ * are not recorded).  mms_profile_end() stops recording, waits for the
+ * recorded events and returns the number of spans and, for the first
+ * `capacity` of them in call order, their duration and which launch they
+ * bracket.  Off by default; events are created on first use, on the device
+ * current then.  For benchmarks only: the recording state is process-wide and
+ * unsynchronised, so use it from ONE host thread with no other thread inside
+ * the library, and on one device. */
+#define MMS_PROFILE_STREAM 0        /* sim_stream_kernel                          */
+#define MMS_PROFILE_CHAIN 1         /* sim_chain_kernel (both forms, one span)    */
+#define MMS_PROFILE_BATCH_STREAM 2  /* batch_stream_kernel                        */
+#define MMS_PROFILE_BATCH_CHAIN 3   /* batch_chain_kernel                         */
 int mms_profile_begin(void);
-int mms_profile_end(int32_t *launches, float *total_ms, float *each_ms, int32_t capacity);
+int mms_profile_end(int32_t *launches, float *each_ms, int32_t *each_tag, int32_t capacity);
 
 /* Summation plan (host side; replaces nothing in the reference — it restates
  * numpy's reduction order, reached from controller.py:402). */
@@ -245,8 +255,10 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands,
  *    MMS_STATIC_SCRATCH_BYTES is rejected with MMS_ERR_UNSUPPORTED and a
  *    message in mms_last_error(); nothing is launched.
  *  - The first call on a device looks up the array's device address (once
- *    per device, with that device current).  Make that first call outside
- *    any stream capture.
+ *    per device, with that device current; host threads that make it together
+ *    are serialised).  Make that first call outside any stream capture.
+ *  - Argument and shape errors are reported with the codes mms_sim_mixed
+ *    returns for them.
  *  - Every call on a device uses the same array, and the array keeps what the
  *    previous call left in it.  The call clears what it needs cleared, so
  *    back-to-back calls on one stream are fine; two calls whose kernels
@@ -258,6 +270,21 @@ int mms_sim_mixed_static(const mms_trace *trace, const mms_placements *cands,
                          const mms_sum_plan *plan, const int32_t *model_hist,
                          const mms_sim_options *opts, const mms_results *out,
                          uint32_t flags, void *stream);
+
+/* The search's selection step over the candidates one call scored
+ * (np.argmax over get_scores, alpa_serve/placement_policy/model_parallelism.py:
+ * 349-351, with the score of base_policy.py:225-226 formed from the reductions:
+ * good_total / N - latency_sum / N / 10000 + num_replicas / 1000000, the same
+ * fp64 operations in the same order).  best: f64[2] = {score, global index}; the
+ * global index of candidate b is index_base + (index_map ? index_map[b] : b) and
+ * the FIRST maximum wins, as in np.argmax.  With accumulate != 0 the pair
+ * already in `best` competes too (a list scored in several calls).  With several
+ * GPUs every rank all-gathers its pair and picks the first maximum again.
+ * num_replicas (sum of len(group_models), i64[B]) and index_map may be NULL. */
+int mms_argmax_scores(const int64_t *good_total, const double *latency_sum,
+                      const int64_t *num_replicas, int64_t num_requests, int32_t num_candidates,
+                      const int64_t *index_map, int64_t index_base, int32_t accumulate,
+                      double *best, void *stream);
 
 /* ---- batching simulator -------------------------------------------------
  * simulate_requests_mixed_batching (controller.py:630-798) for every

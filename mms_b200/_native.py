@@ -34,12 +34,32 @@ FLAG_CROWDED = 8
 
 STATIC_SCRATCH_BYTES = 32 << 20
 
+PROFILE_STREAM, PROFILE_CHAIN, PROFILE_BATCH_STREAM, PROFILE_BATCH_CHAIN = 0, 1, 2, 3
+
+
+def profile_begin():
+    """Starts recording kernel spans (benchmarks only, see include/mms_sim.h)."""
+    check(lib().mms_profile_begin(), "mms_profile_begin")
+
+
+def profile_end():
+    """Stops recording; returns (durations in ms f32[n], tags i32[n]) in call order."""
+    import numpy as np
+    cap = 2048
+    ms = np.zeros(cap, np.float32)
+    tags = np.zeros(cap, np.int32)
+    n = ctypes.c_int32(0)
+    check(lib().mms_profile_end(ctypes.byref(n), ms.ctypes.data, tags.ctypes.data, cap),
+          "mms_profile_end")
+    k = min(int(n.value), cap)
+    return ms[:k], tags[:k]
+
 # Every symbol include/mms_sim.h declares.
 EXPORTS = (
     "mms_abi_version", "mms_last_error", "mms_sum_plan_leaves", "mms_sum_plan_fill",
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
     "mms_sim_mixed_static", "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
-    "mms_profile_begin", "mms_profile_end",
+    "mms_profile_begin", "mms_profile_end", "mms_argmax_scores",
 )
 
 _vp = ctypes.c_void_p
@@ -137,8 +157,7 @@ def lib():
     L.mms_trace_model_histogram.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_profile_begin.restype = ctypes.c_int
     L.mms_profile_end.restype = ctypes.c_int
-    L.mms_profile_end.argtypes = [ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_float),
-                                  _vp, ctypes.c_int32]
+    L.mms_profile_end.argtypes = [ctypes.POINTER(ctypes.c_int32), _vp, _vp, ctypes.c_int32]
     L.mms_sim_workspace_bytes.restype = ctypes.c_size_t
     L.mms_sim_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.POINTER(Placements),
                                           ctypes.POINTER(SimOptions), ctypes.c_uint32]
@@ -151,6 +170,9 @@ def lib():
     L.mms_sim_mixed_static.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
                                        ctypes.POINTER(SumPlan), _vp, ctypes.POINTER(SimOptions),
                                        ctypes.POINTER(Results), ctypes.c_uint32, _vp]
+    L.mms_argmax_scores.restype = ctypes.c_int
+    L.mms_argmax_scores.argtypes = [_vp, _vp, _vp, ctypes.c_int64, ctypes.c_int32, _vp,
+                                    ctypes.c_int64, ctypes.c_int32, _vp, _vp]
     L.mms_trace_next_same_model.restype = ctypes.c_int
     L.mms_trace_next_same_model.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_sim_batching_workspace_bytes.restype = ctypes.c_size_t

@@ -43,7 +43,8 @@ struct Geometry {
         block_warps, narrow_limit, lat_f64;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_decisions, off_work_count, off_work_items,
-        off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf;
+        off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf, off_group_info;
+    size_t smem_count;        // shared memory of count_kernel
     size_t total;
 };
 
@@ -172,6 +173,9 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
     g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    // the tally's per-lane histograms (count_kernel)
+    g->smem_count = sizeof(uint32_t) * (size_t)(c->max_groups + (c->num_models + 1) / 2) * kLanes;
+    if (g->smem_count > 227 * 1024) return MMS_ERR_UNSUPPORTED;
     // one-chunk-per-warp repairs: as many as are resident at once (12 warps of
     // this register use per SM, or what shared memory admits)
     int64_t narrow_per_sm = 233472 / (int64_t)(g->smem_repair + 1024);
@@ -192,53 +196,103 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_seg_src = off;     off += align256(sizeof(int32_t) * (size_t)NS * B);
     g->off_compat = off;      off += align256(sizeof(uint16_t) * (size_t)K * B);
     g->off_seg_leaf = off;    off += align256(sizeof(int32_t) * (size_t)(NS + 1));
+    g->off_group_info = off;  off += align256(sizeof(uint32_t) * (size_t)B * c->max_groups + 4);
     g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
     g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
     g->total = off;
     return MMS_OK;
 }
 
-// Events around the stream kernel, see mms_profile_begin().
-constexpr int kProfileSlots = 256;
+// Events around the dominant kernels, see mms_profile_begin().
+constexpr int kProfileSlots = 2048;
 static cudaEvent_t g_prof_ev[2 * kProfileSlots];
+static int32_t g_prof_tag[kProfileSlots];
 static int g_prof_created = 0;      // events exist
 static int g_prof_on = 0;
 static int g_prof_count = 0;
 
-template <bool kFull, bool kGroupGood, bool kLegacy>
-static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
+// Brackets what is enqueued between its construction and stop() with two events.
+struct ProfileSpan {
+    int slot;
+    cudaStream_t st;
+    ProfileSpan(int32_t tag, cudaStream_t s) : slot(-1), st(s)
+    {
+        if (g_prof_on && g_prof_count < kProfileSlots) {
+            slot = g_prof_count++;
+            g_prof_tag[slot] = tag;
+            (void)cudaEventRecord(g_prof_ev[2 * slot], st);
+        }
+    }
+    void stop()
+    {
+        if (slot >= 0) (void)cudaEventRecord(g_prof_ev[2 * slot + 1], st);
+        slot = -1;
+    }
+};
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is sticky per function and
+// device and not cheap; it is issued only when a call needs more than any
+// earlier one asked for.
+struct SmemGrant { const void *func; int device; size_t bytes; };
+constexpr int kMaxGrants = 128;
+static SmemGrant g_grants[kMaxGrants];
+static int g_num_grants = 0;
+static std::mutex g_grant_mutex;
+
+static int allow_smem(const void *func, size_t bytes)
 {
-    seg_leaf_kernel<<<(unsigned)((ka.NS + 128) / 128), 128, 0, st>>>(ka);
-    MMS_CUDA(cudaGetLastError());
-    const int64_t cells = (int64_t)ka.B * (ka.M + 1);
-    if (cells > 0) {
-        build_rows_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka);
+    int dev = 0;
+    MMS_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_grant_mutex);
+    SmemGrant *slot = nullptr;
+    for (int i = 0; i < g_num_grants; ++i)
+        if (g_grants[i].func == func && g_grants[i].device == dev) { slot = &g_grants[i]; break; }
+    if (slot && slot->bytes >= bytes) return MMS_OK;
+    MMS_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (!slot && g_num_grants < kMaxGrants) slot = &g_grants[g_num_grants++];
+    if (slot) { slot->func = func; slot->device = dev; slot->bytes = bytes; }
+    return MMS_OK;
+}
+
+#define MMS_TRY(call)                  \
+    do {                               \
+        const int rc_ = (call);        \
+        if (rc_ != MMS_OK) return rc_; \
+    } while (0)
+
+template <bool kFull, bool kGroupGood, bool kLegacy>
+static int launch_sim(KernelArgs &ka, const ClearArgs &ca, const Geometry &g, cudaStream_t st)
+{
+    // everything a call clears, then the tables its kernels read: two launches
+    {
+        int64_t cells = (int64_t)ka.NS * ka.B;
+        if ((int64_t)ka.B * (ka.M + 1) > cells) cells = (int64_t)ka.B * (ka.M + 1);
+        int64_t blocks = (cells + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks < 1) blocks = 1;
+        clear_kernel<<<(unsigned)blocks, 256, 0, st>>>(ka, ca);
+        MMS_CUDA(cudaGetLastError());
+        build_tables_kernel<<<(unsigned)blocks, 256, 0, st>>>(ka, ca);
         MMS_CUDA(cudaGetLastError());
     }
     auto stream_k = sim_stream_kernel<kFull, kGroupGood, kLegacy>;
-    MMS_CUDA(cudaFuncSetAttribute(stream_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)g.smem_stream));
+    MMS_TRY(allow_smem((const void *)stream_k, g.smem_stream));
     const int64_t per_block = (int64_t)kLanes * g.block_warps;
     const int64_t streams = (int64_t)ka.B * ka.K;
-    const bool timed = g_prof_on && g_prof_count < kProfileSlots;
-    if (timed) MMS_CUDA(cudaEventRecord(g_prof_ev[2 * g_prof_count], st));
+    ProfileSpan stream_span(MMS_PROFILE_STREAM, st);
     stream_k<<<(unsigned)((streams + per_block - 1) / per_block), (unsigned)per_block,
                g.smem_stream, st>>>(ka);
     MMS_CUDA(cudaGetLastError());
-    if (timed) MMS_CUDA(cudaEventRecord(g_prof_ev[2 * g_prof_count++ + 1], st));
+    stream_span.stop();
     if (ka.K > 1) {
         auto repair_k = sim_repair_kernel<kFull, kGroupGood, kLegacy, false>;
         auto chain_k = sim_chain_kernel<kFull, kGroupGood, kLegacy, false>;
         auto repair_narrow_k = sim_repair_kernel<kFull, kGroupGood, kLegacy, true>;
         auto chain_narrow_k = sim_chain_kernel<kFull, kGroupGood, kLegacy, true>;
-        MMS_CUDA(cudaFuncSetAttribute(repair_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)g.smem_repair));
-        MMS_CUDA(cudaFuncSetAttribute(chain_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)g.smem_repair));
-        MMS_CUDA(cudaFuncSetAttribute(repair_narrow_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)g.smem_repair));
-        MMS_CUDA(cudaFuncSetAttribute(chain_narrow_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)g.smem_repair));
+        MMS_TRY(allow_smem((const void *)repair_k, g.smem_repair));
+        MMS_TRY(allow_smem((const void *)chain_k, g.smem_repair));
+        MMS_TRY(allow_smem((const void *)repair_narrow_k, g.smem_repair));
+        MMS_TRY(allow_smem((const void *)chain_narrow_k, g.smem_repair));
         const int64_t bounds = (int64_t)ka.B * (ka.K - 1);
         for (int r = 0; r < g.rounds; ++r) {
             ka.round = r;
@@ -256,10 +310,12 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
                 MMS_CUDA(cudaGetLastError());
             }
         }
+        ProfileSpan chain_span(MMS_PROFILE_CHAIN, st);
         chain_k<<<(unsigned)((ka.Bs + kLanes - 1) / kLanes), kLanes, g.smem_repair, st>>>(ka);
         MMS_CUDA(cudaGetLastError());
         chain_narrow_k<<<(unsigned)ka.Bs, kLanes, g.smem_repair, st>>>(ka);
         MMS_CUDA(cudaGetLastError());
+        chain_span.stop();
     }
     return MMS_OK;
 }
@@ -268,7 +324,7 @@ static int launch_sim(KernelArgs &ka, const Geometry &g, cudaStream_t st)
 
 extern "C" {
 
-int mms_abi_version(void) { return 7; }
+int mms_abi_version(void) { return 8; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 
@@ -284,20 +340,18 @@ int mms_profile_begin(void)
     return MMS_OK;
 }
 
-int mms_profile_end(int32_t *launches, float *total_ms, float *each_ms, int32_t capacity)
+int mms_profile_end(int32_t *launches, float *each_ms, int32_t *each_tag, int32_t capacity)
 {
     using namespace mms;
     g_prof_on = 0;
-    float total = 0.0f;
     for (int i = 0; i < g_prof_count; ++i) {
         float ms = 0.0f;
         MMS_CUDA(cudaEventSynchronize(g_prof_ev[2 * i + 1]));
         MMS_CUDA(cudaEventElapsedTime(&ms, g_prof_ev[2 * i], g_prof_ev[2 * i + 1]));
-        total += ms;
         if (each_ms && i < capacity) each_ms[i] = ms;
+        if (each_tag && i < capacity) each_tag[i] = g_prof_tag[i];
     }
     if (launches) *launches = g_prof_count;
-    if (total_ms) *total_ms = total;
     g_prof_count = 0;
     return MMS_OK;
 }
@@ -439,37 +493,32 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.finish = out->finish; ka.good = out->good;
     ka.resimulated = out->resimulated;
 
-    MMS_CUDA(cudaMemsetAsync(out->status, 0, sizeof(uint32_t) * (size_t)ka.Bs, st));
-    MMS_CUDA(cudaMemsetAsync(ka.work_count, 0, sizeof(uint32_t) * (kMaxRepairRounds + 1), st));
-    MMS_CUDA(cudaMemsetAsync(ka.repair_from, 0xFF, sizeof(int32_t) * (size_t)ka.K * B, st));
-    MMS_CUDA(cudaMemsetAsync(ka.seg_src, 0xFF, sizeof(int32_t) * (size_t)ka.NS * B, st));
-    if (out->resimulated)
-        MMS_CUDA(cudaMemsetAsync(out->resimulated, 0, sizeof(int32_t) * (size_t)ka.Bs, st));
+    ClearArgs ca;
+    ca.group_info_in = cands->group_info;
+    ca.group_info = (uint32_t *)(scratch + g.off_group_info);
+    ca.model_num_good = out->model_num_good;
+    ca.group_num_requests = out->group_num_requests;
+    ca.group_num_good = gg ? out->group_num_good : nullptr;
+    ca.good_total = out->good_total;
+    ka.group_info = ca.group_info;       // the checked copy, contested bits derived on the device
     const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;
     const int variant = (full ? 4 : 0) | (gg ? 2 : 0) | (legacy ? 1 : 0);
     switch (variant) {
-        case 0: rc = launch_sim<false, false, false>(ka, g, st); break;
-        case 1: rc = launch_sim<false, false, true>(ka, g, st); break;
-        case 2: rc = launch_sim<false, true, false>(ka, g, st); break;
-        case 3: rc = launch_sim<false, true, true>(ka, g, st); break;
-        case 4: rc = launch_sim<true, false, false>(ka, g, st); break;
-        case 5: rc = launch_sim<true, false, true>(ka, g, st); break;
-        case 6: rc = launch_sim<true, true, false>(ka, g, st); break;
-        default: rc = launch_sim<true, true, true>(ka, g, st); break;
+        case 0: rc = launch_sim<false, false, false>(ka, ca, g, st); break;
+        case 1: rc = launch_sim<false, false, true>(ka, ca, g, st); break;
+        case 2: rc = launch_sim<false, true, false>(ka, ca, g, st); break;
+        case 3: rc = launch_sim<false, true, true>(ka, ca, g, st); break;
+        case 4: rc = launch_sim<true, false, false>(ka, ca, g, st); break;
+        case 5: rc = launch_sim<true, false, true>(ka, ca, g, st); break;
+        case 6: rc = launch_sim<true, true, false>(ka, ca, g, st); break;
+        default: rc = launch_sim<true, true, true>(ka, ca, g, st); break;
     }
     if (rc) return rc;
 
-    // tally the recorded decisions of the selected runs
-    const size_t rows = (size_t)ka.Bs;
-    MMS_CUDA(cudaMemsetAsync(out->model_num_good, 0, sizeof(int32_t) * rows * ka.M, st));
-    MMS_CUDA(cudaMemsetAsync(out->group_num_requests, 0, sizeof(int32_t) * rows * ka.G, st));
-    if (gg) MMS_CUDA(cudaMemsetAsync(out->group_num_good, 0, sizeof(int32_t) * rows * ka.G, st));
-    MMS_CUDA(cudaMemsetAsync(out->good_total, 0, sizeof(int64_t) * rows, st));
-    const size_t hist_bytes = sizeof(uint32_t) * (size_t)(ka.G + (ka.M + 1) / 2) * kLanes;
-    if (hist_bytes > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    // tally the recorded decisions of the selected runs (outputs were cleared up front)
+    const size_t hist_bytes = g.smem_count;
     auto count_k = ka.dec_wide ? count_kernel<uint16_t> : count_kernel<uint8_t>;
-    MMS_CUDA(cudaFuncSetAttribute(count_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)hist_bytes));
+    MMS_TRY(allow_smem((const void *)count_k, hist_bytes));
     int32_t seg_per_block = ka.NS / 96 > 0 ? ka.NS / 96 : 1;   // 16-bit counts: at most 32 segments
     if (seg_per_block > 32) seg_per_block = 32;
     // one more row of blocks (the first) forms the latency sums
@@ -490,6 +539,24 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
 
 }  // extern "C"
 
+extern "C" {
+
+int mms_argmax_scores(const int64_t *good_total, const double *latency_sum,
+                      const int64_t *num_replicas, int64_t num_requests, int32_t num_candidates,
+                      const int64_t *index_map, int64_t index_base, int32_t accumulate,
+                      double *best, void *stream)
+{
+    if (num_candidates < 0 || num_requests < 0 || !best) return MMS_ERR_ARG;
+    if (num_candidates > 0 && (!good_total || !latency_sum)) return MMS_ERR_ARG;
+    mms::argmax_scores_kernel<<<1, mms::kArgmaxThreads, 0, (cudaStream_t)stream>>>(
+        good_total, latency_sum, num_replicas, num_requests, num_candidates, index_map,
+        index_base, accumulate != 0, best);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
+}  // extern "C"
+
 namespace mms {
 
 // Scratch of mms_sim_mixed_static.  In host code this name is only a handle
@@ -498,6 +565,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[MMS_STATIC_SCRAT
 
 constexpr int kMaxDevices = 64;
 static void *g_static_scratch_ptr[kMaxDevices];   // device address, per device ordinal
+static std::mutex g_static_scratch_mutex;
 
 }  // namespace mms
 
@@ -509,27 +577,31 @@ int mms_sim_mixed_static(const mms_trace *trace, const mms_placements *cands,
                          uint32_t flags, void *stream)
 {
     if (!trace || !cands) return MMS_ERR_ARG;
-    const size_t need = mms_sim_workspace_bytes(trace->num_requests, cands, opts, flags);
-    if (need == 0 && cands->num_candidates > 0) {
-        snprintf(mms::g_last_error, sizeof(mms::g_last_error),
-                 "mms_sim_mixed_static: shape outside the kernel limits");
-        return MMS_ERR_UNSUPPORTED;
-    }
-    if (need > (size_t)MMS_STATIC_SCRATCH_BYTES) {
+    // the same shape checks as mms_sim_mixed, with the same return codes; only a
+    // shape that is fine but needs more scratch than the array holds is new
+    mms::Geometry geo;
+    const int rc = mms::plan_call(trace->num_requests, cands, opts, flags,
+                                  !(flags & MMS_FLAG_NO_GROUP_GOOD), &geo);
+    if (rc != MMS_OK) return rc;
+    if (geo.total > (size_t)MMS_STATIC_SCRATCH_BYTES) {
         snprintf(mms::g_last_error, sizeof(mms::g_last_error),
                  "mms_sim_mixed_static: needs %zu bytes of scratch, the built-in array holds %u; "
                  "use fewer candidates per call or mms_sim_mixed with a caller workspace",
-                 need, (unsigned)MMS_STATIC_SCRATCH_BYTES);
+                 geo.total, (unsigned)MMS_STATIC_SCRATCH_BYTES);
         return MMS_ERR_UNSUPPORTED;
     }
     int dev = -1;
     MMS_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= mms::kMaxDevices) return MMS_ERR_NO_DEVICE;
-    if (!mms::g_static_scratch_ptr[dev]) {
-        // once per device, with that device current
-        void *p = nullptr;
-        MMS_CUDA(cudaGetSymbolAddress(&p, mms::g_static_scratch));
-        mms::g_static_scratch_ptr[dev] = p;
+    {
+        // once per device, with that device current (under a lock: two host
+        // threads may make the first call together)
+        std::lock_guard<std::mutex> lock(mms::g_static_scratch_mutex);
+        if (!mms::g_static_scratch_ptr[dev]) {
+            void *p = nullptr;
+            MMS_CUDA(cudaGetSymbolAddress(&p, mms::g_static_scratch));
+            mms::g_static_scratch_ptr[dev] = p;
+        }
     }
     mms_workspace ws;
     ws.ptr = mms::g_static_scratch_ptr[dev];
@@ -704,16 +776,18 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
         unsorted_kernel<<<296, 256, 0, st>>>(trace->arrivals, N, (int32_t *)(scratch + geo.off_flag));
         MMS_CUDA(cudaGetLastError());
     }
-    MMS_CUDA(cudaFuncSetAttribute(batch_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)geo.smem));
-    MMS_CUDA(cudaFuncSetAttribute(batch_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)geo.smem));
+    MMS_TRY(allow_smem((const void *)batch_stream_kernel, geo.smem));
+    MMS_TRY(allow_smem((const void *)batch_chain_kernel, geo.smem));
     const int64_t streams = (int64_t)B * a.K;
+    ProfileSpan stream_span(MMS_PROFILE_BATCH_STREAM, st);
     batch_stream_kernel<<<(unsigned)((streams + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
     MMS_CUDA(cudaGetLastError());
+    stream_span.stop();
     if (a.K > 1) {
+        ProfileSpan chain_span(MMS_PROFILE_BATCH_CHAIN, st);
         batch_chain_kernel<<<(unsigned)((B + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
         MMS_CUDA(cudaGetLastError());
+        chain_span.stop();
     }
     const int64_t sum_cells = (int64_t)B * (2 * a.M + 2 * a.G);
     batch_sum_kernel<<<(unsigned)((sum_cells + 127) / 128), 128, 0, st>>>(a);

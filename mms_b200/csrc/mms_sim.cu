@@ -48,6 +48,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "mms_sim.h"
 #include "sim_batching.cuh"
@@ -61,41 +62,102 @@ constexpr int kMaxRepairRounds = 16;
 constexpr int kDefaultRepairRounds = 4;
 constexpr int kDefaultRepairSegments = -1;   // no cap: measured best on the benchmark shape
 
-// One thread per (candidate, model or the extra empty row): checks the model's
-// replica list and writes its 16-byte row (see Lane::rows).  A list with a bad
-// index is reported in the status word and emptied.
-__global__ void build_rows_kernel(const KernelArgs a)
+// What a call clears before its kernels run, in one launch (grid-stride): the
+// work lists and run selections of the time-parallel machinery, the outputs
+// the tally adds into, the status words — and the kernels' own copy of
+// group_info, bounds-checked (a bad entry becomes an empty group) and with the
+// "contested" bit (bit 16) cleared: build_tables_kernel derives that bit from
+// the replica lists, so exactness never rests on what the caller put there.
+struct ClearArgs {
+    const uint32_t *group_info_in;    // the caller's [B][G]
+    uint32_t *group_info;             // scratch copy the kernels read
+    int32_t *model_num_good;          // [Bs][M]
+    int32_t *group_num_requests;      // [Bs][G]
+    int32_t *group_num_good;          // [Bs][G] or null
+    int64_t *good_total;              // [Bs]
+};
+
+__device__ inline bool group_info_valid(const KernelArgs &a, uint32_t info)
 {
-    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (int64_t)a.B * (a.M + 1)) return;
-    const int64_t b = t / (a.M + 1);
-    const int m = (int)(t % (a.M + 1));
-    uint32_t e[8] = {kNoReplica, kNoReplica, kNoReplica, kNoReplica,
-                     kNoReplica, kNoReplica, kNoReplica, kNoReplica};
-    if (m < a.M) {
-        const uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
-        const uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
-        bool bad = lo > hi || hi > (uint32_t)a.P;
-        if (!bad) {
-            for (uint32_t r = lo; r < hi; ++r) {
-                const uint32_t ent = a.model_rep[(size_t)b * a.P + r];
-                const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
-                if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
-                    ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
-                    bad = true;
-                else if (r - lo < 8)
-                    e[r - lo] = rep_to_last(ent);
-            }
-            if (hi - lo > 8) e[7] = kMoreReplicas;
-        }
-        if (bad) {
-            atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
-            for (int k = 0; k < 8; ++k) e[k] = kNoReplica;
-        }
+    const uint32_t slot = info & 0xFFu, ns = (info >> 8) & 0xFFu;
+    return slot + ns <= (uint32_t)a.T && ns <= (uint32_t)a.S;
+}
+
+__global__ void clear_kernel(const KernelArgs a, const ClearArgs c)
+{
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nth = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < (int64_t)a.NS * a.B; i += nth) a.seg_src[i] = -1;
+    for (int64_t i = tid; i < (int64_t)a.K * a.B; i += nth) a.repair_from[i] = -1;
+    for (int64_t i = tid; i < (int64_t)a.B * a.G; i += nth) {
+        const uint32_t info = c.group_info_in[i];
+        c.group_info[i] = group_info_valid(a, info) ? (info & ~0x10000u) : 0u;
     }
-    uint4 *rows = reinterpret_cast<uint4 *>(a.rep_rows);
-    rows[row_index(a, b, m)] = make_uint4(e[0], e[1], e[2], e[3]);
-    rows[row_plane(a) + row_index(a, b, m)] = make_uint4(e[4], e[5], e[6], e[7]);
+    for (int64_t i = tid; i < (int64_t)a.Bs * a.M; i += nth) c.model_num_good[i] = 0;
+    for (int64_t i = tid; i < (int64_t)a.Bs * a.G; i += nth) {
+        c.group_num_requests[i] = 0;
+        if (c.group_num_good) c.group_num_good[i] = 0;
+    }
+    for (int64_t i = tid; i < a.Bs; i += nth) {
+        c.good_total[i] = 0;
+        a.status[i] = 0;
+        if (a.resimulated) a.resimulated[i] = 0;
+    }
+    for (int64_t i = tid; i <= kMaxRepairRounds; i += nth) a.work_count[i] = 0;
+}
+
+// Builds, in one launch behind clear_kernel, the tables the simulation kernels
+// read: (1) one thread per (candidate, model or the extra empty row) checks the
+// model's replica list, writes its two 16-byte rows (see Lane::rows) and marks
+// the groups of a list with more than one replica as contested; a list with a
+// bad index is reported in the status word and emptied.  (2) One thread per
+// (candidate, group) reports a group_info entry that clear_kernel had to empty.
+// (3) One thread per segment finds the segment's first leaf.
+__global__ void build_tables_kernel(const KernelArgs a, const ClearArgs c)
+{
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nth = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t q = tid; q <= a.NS; q += nth)
+        a.seg_first_leaf[q] = q == 0 ? 0 : q == a.NS ? a.num_leaves
+            : leaf_lower_bound(a.leaf_start, a.num_leaves, q * a.seg_len);
+    for (int64_t i = tid; i < (int64_t)a.B * a.G; i += nth)
+        if (!group_info_valid(a, c.group_info_in[i]))
+            atomicOr(&a.status[status_row(a, i / a.G)], MMS_STATUS_BAD_INDEX);
+    for (int64_t t = tid; t < (int64_t)a.B * (a.M + 1); t += nth) {
+        const int64_t b = t / (a.M + 1);
+        const int m = (int)(t % (a.M + 1));
+        uint32_t e[8] = {kNoReplica, kNoReplica, kNoReplica, kNoReplica,
+                         kNoReplica, kNoReplica, kNoReplica, kNoReplica};
+        if (m < a.M) {
+            const uint32_t lo = a.model_off[(size_t)b * (a.M + 1) + m];
+            const uint32_t hi = a.model_off[(size_t)b * (a.M + 1) + m + 1];
+            bool bad = lo > hi || hi > (uint32_t)a.P;
+            if (!bad) {
+                for (uint32_t r = lo; r < hi; ++r) {
+                    const uint32_t ent = a.model_rep[(size_t)b * a.P + r];
+                    const uint32_t ns = (ent >> 16) & 0xFFu, first = (ent >> 8) & 0xFFu;
+                    if ((ent & 0xFFu) >= (uint32_t)a.G || ns == 0 || first + ns > (uint32_t)a.T ||
+                        ns > (uint32_t)a.S || (ent >> 24) >= (uint32_t)a.C)
+                        bad = true;
+                    else if (r - lo < 8)
+                        e[r - lo] = rep_to_last(ent);
+                }
+                if (hi - lo > 8) e[7] = kMoreReplicas;
+            }
+            if (bad) {
+                atomicOr(&a.status[status_row(a, b)], MMS_STATUS_BAD_INDEX);
+                for (int k = 0; k < 8; ++k) e[k] = kNoReplica;
+            } else if (hi - lo > 1) {
+                // dispatch compares the last-stage clocks of these groups with '<'
+                for (uint32_t r = lo; r < hi; ++r)
+                    atomicOr(&c.group_info[(size_t)b * a.G + (a.model_rep[(size_t)b * a.P + r] & 0xFFu)],
+                             0x10000u);
+            }
+        }
+        uint4 *rows = reinterpret_cast<uint4 *>(a.rep_rows);
+        rows[row_index(a, b, m)] = make_uint4(e[0], e[1], e[2], e[3]);
+        rows[row_plane(a) + row_index(a, b, m)] = make_uint4(e[4], e[5], e[6], e[7]);
+    }
 }
 
 // This lane's view of candidate b: offsets of its shared-memory state (clocks
@@ -201,15 +263,6 @@ sim_stream_kernel(const KernelArgs a)
     if (ln.status) atomicOr(&a.status[status_row(a, b)], ln.status);
 }
 
-// First leaf of every segment, once per call.
-__global__ void seg_leaf_kernel(const KernelArgs a)
-{
-    const int q = blockIdx.x * blockDim.x + threadIdx.x;
-    if (q > a.NS) return;
-    a.seg_first_leaf[q] = q == 0 ? 0 : q == a.NS ? a.num_leaves
-        : leaf_lower_bound(a.leaf_start, a.num_leaves, (int64_t)q * a.seg_len);
-}
-
 // One thread per (array u, chunk j >= 1), u a scored candidate or a mirror:
 // which stored runs of chunk j start from a state that continues the state
 // array u holds at the end of chunk j-1 (states_equivalent: equal futures,
@@ -242,6 +295,24 @@ __global__ void validate_kernel(const KernelArgs a)
             mask |= 1u << r;
     }
     a.compat[(size_t)j * B + u] = (uint16_t)mask;
+}
+
+// Chunk j of candidate b is about to be re-simulated from a NEW start state
+// while an earlier, capped repair of it (from an older start state) is still
+// unfinished: that repair left its own end-of-segment states in the segments it
+// got through, and behind them the records are still those of the speculative
+// run, which it never matched.  The new repair must not settle against those
+// left-over states (it would then keep the unmatched rest), so they are made
+// unequal to everything: a NaN in clock slot 0 fails both "equal" and "in the
+// past".  The segments behind them hold states of runs that go on to the end
+// of the chunk, which a repair may settle against as usual.
+__device__ inline void forget_capped_repair(const KernelArgs &a, int64_t b, int32_t j)
+{
+    const int32_t pending = a.repair_from[(size_t)j * a.B + b];
+    const double nan = __longlong_as_double(0x7FF8000000000000LL);
+    for (int32_t q = j * a.seg_per_chunk; q < pending; ++q)
+        a.seg_end[(size_t)q * a.T * a.B + b] = nan;
+    a.repair_from[(size_t)j * a.B + b] = -1;
 }
 
 // One warp per scored candidate: follows the chain of chunks through the
@@ -286,8 +357,12 @@ __global__ void resolve_kernel(const KernelArgs a)
                 a.repair_from[(size_t)j * B + b] = -1;
             } else {
                 copy_from = e < 0 ? b : e;
-                a.repair_from[(size_t)j * B + b] = -1;         // the whole chunk is redone
-                a.seg_src[(size_t)q0 * B + b] = -1;
+                // The whole chunk is redone.  Its run selection stays as it is until the
+                // repair has compared its state with the selected run's, segment by
+                // segment (run_chunk then makes each segment it ran the candidate's own):
+                // the selected runs of consecutive segments continue one another, which a
+                // selection changed here by hand would not.
+                forget_capped_repair(a, b, j);
                 const uint32_t slot = atomicAdd(&a.work_count[a.round], 1u);
                 a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b);
                 ++redone;
@@ -419,6 +494,7 @@ sim_chain_kernel(const KernelArgs a)
             }
             for (int t = 0; t < a.T; ++t)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
+            forget_capped_repair(a, b, j);
         }
         ++redone;
         run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(a, ln, p, b, j, begin, true, true,
@@ -639,6 +715,53 @@ __global__ void histogram_traces_kernel(const double *arrivals, const int32_t *m
             atomicAdd(&hist[tt * (M + 1) + k % (M + 1)], local[k]);
             if (k % (M + 1) == M) atomicAdd(&hist[(size_t)T * (M + 1)], local[k]);
         }
+    }
+}
+
+// The search's selection over one shard of candidates: the score of
+// base_policy.py:225-226 from the reductions (goodput - latency_mean / 10000 +
+// num_replicas / 1000000, the same fp64 operations in the same order as the
+// host forms it), and the FIRST maximum as np.argmax returns it
+// (model_parallelism.py:349-351).  One block; best = {score, global index as a
+// double}.  With `accumulate` the pair already in `best` competes too (a batch
+// scored in several calls), the smaller index winning a tie.
+constexpr int kArgmaxThreads = 256;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_scores_kernel(const int64_t *good_total, const double *latency_sum,
+                     const int64_t *num_replicas, int64_t N, int32_t B, const int64_t *index_map,
+                     int64_t index_base, bool accumulate, double *best)
+{
+    __shared__ double s_score[kArgmaxThreads];
+    __shared__ double s_index[kArgmaxThreads];
+    double top = -kInf, top_i = 9007199254740992.0;     // 2^53: behind every real index
+    for (int32_t b = threadIdx.x; b < B; b += kArgmaxThreads) {
+        const double n = (double)N;
+        const double goodput = (double)good_total[b] / n;
+        const double latency_mean = latency_sum[b] / n;
+        double score = goodput - latency_mean / 10000.0;
+        if (num_replicas) score = score + (double)num_replicas[b] / 1000000.0;
+        const double idx = (double)(index_base + (index_map ? index_map[b] : (int64_t)b));
+        if (score > top || (score == top && idx < top_i)) { top = score; top_i = idx; }
+    }
+    s_score[threadIdx.x] = top;
+    s_index[threadIdx.x] = top_i;
+    __syncthreads();
+    for (int w = kArgmaxThreads / 2; w > 0; w >>= 1) {
+        if ((int)threadIdx.x < w) {
+            const double o = s_score[threadIdx.x + w], oi = s_index[threadIdx.x + w];
+            if (o > s_score[threadIdx.x] || (o == s_score[threadIdx.x] && oi < s_index[threadIdx.x])) {
+                s_score[threadIdx.x] = o;
+                s_index[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        double sc = s_score[0], si = s_index[0];
+        if (accumulate && (best[0] > sc || (best[0] == sc && best[1] < si))) { sc = best[0]; si = best[1]; }
+        best[0] = sc;
+        best[1] = si;
     }
 }
 

@@ -1020,44 +1020,66 @@ def group_lists(model_off, model_rep, group_info, G):
     return group_off.astype(np.uint16), group_mod, group_cfg
 
 
-def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
-                    latency, latency_stride, batch_sizes, heap_capacity=0, per_request=True):
-    """simulate_requests_mixed_batching (controller.py:630-798) for every
-    candidate.  The kernel always writes per-request outputs (the latency sums
-    are formed from them); per_request=False does not download them."""
-    _require_cuda()
-    L = nat.lib()
-    dev = trace.device
-    N = trace.num_requests
-    res = BatchResult()
-    goff, gmod, gcfg = group_lists(model_off, model_rep, group_info, G)
-    with torch.cuda.device(dev):
-        d_off, d_rep = _to_device(model_off, dev), _to_device(model_rep, dev)
-        d_goff, d_gmod, d_gcfg = (_to_device(x, dev) for x in (goff, gmod, gcfg))
-        d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev)
-        cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), None,
-                               _ptr(d_lat), int(latency_stride))
-        bat = nat.Batching(_ptr(d_goff), _ptr(d_gmod), _ptr(d_gcfg), len(batch_sizes),
-                           int(heap_capacity), (ctypes.c_int32 * 8)(*list(batch_sizes)))
-        need = L.mms_sim_batching_workspace_bytes(N, ctypes.byref(cands), ctypes.byref(bat))
-        ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
-        ws = nat.Workspace(_ptr(ws_t), need)
-        i32 = dict(dtype=torch.int32, device=dev)
-        o_mreq, o_mgood = torch.zeros((B, max(M, 1)), **i32), torch.zeros((B, max(M, 1)), **i32)
-        o_greq, o_ggood = torch.zeros((B, G), **i32), torch.zeros((B, G), **i32)
-        o_total = torch.zeros(B, dtype=torch.int64, device=dev)
-        o_lsum = torch.zeros(B, dtype=torch.float64, device=dev)
-        o_status = torch.zeros(B, **i32)
-        o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev)
-        o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev)
-        o_redo = torch.zeros(B, **i32)
-        out = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood), _ptr(o_total),
-                          _ptr(o_lsum), _ptr(o_status), _ptr(o_fin), _ptr(o_good), _ptr(o_redo))
-        tr, plan = trace.c_trace(), trace.c_plan()
-        rc = L.mms_sim_batching(ctypes.byref(tr), ctypes.byref(cands), ctypes.byref(bat),
-                                _ptr(trace.next_same_model()), ctypes.byref(plan),
-                                ctypes.byref(ws), ctypes.byref(out), _stream_ptr())
-        nat.check(rc, "mms_sim_batching")
+class ResidentBatching:
+    """A placement batch for the batching simulator with its tables, scratch
+    and outputs on the GPU, ready to be launched (any number of times) on the
+    current stream."""
+
+    def __init__(self, trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+                 latency, latency_stride, batch_sizes, heap_capacity=0):
+        _require_cuda()
+        L = nat.lib()
+        dev = trace.device
+        N = trace.num_requests
+        self.trace, self.B, self.M, self.G, self.N = trace, B, M, G, N
+        goff, gmod, gcfg = group_lists(model_off, model_rep, group_info, G)
+        self.h2d_bytes = sum(x.nbytes for x in (model_off, model_rep, goff, gmod, gcfg))
+        with torch.cuda.device(dev):
+            d_off, d_rep = _to_device(model_off, dev), _to_device(model_rep, dev)
+            d_goff, d_gmod, d_gcfg = (_to_device(x, dev) for x in (goff, gmod, gcfg))
+            d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev)
+            self.cands = nat.Placements(B, M, G, P, T, S, C, 0, _ptr(d_off), _ptr(d_rep), None,
+                                        _ptr(d_lat), int(latency_stride))
+            self.bat = nat.Batching(_ptr(d_goff), _ptr(d_gmod), _ptr(d_gcfg), len(batch_sizes),
+                                    int(heap_capacity), (ctypes.c_int32 * 8)(*list(batch_sizes)))
+            need = L.mms_sim_batching_workspace_bytes(N, ctypes.byref(self.cands),
+                                                      ctypes.byref(self.bat))
+            ws_t = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+            self.ws = nat.Workspace(_ptr(ws_t), need)
+            i32 = dict(dtype=torch.int32, device=dev)
+            o_mreq, o_mgood = torch.zeros((B, max(M, 1)), **i32), torch.zeros((B, max(M, 1)), **i32)
+            o_greq, o_ggood = torch.zeros((B, G), **i32), torch.zeros((B, G), **i32)
+            o_total = torch.zeros(B, dtype=torch.int64, device=dev)
+            o_lsum = torch.zeros(B, dtype=torch.float64, device=dev)
+            o_status = torch.zeros(B, **i32)
+            o_fin = torch.empty((B, max(N, 1)), dtype=torch.float64, device=dev)
+            o_good = torch.empty((B, max(N, 1)), dtype=torch.uint8, device=dev)
+            o_redo = torch.zeros(B, **i32)
+            self.res = nat.Results(_ptr(o_mreq), _ptr(o_mgood), _ptr(o_greq), _ptr(o_ggood),
+                                   _ptr(o_total), _ptr(o_lsum), _ptr(o_status), _ptr(o_fin),
+                                   _ptr(o_good), _ptr(o_redo))
+            self.next_same = trace.next_same_model()
+        self.keep = (d_off, d_rep, d_goff, d_gmod, d_gcfg, d_lat, ws_t)
+        self.out = (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_fin, o_good,
+                    o_redo)
+
+    def launch(self):
+        trace = self.trace
+        with torch.cuda.device(trace.device):
+            tr, plan = trace.c_trace(), trace.c_plan()
+            rc = nat.lib().mms_sim_batching(ctypes.byref(tr), ctypes.byref(self.cands),
+                                            ctypes.byref(self.bat), _ptr(self.next_same),
+                                            ctypes.byref(plan), ctypes.byref(self.ws),
+                                            ctypes.byref(self.res), _stream_ptr())
+            nat.check(rc, "mms_sim_batching")
+        return self
+
+    def results(self, per_request=True):
+        """Waits and downloads: (BatchResult, d2h bytes)."""
+        (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_fin, o_good,
+         o_redo) = self.out
+        M, N = self.M, self.N
+        res = BatchResult()
         res.model_num_requests = o_mreq.cpu().numpy()[:, :M]
         res.model_num_good = o_mgood.cpu().numpy()[:, :M]
         res.group_num_requests = o_greq.cpu().numpy()
@@ -1068,6 +1090,22 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
         res.resimulated = o_redo.cpu().numpy()
         res.finish = o_fin.cpu().numpy()[:, :N] if per_request else None
         res.good = o_good.cpu().numpy()[:, :N].astype(bool) if per_request else None
+        d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
+                                     res.group_num_requests, res.group_num_good, res.good_total,
+                                     res.latency_sum, res.status))
+        if per_request:
+            d2h += res.finish.nbytes + res.good.nbytes
+        return res, d2h
+
+
+def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+                    latency, latency_stride, batch_sizes, heap_capacity=0, per_request=True):
+    """simulate_requests_mixed_batching (controller.py:630-798) for every
+    candidate.  The kernel always writes per-request outputs (the latency sums
+    are formed from them); per_request=False does not download them."""
+    job = ResidentBatching(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info, latency,
+                           latency_stride, batch_sizes, heap_capacity).launch()
+    res, _ = job.results(per_request)
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         what = {nat.STATUS_HEAP_OVERFLOW: "event heap overflow (raise heap_capacity)",
@@ -1077,6 +1115,16 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
                            f"candidate {bad}: " + ", ".join(v for k, v in what.items()
                                                             if res.status[bad] & k))
     return res
+
+
+def resident_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
+                      heap_capacity=0) -> ResidentBatching:
+    """ResidentBatching for an encoded batch and a table built with batch sizes."""
+    if table.batch_sizes is None:
+        raise ValueError("the latency table has no batch-size axis")
+    return ResidentBatching(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C,
+                            enc.model_off, enc.model_rep, enc.group_info,
+                            table.device(trace.device), 0, table.batch_sizes, heap_capacity)
 
 
 def run_batch_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,

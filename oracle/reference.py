@@ -1,9 +1,13 @@
-"""Imports the live reference (alpa_serve) for differential tests.
+"""Imports the live reference (alpa_serve) for differential tests and for
+timing the reference's own code.
 
-TEST INFRASTRUCTURE ONLY.  The reference checkout is located through the
-MMS_REFERENCE_DIR environment variable, else ../reference beside the
-repository's parent, and is only ever present on the development machine —
-never on a GPU box, so nothing that runs there may call `load()`.
+TEST INFRASTRUCTURE ONLY.  The reference is looked for, in this order, in the
+directory the MMS_REFERENCE_DIR environment variable names, in a checkout
+called `reference` beside this repository, and in `oracle/_ref` — a private,
+git-ignored copy of the reference's Python package that `make -C oracle ref`
+makes on a machine that has the checkout, so that it travels to machines
+that do not (a GPU box) together with the built libraries.  The package
+`mms_b200` never imports this module.
 `ray` and `matplotlib`, which the reference imports at module level but does
 not use on the simulator path, are replaced by the import-only stubs in
 oracle/stubs.
@@ -18,7 +22,8 @@ _mods = None
 
 def reference_dir():
     cands = [os.environ.get("MMS_REFERENCE_DIR"),
-             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference"),
+             os.path.join(_HERE, "_ref")]
     for c in cands:
         if c and os.path.isdir(os.path.join(c, "alpa_serve")):
             return c
@@ -27,6 +32,21 @@ def reference_dir():
 
 def available():
     return reference_dir() is not None
+
+
+def build_copy():
+    """`make -C oracle ref` when a checkout is at hand (the private copy under
+    oracle/_ref); returns the directory the reference will be imported from,
+    or None."""
+    import subprocess
+    here_copy = os.path.join(_HERE, "_ref")
+    for c in (os.environ.get("MMS_REFERENCE_DIR"),
+              os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if c and os.path.isdir(os.path.join(c, "alpa_serve")):
+            subprocess.run(["make", "-C", _HERE, "ref", f"MMS_REFERENCE_DIR={c}"], check=True,
+                           stdout=subprocess.DEVNULL)
+            return here_copy
+    return reference_dir()
 
 
 def load():
@@ -48,12 +68,15 @@ def load():
     import alpa_serve.simulator.workload as workload
     import alpa_serve.simulator.controller as controller
     import alpa_serve.placement_policy.base_policy as base_policy
+    import alpa_serve.placement_policy.model_parallelism as model_parallelism
+    import alpa_serve.placement_policy.selective_replication as selective_replication
 
     class NS:
         pass
     ns = NS()
     ns.util, ns.profiling, ns.workload = util, profiling, workload
     ns.controller, ns.base_policy = controller, base_policy
+    ns.model_parallelism, ns.selective_replication = model_parallelism, selective_replication
     _mods = ns
     return ns
 

@@ -217,5 +217,62 @@ def main():
     print("golden fixtures written to", HERE)
 
 
+def loop_cases():
+    """The problems the reference's own search loops are run on (here by the
+    pure reference, in tests/test_gpu_reference_loops.py by the same loops on
+    this package's evaluator): name -> (Case, loop label -> how to run it)."""
+    from mms_b200 import search_cases
+    datas16, env16, _ = search_cases.all_cases()["mixed-16"]
+    from mms_b200.placement import gen_train_workload
+    mixed16 = cases.Case("mixed-16", datas16, env16, gen_train_workload(datas16), [])
+    big = cases.greedy_search_case(duration=300.0)
+    return {"mixed-16": mixed16, "search-64": big}
+
+
+def run_reference_loops(ref, case_name, rdatas, renv, rw):
+    """Runs the reference's own loops (whatever PlacementEvaluator the
+    reference modules currently hold) and returns label -> placement."""
+    P = ref.profiling.ParallelConfig
+    MP = ref.base_policy.ModelPlacement
+    out = {}
+    if case_name == "mixed-16":
+        c4 = P(1, 1, 4)
+        start = MP([c4, c4, c4, c4], [[0, 3], [1, 4], [2, 5], []])
+        out["on-last-group"] = ref.base_policy.replica_placement_on_last_group(
+            start, rdatas, renv, rw, None, 3, 0)
+        np.random.seed(7)
+        ev = ref.base_policy.PlacementEvaluator(rdatas, renv, rw, "fast_simulator", False)
+        seed_sol = MP([c4, c4, c4, c4], [[0, 3, 6], [1, 4, 7], [2, 5, 0], [3, 6, 1]])
+        out["evolutionary"] = ref.base_policy.evolutionary_search(
+            [seed_sol], rdatas, renv, ev, 2, 0)
+    policy = ref.model_parallelism.ModelParallelismSearch(max_op=1)
+    out["mp-search-max-op-1"] = policy.solve_placement(rdatas, renv, rw)[0]
+    return out
+
+
+def placement_lists(placement):
+    return {"group_configs": [list(map(int, c)) for c in placement.group_configs],
+            "group_models": [[int(m) for m in ms] for ms in placement.group_models]}
+
+
+def reference_loops():
+    """reference_loops.json: what replica_placement_on_last_group
+    (base_policy.py:482), evolutionary_search (:623) and
+    ModelParallelismSearch.solve_placement (model_parallelism.py:411) return
+    when they run on the reference's own evaluator."""
+    import json
+    ref = reference.load()
+    out = {}
+    for name, case in loop_cases().items():
+        rdatas, renv, rw, _ = reference.to_reference_case(case)
+        for label, placement in run_reference_loops(ref, name, rdatas, renv, rw).items():
+            out[f"{name}/{label}"] = placement_lists(placement)
+            print(name, label, out[f"{name}/{label}"]["group_models"])
+    with open(os.path.join(HERE, "reference_loops.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 if __name__ == "__main__":
-    main()
+    if "--only-loops" not in sys.argv:
+        main()
+    reference_loops()

@@ -171,6 +171,64 @@ def test_results_do_not_depend_on_chunking(loaded, chunk, run_in, rounds, cap, c
         assert res.latency_sum[b] == float(np.add.reduce(fin - arr))
 
 
+@pytest.mark.parametrize("cap", [1, 2])
+@pytest.mark.parametrize("rounds", [1, 2, 4])
+def test_capped_repairs_under_sustained_overload(loaded, cap, rounds):
+    """Repairs that are cut off after `cap` segments per round and resumed —
+    or started over, when the chunk before them changed in the same round —
+    on a trace that keeps a few groups busy without a break for whole
+    segments while the others heal: every cut gives the sequential result.
+    Short chunks of three segments after a run-in of 64 requests make nearly
+    every boundary fail; with mirrors and without."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import PlacementEvaluator
+    from mms_b200.simulator import workload_arrays
+    from oracle import tables
+    case = cases.candidate_batch_case(num_candidates=24, duration=240.0, placement_seed=21,
+                                      total_rate=170.0, cv=2.0)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            options=engine.sim_options(3072, 64, rounds, cap))
+    enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    arr = case.workload.arrivals
+    want = [tables.one_placement(p, profs, mids, slos, arr) for p in case.placements]
+    overloaded = np.mean([np.mean(w[1]) for w in want])
+    assert 0.2 < overloaded < 0.9                  # a good part of the requests is dropped
+    for mirrors in (False, True):
+        res, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True,
+                                     options=ev.options, mirrors=mirrors)
+        assert res.resimulated.sum() > 24          # the repair path really ran
+        for b, (fin, good, mreq, mgood, greq, ggood) in enumerate(want):
+            assert res.good_total[b] == np.count_nonzero(good), (b, mirrors)
+            assert res.latency_sum[b] == float(np.add.reduce(fin - arr)), (b, mirrors)
+            assert np.array_equal(res.model_num_good[b], mgood), (b, mirrors)
+            assert np.array_equal(res.group_num_requests[b, :len(greq)], greq), (b, mirrors)
+            assert np.array_equal(res.group_num_good[b, :len(ggood)], ggood), (b, mirrors)
+
+
+def test_contested_bit_of_group_info_is_not_trusted(loaded):
+    """group_info bit 16 (the group serves a model with several replicas) is
+    derived on the device: a caller that leaves it clear gets the same
+    results as one that sets it."""
+    from mms_b200 import cases, engine
+    from mms_b200.placement import PlacementEvaluator
+    case = cases.candidate_batch_case(num_candidates=64, duration=600.0, placement_seed=4)
+    ev = PlacementEvaluator(case.model_datas, case.cluster_env, case.workload,
+                            options=engine.sim_options(4096, 256))
+    enc = engine.encode_placements(case.placements, ev.table, len(ev.model_names))
+    with_bit, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True,
+                                      options=ev.options, mirrors=False)
+    assert np.any(enc.group_info & 0x10000)
+    enc.group_info = enc.group_info & ~np.uint32(0x10000)
+    without, _, _ = engine.run_batch(ev.trace, enc, ev.table, group_good=True,
+                                     options=ev.options, mirrors=False)
+    for name in ("good_total", "latency_sum", "model_num_good", "group_num_requests",
+                 "group_num_good"):
+        assert getattr(with_bit, name).tobytes() == getattr(without, name).tobytes(), name
+
+
 def test_unsorted_trace_falls_back_to_one_chunk(loaded):
     from mms_b200 import simulator
     from oracle import cpu
@@ -518,6 +576,38 @@ def test_split_launch_equals_one_launch(loaded, monkeypatch):
                  "good_total", "latency_sum", "status"):
         assert getattr(first, name).tobytes() == getattr(one, name).tobytes(), name
         assert getattr(again, name).tobytes() == getattr(one, name).tobytes(), name
+
+
+def test_plain_placement_through_approximate_one_case(loaded, golden):
+    """approximate_one_case with a single ModelPlacement
+    (controller.py:341-344) and fast_stats, on the fixed 4 x pp2 case at full
+    size: the StatsResult carries what the reference computed."""
+    from functools import partial
+    from mms_b200 import cases, simulator
+    g = golden("case_fixed_pipeline")
+    case = cases.fixed_pipeline_case()
+    w = case.workload
+    w.cached_data = None
+
+    def register_models(controller):
+        for d in case.model_datas:
+            controller.register_model.remote(d.name, partial(object, d.profiling_result))
+
+    serving = (register_models, lambda start=0: w, lambda controller: case.placements[0])
+    stats, placement = simulator.approximate_one_case(serving, fast_stats=True)
+    assert placement is case.placements[0]
+    assert stats.goodput == float(g["goodput"])
+    assert stats.latency_mean == float(g["latency_mean"])
+    assert stats.num_requests == int(g["num_requests"])
+    assert isinstance(stats.group_num_requests, tuple)
+    assert np.array_equal(np.array(stats.group_num_requests), g["group_num_requests"])
+    mreq, mgood = g["model_num_requests"], g["model_num_good"]
+    for i, pm in enumerate(stats.per_model_stats):
+        assert pm.num_requests == mreq[i]
+        assert pm.goodput == mgood[i] / (mreq[i] + 1e-6)
+    # the second call takes the cached arrays (controller.py:323-327), same result
+    again, _ = simulator.approximate_one_case(serving, fast_stats=True)
+    assert again.goodput == stats.goodput and again.latency_mean == stats.latency_mean
 
 
 @pytest.mark.parametrize("fast", [True, False])

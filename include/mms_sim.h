@@ -225,6 +225,17 @@ int mms_sum_plan_fill(int64_t num_requests, int32_t *leaf_start /*host*/,
 int mms_trace_model_histogram(const mms_trace *trace, int32_t num_models,
                               int32_t *hist, void *stream);
 
+/* Builds the request-major trace batch (an mms_trace with num_traces > 1) on the
+ * device from T traces stored one after the other, as a caller has them when it
+ * uploads each workload's cached arrays (controller.py:335-339) as they are:
+ * trace t is elements [offsets[t], offsets[t+1]) of arrivals / model_ids / slos
+ * (offsets: i64[T+1], device).  out_*: [padded_requests][T]; traces shorter
+ * than padded_requests (>= the longest) are padded as mms_trace describes.
+ * Nothing in the reference corresponds (it simulates one trace per call). */
+int mms_trace_pack(const double *arrivals, const int32_t *model_ids, const float *slos,
+                   const int64_t *offsets, int64_t num_traces, int64_t padded_requests,
+                   double *out_arrivals, int32_t *out_model_ids, float *out_slos, void *stream);
+
 /* Bytes of scratch mms_sim_mixed needs for this shape and these options. */
 size_t mms_sim_workspace_bytes(int64_t num_requests, const mms_placements *cands,
                                const mms_sim_options *opts, uint32_t flags);

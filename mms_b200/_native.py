@@ -60,6 +60,7 @@ EXPORTS = (
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
     "mms_sim_mixed_static", "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
     "mms_profile_begin", "mms_profile_end", "mms_argmax_scores",
+    "mms_trace_pack",
 )
 
 _vp = ctypes.c_void_p
@@ -173,6 +174,9 @@ def lib():
     L.mms_argmax_scores.restype = ctypes.c_int
     L.mms_argmax_scores.argtypes = [_vp, _vp, _vp, ctypes.c_int64, ctypes.c_int32, _vp,
                                     ctypes.c_int64, ctypes.c_int32, _vp, _vp]
+    L.mms_trace_pack.restype = ctypes.c_int
+    L.mms_trace_pack.argtypes = [_vp, _vp, _vp, _vp, ctypes.c_int64, ctypes.c_int64, _vp, _vp, _vp,
+                                 _vp]
     L.mms_trace_next_same_model.restype = ctypes.c_int
     L.mms_trace_next_same_model.argtypes = [ctypes.POINTER(Trace), ctypes.c_int32, _vp, _vp]
     L.mms_sim_batching_workspace_bytes.restype = ctypes.c_size_t

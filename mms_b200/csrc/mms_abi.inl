@@ -541,6 +541,24 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
 
 extern "C" {
 
+int mms_trace_pack(const double *arrivals, const int32_t *model_ids, const float *slos,
+                   const int64_t *offsets, int64_t num_traces, int64_t padded_requests,
+                   double *out_arrivals, int32_t *out_model_ids, float *out_slos, void *stream)
+{
+    if (num_traces < 0 || padded_requests < 0) return MMS_ERR_ARG;
+    if (num_traces == 0 || padded_requests == 0) return MMS_OK;
+    if (!arrivals || !model_ids || !slos || !offsets || !out_arrivals || !out_model_ids || !out_slos)
+        return MMS_ERR_ARG;
+    const int64_t bx = (padded_requests + 31) / 32, by = (num_traces + 31) / 32;
+    if (bx > 0x7FFFFFFF || by > 65535) return MMS_ERR_UNSUPPORTED;
+    mms::pack_traces_kernel<<<dim3((unsigned)bx, (unsigned)by), dim3(32, 8), 0,
+                              (cudaStream_t)stream>>>(arrivals, model_ids, slos, offsets,
+                                                      num_traces, padded_requests, out_arrivals,
+                                                      out_model_ids, out_slos);
+    MMS_CUDA(cudaGetLastError());
+    return MMS_OK;
+}
+
 int mms_argmax_scores(const int64_t *good_total, const double *latency_sum,
                       const int64_t *num_replicas, int64_t num_requests, int32_t num_candidates,
                       const int64_t *index_map, int64_t index_base, int32_t accumulate,

@@ -718,6 +718,44 @@ __global__ void histogram_traces_kernel(const double *arrivals, const int32_t *m
     }
 }
 
+// T traces given one after the other (trace t = elements [offsets[t],
+// offsets[t + 1]) of the three arrays) -> the request-major batch the kernels
+// read ([N][T], see mms_trace.num_traces), shorter traces padded with requests
+// of model -1 that repeat the trace's last arrival time.  A block moves a tile
+// of 32 requests x 32 traces through shared memory, so that both the reads
+// (along a trace) and the writes (across traces) are coalesced.
+__global__ void __launch_bounds__(32 * 8)
+pack_traces_kernel(const double *arrivals, const int32_t *model_ids, const float *slos,
+                   const int64_t *offsets, int64_t T, int64_t N, double *out_arrivals,
+                   int32_t *out_model_ids, float *out_slos)
+{
+    __shared__ double s_arr[32][33];
+    __shared__ int32_t s_mid[32][33];
+    __shared__ float s_slo[32][33];
+    const int64_t i0 = (int64_t)blockIdx.x * 32, t0 = (int64_t)blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += 8) {          // row r of the tile: trace t0 + r
+        const int64_t t = t0 + r, i = i0 + threadIdx.x;
+        double a = 0.0;
+        int32_t m = -1;
+        float s = 0.0f;
+        if (t < T) {
+            const int64_t lo = offsets[t], n = offsets[t + 1] - lo;
+            if (i < n) { a = arrivals[lo + i]; m = model_ids[lo + i]; s = slos[lo + i]; }
+            else if (n > 0) a = arrivals[lo + n - 1];
+        }
+        s_arr[r][threadIdx.x] = a; s_mid[r][threadIdx.x] = m; s_slo[r][threadIdx.x] = s;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += 8) {          // request i0 + r, trace t0 + threadIdx.x
+        const int64_t i = i0 + r, t = t0 + threadIdx.x;
+        if (i < N && t < T) {
+            out_arrivals[i * T + t] = s_arr[threadIdx.x][r];
+            out_model_ids[i * T + t] = s_mid[threadIdx.x][r];
+            out_slos[i * T + t] = s_slo[threadIdx.x][r];
+        }
+    }
+}
+
 // The search's selection over one shard of candidates: the score of
 // base_policy.py:225-226 from the reductions (goodput - latency_mean / 10000 +
 // num_replicas / 1000000, the same fp64 operations in the same order as the

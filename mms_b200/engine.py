@@ -112,6 +112,8 @@ class DeviceTraceBatch:
     are stored request-major ([N][T]: the 32 candidates of a warp read
     consecutive addresses) and padded to the longest one with requests of
     model -1 at the last arrival time, which change no clock and no counter.
+    The host uploads every trace as it is, one after the other; the
+    request-major batch is made on the device (mms_trace_pack).
     Duck-type compatible with DeviceTrace where launches are concerned."""
 
     def __init__(self, arrivals: Sequence, model_ids: Sequence, slos: Sequence, num_models: int,
@@ -123,24 +125,36 @@ class DeviceTraceBatch:
         if T == 0 or not (len(model_ids) == len(slos) == T):
             raise ValueError("need one (arrivals, model_ids, slos) triple per trace")
         self.lengths = np.fromiter((len(a) for a in arrivals), np.int64, T)
-        N = int(self.lengths.max())
-        self.num_traces, self.num_requests, self.num_models = T, N, int(num_models)
-        arr = np.zeros((N, T), np.float64)
-        mid = np.full((N, T), -1, np.int32)
-        slo = np.zeros((N, T), np.float32)
         for t in range(T):
-            n = int(self.lengths[t])
-            if not (len(model_ids[t]) == len(slos[t]) == n):
+            if not (len(model_ids[t]) == len(slos[t]) == int(self.lengths[t])):
                 raise ValueError(f"trace {t}: arrays differ in length")
-            arr[:n, t], mid[:n, t], slo[:n, t] = arrivals[t], model_ids[t], slos[t]
-            if n:
-                arr[n:, t] = arrivals[t][n - 1]
-        self.h2d_bytes = arr.nbytes + mid.nbytes + slo.nbytes
+        N = int(self.lengths.max())
+        total = int(self.lengths.sum())
+        self.num_traces, self.num_requests, self.num_models = T, N, int(num_models)
+        offsets = np.concatenate(([0], np.cumsum(self.lengths))).astype(np.int64)
+        self.h2d_bytes = total * 16 + offsets.nbytes
         L = nat.lib()
-        with torch.cuda.device(self.device):
-            self.arrivals = _to_device(arr, self.device)
-            self.model_ids = _to_device(mid, self.device)
-            self.slos = _to_device(slo, self.device)
+        dev = self.device
+        with torch.cuda.device(dev):
+            cat_arr = torch.empty(max(total, 1), dtype=torch.float64, device=dev)
+            cat_mid = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
+            cat_slo = torch.empty(max(total, 1), dtype=torch.float32, device=dev)
+            for t in range(T):
+                lo, hi = int(offsets[t]), int(offsets[t + 1])
+                if hi > lo:
+                    cat_arr[lo:hi].copy_(torch.from_numpy(
+                        np.ascontiguousarray(arrivals[t], np.float64)), non_blocking=True)
+                    cat_mid[lo:hi].copy_(torch.from_numpy(
+                        np.ascontiguousarray(model_ids[t], np.int32)), non_blocking=True)
+                    cat_slo[lo:hi].copy_(torch.from_numpy(
+                        np.ascontiguousarray(slos[t], np.float32)), non_blocking=True)
+            d_off = _to_device(offsets, dev)
+            self.arrivals = torch.empty((max(N, 1), T), dtype=torch.float64, device=dev)
+            self.model_ids = torch.empty((max(N, 1), T), dtype=torch.int32, device=dev)
+            self.slos = torch.empty((max(N, 1), T), dtype=torch.float32, device=dev)
+            nat.check(L.mms_trace_pack(_ptr(cat_arr), _ptr(cat_mid), _ptr(cat_slo), _ptr(d_off),
+                                       T, N, _ptr(self.arrivals), _ptr(self.model_ids),
+                                       _ptr(self.slos), _stream_ptr()), "mms_trace_pack")
             n_leaves = L.mms_sum_plan_leaves(N)
             if n_leaves < 0:
                 nat.check(n_leaves, "mms_sum_plan_leaves")
@@ -149,11 +163,11 @@ class DeviceTraceBatch:
             nat.check(L.mms_sum_plan_fill(N, leaf_start.ctypes.data, leaf_merges.ctypes.data),
                       "mms_sum_plan_fill")
             self.num_leaves = n_leaves
-            self.leaf_start = _to_device(leaf_start, self.device)
-            self.leaf_merges = _to_device(leaf_merges, self.device)
+            self.leaf_start = _to_device(leaf_start, dev)
+            self.leaf_merges = _to_device(leaf_merges, dev)
             # [T][M + 1] counts, then the total of unsorted positions (T == 1: plain [M + 1])
             cells = T * (self.num_models + 1) + (1 if T > 1 else 0)
-            self.model_hist = torch.zeros(cells, dtype=torch.int32, device=self.device)
+            self.model_hist = torch.zeros(cells, dtype=torch.int32, device=dev)
             tr = self.c_trace()
             nat.check(L.mms_trace_model_histogram(ctypes.byref(tr), self.num_models,
                                                   _ptr(self.model_hist), _stream_ptr()),

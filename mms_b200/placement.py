@@ -229,15 +229,113 @@ class PlacementEvaluator:
         return out
 
 
+def length_groups(lengths, slack=1.125, min_group=32):
+    """Cuts traces into groups of similar length (each at most `slack` times
+    as long as the group's shortest, unless that leaves fewer than
+    `min_group`), so that padding every group to its longest trace adds
+    little: a list of index arrays, each ascending in length."""
+    order = np.argsort(np.asarray(lengths), kind="stable")
+    groups, cur = [], []
+    for t in order.tolist():
+        if cur and lengths[t] > slack * max(lengths[cur[0]], 1) and len(cur) >= min_group:
+            groups.append(np.asarray(cur, np.int64))
+            cur = []
+        cur.append(t)
+    if cur:
+        groups.append(np.asarray(cur, np.int64))
+    return groups
+
+
+class ResidentSweep:
+    """The traces of a sweep on the GPU, grouped by length, every group ready to
+    be launched (any number of times) on a stream of its own."""
+
+    def __init__(self, sweep, workloads, cells):
+        import torch
+        self.sweep = sweep
+        self.T = len(workloads)
+        M = len(sweep.model_names)
+        dev = sweep.device if sweep.device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self.device = torch.device(dev)
+        arrays = sweep._arrays(workloads)
+        lengths = np.array([len(w.arrivals) for w in workloads], np.int64)
+        self.lengths = lengths
+        self.groups = length_groups(lengths)
+        self.h2d_bytes = 0
+        self.jobs, self.streams, self.meta = [], [], []
+        for idx in self.groups:
+            traces = engine.DeviceTraceBatch([workloads[t].arrivals for t in idx],
+                                             [arrays[t][0] for t in idx],
+                                             [arrays[t][1] for t in idx], M, device=self.device)
+            job = engine.ResidentBatch(traces, sweep.enc.repeat(len(idx)), sweep.table,
+                                       options=sweep.options, split=False)
+            self.h2d_bytes += traces.h2d_bytes + job.h2d_bytes
+            self.jobs.append(job)
+            self.streams.append(torch.cuda.Stream(device=self.device))
+            cell = torch.from_numpy(((sweep.first_trace + idx) % cells).astype(np.int64)).to(
+                self.device)
+            n = torch.from_numpy(lengths[idx]).to(self.device)
+            self.meta.append((cell, n))
+        self.cells = cells
+        # per cell: good requests, requests, traces (integers: the sums do not depend on order)
+        self.tally = torch.zeros((cells, 3), dtype=torch.int64, device=self.device)
+
+    def launch(self):
+        """Simulates every group (each on its own stream, all joined behind the
+        current one) and tallies per cell; returns the tally tensor."""
+        import torch
+        main = torch.cuda.current_stream(self.device)
+        self.tally.zero_()
+        for job, side in zip(self.jobs, self.streams):
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                job.launch()
+        for side in self.streams:
+            main.wait_stream(side)
+        for job, (cell, n) in zip(self.jobs, self.meta):
+            for j in job.jobs:
+                j.stream = main
+            good = job.device_outputs()[0][1]
+            self.tally.index_add_(0, cell, torch.stack(
+                (good, n, torch.ones_like(n)), dim=1))
+        return self.tally
+
+    def results(self):
+        """BatchResult over all traces in the order they were given."""
+        parts = [job.results()[0] for job in self.jobs]
+        res = engine.BatchResult()
+        for name in engine.BatchResult.__slots__:
+            first = getattr(parts[0], name)
+            if first is None:
+                setattr(res, name, None)
+                continue
+            whole = np.zeros((self.T,) + first.shape[1:], first.dtype)
+            for idx, part in zip(self.groups, parts):
+                whole[idx] = getattr(part, name)
+            setattr(res, name, whole)
+        self.d2h_bytes = sum(int(getattr(p, n).nbytes) for p in parts
+                             for n in ("model_num_requests", "model_num_good",
+                                       "group_num_requests", "good_total", "status"))
+        return res
+
+    def release(self):
+        for job in self.jobs:
+            job.release()
+        self.jobs = []
+
+
 class TraceSweep:
     """One placement scored on many traces — the robustness sweeps that call
     `approximate_one_case(..., fast_stats=True)` once per trace
     (alpa_serve/simulator/controller.py:308-407) — with the traces as the
-    batch: `batch` of them are uploaded side by side and simulated in one
-    launch, every GPU thread running the placement on a trace of its own."""
+    batch: they are uploaded as they are, grouped by length, and every group
+    is simulated in one launch, every GPU thread running the placement on a
+    trace of its own.  Trace t belongs to cell (first_trace + t) mod cells of
+    the sweep's grid; `evaluate_tally` also returns the per-cell sums."""
 
     def __init__(self, model_datas, cluster_env, placement: ModelPlacement, device=None,
-                 options=None, batch: int = 256):
+                 options=None, batch: int = 4096, cells: int = 1, first_trace: int = 0):
         self.model_datas = model_datas
         self.cluster_env = cluster_env
         self.placement = placement
@@ -247,24 +345,54 @@ class TraceSweep:
         self.device = device
         self.options = options
         self.batch = int(batch)
+        self.cells = int(cells)
+        self.first_trace = int(first_trace)
+        self.last_h2d_bytes = self.last_d2h_bytes = 0
+
+    def _arrays(self, workloads):
+        """(model_ids, slos) of every workload; numpy does the work outside the
+        interpreter lock, so a few threads share it."""
+        from concurrent.futures import ThreadPoolExecutor
+        import os
+        if len(workloads) < 8:
+            return [workload_arrays(w, self.model_names) for w in workloads]
+        with ThreadPoolExecutor(min(16, os.cpu_count() or 1)) as pool:
+            return list(pool.map(lambda w: workload_arrays(w, self.model_names), workloads))
+
+    def resident(self, workloads: Sequence[Workload]) -> ResidentSweep:
+        return ResidentSweep(self, workloads, self.cells)
+
+    def evaluate_tally(self, workloads: Sequence[Workload]):
+        """(per-trace results as `evaluate` returns them, per-cell tally i64[cells][3] =
+        good requests, requests, traces — on the device)."""
+        out = []
+        tally = None
+        self.last_h2d_bytes = self.last_d2h_bytes = 0
+        g = int(self.enc.num_groups[0])
+        for lo in range(0, len(workloads), self.batch):
+            part = workloads[lo:lo + self.batch]
+            first = self.first_trace
+            self.first_trace = first + lo
+            try:
+                run = ResidentSweep(self, part, self.cells)
+            finally:
+                self.first_trace = first
+            t = run.launch().clone()
+            tally = t if tally is None else tally + t
+            res = run.results()
+            engine._check_status(res)
+            self.last_h2d_bytes += run.h2d_bytes
+            self.last_d2h_bytes += run.d2h_bytes
+            run.release()
+            for k in range(len(part)):
+                n = int(run.lengths[k])
+                goodput = float(res.good_total[k]) / n if n else 0.0
+                per_model = res.model_num_good[k] / (res.model_num_requests[k] + eps)
+                out.append((goodput, per_model, tuple(res.group_num_requests[k, :g])))
+        return out, tally
 
     def evaluate(self, workloads: Sequence[Workload]):
         """Per trace: (goodput, per-model goodput, group_num_requests), with
         goodput = np.mean(good) and per-model goodput = good / (requests + eps)
         as in fast_stats (controller.py:393-403)."""
-        out = []
-        M = len(self.model_names)
-        for lo in range(0, len(workloads), self.batch):
-            part = workloads[lo:lo + self.batch]
-            arrays = [workload_arrays(w, self.model_names) for w in part]
-            traces = engine.DeviceTraceBatch([w.arrivals for w in part], [a[0] for a in arrays],
-                                             [a[1] for a in arrays], M, device=self.device)
-            res, _, _ = engine.run_batch(traces, self.enc.repeat(len(part)), self.table,
-                                         options=self.options)
-            g = int(self.enc.num_groups[0])
-            for t in range(len(part)):
-                n = int(traces.lengths[t])
-                goodput = float(res.good_total[t]) / n if n else 0.0
-                per_model = res.model_num_good[t] / (res.model_num_requests[t] + eps)
-                out.append((goodput, per_model, tuple(res.group_num_requests[t, :g])))
-        return out
+        return self.evaluate_tally(workloads)[0]

@@ -83,3 +83,53 @@ def score(placement, finish, good, arrivals):
     latency_mean = np.float64(cpu.pairwise_sum(finish - arrivals)) / n
     replicas = sum(len(x) for x in placement.group_models)
     return goodput - latency_mean / 10000 + replicas / 1000000
+
+
+def dense_tables_batch(placements, prof_ress):
+    """dense_tables for a list of placements, stacked and padded to the
+    widest: (m2g i32[B][M][G], num_stages i32[B][G] (1 where there is no
+    group), lat f32[B][M][G][S] (+inf where there is no group)).  The f32
+    latency row of a (model, parallel config) pair is computed once, with the
+    operations of controller.py:467-476, and copied to every group that has
+    that config."""
+    B, M = len(placements), len(prof_ress)
+    G = max([len(p.group_configs) for p in placements] + [1])
+    S = max([int(c.pp) for p in placements for c in p.group_configs] + [1])
+    m2g = np.full((B, M, G), -1, np.int32)
+    ns = np.ones((B, G), np.int32)
+    lat = np.full((B, M, G, S), np.float32(np.inf), np.float32)
+    rows = {}
+
+    def config_rows(c):
+        key = tuple(c)
+        if key not in rows:
+            tab = np.zeros((M, S), np.float32)
+            with np.errstate(over="ignore"):
+                for m in range(M):
+                    v = prof_ress[m].para_dict.get(c, None)
+                    if v:
+                        pen = 0.009 * len(v.latency[1])
+                        for k in range(int(c.pp)):
+                            tab[m][k] = v.latency[1][k] * (1 + pen)
+                    else:
+                        tab[m][:] = inf
+            rows[key] = tab
+        return rows[key]
+
+    for b, p in enumerate(placements):
+        fill = [0] * M
+        for g, (c, ms) in enumerate(zip(p.group_configs, p.group_models)):
+            ns[b, g] = c.pp
+            lat[b, :, g, :] = config_rows(c)
+            for m in ms:
+                m2g[b, m, fill[m]] = g
+                fill[m] += 1
+    return m2g, ns, lat
+
+
+def score_from_sums(placement, good_total, latency_sum, n):
+    """base_policy.py:225-226 from the reductions np.mean is made of."""
+    goodput = np.float64(int(good_total)) / n
+    latency_mean = np.float64(latency_sum) / n
+    replicas = sum(len(x) for x in placement.group_models)
+    return goodput - latency_mean / 10000 + replicas / 1000000

@@ -508,6 +508,11 @@ def run_candidates(args, D):
     chain_ms = span_ms[span_tag == nat.PROFILE_CHAIN]
     stream_kernel_ms = float(np.mean(stream_ms[big::per_step])) if len(stream_ms) else float("nan")
     chain_kernel_ms = float(np.max(chain_ms)) if len(chain_ms) else 0.0
+    call_ms = span_ms[span_tag == nat.PROFILE_CALL]
+    call_ms_by_launch = [round(float(np.mean(call_ms[k::per_step])), 3) for k in range(per_step)]
+    stream_ms_by_launch = [round(float(np.mean(stream_ms[k::per_step])), 3) for k in range(per_step)]
+    chain_ms_by_launch = [round(float(np.mean(chain_ms[k::per_step])), 3) for k in range(per_step)] \
+        if len(chain_ms) == len(stream_ms) else []
     kernel_units = resident.jobs[big].Bs * N
     total_ms = D.reduce(sum(times), "max")
     by_rank = [round(float(x), 3) for x in D.gather([float(np.mean(own_times))])[:, 0]]
@@ -609,6 +614,10 @@ def run_candidates(args, D):
                          "kernel_candidates": int(resident.jobs[big].Bs),
                          "kernel_launches_timed": int(len(stream_ms)) // per_step,
                          "chain_kernel_ms_max": chain_kernel_ms,
+                         # per launch of a step, in launch order (they overlap on the GPU)
+                         "call_ms_by_launch": call_ms_by_launch,
+                         "stream_kernel_ms_by_launch": stream_ms_by_launch,
+                         "chain_kernel_ms_by_launch": chain_ms_by_launch,
                          "whole_call": {"achieved": call_achieved, "frac": call_achieved / peak,
                                         "ms": float(np.mean(times))},
                          "peak_source": which, "bytes_per_unit": BYTES_PER_UNIT,

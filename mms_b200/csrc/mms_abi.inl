@@ -43,7 +43,8 @@ struct Geometry {
         block_warps, narrow_limit, lat_f64;
     size_t smem_stream, smem_repair;
     size_t off_leaf, off_seg_end, off_chunk_start, off_decisions, off_work_count, off_work_items,
-        off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf, off_group_info;
+        off_repair_from, off_rows, off_seg_src, off_compat, off_seg_leaf, off_group_info,
+        off_own_rewritten;
     size_t smem_count;        // shared memory of count_kernel
     size_t total;
 };
@@ -197,6 +198,7 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
     g->off_compat = off;      off += align256(sizeof(uint16_t) * (size_t)K * B);
     g->off_seg_leaf = off;    off += align256(sizeof(int32_t) * (size_t)(NS + 1));
     g->off_group_info = off;  off += align256(sizeof(uint32_t) * (size_t)B * c->max_groups + 4);
+    g->off_own_rewritten = off; off += align256((size_t)K * B + 4);
     g->off_seg_end = off;     off += K > 1 ? align256(sizeof(double) * (size_t)NS * c->max_slots * B) : 0;
     g->off_chunk_start = off; off += K > 1 ? align256(sizeof(double) * (size_t)K * c->max_slots * B) : 0;
     g->total = off;
@@ -484,6 +486,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ka.repair_from = (int32_t *)(scratch + g.off_repair_from);
     ka.seg_src = (int32_t *)(scratch + g.off_seg_src);
     ka.compat = (uint16_t *)(scratch + g.off_compat);
+    ka.own_rewritten = (uint8_t *)(scratch + g.off_own_rewritten);
     ka.seg_first_leaf = (int32_t *)(scratch + g.off_seg_leaf);
     ka.repair_cap = g.repair_cap;
     ka.narrow_limit = g.narrow_limit;
@@ -501,6 +504,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
     ca.group_num_good = gg ? out->group_num_good : nullptr;
     ca.good_total = out->good_total;
     ka.group_info = ca.group_info;       // the checked copy, contested bits derived on the device
+    ProfileSpan call_span(MMS_PROFILE_CALL, st);
     const bool legacy = (flags & MMS_FLAG_LEGACY_CLOCK) != 0;
     const int variant = (full ? 4 : 0) | (gg ? 2 : 0) | (legacy ? 1 : 0);
     switch (variant) {
@@ -534,6 +538,7 @@ int mms_sim_mixed(const mms_trace *trace, const mms_placements *cands, const mms
         model_requests_kernel<<<(unsigned)((cells + 127) / 128), 128, 0, st>>>(ka, out->model_num_requests);
         MMS_CUDA(cudaGetLastError());
     }
+    call_span.stop();
     return MMS_OK;
 }
 

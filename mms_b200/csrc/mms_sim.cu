@@ -88,7 +88,10 @@ __global__ void clear_kernel(const KernelArgs a, const ClearArgs c)
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nth = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = tid; i < (int64_t)a.NS * a.B; i += nth) a.seg_src[i] = -1;
-    for (int64_t i = tid; i < (int64_t)a.K * a.B; i += nth) a.repair_from[i] = -1;
+    for (int64_t i = tid; i < (int64_t)a.K * a.B; i += nth) {
+        a.repair_from[i] = -1;
+        a.own_rewritten[i] = 0;
+    }
     for (int64_t i = tid; i < (int64_t)a.B * a.G; i += nth) {
         const uint32_t info = c.group_info_in[i];
         c.group_info[i] = group_info_valid(a, info) ? (info & ~0x10000u) : 0u;
@@ -351,6 +354,11 @@ __global__ void resolve_kernel(const KernelArgs a)
                     a.work_items[slot] = (uint32_t)((int64_t)j * a.B + b) | 0x80000000u;
                     settled = false;
                 }
+            } else if (s0 >= 0 && (mask & 1u) && !a.own_rewritten[(size_t)j * B + b]) {
+                // a mirror's run was selected, but it is the candidate's own speculative
+                // run — untouched so far — that continues the chunk before
+                for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * B + b] = -1;
+                a.repair_from[(size_t)j * B + b] = -1;
             } else if (mask >> 1) {
                 const int32_t v = (int32_t)m_first + (__ffs((int)(mask >> 1)) - 1);
                 for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * B + b] = v;
@@ -421,9 +429,11 @@ sim_repair_kernel(const KernelArgs a)
     const int32_t first = a.leaf_start[seg_leaf(a, q_begin)];
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
+    const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
+    a.own_rewritten[(size_t)j * a.B + b] = 1;
     a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(
         a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
-        a.repair_cap, ~0ull, m_first, m_end);
+        a.repair_cap, ~0ull, m_first, m_end, own_pure);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
@@ -485,6 +495,11 @@ sim_chain_kernel(const KernelArgs a)
             for (int t = 0; t < a.T; ++t)
                 SM_F64(ln.clk + t * kLanes) = a.seg_end[((size_t)(q_begin - 1) * a.T + t) * a.B + b];
         } else {
+            const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
+            if (s0 >= 0 && own_pure && continues(b)) {     // back to the own speculative run
+                for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * a.B + b] = -1;
+                continue;
+            }
             int64_t found = -1;
             for (int64_t m = m_first; m < m_end && found < 0; ++m)
                 if (m != s0 && continues(m)) found = m;
@@ -497,9 +512,11 @@ sim_chain_kernel(const KernelArgs a)
             forget_capped_repair(a, b, j);
         }
         ++redone;
+        const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
+        a.own_rewritten[(size_t)j * a.B + b] = 1;
         run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(a, ln, p, b, j, begin, true, true,
                                                        old_state, stale_buf, q_begin, 0, ~0ull,
-                                                       m_first, m_end);
+                                                       m_first, m_end, own_pure);
         a.repair_from[(size_t)j * a.B + b] = -1;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);

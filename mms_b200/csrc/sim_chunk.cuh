@@ -62,6 +62,9 @@ struct KernelArgs {
     int32_t *repair_from;         // [K][B]: segment a capped repair of chunk j stopped at, or -1
     int32_t *seg_src;             // [NS][B]: whose run of segment q counts for candidate b (its
                                   //          own or one of its mirrors'); -1 = its own
+    uint8_t *own_rewritten;       // [K][B]: a repair has written into candidate b's own arrays of
+                                  //         chunk j (they are no longer its speculative run from
+                                  //         the chunk's first segment to its last)
     uint16_t *compat;             // [K][B]: for run u of chunk j-1, the runs of chunk j whose
                                   //         start continues u's end (bit 0: the candidate's own
                                   //         array, bit 1 + i: its i-th mirror)
@@ -210,10 +213,14 @@ __device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X
 //       stored as the chunk's start state, and every segment's end state.
 //   repair: the lane's clocks already hold the true state at `first`.  After
 //       each segment the new state is compared with the states stored runs
-//       had at that point (the run selected for the segment so far, and the
-//       mirrors [m_first, m_end) of the candidate); once it is equivalent to
-//       one, the rest of the chunk is taken from that run (seg_src) and the
-//       lane stops.  The segments a repair runs become the candidate's own.  A repair
+//       had at that point (the run selected for the segment so far, the
+//       mirrors [m_first, m_end) of the candidate and, with own_pure, the
+//       candidate's own speculative run where another run is selected); once
+//       it is equivalent to one, the rest of the chunk is taken from that run
+//       (seg_src) and the lane stops.  own_pure: no repair has written into
+//       the candidate's own arrays of this chunk before this one, so behind
+//       the segment being compared they still hold the speculative run.
+//       The segments a repair runs become the candidate's own.  A repair
 //       may start at a later segment q_begin of the chunk (its clocks then
 //       hold the state after segment q_begin - 1) and may be capped at `cap`
 //       segments (0 = no cap).
@@ -225,7 +232,7 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                                     bool repair, bool snapshots, uint32_t old_state,
                                     uint32_t stale_buf, int32_t q_begin = -1, int32_t cap = 0,
                                     uint64_t swap_pairs = ~0ull, int64_t m_first = 0,
-                                    int64_t m_end = 0)
+                                    int64_t m_end = 0, bool own_pure = false)
 {
     double *fin_out = kFull ? a.finish + (size_t)b * a.N : nullptr;
     uint8_t *good_out = kFull ? a.good + (size_t)b * a.N : nullptr;
@@ -296,14 +303,18 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                 // stored run had at this point: the run currently selected for
                 // this segment, or a mirror's.  The rest of the chunk is then
                 // taken from that run.
-                bool settled = false;
-                int64_t settle_src = -1;
+                bool settled = false, reselect = false;
+                int32_t settle_src = -1;
                 if (repair && snapshots && span_end < a.N) {
                     const double tau = arrival_at(a, b, span_end);
                     const int32_t cur = a.seg_src[(size_t)q * a.B + b];
-                    for (int64_t r = 0; r <= m_end - m_first && !settled; ++r) {
-                        const int64_t v = r == 0 ? (cur < 0 ? b : cur) : m_first + r - 1;
-                        if (r > 0 && v == cur) continue;
+                    // r == 0: the selected run; r == 1: the own speculative run, where
+                    // another is selected; r >= 2: the mirrors
+                    for (int64_t r = 0; r <= m_end - m_first + 1 && !settled; ++r) {
+                        int64_t v;
+                        if (r == 0) v = cur < 0 ? b : cur;
+                        else if (r == 1) { if (cur < 0 || !own_pure) continue; v = b; }
+                        else { v = m_first + r - 2; if (v == cur) continue; }
                         for (int t = 0; t < a.T; ++t)
                             SM_F64(old_state + t * kLanes) =
                                 a.seg_end[((size_t)q * a.T + t) * a.B + v];
@@ -311,7 +322,7 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                             a, b, [&](uint32_t s) { return SM_F64(ln.clk + s * kLanes); },
                             [&](uint32_t s) { return SM_F64(old_state + s * kLanes); }, tau,
                             [&](int u) -> uint8_t & { return smem[stale_buf + u * kLanes]; });
-                        if (settled && r > 0) settle_src = v;
+                        if (settled && r > 0) { reselect = true; settle_src = v == b ? -1 : (int32_t)v; }
                     }
                 }
                 if (snapshots) {
@@ -320,9 +331,9 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                     if (repair) a.seg_src[(size_t)q * a.B + b] = -1;
                 }
                 if (settled) {
-                    if (settle_src >= 0)
+                    if (reselect)
                         for (int32_t r = q + 1; r < q1; ++r)
-                            a.seg_src[(size_t)r * a.B + b] = (int32_t)settle_src;
+                            a.seg_src[(size_t)r * a.B + b] = settle_src;
                     return -1;
                 }
                 if (++q >= q1) return -1;

@@ -653,8 +653,9 @@ int mms_trace_next_same_model(const mms_trace *trace, int32_t num_models, int32_
 namespace mms {
 
 struct BatchGeometry {
-    int32_t lanes, H, K, chunk_len, warmup;
-    size_t smem, off_leaf, off_start, off_end, off_counters, off_carry, off_flag, total;
+    int32_t simd, H, K, chunk_len, warmup, Bp;
+    size_t smem_single, smem_simd;
+    size_t off_leaf, off_start, off_end, off_counters, off_carry, off_flag, off_tables, total;
 };
 
 // Chunking and scratch layout of one mms_sim_batching call.
@@ -663,32 +664,36 @@ static int plan_batching(int64_t N, const mms_placements *c, const mms_batching 
 {
     if (!c || !bt || N < 0 || N > 0x7FFFFFFF || c->num_candidates < 0) return MMS_ERR_ARG;
     const int64_t B = c->num_candidates;
-    g->H = bt->heap_capacity > 0 ? bt->heap_capacity : 4 * c->max_groups + 16;
-    // one candidate per warp unless there are too many candidates for that to fill the GPU
-    // better than warps of 32 candidates do
-    g->lanes = B <= 16384 ? 1 : kLanes;
-    const BatchSmem L = batch_smem(c->num_models, c->max_groups, c->max_placed, c->max_slots,
-                                   g->H, g->lanes);
-    g->smem = L.total;
+    g->H = bt->heap_capacity > 0 ? bt->heap_capacity : c->max_groups + 16;
+    // 32 candidates per warp (batch_simd_kernel) once there are enough of them to fill
+    // warps; else one candidate per warp
+    g->simd = B >= 24 ? 1 : 0;
+    g->Bp = (int32_t)((B + kLanes - 1) / kLanes * kLanes);
+    g->smem_single = batch_smem(c->num_models, c->max_groups, c->max_placed, c->max_slots,
+                                g->H, 1).total;
+    g->smem_simd = batch_smem(c->num_models, c->max_groups, c->max_placed, c->max_slots,
+                              g->H, kLanes).total;
+    if (g->smem_simd > 227 * 1024) g->simd = 0;
     int sm_count = 148, dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
         (void)cudaGetLastError();
         sm_count = 148;
     }
-    // Chunks: with one candidate per warp, as many as fill ONE wave of the resident blocks,
-    // none shorter than twice the run-in — and none at all when that leaves fewer than four:
-    // the kernels are issue-bound (one lane of each warp works), so a batch that fills a
-    // quarter of the GPU by itself gains less from cutting than the re-simulated chunks cost.
+    // Chunks: as many as fill ONE wave of the blocks that can be resident (shared memory
+    // decides), none shorter than twice the run-in, and no cut at all when that leaves fewer
+    // than two.
     g->warmup = 2048;
     int64_t K = 1;
-    if (g->lanes == 1 && B > 0 && N >= 4 * 4096) {
-        int64_t per_sm = (int64_t)(233472 / (L.total + 1024));
+    if (B > 0 && N >= 4 * 4096) {
+        const size_t smem = g->simd ? g->smem_simd : g->smem_single;
+        int64_t per_sm = (int64_t)(233472 / (smem + 1024));
         if (per_sm > kBatchBlocksPerSm) per_sm = kBatchBlocksPerSm;
         if (per_sm < 1) per_sm = 1;
-        K = per_sm * sm_count / B;
+        const int64_t blocks_per_chunk = g->simd ? g->Bp / kLanes : B;
+        K = per_sm * sm_count / blocks_per_chunk;
         if (K > N / 4096) K = N / 4096;
-        if (K < 4) K = 1;
+        if (K < (g->simd ? 2 : 4)) K = 1;
     }
     const int64_t len = (N + K - 1) / (K > 0 ? K : 1);
     g->chunk_len = (int32_t)(len > 0 ? len : 1);
@@ -700,6 +705,11 @@ static int plan_batching(int64_t N, const mms_placements *c, const mms_batching 
     g->off_flag = off;     off += 256;
     g->off_counters = off; off += align256(sizeof(uint32_t) * cells * (2 * c->num_models + 2 * c->max_groups));
     g->off_carry = off;    off += align256(cells * batch_carry_bytes());
+    g->off_tables = off;
+    if (g->simd)           // t_mrep, t_gcfg, t_status (u32), then t_moff, t_goff, t_gmod (u16)
+        off += align256((size_t)g->Bp * (4 * ((size_t)c->max_placed + c->max_groups + 1) +
+                                          2 * ((size_t)c->num_models + c->max_groups + 2 +
+                                               c->max_placed)) + 64);
     g->off_start = off;    off += g->K > 1 ? align256(cells * sb) : 0;
     g->off_end = off;      off += g->K > 1 ? align256(cells * sb) : 0;
     g->total = off;
@@ -779,8 +789,8 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
     a.model_num_requests = out->model_num_requests; a.model_num_good = out->model_num_good;
     a.group_num_requests = out->group_num_requests; a.group_num_good = out->group_num_good;
     a.status = out->status;
-    a.lanes = geo.lanes;
-    if (geo.smem > 227 * 1024) return MMS_ERR_UNSUPPORTED;
+    a.lanes = geo.simd ? kLanes : 1;
+    if (geo.smem_single > 227 * 1024) return MMS_ERR_UNSUPPORTED;
     unsigned char *scratch = (unsigned char *)ws->ptr;
     a.K = geo.K; a.chunk_len = geo.chunk_len; a.warmup = geo.warmup;
     a.unsorted = (const int32_t *)(scratch + geo.off_flag);
@@ -789,6 +799,17 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
     a.snap_start = scratch + geo.off_start;
     a.snap_end = scratch + geo.off_end;
     a.resimulated = out->resimulated;
+    a.Bp = geo.Bp;
+    if (geo.simd) {
+        const size_t Bp = (size_t)geo.Bp;
+        unsigned char *t = scratch + geo.off_tables;
+        a.t_mrep = (uint32_t *)t;   t += 4 * Bp * (size_t)a.P;
+        a.t_gcfg = (uint32_t *)t;   t += 4 * Bp * (size_t)a.G;
+        a.t_status = (uint32_t *)t; t += 4 * Bp;
+        a.t_moff = (uint16_t *)t;   t += 2 * Bp * (size_t)(a.M + 1);
+        a.t_goff = (uint16_t *)t;   t += 2 * Bp * (size_t)(a.G + 1);
+        a.t_gmod = (uint16_t *)t;
+    }
 
     cudaStream_t st = (cudaStream_t)stream;
     MMS_CUDA(cudaMemsetAsync(scratch + geo.off_flag, 0, 256, st));
@@ -799,16 +820,29 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
         unsorted_kernel<<<296, 256, 0, st>>>(trace->arrivals, N, (int32_t *)(scratch + geo.off_flag));
         MMS_CUDA(cudaGetLastError());
     }
-    MMS_TRY(allow_smem((const void *)batch_stream_kernel, geo.smem));
-    MMS_TRY(allow_smem((const void *)batch_chain_kernel, geo.smem));
-    const int64_t streams = (int64_t)B * a.K;
-    ProfileSpan stream_span(MMS_PROFILE_BATCH_STREAM, st);
-    batch_stream_kernel<<<(unsigned)((streams + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
-    MMS_CUDA(cudaGetLastError());
-    stream_span.stop();
+    MMS_TRY(allow_smem((const void *)batch_chain_kernel, geo.smem_single));
+    if (geo.simd) {
+        // the lanes add to the chunks' counters in global memory
+        MMS_CUDA(cudaMemsetAsync(a.chunk_counters, 0,
+                                 sizeof(uint32_t) * (size_t)a.K * B * (2 * a.M + 2 * a.G), st));
+        batch_tables_kernel<<<(unsigned)((geo.Bp + 127) / 128), 128, 0, st>>>(a);
+        MMS_CUDA(cudaGetLastError());
+        MMS_TRY(allow_smem((const void *)batch_simd_kernel, geo.smem_simd));
+        ProfileSpan stream_span(MMS_PROFILE_BATCH_STREAM, st);
+        batch_simd_kernel<<<(unsigned)((int64_t)a.K * (geo.Bp / kLanes)), kLanes, geo.smem_simd,
+                            st>>>(a);
+        MMS_CUDA(cudaGetLastError());
+        stream_span.stop();
+    } else {
+        MMS_TRY(allow_smem((const void *)batch_stream_kernel, geo.smem_single));
+        ProfileSpan stream_span(MMS_PROFILE_BATCH_STREAM, st);
+        batch_stream_kernel<<<(unsigned)((int64_t)B * a.K), kLanes, geo.smem_single, st>>>(a);
+        MMS_CUDA(cudaGetLastError());
+        stream_span.stop();
+    }
     if (a.K > 1) {
         ProfileSpan chain_span(MMS_PROFILE_BATCH_CHAIN, st);
-        batch_chain_kernel<<<(unsigned)((B + a.lanes - 1) / a.lanes), kLanes, geo.smem, st>>>(a);
+        batch_chain_kernel<<<(unsigned)B, kLanes, geo.smem_single, st>>>(a);
         MMS_CUDA(cudaGetLastError());
         chain_span.stop();
     }

@@ -1,4 +1,4 @@
-// sim_batching.cuh — the batching simulator, one thread per candidate.
+// sim_batching.cuh — the batching simulator.
 //
 // Restates simulate_requests_mixed_batching
 // (alpa_serve/simulator/controller.py:630-798; pure Python in the reference:
@@ -14,15 +14,33 @@
 // clocks are lane-private shared memory, [entry][lane].
 //
 // Like the unbatched path, the trace is cut into chunks that are simulated
-// speculatively at the same time (batch_stream_kernel: idle start, a run-in,
-// then the chunk) and stitched exactly afterwards (batch_chain_kernel: a
-// chunk is kept if the state it started from is equivalent to the state the
-// chunk before it ended in — batch_states_equivalent — and re-simulated from
-// the true state otherwise).  A request that is still queued at a chunk
-// boundary is served by the NEXT chunk's run; a speculative run does not
-// write the outputs of such carried requests itself (a wrong guess would
-// clobber what the chunk before it wrote) but lists them, and the chain
-// kernel applies the list when it accepts the chunk.
+// speculatively at the same time (idle start, a run-in, then the chunk) and
+// stitched exactly afterwards (batch_chain_kernel: a chunk is kept if the state
+// it started from is equivalent to the state the chunk before it ended in —
+// batch_states_equivalent — and re-simulated from the true state otherwise).
+// A request that is still queued at a chunk boundary is served by the NEXT
+// chunk's run; a speculative run does not write the outputs of such carried
+// requests itself (a wrong guess would clobber what the chunk before it
+// wrote) but lists them, and the chain kernel applies the list when it
+// accepts the chunk.
+//
+// Two forms of the speculative pass.  The control flow of this simulator
+// (heap pops, queue scans, dropped heads, batch growth) differs from
+// candidate to candidate, so 32 candidates that run the sequential code side
+// by side in a warp spend most of their time waiting for each other, and one
+// candidate per warp leaves 31 lanes idle.  batch_simd_kernel runs 32
+// candidates per warp as a STATE MACHINE instead: every lane has its own
+// cursor into the trace and is in one of a few states (due events, enqueue,
+// one step of serving, next arrival); an iteration of the warp's loop runs
+// the code of each state once for the lanes that are in it, and a lane passes
+// through as many states per iteration as its requests allow — nothing makes
+// a lane wait for another lane's request.  The candidates' tables are read
+// from global memory (transposed so that a warp's loads coalesce) and the
+// counters are added to global memory without a return value, which leaves
+// shared memory to the mutable state alone.  batch_stream_kernel (one
+// candidate per warp, plain sequential code) serves batches too small to fill
+// warps, and batch_chain_kernel's serial repairs.  All of them work on the
+// same helpers, templated on the number of lanes L a block interleaves.
 #pragma once
 #include "sim_core.cuh"
 
@@ -63,6 +81,15 @@ struct BatchArgs {
     uint32_t *chunk_counters;     // [K][B][2M + 2G]
     unsigned char *carry;         // [K][B][carry_bytes]: outputs of carried requests
     int32_t *resimulated;         // [B] or null: chunks the chain kernel re-simulated
+    // the candidates' tables as batch_simd_kernel reads them: checked, transposed to
+    // [entry][Bp] (Bp = B rounded up to 32), built by batch_tables_kernel
+    int32_t Bp;
+    uint32_t *t_mrep;             // [P][Bp]
+    uint32_t *t_gcfg;             // [G][Bp]
+    uint16_t *t_moff;             // [M+1][Bp]
+    uint16_t *t_goff;             // [G+1][Bp]
+    uint16_t *t_gmod;             // [P][Bp]
+    uint32_t *t_status;           // [Bp]: MMS_STATUS_BAD_INDEX where a table index was bad
 };
 
 constexpr int kMaxCarry = 120;    // carried requests a speculative chunk may list
@@ -88,32 +115,40 @@ struct BatchSmem {
         model_off, group_off, group_mod, total;
 };
 
-__host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int H, int kLanes)
+// Shared memory of a block that interleaves L lanes.  L == 1: everything a
+// candidate needs (state, counters, tables).  L == 32: the mutable state only
+// (clocks, heap, queues; a group's idle time IS the clock of its first stage —
+// controller.py:727 stores tmp[0] in both — and is not kept twice).
+__host__ __device__ inline BatchSmem batch_smem(int M, int G, int P, int T, int H, int L)
 {
-    BatchSmem L;
+    BatchSmem S;
     size_t off = 0;
-    L.clocks = off;    off += sizeof(double) * (size_t)T * kLanes;
-    L.idle = off;      off += sizeof(double) * (size_t)G * kLanes;
-    L.heap_t = off;    off += sizeof(double) * (size_t)H * kLanes;
-    L.qhead = off;     off += sizeof(int32_t) * (size_t)M * kLanes;
-    L.qlen = off;      off += sizeof(int32_t) * (size_t)M * kLanes;
-    L.heap_g = off;    off += sizeof(uint32_t) * (size_t)H * kLanes;
-    L.counters = off;  off += sizeof(uint32_t) * (size_t)(2 * M + 2 * G) * kLanes;
-    L.model_rep = off; off += sizeof(uint32_t) * (size_t)P * kLanes;
-    L.group_cfg = off; off += sizeof(uint32_t) * (size_t)G * kLanes;
-    L.model_off = off; off += sizeof(uint16_t) * (size_t)(M + 1) * kLanes;
-    L.group_off = off; off += sizeof(uint16_t) * (size_t)(G + 1) * kLanes;
-    L.group_mod = off; off += sizeof(uint16_t) * (size_t)P * kLanes;
-    L.total = (off + 15) & ~(size_t)15;
-    return L;
+    S.clocks = off;    off += sizeof(double) * (size_t)T * L;
+    S.idle = off;      off += L == 1 ? sizeof(double) * (size_t)G : 0;
+    S.heap_t = off;    off += sizeof(double) * (size_t)H * L;
+    S.qhead = off;     off += sizeof(int32_t) * (size_t)M * L;
+    S.qlen = off;      off += sizeof(int32_t) * (size_t)M * L;
+    S.heap_g = off;    off += (L == 1 ? sizeof(uint32_t) : sizeof(uint8_t)) * (size_t)H * L;
+    off = (off + 3) & ~(size_t)3;
+    S.counters = off;  off += L == 1 ? sizeof(uint32_t) * (size_t)(2 * M + 2 * G) : 0;
+    S.model_rep = off; off += L == 1 ? sizeof(uint32_t) * (size_t)P : 0;
+    S.group_cfg = off; off += L == 1 ? sizeof(uint32_t) * (size_t)G : 0;
+    S.model_off = off; off += L == 1 ? sizeof(uint16_t) * (size_t)(M + 1) : 0;
+    S.group_off = off; off += L == 1 ? sizeof(uint16_t) * (size_t)(G + 1) : 0;
+    S.group_mod = off; off += L == 1 ? sizeof(uint16_t) * (size_t)P : 0;
+    S.total = (off + 15) & ~(size_t)15;
+    return S;
 }
 
-// One candidate's state; every member is an element offset (lane included).
-// Entries are a.lanes elements apart.
+// One candidate's state; the shared-memory members are element offsets (lane
+// included), entries L elements apart.
 struct BLane {
     uint32_t clk, idle, heap_t, heap_g, qhead, qlen;
-    uint32_t model_req, model_good, group_req, group_good;
-    uint32_t mrep, gcfg, moff, goff, gmod;
+    uint32_t counters;                   // L == 1: [2M + 2G] in shared memory
+    uint32_t mrep, gcfg, moff, goff, gmod;   // L == 1: the tables in shared memory
+    const uint32_t *g_mrep, *g_gcfg;     // L == 32: the transposed tables, at this candidate
+    const uint16_t *g_moff, *g_goff, *g_gmod;
+    uint32_t *g_counters;                // L == 32: this run's [2M + 2G] counters in global memory
     uint32_t heap_n, status;
     const float *lat;
     double *finish;
@@ -126,6 +161,58 @@ struct BLane {
     double *carry_fin;
     uint32_t *carry_req;
 };
+
+// Counter c of the run: [0, M) requests per model, [M, 2M) good per model,
+// [2M, 2M + G) requests per group, then good per group.
+template <int L>
+__device__ __forceinline__ void count_add(const BatchArgs &, BLane &ln, uint32_t c, uint32_t v)
+{
+    if constexpr (L == 1) SM_U32(ln.counters + c) += v;
+    else if (ln.record) atomicAdd(ln.g_counters + c, v);      // no return value: fire and forget
+}
+
+template <int L>
+__device__ __forceinline__ uint32_t tab_mrep(const BatchArgs &a, const BLane &ln, uint32_t e)
+{
+    if constexpr (L == 1) return SM_U32(ln.mrep + e);
+    else return __ldg(ln.g_mrep + (size_t)e * a.Bp);
+}
+template <int L>
+__device__ __forceinline__ uint32_t tab_gcfg(const BatchArgs &a, const BLane &ln, uint32_t g)
+{
+    if constexpr (L == 1) return SM_U32(ln.gcfg + g);
+    else return __ldg(ln.g_gcfg + (size_t)g * a.Bp);
+}
+template <int L>
+__device__ __forceinline__ uint32_t tab_moff(const BatchArgs &a, const BLane &ln, uint32_t m)
+{
+    if constexpr (L == 1) return SM_U16(ln.moff + m);
+    else return __ldg(ln.g_moff + (size_t)m * a.Bp);
+}
+template <int L>
+__device__ __forceinline__ uint32_t tab_goff(const BatchArgs &a, const BLane &ln, uint32_t g)
+{
+    if constexpr (L == 1) return SM_U16(ln.goff + g);
+    else return __ldg(ln.g_goff + (size_t)g * a.Bp);
+}
+template <int L>
+__device__ __forceinline__ uint32_t tab_gmod(const BatchArgs &a, const BLane &ln, uint32_t e)
+{
+    if constexpr (L == 1) return SM_U16(ln.gmod + e);
+    else return __ldg(ln.g_gmod + (size_t)e * a.Bp);
+}
+template <int L>
+__device__ __forceinline__ uint32_t heap_group(const BLane &ln, uint32_t h)
+{
+    if constexpr (L == 1) return SM_U32(ln.heap_g + h);
+    else return smem[ln.heap_g + h * L];
+}
+template <int L>
+__device__ __forceinline__ void heap_group_set(const BLane &ln, uint32_t h, uint32_t g)
+{
+    if constexpr (L == 1) SM_U32(ln.heap_g + h) = g;
+    else smem[ln.heap_g + h * L] = (uint8_t)g;
+}
 
 // Output of request r.
 __device__ inline void put(BLane &ln, int32_t r, double fin, bool good)
@@ -149,61 +236,64 @@ __device__ inline bool event_less(double ta, uint32_t ga, double tb, uint32_t gb
     return ta < tb || (ta == tb && ga < gb);
 }
 
+template <int L>
 __device__ inline void heap_push(const BatchArgs &a, BLane &ln, double t, uint32_t g)
 {
     if (ln.heap_n >= (uint32_t)a.H) { ln.status |= MMS_STATUS_HEAP_OVERFLOW; return; }
     uint32_t i = ln.heap_n++;
     while (i > 0) {
         const uint32_t p = (i - 1) >> 1;
-        const double tp = SM_F64(ln.heap_t + p * a.lanes);
-        const uint32_t gp = SM_U32(ln.heap_g + p * a.lanes);
+        const double tp = SM_F64(ln.heap_t + p * L);
+        const uint32_t gp = heap_group<L>(ln, p);
         if (!event_less(t, g, tp, gp)) break;
-        SM_F64(ln.heap_t + i * a.lanes) = tp;
-        SM_U32(ln.heap_g + i * a.lanes) = gp;
+        SM_F64(ln.heap_t + i * L) = tp;
+        heap_group_set<L>(ln, i, gp);
         i = p;
     }
-    SM_F64(ln.heap_t + i * a.lanes) = t;
-    SM_U32(ln.heap_g + i * a.lanes) = g;
+    SM_F64(ln.heap_t + i * L) = t;
+    heap_group_set<L>(ln, i, g);
 }
 
-__device__ inline void heap_pop(const BatchArgs &a, BLane &ln, double &t, uint32_t &g)
+template <int L>
+__device__ inline void heap_pop(const BatchArgs &, BLane &ln, double &t, uint32_t &g)
 {
     t = SM_F64(ln.heap_t);
-    g = SM_U32(ln.heap_g);
+    g = heap_group<L>(ln, 0);
     const uint32_t n = --ln.heap_n;
     if (n == 0) return;
-    const double te = SM_F64(ln.heap_t + n * a.lanes);
-    const uint32_t ge = SM_U32(ln.heap_g + n * a.lanes);
+    const double te = SM_F64(ln.heap_t + n * L);
+    const uint32_t ge = heap_group<L>(ln, n);
     uint32_t i = 0;
     for (;;) {
         uint32_t c = 2 * i + 1;
         if (c >= n) break;
-        double tc = SM_F64(ln.heap_t + c * a.lanes);
-        uint32_t gc = SM_U32(ln.heap_g + c * a.lanes);
+        double tc = SM_F64(ln.heap_t + c * L);
+        uint32_t gc = heap_group<L>(ln, c);
         if (c + 1 < n) {
-            const double tr = SM_F64(ln.heap_t + (c + 1) * a.lanes);
-            const uint32_t gr = SM_U32(ln.heap_g + (c + 1) * a.lanes);
+            const double tr = SM_F64(ln.heap_t + (c + 1) * L);
+            const uint32_t gr = heap_group<L>(ln, c + 1);
             if (event_less(tr, gr, tc, gc)) { c += 1; tc = tr; gc = gr; }
         }
         if (!event_less(tc, gc, te, ge)) break;
-        SM_F64(ln.heap_t + i * a.lanes) = tc;
-        SM_U32(ln.heap_g + i * a.lanes) = gc;
+        SM_F64(ln.heap_t + i * L) = tc;
+        heap_group_set<L>(ln, i, gc);
         i = c;
     }
-    SM_F64(ln.heap_t + i * a.lanes) = te;
-    SM_U32(ln.heap_g + i * a.lanes) = ge;
+    SM_F64(ln.heap_t + i * L) = te;
+    heap_group_set<L>(ln, i, ge);
 }
 
 // select_model, :654-664: the group's model whose queue head arrived first.
+template <int L>
 __device__ inline int32_t pick_model(const BatchArgs &a, const BLane &ln, uint32_t g)
 {
-    const uint32_t lo = SM_U16(ln.goff + g * a.lanes), hi = SM_U16(ln.goff + (g + 1) * a.lanes);
+    const uint32_t lo = tab_goff<L>(a, ln, g), hi = tab_goff<L>(a, ln, g + 1);
     double first = kInf;
     int32_t pick = -1;
     for (uint32_t e = lo; e < hi; ++e) {
-        const uint32_t m = SM_U16(ln.gmod + e * a.lanes);
-        if ((int32_t)SM_U32(ln.qlen + m * a.lanes) > 0) {
-            const double ts = a.arrivals[(int32_t)SM_U32(ln.qhead + m * a.lanes)];
+        const uint32_t m = tab_gmod<L>(a, ln, e);
+        if ((int32_t)SM_U32(ln.qlen + m * L) > 0) {
+            const double ts = a.arrivals[(int32_t)SM_U32(ln.qhead + m * L)];
             if (ts < first) { first = ts; pick = (int32_t)m; }
         }
     }
@@ -211,6 +301,7 @@ __device__ inline int32_t pick_model(const BatchArgs &a, const BLane &ln, uint32
 }
 
 // check_slo, :666-672.
+template <int L>
 __device__ inline bool meets_deadline(const BatchArgs &a, const BLane &ln, double ts, uint32_t m,
                                       uint32_t slot, uint32_t ns, uint32_t col, int bcol,
                                       double deadline)
@@ -218,90 +309,102 @@ __device__ inline bool meets_deadline(const BatchArgs &a, const BLane &ln, doubl
     const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
     double t = ts;
     for (uint32_t k = 0; k < ns; ++k)
-        t = fmax(SM_F64(ln.clk + (slot + k) * a.lanes), t) + (double)__ldg(lat + (size_t)k * a.NB);
+        t = fmax(SM_F64(ln.clk + (slot + k) * L), t) + (double)__ldg(lat + (size_t)k * a.NB);
     return t + kOverhead <= deadline;
 }
 
+template <int L>
 __device__ inline int32_t queue_pop(const BatchArgs &a, BLane &ln, uint32_t m)
 {
-    const int32_t r = (int32_t)SM_U32(ln.qhead + m * a.lanes);
-    SM_U32(ln.qhead + m * a.lanes) = (uint32_t)a.next_same[r];
-    SM_U32(ln.qlen + m * a.lanes) -= 1;
+    const int32_t r = (int32_t)SM_U32(ln.qhead + m * L);
+    SM_U32(ln.qhead + m * L) = (uint32_t)a.next_same[r];
+    SM_U32(ln.qlen + m * L) -= 1;
     return r;
+}
+
+// The head request `head` of model m's queue can be served by group g at time
+// ts: grows the batch while the HEAD's deadline still holds (:693-702),
+// dispatches it (:715-725: overhead first, then the stages; clocks move to the
+// new times), and books the group's next idle time and the counters (:727-732).
+template <int L>
+__device__ inline void dispatch_batch(const BatchArgs &a, BLane &ln, double ts, uint32_t m,
+                                      uint32_t g, uint32_t cfg, int32_t head)
+{
+    const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu, col = cfg >> 16;
+    const double deadline = a.arrivals[head] + (double)a.slos[head];
+    int32_t bs = 1, bcol = a.batch_cols[0];
+    for (int j = 1; j < a.NB; ++j) {
+        if (a.batch_sizes[j] - 1 > (int32_t)SM_U32(ln.qlen + m * L)) break;
+        if (!meets_deadline<L>(a, ln, ts, m, slot, ns, col, a.batch_cols[j], deadline)) break;
+        bs = a.batch_sizes[j];
+        bcol = a.batch_cols[j];
+    }
+    const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
+    double t = ts + kOverhead, t_first = 0.0;
+    for (uint32_t k = 0; k < ns; ++k) {
+        t = fmax(t, SM_F64(ln.clk + (slot + k) * L)) + (double)__ldg(lat + (size_t)k * a.NB);
+        SM_F64(ln.clk + (slot + k) * L) = t;   // each stage reads only its own clock
+        if (k == 0) t_first = t;
+    }
+    put(ln, head, t, true);
+    for (int32_t k = 1; k < bs; ++k) {
+        const int32_t r = queue_pop<L>(a, ln, m);
+        put(ln, r, t, true);
+    }
+    if constexpr (L == 1) SM_F64(ln.idle + g) = t_first;    // L == 32: it is clk[slot]
+    heap_push<L>(a, ln, t_first, g);
+    count_add<L>(a, ln, 2 * a.M + g, (uint32_t)bs);
+    count_add<L>(a, ln, 2 * a.M + a.G + g, (uint32_t)bs);
+    count_add<L>(a, ln, a.M + m, (uint32_t)bs);
 }
 
 // handle_batched_requests with get_max_batch_under_slo, :674-732.  The
 // reference recurses when a model's whole queue was dropped; the loop is the
 // same tail call.
+template <int L>
 __device__ inline void serve_group(const BatchArgs &a, BLane &ln, double ts, int32_t m_in,
                                    uint32_t g)
 {
-    const uint32_t cfg = SM_U32(ln.gcfg + g * a.lanes);
+    const uint32_t cfg = tab_gcfg<L>(a, ln, g);
     const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu, col = cfg >> 16;
     int32_t m = m_in;
     while (m >= 0) {
         // :677-686 drop queue heads that cannot make their deadline even alone
         int32_t head = -1;
-        while ((int32_t)SM_U32(ln.qlen + m * a.lanes) > 0) {
-            const int32_t r = queue_pop(a, ln, m);
+        while ((int32_t)SM_U32(ln.qlen + m * L) > 0) {
+            const int32_t r = queue_pop<L>(a, ln, m);
             const double dl = a.arrivals[r] + (double)a.slos[r];
-            if (meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[0], dl)) { head = r; break; }
-            SM_U32(ln.group_req + g * a.lanes) += 1;
+            if (meets_deadline<L>(a, ln, ts, m, slot, ns, col, a.batch_cols[0], dl)) { head = r; break; }
+            count_add<L>(a, ln, 2 * a.M + g, 1u);
             put(ln, r, a.arrivals[r], false);
         }
-        if (head < 0) { m = pick_model(a, ln, g); continue; }      // :709-713
-        // :693-702 grow the batch while the HEAD's deadline still holds
-        const double deadline = a.arrivals[head] + (double)a.slos[head];
-        int32_t bs = 1, bcol = a.batch_cols[0];
-        for (int j = 1; j < a.NB; ++j) {
-            if (a.batch_sizes[j] - 1 > (int32_t)SM_U32(ln.qlen + m * a.lanes)) break;
-            if (!meets_deadline(a, ln, ts, m, slot, ns, col, a.batch_cols[j], deadline)) break;
-            bs = a.batch_sizes[j];
-            bcol = a.batch_cols[j];
-        }
-        // :715-725 overhead first, then the stages; clocks move to the new times
-        const float *lat = ln.lat + (((size_t)m * a.C + col) * a.S) * a.NB + bcol;
-        double t = ts + kOverhead, t_first = 0.0;
-        for (uint32_t k = 0; k < ns; ++k) {
-            t = fmax(t, SM_F64(ln.clk + (slot + k) * a.lanes)) + (double)__ldg(lat + (size_t)k * a.NB);
-            SM_F64(ln.clk + (slot + k) * a.lanes) = t;   // each stage reads only its own clock
-            if (k == 0) t_first = t;
-        }
-        put(ln, head, t, true);
-        for (int32_t k = 1; k < bs; ++k) {
-            const int32_t r = queue_pop(a, ln, m);
-            put(ln, r, t, true);
-        }
-        // :727-732
-        SM_F64(ln.idle + g * a.lanes) = t_first;
-        heap_push(a, ln, t_first, g);
-        SM_U32(ln.group_req + g * a.lanes) += (uint32_t)bs;
-        SM_U32(ln.group_good + g * a.lanes) += (uint32_t)bs;
-        SM_U32(ln.model_good + m * a.lanes) += (uint32_t)bs;
+        if (head < 0) { m = pick_model<L>(a, ln, g); continue; }      // :709-713
+        dispatch_batch<L>(a, ln, ts, (uint32_t)m, g, cfg, head);
         return;
     }
 }
 
-// This lane's view of candidate b and the candidate's tables on chip, every
-// index checked (a bad one is reported in ln.status).
-__device__ inline void batch_setup(const BatchArgs &a, BLane &ln, int lane, int64_t b)
+// This lane's view of candidate b with ONE lane per block: offsets of the
+// state, and the candidate's tables copied on chip, every index checked (a
+// bad one is reported in ln.status).
+__device__ inline void batch_setup(const BatchArgs &a, BLane &ln, int64_t b)
 {
-    const BatchSmem L = batch_smem(a.M, a.G, a.P, a.T, a.H, a.lanes);
-    ln.clk = (uint32_t)(L.clocks / 8) + lane;
-    ln.idle = (uint32_t)(L.idle / 8) + lane;
-    ln.heap_t = (uint32_t)(L.heap_t / 8) + lane;
-    ln.heap_g = (uint32_t)(L.heap_g / 4) + lane;
-    ln.qhead = (uint32_t)(L.qhead / 4) + lane;
-    ln.qlen = (uint32_t)(L.qlen / 4) + lane;
-    ln.model_req = (uint32_t)(L.counters / 4) + lane;
-    ln.model_good = ln.model_req + (uint32_t)a.M * a.lanes;
-    ln.group_req = ln.model_good + (uint32_t)a.M * a.lanes;
-    ln.group_good = ln.group_req + (uint32_t)a.G * a.lanes;
-    ln.mrep = (uint32_t)(L.model_rep / 4) + lane;
-    ln.gcfg = (uint32_t)(L.group_cfg / 4) + lane;
-    ln.moff = (uint32_t)(L.model_off / 2) + lane;
-    ln.goff = (uint32_t)(L.group_off / 2) + lane;
-    ln.gmod = (uint32_t)(L.group_mod / 2) + lane;
+    const BatchSmem S = batch_smem(a.M, a.G, a.P, a.T, a.H, 1);
+    ln.clk = (uint32_t)(S.clocks / 8);
+    ln.idle = (uint32_t)(S.idle / 8);
+    ln.heap_t = (uint32_t)(S.heap_t / 8);
+    ln.heap_g = (uint32_t)(S.heap_g / 4);
+    ln.qhead = (uint32_t)(S.qhead / 4);
+    ln.qlen = (uint32_t)(S.qlen / 4);
+    ln.counters = (uint32_t)(S.counters / 4);
+    ln.mrep = (uint32_t)(S.model_rep / 4);
+    ln.gcfg = (uint32_t)(S.group_cfg / 4);
+    ln.moff = (uint32_t)(S.model_off / 2);
+    ln.goff = (uint32_t)(S.group_off / 2);
+    ln.gmod = (uint32_t)(S.group_mod / 2);
+    ln.g_mrep = ln.g_gcfg = nullptr;
+    ln.g_moff = ln.g_goff = ln.g_gmod = nullptr;
+    ln.g_counters = nullptr;
     ln.heap_n = 0;
     ln.status = 0;
     ln.lat = a.latency + (size_t)b * a.latency_stride;
@@ -317,88 +420,157 @@ __device__ inline void batch_setup(const BatchArgs &a, BLane &ln, int lane, int6
             ln.status |= MMS_STATUS_BAD_INDEX;
             cfg = 0;
         }
-        SM_U32(ln.gcfg + g * a.lanes) = cfg;
+        SM_U32(ln.gcfg + g) = cfg;
     }
     uint32_t prev = 0;
     for (int m = 0; m <= a.M; ++m) {
         uint32_t o = a.model_off[(size_t)b * (a.M + 1) + m];
         if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
-        SM_U16(ln.moff + m * a.lanes) = (uint16_t)o;
+        SM_U16(ln.moff + m) = (uint16_t)o;
         prev = o;
     }
     for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
         uint32_t ent = e < prev ? a.model_rep[(size_t)b * a.P + e] : 0u;
         if (e < prev) {
             const uint32_t g = ent & 0xFFu;
-            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (SM_U32(ln.gcfg + g * a.lanes) & 0xFFFFu))
+            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (SM_U32(ln.gcfg + g) & 0xFFFFu))
                 ln.status |= MMS_STATUS_BAD_INDEX;
         }
-        SM_U32(ln.mrep + e * a.lanes) = ent;
+        SM_U32(ln.mrep + e) = ent;
     }
     prev = 0;
     for (int g = 0; g <= a.G; ++g) {
         uint32_t o = a.group_off[(size_t)b * (a.G + 1) + g];
         if (o < prev || o > (uint32_t)a.P) { ln.status |= MMS_STATUS_BAD_INDEX; o = prev; }
-        SM_U16(ln.goff + g * a.lanes) = (uint16_t)o;
+        SM_U16(ln.goff + g) = (uint16_t)o;
         prev = o;
     }
     for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
         uint32_t m = e < prev ? a.group_mod[(size_t)b * a.P + e] : 0u;
         if (m >= (uint32_t)a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = 0; }
-        SM_U16(ln.gmod + e * a.lanes) = (uint16_t)m;
+        SM_U16(ln.gmod + e) = (uint16_t)m;
     }
+}
+
+// The same checks, one thread per candidate, writing the tables transposed
+// ([entry][Bp]) for batch_simd_kernel.
+__global__ void batch_tables_kernel(const BatchArgs a)
+{
+    const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= a.Bp) return;
+    const size_t Bp = (size_t)a.Bp;
+    uint32_t status = 0;
+    if (b >= a.B) {                         // padding lanes: empty tables
+        for (int g = 0; g < a.G; ++g) a.t_gcfg[g * Bp + b] = 0;
+        for (int m = 0; m <= a.M; ++m) a.t_moff[m * Bp + b] = 0;
+        for (int g = 0; g <= a.G; ++g) a.t_goff[g * Bp + b] = 0;
+        for (int e = 0; e < a.P; ++e) { a.t_mrep[e * Bp + b] = 0; a.t_gmod[e * Bp + b] = 0; }
+        a.t_status[b] = 0;
+        return;
+    }
+    for (int g = 0; g < a.G; ++g) {
+        uint32_t cfg = a.group_cfg[(size_t)b * a.G + g];
+        const uint32_t slot = cfg & 0xFFu, ns = (cfg >> 8) & 0xFFu;
+        if (slot + ns > (uint32_t)a.T || ns > (uint32_t)a.S || (cfg >> 16) >= (uint32_t)a.C) {
+            status |= MMS_STATUS_BAD_INDEX;
+            cfg = 0;
+        }
+        a.t_gcfg[g * Bp + b] = cfg;
+    }
+    uint32_t prev = 0;
+    for (int m = 0; m <= a.M; ++m) {
+        uint32_t o = a.model_off[(size_t)b * (a.M + 1) + m];
+        if (o < prev || o > (uint32_t)a.P) { status |= MMS_STATUS_BAD_INDEX; o = prev; }
+        a.t_moff[m * Bp + b] = (uint16_t)o;
+        prev = o;
+    }
+    for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
+        uint32_t ent = e < prev ? a.model_rep[(size_t)b * a.P + e] : 0u;
+        if (e < prev) {
+            const uint32_t g = ent & 0xFFu;
+            if (g >= (uint32_t)a.G || ((ent >> 8) & 0xFFFFu) != (a.t_gcfg[g * Bp + b] & 0xFFFFu))
+                status |= MMS_STATUS_BAD_INDEX;
+        }
+        a.t_mrep[e * Bp + b] = ent;
+    }
+    prev = 0;
+    for (int g = 0; g <= a.G; ++g) {
+        uint32_t o = a.group_off[(size_t)b * (a.G + 1) + g];
+        if (o < prev || o > (uint32_t)a.P) { status |= MMS_STATUS_BAD_INDEX; o = prev; }
+        a.t_goff[g * Bp + b] = (uint16_t)o;
+        prev = o;
+    }
+    for (uint32_t e = 0; e < (uint32_t)a.P; ++e) {
+        uint32_t m = e < prev ? a.group_mod[(size_t)b * a.P + e] : 0u;
+        if (m >= (uint32_t)a.M) { status |= MMS_STATUS_BAD_INDEX; m = 0; }
+        a.t_gmod[e * Bp + b] = (uint16_t)m;
+    }
+    a.t_status[b] = status;
 }
 
 __device__ inline void batch_zero_counters(const BatchArgs &a, BLane &ln)
 {
-    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.model_req + c * a.lanes) = 0;
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) SM_U32(ln.counters + c) = 0;
 }
 
 // Idle clocks, empty queues, empty heap.
+template <int L>
 __device__ inline void batch_zero_state(const BatchArgs &a, BLane &ln)
 {
-    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = 0.0;
-    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = 0.0;
-    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * a.lanes) = 0; SM_U32(ln.qlen + m * a.lanes) = 0; }
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * L) = 0.0;
+    if constexpr (L == 1)
+        for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g) = 0.0;
+    for (int m = 0; m < a.M; ++m) { SM_U32(ln.qhead + m * L) = 0; SM_U32(ln.qlen + m * L) = 0; }
     ln.heap_n = 0;
 }
 
-// Arrival i, :736-778.
+// :759-773 for arrival i of model m with replicas [lo, hi): the replica whose
+// last-stage clock is strictly smallest; the request joins its MODEL's queue.
+// Returns the chosen replica entry, `found` false when no replica qualifies.
+template <int L>
+__device__ inline uint32_t choose_and_enqueue(const BatchArgs &a, BLane &ln, int64_t i, int32_t m,
+                                              uint32_t lo, uint32_t hi, bool &found)
+{
+    double best = kInf;
+    uint32_t pick = 0;
+    found = false;
+    for (uint32_t e = lo; e < hi; ++e) {
+        const uint32_t ent = tab_mrep<L>(a, ln, e);
+        const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
+        const double c = SM_F64(ln.clk + last * L);
+        if (c < best) { best = c; pick = ent; found = true; }
+    }
+    if ((int32_t)SM_U32(ln.qlen + m * L) == 0) SM_U32(ln.qhead + m * L) = (uint32_t)i;
+    SM_U32(ln.qlen + m * L) += 1;
+    count_add<L>(a, ln, (uint32_t)m, 1u);
+    return pick;
+}
+
+// Arrival i, :736-778 (plain sequential form).
 __device__ inline void batch_arrival(const BatchArgs &a, BLane &ln, int64_t i)
 {
     const double ts = a.arrivals[i];
     // :739-744 groups whose first stage became free before this arrival
     while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
         double te; uint32_t ge;
-        heap_pop(a, ln, te, ge);
-        const int32_t pm = pick_model(a, ln, ge);
+        heap_pop<1>(a, ln, te, ge);
+        const int32_t pm = pick_model<1>(a, ln, ge);
         if (pm < 0) break;                     // the reference breaks here, not continues
-        serve_group(a, ln, te, pm, ge);
+        serve_group<1>(a, ln, te, pm, ge);
     }
     int32_t m = a.model_ids[i];
     if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
     uint32_t lo = 0, hi = 0;
-    if (m >= 0) { lo = SM_U16(ln.moff + m * a.lanes); hi = SM_U16(ln.moff + (m + 1) * a.lanes); }
+    if (m >= 0) { lo = SM_U16(ln.moff + m); hi = SM_U16(ln.moff + (m + 1)); }
     if (lo == hi) {                            // :748-757 unknown model or no replica
         put(ln, (int32_t)i, ts, false);
         return;
     }
-    double best = kInf;                        // :759-770
-    uint32_t pick = 0;
-    bool found = false;
-    for (uint32_t e = lo; e < hi; ++e) {
-        const uint32_t ent = SM_U32(ln.mrep + e * a.lanes);
-        const uint32_t last = ((ent >> 8) & 0xFFu) + ((ent >> 16) & 0xFFu) - 1;
-        const double c = SM_F64(ln.clk + last * a.lanes);
-        if (c < best) { best = c; pick = ent; found = true; }
-    }
-    // :772-773 the request joins its MODEL's queue
-    if ((int32_t)SM_U32(ln.qlen + m * a.lanes) == 0) SM_U32(ln.qhead + m * a.lanes) = (uint32_t)i;
-    SM_U32(ln.qlen + m * a.lanes) += 1;
-    SM_U32(ln.model_req + m * a.lanes) += 1;
+    bool found;
+    const uint32_t pick = choose_and_enqueue<1>(a, ln, i, m, lo, hi, found);
     const uint32_t g = pick & 0xFFu;
-    if (found && ts >= SM_F64(ln.idle + g * a.lanes))   // :776-778
-        serve_group(a, ln, ts, m, g);
+    if (found && ts >= SM_F64(ln.idle + g))   // :776-778
+        serve_group<1>(a, ln, ts, m, g);
 }
 
 // After the last arrival, :781-790.
@@ -406,13 +578,13 @@ __device__ inline void batch_drain(const BatchArgs &a, BLane &ln)
 {
     while (ln.heap_n > 0) {
         double te; uint32_t ge;
-        heap_pop(a, ln, te, ge);
-        const int32_t pm = pick_model(a, ln, ge);
+        heap_pop<1>(a, ln, te, ge);
+        const int32_t pm = pick_model<1>(a, ln, ge);
         if (pm < 0) continue;
-        serve_group(a, ln, te, pm, ge);
+        serve_group<1>(a, ln, te, pm, ge);
     }
     for (int m = 0; m < a.M; ++m)
-        if ((int32_t)SM_U32(ln.qlen + m * a.lanes) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+        if ((int32_t)SM_U32(ln.qlen + m) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
 }
 
 // A saved state, see batch_state_bytes.
@@ -436,18 +608,26 @@ __device__ inline StateView state_view(const BatchArgs &a, unsigned char *p)
     return v;
 }
 
+template <int L>
 __device__ inline void state_save(const BatchArgs &a, const BLane &ln, unsigned char *p)
 {
     const StateView v = state_view(a, p);
-    for (int t = 0; t < a.T; ++t) v.clk[t] = SM_F64(ln.clk + t * a.lanes);
-    for (int g = 0; g < a.G; ++g) v.idle[g] = SM_F64(ln.idle + g * a.lanes);
+    for (int t = 0; t < a.T; ++t) v.clk[t] = SM_F64(ln.clk + t * L);
+    for (int g = 0; g < a.G; ++g) {
+        if constexpr (L == 1) {
+            v.idle[g] = SM_F64(ln.idle + g);
+        } else {        // the clock of the group's first stage; 0 for a row of padding
+            const uint32_t cfg = tab_gcfg<L>(a, ln, g);
+            v.idle[g] = ((cfg >> 8) & 0xFFu) ? SM_F64(ln.clk + (cfg & 0xFFu) * L) : 0.0;
+        }
+    }
     for (uint32_t h = 0; h < ln.heap_n; ++h) {
-        v.heap_t[h] = SM_F64(ln.heap_t + h * a.lanes);
-        v.heap_g[h] = SM_U32(ln.heap_g + h * a.lanes);
+        v.heap_t[h] = SM_F64(ln.heap_t + h * L);
+        v.heap_g[h] = heap_group<L>(ln, h);
     }
     for (int m = 0; m < a.M; ++m) {
-        v.qhead[m] = (int32_t)SM_U32(ln.qhead + m * a.lanes);
-        v.qlen[m] = (int32_t)SM_U32(ln.qlen + m * a.lanes);
+        v.qhead[m] = (int32_t)SM_U32(ln.qhead + m * L);
+        v.qlen[m] = (int32_t)SM_U32(ln.qlen + m * L);
     }
     *v.heap_n = ln.heap_n;
 }
@@ -455,16 +635,16 @@ __device__ inline void state_save(const BatchArgs &a, const BLane &ln, unsigned 
 __device__ inline void state_load(const BatchArgs &a, BLane &ln, unsigned char *p)
 {
     const StateView v = state_view(a, p);
-    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t * a.lanes) = v.clk[t];
-    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g * a.lanes) = v.idle[g];
+    for (int t = 0; t < a.T; ++t) SM_F64(ln.clk + t) = v.clk[t];
+    for (int g = 0; g < a.G; ++g) SM_F64(ln.idle + g) = v.idle[g];
     ln.heap_n = *v.heap_n;
     for (uint32_t h = 0; h < ln.heap_n; ++h) {
-        SM_F64(ln.heap_t + h * a.lanes) = v.heap_t[h];
-        SM_U32(ln.heap_g + h * a.lanes) = v.heap_g[h];
+        SM_F64(ln.heap_t + h) = v.heap_t[h];
+        SM_U32(ln.heap_g + h) = v.heap_g[h];
     }
     for (int m = 0; m < a.M; ++m) {
-        SM_U32(ln.qhead + m * a.lanes) = (uint32_t)v.qhead[m];
-        SM_U32(ln.qlen + m * a.lanes) = (uint32_t)v.qlen[m];
+        SM_U32(ln.qhead + m) = (uint32_t)v.qhead[m];
+        SM_U32(ln.qlen + m) = (uint32_t)v.qlen[m];
     }
 }
 
@@ -491,34 +671,34 @@ __device__ inline bool batch_states_equivalent(const BatchArgs &a, const BLane &
     if (*y.heap_n != ln.heap_n) return false;
     double theta = tau;
     for (uint32_t h = 0; h < ln.heap_n; ++h) {
-        const double t = SM_F64(ln.heap_t + h * a.lanes);
-        if (t != y.heap_t[h] || SM_U32(ln.heap_g + h * a.lanes) != y.heap_g[h]) return false;
+        const double t = SM_F64(ln.heap_t + h);
+        if (t != y.heap_t[h] || SM_U32(ln.heap_g + h) != y.heap_g[h]) return false;
         if (t < theta) theta = t;
     }
     for (int m = 0; m < a.M; ++m) {
-        const int32_t n = (int32_t)SM_U32(ln.qlen + m * a.lanes);
+        const int32_t n = (int32_t)SM_U32(ln.qlen + m);
         if (n != y.qlen[m]) return false;
-        if (n > 0 && (int32_t)SM_U32(ln.qhead + m * a.lanes) != y.qhead[m]) return false;
+        if (n > 0 && (int32_t)SM_U32(ln.qhead + m) != y.qhead[m]) return false;
     }
     for (int g = 0; g < a.G; ++g) {
-        const double x = SM_F64(ln.idle + g * a.lanes), v = y.idle[g];
+        const double x = SM_F64(ln.idle + g), v = y.idle[g];
         if (!(x == v || (x <= tau && v <= tau))) return false;
     }
     for (int t = 0; t < a.T; ++t) {
-        const double x = SM_F64(ln.clk + t * a.lanes), v = y.clk[t];
+        const double x = SM_F64(ln.clk + t), v = y.clk[t];
         if (!(x == v || (x < theta && v < theta))) return false;
     }
     // order of differing last-stage clocks among groups that share a model
     for (int m = 0; m < a.M; ++m) {
-        const uint32_t lo = SM_U16(ln.moff + m * a.lanes), hi = SM_U16(ln.moff + (m + 1) * a.lanes);
+        const uint32_t lo = SM_U16(ln.moff + m), hi = SM_U16(ln.moff + (m + 1));
         for (uint32_t e = lo; e + 1 < hi; ++e) {
-            const uint32_t eu = SM_U32(ln.mrep + e * a.lanes);
+            const uint32_t eu = SM_U32(ln.mrep + e);
             const uint32_t su = ((eu >> 8) & 0xFFu) + ((eu >> 16) & 0xFFu) - 1;
-            const double xu = SM_F64(ln.clk + su * a.lanes), yu = y.clk[su];
+            const double xu = SM_F64(ln.clk + su), yu = y.clk[su];
             for (uint32_t f = e + 1; f < hi; ++f) {
-                const uint32_t ev = SM_U32(ln.mrep + f * a.lanes);
+                const uint32_t ev = SM_U32(ln.mrep + f);
                 const uint32_t sv = ((ev >> 8) & 0xFFu) + ((ev >> 16) & 0xFFu) - 1;
-                const double xv = SM_F64(ln.clk + sv * a.lanes), yv = y.clk[sv];
+                const double xv = SM_F64(ln.clk + sv), yv = y.clk[sv];
                 if ((xu < xv) != (yu < yv) || (xu > xv) != (yu > yv)) return false;
             }
         }
@@ -528,7 +708,7 @@ __device__ inline bool batch_states_equivalent(const BatchArgs &a, const BLane &
 
 __device__ inline void counters_store(const BatchArgs &a, const BLane &ln, uint32_t *dst)
 {
-    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) dst[c] = SM_U32(ln.model_req + c * a.lanes);
+    for (int c = 0; c < 2 * a.M + 2 * a.G; ++c) dst[c] = SM_U32(ln.counters + c);
 }
 
 // First arrival of chunk j (j == K: one past the last arrival).
@@ -540,24 +720,23 @@ __device__ inline int64_t chunk_first(const BatchArgs &a, int32_t j)
 
 __device__ inline bool batch_can_chunk(const BatchArgs &a) { return a.K > 1 && *a.unsorted == 0; }
 
-// One thread per (candidate, chunk); with lanes == 1 thread 0 of the block
-// alone, so that a candidate's branches are not serialised against 31
-// others'.  Chunk 0 starts from the true (idle) state; the others start idle
+// One candidate per warp (thread 0 of the block alone, so that a candidate's
+// branches are not serialised against 31 others'): one thread per (candidate,
+// chunk).  Chunk 0 starts from the true (idle) state; the others start idle
 // `warmup` arrivals early and store the state they have at their first arrival.
 __global__ void __launch_bounds__(kLanes, kBatchBlocksPerSm)
 batch_stream_kernel(const BatchArgs a)
 {
-    if ((int)threadIdx.x >= a.lanes) return;
-    const int lane = threadIdx.x;
-    const int64_t stream = (int64_t)blockIdx.x * a.lanes + lane;
+    if (threadIdx.x != 0) return;
+    const int64_t stream = blockIdx.x;
     if (stream >= (int64_t)a.B * a.K) return;
     const int32_t j = (int32_t)(stream / a.B);
     const int64_t b = stream % a.B;
     const bool chunked = batch_can_chunk(a);
     if (!chunked && j > 0) return;
     BLane ln;
-    batch_setup(a, ln, lane, b);
-    batch_zero_state(a, ln);
+    batch_setup(a, ln, b);
+    batch_zero_state<1>(a, ln);
     batch_zero_counters(a, ln);
     const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
     const size_t cell = (size_t)j * a.B + b;
@@ -576,11 +755,11 @@ batch_stream_kernel(const BatchArgs a)
             ln.record = true;
             ln.status &= MMS_STATUS_BAD_INDEX;       // overflows of the run-in are not the chunk's
             batch_zero_counters(a, ln);
-            state_save(a, ln, a.snap_start + cell * sb);
+            state_save<1>(a, ln, a.snap_start + cell * sb);
         }
         for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
         if (end == a.N) batch_drain(a, ln);
-        if (chunked) state_save(a, ln, a.snap_end + cell * sb);
+        if (chunked) state_save<1>(a, ln, a.snap_end + cell * sb);
     }
     counters_store(a, ln, a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G));
     if (chunked) {
@@ -593,19 +772,199 @@ batch_stream_kernel(const BatchArgs a)
     }
 }
 
-// One thread per candidate: walks the chunk boundaries in order; a chunk
-// whose start state is equivalent to the true state is kept (and the outputs
-// of the requests it carried over are written), any other is re-simulated
-// from the true state.
+// States of a lane of batch_simd_kernel.
+enum : int {
+    kStDue = 0,      // groups whose first stage became free before the current arrival (:739-744)
+    kStEnqueue,      // the current arrival joins its model's queue (:746-778)
+    kStServe,        // one step of handle_batched_requests for (serve_ts, serve_m, serve_g)
+    kStNext,         // on to the next arrival
+    kStDrain,        // behind the last arrival: the heap is emptied (:781-787)
+    kStFinish,       // store the end state and the run's status
+    kStDone
+};
+
+// 32 candidates per warp, one block per (32 consecutive candidates, chunk); the
+// counters of the chunk (a.chunk_counters) must be zero on entry.  Every lane
+// runs the same simulation as batch_stream_kernel's sequential code, cut into
+// the states above: an iteration of the loop runs each state's code once, for
+// the lanes that are in it, and in an order that lets a lane go from one
+// arrival to the next in a single iteration when nothing holds it up (due
+// events: none; enqueue; serve: the head fits, dispatch; next).  Lanes keep
+// cursors of their own, so a lane with more to do for one request (events to
+// pop, heads to drop) falls behind the others for a while instead of making
+// them wait.
+__global__ void __launch_bounds__(kLanes)
+batch_simd_kernel(const BatchArgs a)
+{
+    constexpr int L = kLanes;
+    const int lane = threadIdx.x;
+    const int32_t Bw = a.Bp / kLanes;
+    const int32_t j = (int32_t)(blockIdx.x / Bw);
+    const int64_t b = (int64_t)(blockIdx.x % Bw) * kLanes + lane;
+    const bool chunked = batch_can_chunk(a);
+    if (!chunked && j > 0) return;              // the whole block
+    const BatchSmem S = batch_smem(a.M, a.G, a.P, a.T, a.H, L);
+    BLane ln;
+    ln.clk = (uint32_t)(S.clocks / 8) + lane;
+    ln.heap_t = (uint32_t)(S.heap_t / 8) + lane;
+    ln.heap_g = (uint32_t)S.heap_g + lane;           // bytes
+    ln.qhead = (uint32_t)(S.qhead / 4) + lane;
+    ln.qlen = (uint32_t)(S.qlen / 4) + lane;
+    ln.idle = ln.counters = ln.mrep = ln.gcfg = ln.moff = ln.goff = ln.gmod = 0;
+    const int64_t bb = b < a.Bp ? b : 0;
+    ln.g_mrep = a.t_mrep + bb; ln.g_gcfg = a.t_gcfg + bb;
+    ln.g_moff = a.t_moff + bb; ln.g_goff = a.t_goff + bb; ln.g_gmod = a.t_gmod + bb;
+    const bool valid = b < a.B;
+    const size_t cell = (size_t)j * a.B + (valid ? b : 0);
+    ln.g_counters = a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G);
+    ln.heap_n = 0;
+    ln.status = valid ? a.t_status[b] : 0;
+    ln.lat = a.latency + (size_t)(valid ? b : 0) * a.latency_stride;
+    ln.finish = a.finish + (size_t)(valid ? b : 0) * a.N;
+    ln.good = a.good + (size_t)(valid ? b : 0) * a.N;
+    ln.own_begin = 0; ln.direct = true; ln.record = true;
+    ln.carry_n = 0; ln.carry_fin = nullptr; ln.carry_req = nullptr;
+    batch_zero_state<L>(a, ln);
+
+    const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
+    const int64_t first = chunked ? chunk_first(a, j) : 0;
+    const int64_t end = chunked ? chunk_first(a, j + 1) : a.N;
+    int64_t i = first;
+    if (j > 0) {
+        unsigned char *carry = a.carry + cell * batch_carry_bytes();
+        ln.carry_fin = reinterpret_cast<double *>(carry + 16);
+        ln.carry_req = reinterpret_cast<uint32_t *>(carry + 16 + (size_t)kMaxCarry * 8);
+        ln.own_begin = (int32_t)first;
+        ln.direct = false;
+        i = first - a.warmup > 0 ? first - a.warmup : 0;
+        ln.record = false;                           // run-in
+    }
+    int st = kStDone;
+    double ts = 0.0;                                 // the current arrival
+    int32_t m = -1;
+    double serve_ts = 0.0;                           // what kStServe works on
+    int32_t serve_m = -1;
+    uint32_t serve_g = 0;
+    int serve_back = kStNext;                        // where kStServe returns to
+    if (valid && !(ln.status & MMS_STATUS_BAD_INDEX)) {
+        // take up arrival i (or what comes behind the last one): shared with kStNext below
+        st = kStNext;
+        --i;
+    } else if (valid) {
+        st = kStFinish;
+    }
+
+    while (__any_sync(0xFFFFFFFFu, st != kStDone)) {
+        if (st == kStNext) {
+            ++i;
+            if (i == first && !ln.record) {          // the run-in ends here
+                ln.record = true;
+                ln.status &= MMS_STATUS_BAD_INDEX;   // overflows of the run-in are not the chunk's
+                state_save<L>(a, ln, a.snap_start + cell * sb);
+            }
+            if (i >= end) {
+                st = end == a.N ? kStDrain : kStFinish;
+            } else {
+                ts = a.arrivals[i];
+                m = a.model_ids[i];
+                st = kStDue;
+            }
+        }
+        __syncwarp();
+        if (st == kStDue || st == kStDrain) {
+            const bool drain = st == kStDrain;
+            if (ln.heap_n > 0 && (drain || SM_F64(ln.heap_t) <= ts)) {
+                double te; uint32_t ge;
+                heap_pop<L>(a, ln, te, ge);
+                const int32_t pm = pick_model<L>(a, ln, ge);
+                if (pm >= 0) {
+                    serve_ts = te; serve_m = pm; serve_g = ge; serve_back = st;
+                    st = kStServe;
+                } else if (!drain) {
+                    st = kStEnqueue;                 // the reference breaks here, not continues
+                }
+            } else if (drain) {
+                for (int mm = 0; mm < a.M; ++mm)
+                    if ((int32_t)SM_U32(ln.qlen + mm * L) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+                st = kStFinish;
+            } else {
+                st = kStEnqueue;
+            }
+        }
+        __syncwarp();
+        if (st == kStEnqueue) {
+            int32_t mm = m;
+            if (mm >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; mm = -1; }
+            uint32_t lo = 0, hi = 0;
+            if (mm >= 0) { lo = tab_moff<L>(a, ln, mm); hi = tab_moff<L>(a, ln, mm + 1); }
+            if (lo == hi) {                          // :748-757 unknown model or no replica
+                put(ln, (int32_t)i, ts, false);
+                st = kStNext;
+            } else {
+                bool found;
+                const uint32_t pick = choose_and_enqueue<L>(a, ln, i, mm, lo, hi, found);
+                // the group's idle time is the clock of its first stage
+                const double idle = SM_F64(ln.clk + ((pick >> 8) & 0xFFu) * L);
+                if (found && ts >= idle) {           // :776-778
+                    serve_ts = ts; serve_m = mm; serve_g = pick & 0xFFu; serve_back = kStNext;
+                    st = kStServe;
+                } else {
+                    st = kStNext;
+                }
+            }
+        }
+        __syncwarp();
+        if (st == kStServe) {
+            // one step of serve_group(): drop a head that cannot make its deadline even
+            // alone (:677-686), or dispatch the batch behind a head that can, or — the
+            // queue is empty — go on with the group's next model (:709-713)
+            const uint32_t cfg = tab_gcfg<L>(a, ln, serve_g);
+            if ((int32_t)SM_U32(ln.qlen + serve_m * L) > 0) {
+                const int32_t r = queue_pop<L>(a, ln, serve_m);
+                const double dl = a.arrivals[r] + (double)a.slos[r];
+                if (meets_deadline<L>(a, ln, serve_ts, serve_m, cfg & 0xFFu, (cfg >> 8) & 0xFFu,
+                                      cfg >> 16, a.batch_cols[0], dl)) {
+                    dispatch_batch<L>(a, ln, serve_ts, (uint32_t)serve_m, serve_g, cfg, r);
+                    st = serve_back;
+                } else {
+                    count_add<L>(a, ln, 2 * a.M + serve_g, 1u);
+                    put(ln, r, a.arrivals[r], false);
+                }
+            } else {
+                serve_m = pick_model<L>(a, ln, serve_g);
+                if (serve_m < 0) st = serve_back;
+            }
+        }
+        __syncwarp();
+        if (st == kStFinish) {
+            if (chunked) {
+                if (!(ln.status & MMS_STATUS_BAD_INDEX))
+                    state_save<L>(a, ln, a.snap_end + cell * sb);
+                // the chain kernel decides whether this run, and with it its status word, counts
+                uint32_t *hdr = reinterpret_cast<uint32_t *>(a.carry + cell * batch_carry_bytes());
+                hdr[0] = ln.carry_n;
+                hdr[1] = ln.status;
+            } else if (ln.status) {
+                atomicOr(&a.status[b], ln.status);
+            }
+            st = kStDone;
+        }
+        __syncwarp();
+    }
+}
+
+// One thread per candidate (one candidate per warp): walks the chunk
+// boundaries in order; a chunk whose start state is equivalent to the true
+// state is kept (and the outputs of the requests it carried over are
+// written), any other is re-simulated from the true state.
 __global__ void __launch_bounds__(kLanes, kBatchBlocksPerSm)
 batch_chain_kernel(const BatchArgs a)
 {
-    if ((int)threadIdx.x >= a.lanes) return;
-    const int lane = threadIdx.x;
-    const int64_t b = (int64_t)blockIdx.x * a.lanes + lane;
+    if (threadIdx.x != 0) return;
+    const int64_t b = blockIdx.x;
     if (b >= a.B || !batch_can_chunk(a)) return;
     BLane ln;
-    batch_setup(a, ln, lane, b);
+    batch_setup(a, ln, b);
     if (ln.status & MMS_STATUS_BAD_INDEX) {             // bad tables: nothing was simulated
         atomicOr(&a.status[b], ln.status);
         return;

@@ -1120,6 +1120,12 @@ def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_re
     job = ResidentBatching(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info, latency,
                            latency_stride, batch_sizes, heap_capacity).launch()
     res, _ = job.results(per_request)
+    if heap_capacity == 0 and np.any(res.status & nat.STATUS_HEAP_OVERFLOW):
+        # the default capacity (G + 16 pending events) is what the simulation was seen to
+        # need; nothing bounds it, so a run that overflowed is repeated with room to spare
+        job = ResidentBatching(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
+                               latency, latency_stride, batch_sizes, 8 * G + 64).launch()
+        res, _ = job.results(per_request)
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         what = {nat.STATUS_HEAP_OVERFLOW: "event heap overflow (raise heap_capacity)",

@@ -274,6 +274,49 @@ def test_batching_kernel_golden(loaded, golden):
     same_counters(got, g)
 
 
+@pytest.mark.parametrize("copies", [32, 45])
+def test_batching_kernel_golden_32_to_a_warp(loaded, golden, copies):
+    """The same fixture (unknown models, a model without replica, +inf
+    latencies, replicated models) as a batch of identical candidates, which
+    takes the kernel that runs 32 candidates per warp: every copy — also in a
+    warp that is only partly filled — equals the reference's output."""
+    from mms_b200 import engine
+    g = golden("kernel_batching")
+    N = len(g["tstamps"])
+    lat = np.ascontiguousarray(g["stage_latency"], np.float32)
+    M, G, S, NB = lat.shape
+    trace = engine.DeviceTrace(g["tstamps"], g["model_ids"], g["slos"], M)
+    off, rep, info, T = engine.encode_dense(g["m_id2g_id"], g["num_stages"], M)
+    tile = lambda x: np.ascontiguousarray(np.tile(x, (copies, 1)))
+    res = engine.launch_batching(trace, copies, M, G, rep.shape[1], T, S, G, tile(off), tile(rep),
+                                 tile(info), lat, 0, [int(x) for x in g["batchsize_config"]])
+    for b in (0, 1, 31, copies - 1):
+        assert res.finish[b].tobytes() == g["finish"].tobytes(), b
+        assert np.array_equal(res.good[b], g["good"])
+        assert np.array_equal(res.model_num_requests[b], g["model_num_requests"])
+        assert np.array_equal(res.model_num_good[b], g["model_num_good"])
+        assert np.array_equal(res.group_num_requests[b], g["group_num_requests"])
+        assert np.array_equal(res.group_num_good[b], g["group_num_good"])
+
+
+def test_batching_heap_overflow_is_reported_and_retried(loaded):
+    """A pending-event heap that is too small is reported per candidate, and
+    the default capacity is raised and the run repeated when it overflows."""
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    case = cases.candidate_batch_case(num_candidates=32, duration=120.0, batching=True,
+                                      placement_seed=2, total_rate=200.0)
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(case.workload, names)
+    trace = engine.DeviceTrace(case.workload.arrivals, mids, slos, len(names))
+    table = engine.LatencyTable(profs, [1, 2, 4, 8])
+    enc = engine.encode_placements(case.placements, table, len(names))
+    with pytest.raises(RuntimeError, match="heap overflow"):
+        engine.run_batch_batching(trace, enc, table, heap_capacity=2)
+    engine.run_batch_batching(trace, enc, table)            # default capacity: fine
+
+
 def test_batching_candidates_golden(loaded, golden):
     from mms_b200 import cases, engine
     from mms_b200.simulator import workload_arrays

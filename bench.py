@@ -102,6 +102,9 @@ def parse_args():
     ap.add_argument("--rounds", type=int, default=0, help="validate+repair rounds (0 auto)")
     ap.add_argument("--repair-segments", type=int, default=0,
                     help="segments a repair runs per round (0 auto, <0 no cap)")
+    ap.add_argument("--hard", default="",
+                    help="candidates: chunk,run-in,rounds,repair-segments of the launch that holds "
+                         "the placements with mirror candidates (default: as the others)")
     ap.add_argument("--traces", type=int, default=0, help="sweep: traces per GPU (default 1024)")
     ap.add_argument("--placement-seed", type=int, default=-1,
                     help="seed of the candidate list (default: the rank; strong scaling: 0)")
@@ -450,8 +453,10 @@ def run_candidates(args, D):
     # B placements are scored; the ones with interchangeable groups bring mirror candidates
     # and go into a launch of their own beside the rest (engine.ResidentBatch)
     enc = engine.encode_placements(mine, ev.table, len(ev.model_names))
+    hard = engine.sim_options(*[int(x) for x in args.hard.split(",")]) if args.hard else None
     resident = engine.ResidentBatch(ev.trace, enc, ev.table, options=opts,
-                                    mirrors=not args.no_mirrors, split=not args.no_split)
+                                    mirrors=not args.no_mirrors, split=not args.no_split,
+                                    hard_options=hard)
     n_mirrors = sum(job.B - job.Bs for job in resident.jobs)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB of L2
     best = torch.zeros(2, dtype=torch.float64, device=dev)

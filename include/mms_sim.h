@@ -207,6 +207,7 @@ const char *mms_last_error(void);
 #define MMS_PROFILE_BATCH_STREAM 2  /* batch_stream_kernel                        */
 #define MMS_PROFILE_BATCH_CHAIN 3   /* batch_chain_kernel                         */
 #define MMS_PROFILE_CALL 4          /* a whole mms_sim_mixed call                 */
+#define MMS_PROFILE_BATCH_REPAIR 5  /* the repair rounds of mms_sim_batching      */
 int mms_profile_begin(void);
 int mms_profile_end(int32_t *launches, float *each_ms, int32_t *each_tag, int32_t capacity);
 

@@ -35,7 +35,7 @@ FLAG_CROWDED = 8
 STATIC_SCRATCH_BYTES = 32 << 20
 
 PROFILE_STREAM, PROFILE_CHAIN, PROFILE_BATCH_STREAM, PROFILE_BATCH_CHAIN = 0, 1, 2, 3
-PROFILE_CALL = 4
+PROFILE_CALL, PROFILE_BATCH_REPAIR = 4, 5
 
 
 def profile_begin():

@@ -655,8 +655,12 @@ namespace mms {
 struct BatchGeometry {
     int32_t simd, H, K, chunk_len, warmup, Bp;
     size_t smem_single, smem_simd;
-    size_t off_leaf, off_start, off_end, off_counters, off_carry, off_flag, off_tables, total;
+    size_t off_leaf, off_start, off_end, off_counters, off_carry, off_flag, off_tables, off_work,
+        total;
+    int32_t rounds;
 };
+
+constexpr int kBatchRepairRounds = 3;
 
 // Chunking and scratch layout of one mms_sim_batching call.
 static int plan_batching(int64_t N, const mms_placements *c, const mms_batching *bt,
@@ -710,6 +714,8 @@ static int plan_batching(int64_t N, const mms_placements *c, const mms_batching 
         off += align256((size_t)g->Bp * (4 * ((size_t)c->max_placed + c->max_groups + 1) +
                                           2 * ((size_t)c->num_models + c->max_groups + 2 +
                                                c->max_placed)) + 64);
+    g->rounds = kBatchRepairRounds;
+    g->off_work = off;     off += g->K > 1 ? align256(sizeof(uint32_t) * (cells + 64)) : 0;
     g->off_start = off;    off += g->K > 1 ? align256(cells * sb) : 0;
     g->off_end = off;      off += g->K > 1 ? align256(cells * sb) : 0;
     g->total = off;
@@ -841,6 +847,21 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
         stream_span.stop();
     }
     if (a.K > 1) {
+        // a few rounds of parallel repairs, one re-simulated chunk per warp, then the chain
+        a.work_count = (uint32_t *)(scratch + geo.off_work);
+        a.work_items = a.work_count + 64;
+        MMS_CUDA(cudaMemsetAsync(a.work_count, 0, sizeof(uint32_t) * 64, st));
+        MMS_TRY(allow_smem((const void *)batch_repair_kernel, geo.smem_single));
+        const int64_t bounds = (int64_t)B * (a.K - 1);
+        ProfileSpan repair_span(MMS_PROFILE_BATCH_REPAIR, st);
+        for (int r = 0; r < geo.rounds; ++r) {
+            a.round = r;
+            batch_validate_kernel<<<(unsigned)((bounds + 127) / 128), 128, 0, st>>>(a);
+            MMS_CUDA(cudaGetLastError());
+            batch_repair_kernel<<<(unsigned)bounds, kLanes, geo.smem_single, st>>>(a);
+            MMS_CUDA(cudaGetLastError());
+        }
+        repair_span.stop();
         ProfileSpan chain_span(MMS_PROFILE_BATCH_CHAIN, st);
         batch_chain_kernel<<<(unsigned)B, kLanes, geo.smem_single, st>>>(a);
         MMS_CUDA(cudaGetLastError());

@@ -81,6 +81,10 @@ struct BatchArgs {
     uint32_t *chunk_counters;     // [K][B][2M + 2G]
     unsigned char *carry;         // [K][B][carry_bytes]: outputs of carried requests
     int32_t *resimulated;         // [B] or null: chunks the chain kernel re-simulated
+    // repair rounds between the speculative pass and the chain kernel
+    uint32_t *work_count;         // [rounds]
+    uint32_t *work_items;         // [K * B]: chunk * B + candidate
+    int32_t round;
     // the candidates' tables as batch_simd_kernel reads them: checked, transposed to
     // [entry][Bp] (Bp = B rounded up to 32), built by batch_tables_kernel
     int32_t Bp;
@@ -664,46 +668,81 @@ __device__ inline void state_load(const BatchArgs &a, BLane &ln, unsigned char *
 //    replicated model are in the same order (ties included) relative to all
 //    such groups' last-stage clocks: dispatch compares them with '<' (:764).
 // Sufficient, not necessary: a failed check only costs a re-simulation.
-__device__ inline bool batch_states_equivalent(const BatchArgs &a, const BLane &ln,
-                                               unsigned char *saved, double tau)
+// X, Y: anything with heap_n(), heap_t(h), heap_g(h), qlen(m), qhead(m), idle(g),
+// clk(t); moff(m) / mrep(e): the candidate's replica lists.
+template <typename XS, typename YS, typename Moff, typename Mrep>
+__device__ inline bool batch_equivalent(const BatchArgs &a, const XS &x, const YS &y, double tau,
+                                        Moff moff, Mrep mrep)
 {
-    const StateView y = state_view(a, saved);
-    if (*y.heap_n != ln.heap_n) return false;
+    if (y.heap_n() != x.heap_n()) return false;
     double theta = tau;
-    for (uint32_t h = 0; h < ln.heap_n; ++h) {
-        const double t = SM_F64(ln.heap_t + h);
-        if (t != y.heap_t[h] || SM_U32(ln.heap_g + h) != y.heap_g[h]) return false;
+    for (uint32_t h = 0; h < x.heap_n(); ++h) {
+        const double t = x.heap_t(h);
+        if (t != y.heap_t(h) || x.heap_g(h) != y.heap_g(h)) return false;
         if (t < theta) theta = t;
     }
     for (int m = 0; m < a.M; ++m) {
-        const int32_t n = (int32_t)SM_U32(ln.qlen + m);
-        if (n != y.qlen[m]) return false;
-        if (n > 0 && (int32_t)SM_U32(ln.qhead + m) != y.qhead[m]) return false;
+        const int32_t n = x.qlen(m);
+        if (n != y.qlen(m)) return false;
+        if (n > 0 && x.qhead(m) != y.qhead(m)) return false;
     }
     for (int g = 0; g < a.G; ++g) {
-        const double x = SM_F64(ln.idle + g), v = y.idle[g];
-        if (!(x == v || (x <= tau && v <= tau))) return false;
+        const double u = x.idle(g), v = y.idle(g);
+        if (!(u == v || (u <= tau && v <= tau))) return false;
     }
     for (int t = 0; t < a.T; ++t) {
-        const double x = SM_F64(ln.clk + t), v = y.clk[t];
-        if (!(x == v || (x < theta && v < theta))) return false;
+        const double u = x.clk(t), v = y.clk(t);
+        if (!(u == v || (u < theta && v < theta))) return false;
     }
     // order of differing last-stage clocks among groups that share a model
     for (int m = 0; m < a.M; ++m) {
-        const uint32_t lo = SM_U16(ln.moff + m), hi = SM_U16(ln.moff + (m + 1));
+        const uint32_t lo = moff(m), hi = moff(m + 1);
         for (uint32_t e = lo; e + 1 < hi; ++e) {
-            const uint32_t eu = SM_U32(ln.mrep + e);
+            const uint32_t eu = mrep(e);
             const uint32_t su = ((eu >> 8) & 0xFFu) + ((eu >> 16) & 0xFFu) - 1;
-            const double xu = SM_F64(ln.clk + su), yu = y.clk[su];
+            const double xu = x.clk(su), yu = y.clk(su);
             for (uint32_t f = e + 1; f < hi; ++f) {
-                const uint32_t ev = SM_U32(ln.mrep + f);
+                const uint32_t ev = mrep(f);
                 const uint32_t sv = ((ev >> 8) & 0xFFu) + ((ev >> 16) & 0xFFu) - 1;
-                const double xv = SM_F64(ln.clk + sv), yv = y.clk[sv];
+                const double xv = x.clk(sv), yv = y.clk(sv);
                 if ((xu < xv) != (yu < yv) || (xu > xv) != (yu > yv)) return false;
             }
         }
     }
     return true;
+}
+
+// A saved state as batch_equivalent reads it.
+struct SavedState {
+    StateView v;
+    __device__ uint32_t heap_n() const { return *v.heap_n; }
+    __device__ double heap_t(uint32_t h) const { return v.heap_t[h]; }
+    __device__ uint32_t heap_g(uint32_t h) const { return v.heap_g[h]; }
+    __device__ int32_t qlen(int m) const { return v.qlen[m]; }
+    __device__ int32_t qhead(int m) const { return v.qhead[m]; }
+    __device__ double idle(int g) const { return v.idle[g]; }
+    __device__ double clk(int t) const { return v.clk[t]; }
+};
+
+// The state of a one-lane block on chip.
+struct ChipState {
+    const BLane &ln;
+    __device__ uint32_t heap_n() const { return ln.heap_n; }
+    __device__ double heap_t(uint32_t h) const { return SM_F64(ln.heap_t + h); }
+    __device__ uint32_t heap_g(uint32_t h) const { return SM_U32(ln.heap_g + h); }
+    __device__ int32_t qlen(int m) const { return (int32_t)SM_U32(ln.qlen + m); }
+    __device__ int32_t qhead(int m) const { return (int32_t)SM_U32(ln.qhead + m); }
+    __device__ double idle(int g) const { return SM_F64(ln.idle + g); }
+    __device__ double clk(int t) const { return SM_F64(ln.clk + t); }
+};
+
+__device__ inline bool batch_states_equivalent(const BatchArgs &a, const BLane &ln,
+                                               unsigned char *saved, double tau)
+{
+    const ChipState x{ln};
+    const SavedState y{state_view(a, saved)};
+    return batch_equivalent(a, x, y, tau, [&](int m) { return (uint32_t)SM_U16(ln.moff + m); },
+                            [&](uint32_t e) { return SM_U32(ln.mrep + e); });
 }
 
 __device__ inline void counters_store(const BatchArgs &a, const BLane &ln, uint32_t *dst)
@@ -953,6 +992,80 @@ batch_simd_kernel(const BatchArgs a)
     }
 }
 
+// Repair rounds.  One thread per (candidate, chunk j >= 1): does the state the
+// chunk's stored run started from (snap_start[j]) continue the state the run
+// of the chunk before it ended in (snap_end[j - 1])?  If not, that end state
+// becomes the chunk's start state and the chunk goes on the round's work list.
+// The end state may itself be wrong still (its chunk is on the list too);
+// then the next round, or the chain kernel, catches what follows from it.
+__global__ void batch_validate_kernel(const BatchArgs a)
+{
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (!batch_can_chunk(a) || t >= (int64_t)a.B * (a.K - 1)) return;
+    if (a.round > 0 && a.work_count[a.round - 1] == 0) return;      // nothing changed since
+    const int32_t j = (int32_t)(t / a.B) + 1;
+    const int64_t b = t % a.B;
+    const int64_t first = chunk_first(a, j);
+    if (first >= a.N) return;
+    const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
+    const size_t cell = (size_t)j * a.B + b;
+    unsigned char *end_prev = a.snap_end + (cell - a.B) * sb;
+    unsigned char *start = a.snap_start + cell * sb;
+    const uint32_t *hdr_prev = reinterpret_cast<const uint32_t *>(a.carry + (cell - a.B) * batch_carry_bytes());
+    // tables with a bad index: nothing was simulated, the chain kernel reports it
+    if (hdr_prev[1] & MMS_STATUS_BAD_INDEX) return;
+    const SavedState x{state_view(a, end_prev)}, y{state_view(a, start)};
+    const uint16_t *moff = a.model_off + (size_t)b * (a.M + 1);
+    const uint32_t *mrep = a.model_rep + (size_t)b * a.P;
+    if (batch_equivalent(a, x, y, a.arrivals[first], [&](int m) { return (uint32_t)moff[m]; },
+                         [&](uint32_t e) { return mrep[e]; }))
+        return;
+    // the heap is saved up to its size only: copy field by field
+    const StateView src = x.v, dst = y.v;
+    for (int k = 0; k < a.T; ++k) dst.clk[k] = src.clk[k];
+    for (int g = 0; g < a.G; ++g) dst.idle[g] = src.idle[g];
+    const uint32_t n = *src.heap_n;
+    for (uint32_t h = 0; h < n && h < (uint32_t)a.H; ++h) { dst.heap_t[h] = src.heap_t[h]; dst.heap_g[h] = src.heap_g[h]; }
+    for (int m = 0; m < a.M; ++m) { dst.qhead[m] = src.qhead[m]; dst.qlen[m] = src.qlen[m]; }
+    *dst.heap_n = n;
+    a.work_items[atomicAdd(&a.work_count[a.round], 1u)] = (uint32_t)((int64_t)j * a.B + b);
+}
+
+// One listed chunk per warp (thread 0 alone): re-simulated from the start state
+// batch_validate_kernel copied in.  That state is not known to be the true one
+// yet, so the outputs of carried requests are listed, not written, like in a
+// speculative run.
+__global__ void __launch_bounds__(kLanes, kBatchBlocksPerSm)
+batch_repair_kernel(const BatchArgs a)
+{
+    if (threadIdx.x != 0 || !batch_can_chunk(a)) return;
+    if (blockIdx.x >= a.work_count[a.round]) return;
+    const uint32_t item = a.work_items[blockIdx.x];
+    const int32_t j = (int32_t)(item / (uint32_t)a.B);
+    const int64_t b = item % (uint32_t)a.B;
+    BLane ln;
+    batch_setup(a, ln, b);
+    if (ln.status & MMS_STATUS_BAD_INDEX) return;
+    const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
+    const size_t cell = (size_t)j * a.B + b;
+    const int64_t first = chunk_first(a, j), end = chunk_first(a, j + 1);
+    unsigned char *carry = a.carry + cell * batch_carry_bytes();
+    ln.carry_fin = reinterpret_cast<double *>(carry + 16);
+    ln.carry_req = reinterpret_cast<uint32_t *>(carry + 16 + (size_t)kMaxCarry * 8);
+    ln.own_begin = (int32_t)first;
+    ln.direct = false;
+    state_load(a, ln, a.snap_start + cell * sb);
+    batch_zero_counters(a, ln);
+    for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
+    if (end == a.N) batch_drain(a, ln);
+    state_save<1>(a, ln, a.snap_end + cell * sb);
+    counters_store(a, ln, a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G));
+    uint32_t *hdr = reinterpret_cast<uint32_t *>(carry);
+    hdr[0] = ln.carry_n;
+    hdr[1] = ln.status;
+    if (a.resimulated) atomicAdd(&a.resimulated[b], 1);
+}
+
 // One thread per candidate (one candidate per warp): walks the chunk
 // boundaries in order; a chunk whose start state is equivalent to the true
 // state is kept (and the outputs of the requests it carried over are
@@ -1000,7 +1113,7 @@ batch_chain_kernel(const BatchArgs a)
         counters_store(a, ln, a.chunk_counters + cell * n_counters);
         status |= ln.status;
     }
-    if (a.resimulated) a.resimulated[b] = redone;
+    if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
     if (status) atomicOr(&a.status[b], status);
 }
 

@@ -869,9 +869,12 @@ class ResidentBatch:
     still in theirs.  Results are the same as from one call."""
 
     def __init__(self, trace, enc: EncodedBatch, table: LatencyTable, group_good=False,
-                 pinned=False, options=None, mirrors=True, split=True, crowded=False):
+                 pinned=False, options=None, mirrors=True, split=True, crowded=False,
+                 hard_options=None):
         """crowded: other launches will be filling the GPU while this batch
-        repairs its chunks (a pipelined part that is not the last)."""
+        repairs its chunks (a pipelined part that is not the last).
+        hard_options: sim_options for the launch that holds the placements with
+        mirrors, when the batch is split (default: `options`)."""
         self.trace, self.enc = trace, enc
         dev = trace.device
         ext_owner = [b for b, cl in (enc.twins or []) if mirror_swaps(cl)] if mirrors else []
@@ -889,13 +892,15 @@ class ResidentBatch:
             # the first of two calls repairs while the second one fills the GPU
             flags = nat.FLAG_CROWDED if (crowded or k + 1 < len(parts)) else 0
             ext = e.with_mirrors() if mirrors else None
+            opts_k = hard_options if (hard_options is not None and len(parts) > 1 and k == 0) \
+                else options
             if ext is not None:
                 off, rep, info, partner, swap = ext
                 job = _prepare(trace, len(partner), e.M, e.G, e.P, e.T, e.S, e.C, off, rep, info,
-                               lat, 0, flags, group_good, pinned, options, e.B, partner, swap)
+                               lat, 0, flags, group_good, pinned, opts_k, e.B, partner, swap)
             else:
                 job = _prepare(trace, e.B, e.M, e.G, e.P, e.T, e.S, e.C, e.model_off, e.model_rep,
-                               e.group_info, lat, 0, flags, group_good, pinned, options)
+                               e.group_info, lat, 0, flags, group_good, pinned, opts_k)
             self.jobs.append(job)
             self.h2d_bytes += job.h2d
 

@@ -178,6 +178,7 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
     ln.dec = a.dec_wide ? static_cast<void *>(static_cast<uint16_t *>(a.decisions) + 4 * b)
                         : static_cast<void *>(static_cast<uint8_t *>(a.decisions) + 4 * b);
     ln.dec_pitch = (uint32_t)a.dec_pitch;
+    ln.dec_word = 0;
     ln.rows = reinterpret_cast<const uint4 *>(a.rep_rows) + row_index(a, b, 0);
     ln.rows_b = ln.rows + row_plane(a);
     ln.rep_raw = a.model_rep + (size_t)b * a.P;

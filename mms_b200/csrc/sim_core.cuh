@@ -87,6 +87,9 @@ struct Lane {
                               //   byte (up to 126 groups), or | accepted << 15 in 16 bits
     uint32_t dec_pitch;       // elements between consecutive requests in that array
     bool dec_wide;            // 16-bit decisions
+    uint32_t dec_word;        // byte decisions: the records of up to four consecutive requests,
+                              //   gathered here and stored as one 32-bit word behind every fourth
+                              //   request (recorded stretches begin at multiples of 4)
     const uint4 *rows;        // [M + 1] replica rows of this candidate (global memory,
                               //   kLanes apart: the rows of 32 consecutive candidates for one
                               //   model are contiguous, so a warp fetches them coalesced): the
@@ -378,13 +381,20 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     if (record) {   // :611, :617-618 are tallied from this record by count_kernel
         // four consecutive requests of a candidate sit side by side (count_kernel reads them
         // with one load): element (i, b) is at ((i / 4) * pitch + b) * 4 + i % 4
-        const size_t at = ((size_t)(i >> 2) * ln.dec_pitch) * 4 + (size_t)(i & 3);
-        if (ln.dec_wide)
+        if (ln.dec_wide) {
+            const size_t at = ((size_t)(i >> 2) * ln.dec_pitch) * 4 + (size_t)(i & 3);
             static_cast<uint16_t *>(ln.dec)[at] =
                 (uint16_t)(found ? (g + 1u) | (accept ? 0x8000u : 0u) : 0u);
-        else
-            static_cast<uint8_t *>(ln.dec)[at] =
-                (uint8_t)(found ? (g + 1u) | (accept ? 0x80u : 0u) : 0u);
+        } else {
+            // one 32-bit store per four requests instead of four byte stores: a quarter
+            // of the store instructions, and every sector a warp writes is written whole
+            const uint32_t rec = found ? (g + 1u) | (accept ? 0x80u : 0u) : 0u;
+            ln.dec_word |= rec << (8 * (i & 3));
+            if ((i & 3) == 3 || i == p.last) {
+                static_cast<uint32_t *>(ln.dec)[(size_t)(i >> 2) * ln.dec_pitch] = ln.dec_word;
+                ln.dec_word = 0;
+            }
+        }
     }
     if (kFull && record) {
         finish_out[i] = fin;

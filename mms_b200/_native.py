@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libmms_sim.so")
+# MMS_B200_LIB names another build of the library (development: comparing two builds)
+LIB_PATH = os.environ.get("MMS_B200_LIB") or os.path.join(_PKG_DIR, "libmms_sim.so")
 
 MMS_OK = 0
 ERRORS = {

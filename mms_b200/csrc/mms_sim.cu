@@ -220,6 +220,12 @@ __device__ inline void init_pipe(const KernelArgs &a, Pipe &p, int64_t b)
     p.last = (int32_t)(a.N - 1);
 }
 
+// What the slim form of the narrow step (sim_step, kSlim) takes for granted.
+__device__ inline bool slim_shape(const KernelArgs &a)
+{
+    return a.lat_smem_elems != 0 && a.lat_f64 != 0 && !a.dec_wide;
+}
+
 // Extra shared memory of the kernels that repair: the state the previous run
 // stored (f64 [T]) and the scratch list of states_equivalent (u8 [G]).
 __device__ inline void repair_scratch(const KernelArgs &a, const SmemLayout &L, int lane,
@@ -432,9 +438,16 @@ sim_repair_kernel(const KernelArgs a)
     const int64_t m_first = mirrors_of(a, b, m_end);
     const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
     a.own_rewritten[(size_t)j * a.B + b] = 1;
-    a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(
-        a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
-        a.repair_cap, ~0ull, m_first, m_end, own_pure);
+    constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
+    if (kCanSlim && slim_shape(a))
+        a.repair_from[(size_t)j * a.B + b] =
+            run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim>(
+                a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
+                a.repair_cap, ~0ull, m_first, m_end, own_pure);
+    else
+        a.repair_from[(size_t)j * a.B + b] = run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(
+            a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
+            a.repair_cap, ~0ull, m_first, m_end, own_pure);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 
@@ -515,9 +528,15 @@ sim_chain_kernel(const KernelArgs a)
         ++redone;
         const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
         a.own_rewritten[(size_t)j * a.B + b] = 1;
-        run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(a, ln, p, b, j, begin, true, true,
-                                                       old_state, stale_buf, q_begin, 0, ~0ull,
-                                                       m_first, m_end, own_pure);
+        constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
+        if (kCanSlim && slim_shape(a))
+            run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim>(
+                a, ln, p, b, j, begin, true, true, old_state, stale_buf, q_begin, 0, ~0ull,
+                m_first, m_end, own_pure);
+        else
+            run_chunk<kFull, kGroupGood, kLegacy, kNarrow>(a, ln, p, b, j, begin, true, true,
+                                                           old_state, stale_buf, q_begin, 0, ~0ull,
+                                                           m_first, m_end, own_pure);
         a.repair_from[(size_t)j * a.B + b] = -1;
     }
     if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);

@@ -226,7 +226,7 @@ __device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X
 //       segments (0 = no cap).
 // Returns -1 when the chunk is finished (ran to its end, or settled), else
 // the segment at which the capped repair has to be continued.
-template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false>
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false, bool kSlim = false>
 __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                                     int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
@@ -257,23 +257,33 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
         const uint32_t ring = ln.clk + (uint32_t)a.T * kLanes;
         double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
         double r = 0.0;
-        for (; i < span_end; ++i) {
-            const double d = sim_step<kFull, kGroupGood, kLegacy, kNarrow>(ln, p, i, record,
-                                                                           fin_out, good_out);
-            if (i < body_end) {
-                SM_F64(ring + (uint32_t)(i & 7) * kLanes) = d;
-                if ((i & 7) == 7) {
+        auto one = [&](int32_t ii) {
+            const double d = sim_step<kFull, kGroupGood, kLegacy, kNarrow, kSlim>(
+                ln, p, ii, record, fin_out, good_out);
+            if (ii < body_end) {
+                SM_F64(ring + (uint32_t)(ii & 7) * kLanes) = d;
+                if ((ii & 7) == 7) {
                     p0 += SM_F64(ring); p1 += SM_F64(ring + kLanes);
                     p2 += SM_F64(ring + 2 * kLanes); p3 += SM_F64(ring + 3 * kLanes);
                     p4 += SM_F64(ring + 4 * kLanes); p5 += SM_F64(ring + 5 * kLanes);
                     p6 += SM_F64(ring + 6 * kLanes); p7 += SM_F64(ring + 7 * kLanes);
-                    if (i + 1 == body_end)
+                    if (ii + 1 == body_end)
                         r = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7));
                 }
             } else {
                 r += d;
             }
+        };
+#ifndef MMS_SLIM_UNROLL
+#define MMS_SLIM_UNROLL 1
+#endif
+        if constexpr (kSlim && MMS_SLIM_UNROLL) {
+            // three requests per turn: the values fetched ahead rotate through three sets of
+            // registers, and after three steps every set is back where it was — no moves
+            for (; i + 3 <= span_end; i += 3) { one(i); one(i + 1); one(i + 2); }
         }
+#pragma unroll 1
+        for (; i < span_end; ++i) one(i);
         if (!record) {
             // a mirror starts its chunk with interchangeable groups exchanged
             for (int k = 0; k < 4 && swap_pairs != ~0ull; ++k) {

@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <type_traits>
 
 #include "mms_sim.h"
 
@@ -158,7 +159,7 @@ __device__ __forceinline__ void pipe_prime(Lane &ln, Pipe &p, int32_t i)
     p.ts1 = __ldg(p.arrivals + o1); p.slo1 = __ldg(p.slos + o1);
     p.m1 = clean_model(ln, __ldg(p.model_ids + o1));
     p.ts2 = __ldg(p.arrivals + o2); p.slo2 = __ldg(p.slos + o2);
-    p.m2 = clean_model(ln, __ldg(p.model_ids + o2));
+    p.m2 = __ldg(p.model_ids + o2);            // checked by the step that fetches its row
     p.r = fetch_row(ln, p.m);
     p.r1 = fetch_row(ln, p.m1);
     p.rb = fetch_row_b(ln, p.m, p.r);
@@ -194,16 +195,25 @@ __device__ __forceinline__ uint32_t rep_to_last(uint32_t e)
 //   kNarrow  for a warp in which ONE lane works (the serial repairs): real
 //            branches, so that only the replicas and the stages that exist are
 //            touched — about a quarter fewer instructions, and no other lane to hold up.
-template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false>
+//   kSlim    (with kNarrow) what the caller checked once is known at compile
+//            time here: the latency table is on chip as doubles and decisions
+//            are bytes.  The pipelines of 1, 2, 4 and 8 stages — every power-
+//            of-two partition of a node — then run as straight-line code (all
+//            loads first, one chain, the stores), without a test per stage.
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false, bool kSlim = false>
 __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool record,
                                            double *finish_out, uint8_t *good_out)
 {
+    static_assert(!kSlim || (kNarrow && !kLegacy && !kFull), "kSlim is a form of the narrow step");
     const double ts = p.ts;
     const float slo_f = p.slo;
     const int32_t m = p.m;
     const uint32_t e0 = p.r.x, e1 = p.r.y, e2 = p.r.z, e3 = p.r.w;
 
     // ---- state-independent fetches for the requests behind this one -------
+    // the model id fetched a step ago is looked at only now, a whole step after its load
+    // was issued (checking it when it is fetched would make every step wait for that load)
+    p.m2 = clean_model(ln, p.m2);
     const uint4 r2 = fetch_row(ln, p.m2);
     const uint4 rb1 = fetch_row_b(ln, p.m1, p.r1);
     const size_t i3 = (size_t)(i + 3 < p.last ? i + 3 : p.last) * p.pitch;
@@ -273,7 +283,43 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     double f;
     double t0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t6 = 0, t7 = 0;
     (void)t2; (void)t3; (void)t4; (void)t5; (void)t6; (void)t7;
-    if constexpr (kNarrow && !kLegacy) {
+    bool slim_done = false;          // kSlim: the chain, the test and the stores are through
+    bool slim_accept = false;
+    if constexpr (kSlim) {
+        const uint32_t lr = ln.lat_sm + row;             // the table holds doubles
+        auto run = [&](auto depth) {
+            constexpr int kDepth = decltype(depth)::value;
+            double k[kDepth], l[kDepth], t[kDepth];
+#pragma unroll
+            for (int s = 0; s < kDepth; ++s) {
+                k[s] = SM_F64(ck + s * kLanes);
+                l[s] = SM_F64(lr + s);
+            }
+            double cur = ts;
+#pragma unroll
+            for (int s = 0; s < kDepth; ++s) {           // :605-608
+                cur = tmax(cur, k[s]) + l[s];
+                t[s] = cur;
+            }
+            f = cur + kOverhead;                         // :610
+            slim_accept = found && (f - ts <= (double)slo_f);     // :613
+            if (slim_accept) {
+#pragma unroll
+                for (int s = 0; s < kDepth; ++s) SM_F64(ck + s * kLanes) = t[s];
+            }
+            slim_done = true;
+        };
+        switch (ns) {
+            case 1: run(std::integral_constant<int, 1>{}); break;
+            case 2: run(std::integral_constant<int, 2>{}); break;
+            case 4: run(std::integral_constant<int, 4>{}); break;
+            case 8: run(std::integral_constant<int, 8>{}); break;
+            default: break;                              // other depths: the general code below
+        }
+    }
+    if (slim_done) {
+        t0 = 0;
+    } else if constexpr (kNarrow && !kLegacy) {
         // :605-610 stage by stage, as far as the group has stages
         auto lat = [&](uint32_t k) { return lat_at(ln, row + k); };
         t0 = tmax(ts, SM_F64(ck)) + lat(0);
@@ -363,9 +409,9 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
             f = t + kOverhead;                               // :610
         }
     }
-    const bool accept = found && (f - ts <= (double)slo_f);   // :613-619
+    const bool accept = slim_done ? slim_accept : (found && (f - ts <= (double)slo_f));   // :613-619
     const double fin = accept ? f : ts;
-    if (accept) {
+    if (accept && !slim_done) {
         SM_F64(ck) = t0;
         if (ns > 1) SM_F64(ck + kLanes) = t1;
         if (ns > 2) SM_F64(ck + 2 * kLanes) = t2;
@@ -381,7 +427,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     if (record) {   // :611, :617-618 are tallied from this record by count_kernel
         // four consecutive requests of a candidate sit side by side (count_kernel reads them
         // with one load): element (i, b) is at ((i / 4) * pitch + b) * 4 + i % 4
-        if (ln.dec_wide) {
+        if (!kSlim && ln.dec_wide) {
             const size_t at = ((size_t)(i >> 2) * ln.dec_pitch) * 4 + (size_t)(i & 3);
             static_cast<uint16_t *>(ln.dec)[at] =
                 (uint16_t)(found ? (g + 1u) | (accept ? 0x8000u : 0u) : 0u);
@@ -404,7 +450,7 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     // ---- advance the pipe ---------------------------------------------------
     p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1; p.r = p.r1; p.rb = rb1;
     p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2; p.r1 = r2;
-    p.ts2 = ts3; p.slo2 = slo3; p.m2 = clean_model(ln, m3raw);
+    p.ts2 = ts3; p.slo2 = slo3; p.m2 = m3raw;      // unchecked until the next step fetches its row
     return fin - ts;
 }
 

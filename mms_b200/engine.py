@@ -847,10 +847,10 @@ SPLIT_MIN_HARD = 32       # ... and placements with mirrors
 # Run-in of the launch that holds the placements with mirrors, when a batch is split (the
 # library's default is 2048): the few chunks of these placements that no stored run continues
 # are re-simulated one after the other by single lanes, and the longest such chain decides when
-# the launch ends.  A longer run-in costs its speculative pass a fifth more and halves those
-# chains: measured over eight candidate lists, the slowest step 23.7 ms instead of 28.4 and the
-# mean 23.1 instead of 23.7.
-HARD_RUN_IN = 3072
+# the launch ends.  A longer run-in makes its speculative pass longer (which delays the other
+# launch's) and those chains shorter.  Measured over four candidate lists, slowest / mean step:
+# 24.7 / 22.6 ms with 2048, 22.6 / 22.0 ms with 2560, 22.9 / 22.3 ms with 3072.
+HARD_RUN_IN = 2560
 _SIDE_STREAMS = {}
 
 

@@ -24,23 +24,17 @@
 // wrote) but lists them, and the chain kernel applies the list when it
 // accepts the chunk.
 //
-// Two forms of the speculative pass.  The control flow of this simulator
-// (heap pops, queue scans, dropped heads, batch growth) differs from
-// candidate to candidate, so 32 candidates that run the sequential code side
-// by side in a warp spend most of their time waiting for each other, and one
-// candidate per warp leaves 31 lanes idle.  batch_simd_kernel runs 32
-// candidates per warp as a STATE MACHINE instead: every lane has its own
-// cursor into the trace and is in one of a few states (due events, enqueue,
-// one step of serving, next arrival); an iteration of the warp's loop runs
-// the code of each state once for the lanes that are in it, and a lane passes
-// through as many states per iteration as its requests allow — nothing makes
-// a lane wait for another lane's request.  The candidates' tables are read
-// from global memory (transposed so that a warp's loads coalesce) and the
+// Two forms of the speculative pass.  batch_simd_kernel runs 32 candidates per
+// warp, in step over the arrivals of one chunk; the candidates' tables are
+// read from global memory (transposed so that a warp's loads coalesce) and the
 // counters are added to global memory without a return value, which leaves
-// shared memory to the mutable state alone.  batch_stream_kernel (one
-// candidate per warp, plain sequential code) serves batches too small to fill
-// warps, and batch_chain_kernel's serial repairs.  All of them work on the
-// same helpers, templated on the number of lanes L a block interleaves.
+// shared memory to the mutable state alone (clocks, heap, queues: about 1.4 KB
+// per candidate).  batch_stream_kernel (one candidate per warp) serves batches
+// too small to fill warps.  The repairs — batch_repair_kernel, batch_chain_kernel
+// — run one chunk or candidate per warp: what they re-simulate is a dependent
+// chain whose latency counts, and a lone lane gets through it fastest.  All of
+// them work on the same helpers, templated on the number of lanes L a block
+// interleaves.
 #pragma once
 #include "sim_core.cuh"
 
@@ -550,45 +544,49 @@ __device__ inline uint32_t choose_and_enqueue(const BatchArgs &a, BLane &ln, int
     return pick;
 }
 
-// Arrival i, :736-778 (plain sequential form).
+// Arrival i, :736-778.
+template <int L>
 __device__ inline void batch_arrival(const BatchArgs &a, BLane &ln, int64_t i)
 {
     const double ts = a.arrivals[i];
     // :739-744 groups whose first stage became free before this arrival
     while (ln.heap_n > 0 && SM_F64(ln.heap_t) <= ts) {
         double te; uint32_t ge;
-        heap_pop<1>(a, ln, te, ge);
-        const int32_t pm = pick_model<1>(a, ln, ge);
+        heap_pop<L>(a, ln, te, ge);
+        const int32_t pm = pick_model<L>(a, ln, ge);
         if (pm < 0) break;                     // the reference breaks here, not continues
-        serve_group<1>(a, ln, te, pm, ge);
+        serve_group<L>(a, ln, te, pm, ge);
     }
     int32_t m = a.model_ids[i];
     if (m >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; m = -1; }
     uint32_t lo = 0, hi = 0;
-    if (m >= 0) { lo = SM_U16(ln.moff + m); hi = SM_U16(ln.moff + (m + 1)); }
+    if (m >= 0) { lo = tab_moff<L>(a, ln, m); hi = tab_moff<L>(a, ln, m + 1); }
     if (lo == hi) {                            // :748-757 unknown model or no replica
         put(ln, (int32_t)i, ts, false);
         return;
     }
     bool found;
-    const uint32_t pick = choose_and_enqueue<1>(a, ln, i, m, lo, hi, found);
+    const uint32_t pick = choose_and_enqueue<L>(a, ln, i, m, lo, hi, found);
     const uint32_t g = pick & 0xFFu;
-    if (found && ts >= SM_F64(ln.idle + g))   // :776-778
-        serve_group<1>(a, ln, ts, m, g);
+    // a group's idle time is the clock of its first stage (kept twice only with L == 1)
+    const double idle = L == 1 ? SM_F64(ln.idle + g) : SM_F64(ln.clk + ((pick >> 8) & 0xFFu) * L);
+    if (found && ts >= idle)                   // :776-778
+        serve_group<L>(a, ln, ts, m, g);
 }
 
 // After the last arrival, :781-790.
+template <int L>
 __device__ inline void batch_drain(const BatchArgs &a, BLane &ln)
 {
     while (ln.heap_n > 0) {
         double te; uint32_t ge;
-        heap_pop<1>(a, ln, te, ge);
-        const int32_t pm = pick_model<1>(a, ln, ge);
+        heap_pop<L>(a, ln, te, ge);
+        const int32_t pm = pick_model<L>(a, ln, ge);
         if (pm < 0) continue;
-        serve_group<1>(a, ln, te, pm, ge);
+        serve_group<L>(a, ln, te, pm, ge);
     }
     for (int m = 0; m < a.M; ++m)
-        if ((int32_t)SM_U32(ln.qlen + m) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
+        if ((int32_t)SM_U32(ln.qlen + m * L) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
 }
 
 // A saved state, see batch_state_bytes.
@@ -790,14 +788,14 @@ batch_stream_kernel(const BatchArgs a)
             ln.direct = false;
             ln.record = false;
             for (int64_t i = first - a.warmup > 0 ? first - a.warmup : 0; i < first; ++i)
-                batch_arrival(a, ln, i);
+                batch_arrival<1>(a, ln, i);
             ln.record = true;
             ln.status &= MMS_STATUS_BAD_INDEX;       // overflows of the run-in are not the chunk's
             batch_zero_counters(a, ln);
             state_save<1>(a, ln, a.snap_start + cell * sb);
         }
-        for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
-        if (end == a.N) batch_drain(a, ln);
+        for (int64_t i = first; i < end; ++i) batch_arrival<1>(a, ln, i);
+        if (end == a.N) batch_drain<1>(a, ln);
         if (chunked) state_save<1>(a, ln, a.snap_end + cell * sb);
     }
     counters_store(a, ln, a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G));
@@ -811,27 +809,14 @@ batch_stream_kernel(const BatchArgs a)
     }
 }
 
-// States of a lane of batch_simd_kernel.
-enum : int {
-    kStDue = 0,      // groups whose first stage became free before the current arrival (:739-744)
-    kStEnqueue,      // the current arrival joins its model's queue (:746-778)
-    kStServe,        // one step of handle_batched_requests for (serve_ts, serve_m, serve_g)
-    kStNext,         // on to the next arrival
-    kStDrain,        // behind the last arrival: the heap is emptied (:781-787)
-    kStFinish,       // store the end state and the run's status
-    kStDone
-};
-
 // 32 candidates per warp, one block per (32 consecutive candidates, chunk); the
-// counters of the chunk (a.chunk_counters) must be zero on entry.  Every lane
-// runs the same simulation as batch_stream_kernel's sequential code, cut into
-// the states above: an iteration of the loop runs each state's code once, for
-// the lanes that are in it, and in an order that lets a lane go from one
-// arrival to the next in a single iteration when nothing holds it up (due
-// events: none; enqueue; serve: the head fits, dispatch; next).  Lanes keep
-// cursors of their own, so a lane with more to do for one request (events to
-// pop, heads to drop) falls behind the others for a while instead of making
-// them wait.
+// counters of the chunk (a.chunk_counters) must be zero on entry.  The lanes go
+// through the chunk's arrivals in step — the trace values are one broadcast
+// load per warp — and each runs the sequential code for its candidate; where
+// their control flow differs (events to pop, heads to drop, batch sizes,
+// pipeline depths) the warp serialises, and it is whole again at the next
+// arrival.  What this form shares with the one-candidate-per-warp kernels is
+// every helper above; what differs is where tables and counters live.
 __global__ void __launch_bounds__(kLanes)
 batch_simd_kernel(const BatchArgs a)
 {
@@ -850,145 +835,55 @@ batch_simd_kernel(const BatchArgs a)
     ln.qhead = (uint32_t)(S.qhead / 4) + lane;
     ln.qlen = (uint32_t)(S.qlen / 4) + lane;
     ln.idle = ln.counters = ln.mrep = ln.gcfg = ln.moff = ln.goff = ln.gmod = 0;
-    const int64_t bb = b < a.Bp ? b : 0;
+    const bool valid = b < a.B;
+    const int64_t bb = valid ? b : 0;
     ln.g_mrep = a.t_mrep + bb; ln.g_gcfg = a.t_gcfg + bb;
     ln.g_moff = a.t_moff + bb; ln.g_goff = a.t_goff + bb; ln.g_gmod = a.t_gmod + bb;
-    const bool valid = b < a.B;
-    const size_t cell = (size_t)j * a.B + (valid ? b : 0);
+    const size_t cell = (size_t)j * a.B + bb;
     ln.g_counters = a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G);
     ln.heap_n = 0;
     ln.status = valid ? a.t_status[b] : 0;
-    ln.lat = a.latency + (size_t)(valid ? b : 0) * a.latency_stride;
-    ln.finish = a.finish + (size_t)(valid ? b : 0) * a.N;
-    ln.good = a.good + (size_t)(valid ? b : 0) * a.N;
+    ln.lat = a.latency + (size_t)bb * a.latency_stride;
+    ln.finish = a.finish + (size_t)bb * a.N;
+    ln.good = a.good + (size_t)bb * a.N;
     ln.own_begin = 0; ln.direct = true; ln.record = true;
     ln.carry_n = 0; ln.carry_fin = nullptr; ln.carry_req = nullptr;
     batch_zero_state<L>(a, ln);
+    // a lane simulates when it has a candidate and the candidate's tables are sound
+    const bool run = valid && !(ln.status & MMS_STATUS_BAD_INDEX);
 
     const size_t sb = batch_state_bytes(a.M, a.G, a.T, a.H);
     const int64_t first = chunked ? chunk_first(a, j) : 0;
     const int64_t end = chunked ? chunk_first(a, j + 1) : a.N;
-    int64_t i = first;
     if (j > 0) {
         unsigned char *carry = a.carry + cell * batch_carry_bytes();
         ln.carry_fin = reinterpret_cast<double *>(carry + 16);
         ln.carry_req = reinterpret_cast<uint32_t *>(carry + 16 + (size_t)kMaxCarry * 8);
         ln.own_begin = (int32_t)first;
         ln.direct = false;
-        i = first - a.warmup > 0 ? first - a.warmup : 0;
         ln.record = false;                           // run-in
+        for (int64_t i = first - a.warmup > 0 ? first - a.warmup : 0; i < first; ++i) {
+            if (run) batch_arrival<L>(a, ln, i);
+            __syncwarp();
+        }
+        ln.record = true;
+        ln.status &= MMS_STATUS_BAD_INDEX;           // overflows of the run-in are not the chunk's
+        if (run) state_save<L>(a, ln, a.snap_start + cell * sb);
     }
-    int st = kStDone;
-    double ts = 0.0;                                 // the current arrival
-    int32_t m = -1;
-    double serve_ts = 0.0;                           // what kStServe works on
-    int32_t serve_m = -1;
-    uint32_t serve_g = 0;
-    int serve_back = kStNext;                        // where kStServe returns to
-    if (valid && !(ln.status & MMS_STATUS_BAD_INDEX)) {
-        // take up arrival i (or what comes behind the last one): shared with kStNext below
-        st = kStNext;
-        --i;
-    } else if (valid) {
-        st = kStFinish;
+    for (int64_t i = first; i < end; ++i) {
+        if (run) batch_arrival<L>(a, ln, i);
+        __syncwarp();
     }
-
-    while (__any_sync(0xFFFFFFFFu, st != kStDone)) {
-        if (st == kStNext) {
-            ++i;
-            if (i == first && !ln.record) {          // the run-in ends here
-                ln.record = true;
-                ln.status &= MMS_STATUS_BAD_INDEX;   // overflows of the run-in are not the chunk's
-                state_save<L>(a, ln, a.snap_start + cell * sb);
-            }
-            if (i >= end) {
-                st = end == a.N ? kStDrain : kStFinish;
-            } else {
-                ts = a.arrivals[i];
-                m = a.model_ids[i];
-                st = kStDue;
-            }
-        }
-        __syncwarp();
-        if (st == kStDue || st == kStDrain) {
-            const bool drain = st == kStDrain;
-            if (ln.heap_n > 0 && (drain || SM_F64(ln.heap_t) <= ts)) {
-                double te; uint32_t ge;
-                heap_pop<L>(a, ln, te, ge);
-                const int32_t pm = pick_model<L>(a, ln, ge);
-                if (pm >= 0) {
-                    serve_ts = te; serve_m = pm; serve_g = ge; serve_back = st;
-                    st = kStServe;
-                } else if (!drain) {
-                    st = kStEnqueue;                 // the reference breaks here, not continues
-                }
-            } else if (drain) {
-                for (int mm = 0; mm < a.M; ++mm)
-                    if ((int32_t)SM_U32(ln.qlen + mm * L) != 0) ln.status |= MMS_STATUS_QUEUE_LEFT;
-                st = kStFinish;
-            } else {
-                st = kStEnqueue;
-            }
-        }
-        __syncwarp();
-        if (st == kStEnqueue) {
-            int32_t mm = m;
-            if (mm >= a.M) { ln.status |= MMS_STATUS_BAD_INDEX; mm = -1; }
-            uint32_t lo = 0, hi = 0;
-            if (mm >= 0) { lo = tab_moff<L>(a, ln, mm); hi = tab_moff<L>(a, ln, mm + 1); }
-            if (lo == hi) {                          // :748-757 unknown model or no replica
-                put(ln, (int32_t)i, ts, false);
-                st = kStNext;
-            } else {
-                bool found;
-                const uint32_t pick = choose_and_enqueue<L>(a, ln, i, mm, lo, hi, found);
-                // the group's idle time is the clock of its first stage
-                const double idle = SM_F64(ln.clk + ((pick >> 8) & 0xFFu) * L);
-                if (found && ts >= idle) {           // :776-778
-                    serve_ts = ts; serve_m = mm; serve_g = pick & 0xFFu; serve_back = kStNext;
-                    st = kStServe;
-                } else {
-                    st = kStNext;
-                }
-            }
-        }
-        __syncwarp();
-        if (st == kStServe) {
-            // one step of serve_group(): drop a head that cannot make its deadline even
-            // alone (:677-686), or dispatch the batch behind a head that can, or — the
-            // queue is empty — go on with the group's next model (:709-713)
-            const uint32_t cfg = tab_gcfg<L>(a, ln, serve_g);
-            if ((int32_t)SM_U32(ln.qlen + serve_m * L) > 0) {
-                const int32_t r = queue_pop<L>(a, ln, serve_m);
-                const double dl = a.arrivals[r] + (double)a.slos[r];
-                if (meets_deadline<L>(a, ln, serve_ts, serve_m, cfg & 0xFFu, (cfg >> 8) & 0xFFu,
-                                      cfg >> 16, a.batch_cols[0], dl)) {
-                    dispatch_batch<L>(a, ln, serve_ts, (uint32_t)serve_m, serve_g, cfg, r);
-                    st = serve_back;
-                } else {
-                    count_add<L>(a, ln, 2 * a.M + serve_g, 1u);
-                    put(ln, r, a.arrivals[r], false);
-                }
-            } else {
-                serve_m = pick_model<L>(a, ln, serve_g);
-                if (serve_m < 0) st = serve_back;
-            }
-        }
-        __syncwarp();
-        if (st == kStFinish) {
-            if (chunked) {
-                if (!(ln.status & MMS_STATUS_BAD_INDEX))
-                    state_save<L>(a, ln, a.snap_end + cell * sb);
-                // the chain kernel decides whether this run, and with it its status word, counts
-                uint32_t *hdr = reinterpret_cast<uint32_t *>(a.carry + cell * batch_carry_bytes());
-                hdr[0] = ln.carry_n;
-                hdr[1] = ln.status;
-            } else if (ln.status) {
-                atomicOr(&a.status[b], ln.status);
-            }
-            st = kStDone;
-        }
-        __syncwarp();
+    if (run && end == a.N) batch_drain<L>(a, ln);
+    if (!valid) return;
+    if (chunked) {
+        if (run) state_save<L>(a, ln, a.snap_end + cell * sb);
+        // the chain kernel decides whether this run, and with it its status word, counts
+        uint32_t *hdr = reinterpret_cast<uint32_t *>(a.carry + cell * batch_carry_bytes());
+        hdr[0] = ln.carry_n;
+        hdr[1] = ln.status;
+    } else if (ln.status) {
+        atomicOr(&a.status[b], ln.status);
     }
 }
 
@@ -1056,8 +951,8 @@ batch_repair_kernel(const BatchArgs a)
     ln.direct = false;
     state_load(a, ln, a.snap_start + cell * sb);
     batch_zero_counters(a, ln);
-    for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
-    if (end == a.N) batch_drain(a, ln);
+    for (int64_t i = first; i < end; ++i) batch_arrival<1>(a, ln, i);
+    if (end == a.N) batch_drain<1>(a, ln);
     state_save<1>(a, ln, a.snap_end + cell * sb);
     counters_store(a, ln, a.chunk_counters + cell * (size_t)(2 * a.M + 2 * a.G));
     uint32_t *hdr = reinterpret_cast<uint32_t *>(carry);
@@ -1108,8 +1003,8 @@ batch_chain_kernel(const BatchArgs a)
         ++redone;                          // the speculative run of chunk j is dropped, status and all
         batch_zero_counters(a, ln);
         ln.status = 0;
-        for (int64_t i = first; i < end; ++i) batch_arrival(a, ln, i);
-        if (end == a.N) batch_drain(a, ln);
+        for (int64_t i = first; i < end; ++i) batch_arrival<1>(a, ln, i);
+        if (end == a.N) batch_drain<1>(a, ln);
         counters_store(a, ln, a.chunk_counters + cell * n_counters);
         status |= ln.status;
     }

@@ -313,7 +313,8 @@ int mms_argmax_scores(const int64_t *good_total, const double *latency_sum,
  *                         of two starting at 1; column log2(bs) of the table
  *                         is read for batch size bs, as the reference does
  *  heap_capacity          pending (time, group) events per candidate; 0 picks
- *                         4*G + 16.  Overflow sets MMS_STATUS_HEAP_OVERFLOW.
+ *                         G + 16.  Overflow sets MMS_STATUS_HEAP_OVERFLOW in the
+ *                         candidate's status; run it again with a larger heap.
  */
 typedef struct {
     const uint16_t *group_off;
@@ -342,6 +343,48 @@ int mms_sim_batching(const mms_trace *trace, const mms_placements *cands,
                      const mms_batching *batching, const int32_t *next_same,
                      const mms_sum_plan *plan, const mms_workspace *ws, const mms_results *out,
                      void *stream);
+
+/* ---- Workload.compute_stats ----------------------------------------------
+ * alpa_serve/simulator/workload.py:308-354 on the device: per-model and
+ * overall statistics of the per-request outputs (mms_results.finish / .good,
+ * or any arrays of that layout) over the requests [first, first + window) —
+ * the caller cuts `warmup` seconds off both ends as workload.py:312-318 does
+ * and passes what is left.  model_ids here are indices into the WORKLOAD's
+ * model names (compute_stats groups by request.model_name, whether or not the
+ * model is registered); ids outside [0, num_models) are counted in no model.
+ * One trace for all candidates.
+ *
+ *  num_requests  i32[M]     requests of the model in the window (may be NULL)
+ *  num_good      i32[B][M]  ... of which good
+ *  first_start,
+ *  last_start    f64[B][M]  arrival of the model's first / last good request
+ *                           (throughput = num_good / (last - first), :338)
+ *  latency_mean  f64[B][M]  np.mean(finish - start) over the good requests,
+ *  latency_std              np.std of the same, bit for bit (numpy's pairwise
+ *                           sums); 0 where no request is good (:340-341)
+ *  latency_p90,
+ *  latency_p99   f64[B][M]  sorted[int(0.90 * n)], sorted[int(0.99 * n)]
+ *  good_total    i64[B]     good requests in the window (np.mean(good) * n)
+ *  latency_sum   f64[B]     numpy-ordered sum of finish - start over the
+ *                           window (np.mean(finish - start) * n, :352)
+ */
+typedef struct {
+    int32_t *num_requests;
+    int32_t *num_good;
+    double *first_start, *last_start;
+    double *latency_mean, *latency_std, *latency_p90, *latency_p99;
+    int64_t *good_total;
+    double *latency_sum;
+} mms_stats_out;
+
+size_t mms_compute_stats_workspace_bytes(int64_t window, int32_t num_models,
+                                         int32_t num_candidates);
+
+/* finish f64 / good u8: row b starts at element b * row_stride. */
+int mms_compute_stats(const double *arrivals, const int32_t *model_ids, int32_t num_models,
+                      const double *finish, const uint8_t *good, int64_t row_stride,
+                      int32_t num_candidates, int64_t first, int64_t window,
+                      const mms_workspace *ws, const mms_stats_out *out, void *stream);
 
 #ifdef __cplusplus
 }

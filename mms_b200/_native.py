@@ -62,7 +62,7 @@ EXPORTS = (
     "mms_trace_model_histogram", "mms_sim_workspace_bytes", "mms_sim_mixed",
     "mms_sim_mixed_static", "mms_trace_next_same_model", "mms_sim_batching_workspace_bytes", "mms_sim_batching",
     "mms_profile_begin", "mms_profile_end", "mms_argmax_scores",
-    "mms_trace_pack",
+    "mms_trace_pack", "mms_compute_stats_workspace_bytes", "mms_compute_stats",
 )
 
 _vp = ctypes.c_void_p
@@ -107,6 +107,13 @@ class Batching(ctypes.Structure):
     _fields_ = [("group_off", _vp), ("group_mod", _vp), ("group_cfg", _vp),
                 ("num_batch_sizes", ctypes.c_int32), ("heap_capacity", ctypes.c_int32),
                 ("batch_sizes", ctypes.c_int32 * 8)]
+
+
+class StatsOut(ctypes.Structure):
+    _fields_ = [("num_requests", _vp), ("num_good", _vp), ("first_start", _vp),
+                ("last_start", _vp), ("latency_mean", _vp), ("latency_std", _vp),
+                ("latency_p90", _vp), ("latency_p99", _vp), ("good_total", _vp),
+                ("latency_sum", _vp)]
 
 
 _lib = None
@@ -188,6 +195,12 @@ def lib():
     L.mms_sim_batching.argtypes = [ctypes.POINTER(Trace), ctypes.POINTER(Placements),
                                    ctypes.POINTER(Batching), _vp, ctypes.POINTER(SumPlan),
                                    ctypes.POINTER(Workspace), ctypes.POINTER(Results), _vp]
+    L.mms_compute_stats_workspace_bytes.restype = ctypes.c_size_t
+    L.mms_compute_stats_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+    L.mms_compute_stats.restype = ctypes.c_int
+    L.mms_compute_stats.argtypes = [_vp, _vp, ctypes.c_int32, _vp, _vp, ctypes.c_int64,
+                                    ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
+                                    ctypes.POINTER(Workspace), ctypes.POINTER(StatsOut), _vp]
     _lib = L
     return L
 

@@ -9,7 +9,8 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 REPO_DIR = os.path.dirname(PKG_DIR)
 LIB_PATH = os.path.join(PKG_DIR, "libmms_sim.so")
-SOURCES = [os.path.join(PKG_DIR, "csrc", "mms_sim.cu")]
+SOURCES = [os.path.join(PKG_DIR, "csrc", "mms_sim.cu"),
+           os.path.join(PKG_DIR, "csrc", "latency_stats.cu")]
 HEADERS = [os.path.join(REPO_DIR, "include", "mms_sim.h"),
            os.path.join(PKG_DIR, "csrc", "sim_core.cuh"),
            os.path.join(PKG_DIR, "csrc", "sim_chunk.cuh"),

@@ -1,0 +1,477 @@
+// latency_stats.cu — Workload.compute_stats on the device.
+//
+// alpa_serve/simulator/workload.py:308-354 turns the per-request outputs of a
+// simulation (finish time and good flag of every request) into per-model
+// statistics: request count, goodput, throughput, mean / standard deviation /
+// 90th / 99th percentile of the latency of the good requests, plus the overall
+// goodput and mean latency, all over the trace with `warmup` seconds cut off at
+// both ends.  The reference does it with numpy on the host, which for this
+// library means downloading 9 bytes per request and candidate first.  These
+// kernels produce the same numbers, bit for bit, from the arrays where the
+// simulator left them:
+//
+//   window_hist_kernel      requests of each model inside the window
+//   window_offsets_kernel   where each model's latencies go in scratch
+//   compact_latency_kernel  one block per (model, candidate): finish - start of
+//                           the model's good requests, in request order (the
+//                           order numpy's fancy indexing gives them)
+//   latency_moments_kernel  one block per (model or whole window, candidate):
+//                           the sums in numpy's pairwise order (blocks of at
+//                           most 128 elements with eight partial sums, halves
+//                           rounded down to multiples of eight: numpy/_core/
+//                           src/umath/loops_utils.h.src), mean and standard
+//                           deviation as np.mean / np.std form them, and the
+//                           two order statistics by a radix selection over the
+//                           bit patterns (sorted[int(0.90 * n)] needs no sort)
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "mms_sim.h"
+
+namespace mms {
+
+extern thread_local char g_last_error[256];
+
+constexpr int kStatsThreads = 256;
+constexpr int kStatsItems = 4;                     // requests per thread and tile
+constexpr int kStatsSmemBins = 4096;               // models counted in shared memory
+constexpr int kStatsDepth = 48;                    // pair-sum stack
+
+struct StatsArgs {
+    const double *arrivals;
+    const int32_t *model_ids;
+    const double *finish;
+    const uint8_t *good;
+    int64_t row_stride;        // elements between two candidates' rows of finish / good
+    int64_t first, window;     // requests [first, first + window)
+    int32_t M, B;
+    // scratch
+    int32_t *counts;           // [M]
+    int64_t *offsets;          // [M + 1] start of each model's latencies inside a row of lat
+    int64_t *leaf_off;         // [M + 2] start of each unit's leaves (unit M: the whole window)
+    double *lat;               // [B][window]
+    int32_t *leaf_start;       // [B][leaf_cap]
+    uint8_t *leaf_merges;      // [B][leaf_cap]
+    double *leaf_sums;         // [B][leaf_cap]
+    int64_t leaf_cap;
+    mms_stats_out out;
+};
+
+__global__ void __launch_bounds__(kStatsThreads)
+window_hist_kernel(const int32_t *model_ids, int64_t first, int64_t window, int32_t M,
+                   int32_t *counts)
+{
+    __shared__ int32_t s_bins[kStatsSmemBins];
+    const bool in_smem = M <= kStatsSmemBins;
+    if (in_smem) {
+        for (int m = threadIdx.x; m < M; m += blockDim.x) s_bins[m] = 0;
+        __syncthreads();
+    }
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < window; i += step) {
+        const int32_t m = model_ids[first + i];
+        if (m < 0 || m >= M) continue;
+        if (in_smem) atomicAdd(&s_bins[m], 1); else atomicAdd(&counts[m], 1);
+    }
+    if (in_smem) {
+        __syncthreads();
+        for (int m = threadIdx.x; m < M; m += blockDim.x)
+            if (s_bins[m]) atomicAdd(&counts[m], s_bins[m]);
+    }
+}
+
+// Leaves of numpy's pairwise split never have fewer than 64 elements unless the
+// whole array is one leaf, so n / 64 + 2 entries hold the leaf starts of n
+// elements and the end mark behind them.
+__host__ __device__ inline int64_t leaf_room(int64_t n) { return n / 64 + 2; }
+
+__global__ void window_offsets_kernel(StatsArgs a)
+{
+    if (blockIdx.x || threadIdx.x) return;
+    int64_t at = 0, leaves = 0;
+    for (int32_t m = 0; m < a.M; ++m) {
+        a.offsets[m] = at;
+        a.leaf_off[m] = leaves;
+        at += a.counts[m];
+        leaves += leaf_room(a.counts[m]);
+        if (a.out.num_requests) a.out.num_requests[m] = a.counts[m];
+    }
+    a.offsets[a.M] = at;
+    a.leaf_off[a.M] = leaves;
+    a.leaf_off[a.M + 1] = leaves + leaf_room(a.window);
+}
+
+// Block (m, b): the latencies of model m's good requests of candidate b, in
+// request order, into lat[b][offsets[m] ..]; their number; the arrival times
+// of the first and the last of them.
+__global__ void __launch_bounds__(kStatsThreads)
+compact_latency_kernel(StatsArgs a)
+{
+    const int32_t m = blockIdx.x;
+    const int64_t b = blockIdx.y;
+    __shared__ int32_t s_warp[kStatsThreads / 32];
+    __shared__ long long s_first, s_last;
+    if (threadIdx.x == 0) { s_first = INT64_MAX; s_last = -1; }
+    __syncthreads();
+    const double *fin = a.finish + (size_t)b * a.row_stride + a.first;
+    const uint8_t *good = a.good + (size_t)b * a.row_stride + a.first;
+    const double *arr = a.arrivals + a.first;
+    const int32_t *ids = a.model_ids + a.first;
+    double *dst = a.lat + (size_t)b * a.window + a.offsets[m];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int64_t written = 0, mine_first = INT64_MAX, mine_last = -1;
+    constexpr int64_t kTile = (int64_t)kStatsThreads * kStatsItems;
+    for (int64_t base = 0; base < a.window; base += kTile) {
+        const int64_t i0 = base + (int64_t)threadIdx.x * kStatsItems;
+        bool take[kStatsItems];
+        int mine = 0;
+#pragma unroll
+        for (int k = 0; k < kStatsItems; ++k) {
+            const int64_t i = i0 + k;
+            take[k] = i < a.window && ids[i] == m && good[i] != 0;
+            mine += take[k];
+        }
+        int incl = mine;                                  // inclusive scan inside the warp
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= d) incl += o;
+        }
+        if (lane == 31) s_warp[warp] = incl;
+        __syncthreads();
+        int before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kStatsThreads / 32; ++w) {
+            const int c = s_warp[w];
+            if (w < warp) before += c;
+            total += c;
+        }
+        int64_t pos = written + before + incl - mine;
+#pragma unroll
+        for (int k = 0; k < kStatsItems; ++k)
+            if (take[k]) {
+                const int64_t i = i0 + k;
+                dst[pos++] = fin[i] - arr[i];
+                if (i < mine_first) mine_first = i;
+                mine_last = i;
+            }
+        written += total;
+        __syncthreads();                                  // s_warp is rewritten next tile
+    }
+    if (mine_last >= 0) {
+        atomicMin(&s_first, (long long)mine_first);
+        atomicMax(&s_last, (long long)mine_last);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const size_t cell = (size_t)b * a.M + m;
+        a.out.num_good[cell] = (int32_t)written;
+        a.out.first_start[cell] = written ? arr[s_first] : 0.0;
+        a.out.last_start[cell] = written ? arr[s_last] : 0.0;
+    }
+}
+
+// numpy's split of n elements into leaves, by one thread: leaf_start[0 .. count]
+// (the last entry is n) and, per leaf, how many pair sums follow it.
+__device__ inline int32_t plan_leaves(int64_t n, int32_t *leaf_start, uint8_t *merges)
+{
+    int64_t st_base[kStatsDepth], st_n[kStatsDepth];
+    uint8_t st_phase[kStatsDepth];
+    int sp = 0;
+    int32_t count = 0;
+    st_base[0] = 0; st_n[0] = n; st_phase[0] = 0; sp = 1;
+    while (sp > 0) {
+        const int t = sp - 1;
+        if (st_n[t] <= 128) {
+            leaf_start[count] = (int32_t)st_base[t];
+            merges[count] = 0;
+            ++count;
+            --sp;
+            continue;
+        }
+        int64_t half = st_n[t] / 2;
+        half -= half % 8;
+        if (st_phase[t] == 0) {
+            st_phase[t] = 1;
+            st_base[sp] = st_base[t]; st_n[sp] = half; st_phase[sp] = 0; ++sp;
+        } else if (st_phase[t] == 1) {
+            st_phase[t] = 2;
+            st_base[sp] = st_base[t] + half; st_n[sp] = st_n[t] - half; st_phase[sp] = 0; ++sp;
+        } else {
+            merges[count - 1] += 1;
+            --sp;
+        }
+    }
+    leaf_start[count] = (int32_t)n;
+    return count;
+}
+
+// One leaf the way numpy adds it up: eight partial sums over the multiples of
+// eight, paired, then the rest one by one.
+template <typename F>
+__device__ inline double leaf_sum(int64_t s, int64_t e, F value)
+{
+    const int64_t body_end = s + ((e - s) & ~(int64_t)7);
+    double p[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int64_t i = s;
+    for (; i < body_end; i += 8)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) p[j] += value(i + j);
+    double r = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));
+    for (; i < e; ++i) r += value(i);
+    return r;
+}
+
+__device__ inline double merge_leaves(int32_t num_leaves, const double *sums, const uint8_t *merges)
+{
+    double stack[kStatsDepth];
+    int sp = 0;
+    for (int32_t k = 0; k < num_leaves; ++k) {
+        stack[sp++] = sums[k];
+        for (int g = merges[k]; g > 0 && sp >= 2; --g) {
+            --sp;
+            stack[sp - 1] = stack[sp - 1] + stack[sp];
+        }
+    }
+    return num_leaves > 0 ? stack[0] : 0.0;
+}
+
+// Block-wide numpy-ordered sum of value(0 .. n-1); every thread gets the result.
+template <typename F>
+__device__ inline double block_numpy_sum(int32_t num_leaves, const int32_t *leaf_start,
+                                         const uint8_t *merges, double *sums, F value)
+{
+    __shared__ double s_total;
+    for (int32_t k = threadIdx.x; k < num_leaves; k += blockDim.x)
+        sums[k] = leaf_sum(leaf_start[k], leaf_start[k + 1], value);
+    __syncthreads();
+    if (threadIdx.x == 0) s_total = merge_leaves(num_leaves, sums, merges);
+    __syncthreads();
+    const double total = s_total;
+    __syncthreads();
+    return total;
+}
+
+// Bit pattern of a double as an unsigned number that orders like the double.
+__device__ inline uint64_t order_key(double x)
+{
+    const uint64_t u = (uint64_t)__double_as_longlong(x);
+    return (u >> 63) ? ~u : (u | 0x8000000000000000ull);
+}
+
+__device__ inline double key_value(uint64_t k)
+{
+    const uint64_t u = (k >> 63) ? (k & 0x7FFFFFFFFFFFFFFFull) : ~k;
+    return __longlong_as_double((long long)u);
+}
+
+// The element of rank `rank` (0-based, ascending) of x[0 .. n): eight passes
+// over the data, one byte of the key per pass, most significant first.
+__device__ inline double block_select(const double *x, int64_t n, int64_t rank)
+{
+    __shared__ unsigned int s_hist[256];
+    __shared__ unsigned long long s_prefix;
+    __shared__ long long s_rank;
+    if (threadIdx.x == 0) { s_prefix = 0; s_rank = rank; }
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int k = threadIdx.x; k < 256; k += blockDim.x) s_hist[k] = 0;
+        __syncthreads();
+        const uint64_t prefix = s_prefix;
+        const uint64_t above = shift == 56 ? 0 : (~0ull << (shift + 8));
+        const int64_t rounds = (n + blockDim.x - 1) / blockDim.x;
+        for (int64_t r = 0; r < rounds; ++r) {
+            const int64_t i = r * blockDim.x + threadIdx.x;
+            bool in = false;
+            unsigned int byte = 0;
+            if (i < n) {
+                const uint64_t k = order_key(x[i]);
+                in = (k & above) == prefix;
+                byte = (unsigned int)(k >> shift) & 255u;
+            }
+            // equal bytes of a warp go in with one addition
+            const unsigned int live = __ballot_sync(0xFFFFFFFFu, in);
+            if (in) {
+                const unsigned int same = __match_any_sync(live, byte);
+                if ((int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_hist[byte], __popc(same));
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            long long left = s_rank;
+            int bin = 0;
+            while (bin < 255 && (long long)s_hist[bin] <= left) { left -= s_hist[bin]; ++bin; }
+            s_rank = left;
+            s_prefix = prefix | ((unsigned long long)bin << shift);
+        }
+        __syncthreads();
+    }
+    const double v = key_value(s_prefix);
+    __syncthreads();
+    return v;
+}
+
+// Block (u, b): u < M is model u, u == M the whole window.
+__global__ void __launch_bounds__(kStatsThreads)
+latency_moments_kernel(StatsArgs a)
+{
+    const int32_t u = blockIdx.x;
+    const int64_t b = blockIdx.y;
+    __shared__ int32_t s_leaves;
+    int32_t *leaf_start = a.leaf_start + (size_t)b * a.leaf_cap + a.leaf_off[u];
+    uint8_t *merges = a.leaf_merges + (size_t)b * a.leaf_cap + a.leaf_off[u];
+    double *sums = a.leaf_sums + (size_t)b * a.leaf_cap + a.leaf_off[u];
+    if (u == a.M) {
+        // np.mean(good) and np.mean(finish - start) over the window (workload.py:352)
+        const double *fin = a.finish + (size_t)b * a.row_stride + a.first;
+        const uint8_t *good = a.good + (size_t)b * a.row_stride + a.first;
+        const double *arr = a.arrivals + a.first;
+        if (threadIdx.x == 0) s_leaves = a.window > 0 ? plan_leaves(a.window, leaf_start, merges) : 0;
+        __syncthreads();
+        const double total = block_numpy_sum(s_leaves, leaf_start, merges, sums,
+                                             [&](int64_t i) { return fin[i] - arr[i]; });
+        __shared__ unsigned long long s_good;
+        if (threadIdx.x == 0) s_good = 0;
+        __syncthreads();
+        unsigned long long mine = 0;
+        for (int64_t i = threadIdx.x; i < a.window; i += blockDim.x) mine += good[i] != 0;
+        atomicAdd(&s_good, mine);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            a.out.latency_sum[b] = total;
+            a.out.good_total[b] = (int64_t)s_good;
+        }
+        return;
+    }
+    const size_t cell = (size_t)b * a.M + u;
+    const int64_t n = a.out.num_good[cell];
+    if (n == 0) {            // the reference puts latency = [0] here (workload.py:339-341)
+        if (threadIdx.x == 0) {
+            a.out.latency_mean[cell] = 0.0; a.out.latency_std[cell] = 0.0;
+            a.out.latency_p90[cell] = 0.0; a.out.latency_p99[cell] = 0.0;
+        }
+        return;
+    }
+    const double *x = a.lat + (size_t)b * a.window + a.offsets[u];
+    if (threadIdx.x == 0) s_leaves = plan_leaves(n, leaf_start, merges);
+    __syncthreads();
+    const int32_t num_leaves = s_leaves;
+    // np.mean: the pairwise sum divided by the count
+    const double mean = block_numpy_sum(num_leaves, leaf_start, merges, sums,
+                                        [&](int64_t i) { return x[i]; }) / (double)n;
+    // np.std: sqrt(sum((x - mean) * (x - mean)) / n), the sum pairwise again
+    const double sq = block_numpy_sum(num_leaves, leaf_start, merges, sums,
+                                      [&](int64_t i) { const double d = x[i] - mean; return d * d; });
+    // sorted[int(0.90 * n)], sorted[int(0.99 * n)] (workload.py:344-345)
+    const double p90 = block_select(x, n, (int64_t)(0.90 * (double)n));
+    const double p99 = block_select(x, n, (int64_t)(0.99 * (double)n));
+    if (threadIdx.x == 0) {
+        a.out.latency_mean[cell] = mean;
+        a.out.latency_std[cell] = sqrt(sq / (double)n);
+        a.out.latency_p90[cell] = p90;
+        a.out.latency_p99[cell] = p99;
+    }
+}
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct StatsGeometry {
+    int64_t leaf_cap;
+    size_t off_counts, off_offsets, off_leaf_off, off_lat, off_leaf_start, off_leaf_merges,
+        off_leaf_sums, total;
+};
+
+static int plan_stats(int64_t window, int32_t M, int32_t B, StatsGeometry *g)
+{
+    if (window < 0 || M < 0 || B < 0) return MMS_ERR_ARG;
+    if (window > 0x7FFFFFFF || M > 65535 || B > 65535) return MMS_ERR_UNSUPPORTED;
+    // every model's leaves and end mark, then the whole window's
+    g->leaf_cap = window / 64 + 2 * (int64_t)M + leaf_room(window);
+    size_t at = 0;
+    g->off_counts = at;      at = align256(at + (size_t)(M + 1) * 4);
+    g->off_offsets = at;     at = align256(at + (size_t)(M + 1) * 8);
+    g->off_leaf_off = at;    at = align256(at + (size_t)(M + 2) * 8);
+    g->off_lat = at;         at = align256(at + (size_t)B * window * 8);
+    g->off_leaf_start = at;  at = align256(at + (size_t)B * g->leaf_cap * 4);
+    g->off_leaf_merges = at; at = align256(at + (size_t)B * g->leaf_cap);
+    g->off_leaf_sums = at;   at = align256(at + (size_t)B * g->leaf_cap * 8);
+    g->total = at;
+    return MMS_OK;
+}
+
+}  // namespace mms
+
+extern "C" {
+
+size_t mms_compute_stats_workspace_bytes(int64_t window, int32_t num_models, int32_t num_candidates)
+{
+    mms::StatsGeometry g;
+    if (mms::plan_stats(window, num_models, num_candidates, &g) != MMS_OK) return 0;
+    return g.total;
+}
+
+int mms_compute_stats(const double *arrivals, const int32_t *model_ids, int32_t num_models,
+                      const double *finish, const uint8_t *good, int64_t row_stride,
+                      int32_t num_candidates, int64_t first, int64_t window,
+                      const mms_workspace *ws, const mms_stats_out *out, void *stream)
+{
+    mms::StatsGeometry g;
+    const int rc = mms::plan_stats(window, num_models, num_candidates, &g);
+    if (rc != MMS_OK) return rc;
+    if (first < 0 || row_stride < first + window || !out) return MMS_ERR_ARG;
+    const int32_t M = num_models, B = num_candidates;
+    if (B == 0) return MMS_OK;
+    if (!out->good_total || !out->latency_sum) return MMS_ERR_ARG;
+    if (M > 0 && (!out->num_good || !out->first_start || !out->last_start || !out->latency_mean ||
+                  !out->latency_std || !out->latency_p90 || !out->latency_p99))
+        return MMS_ERR_ARG;
+    if (window > 0 && (!arrivals || !model_ids || !finish || !good)) return MMS_ERR_ARG;
+    if (!ws || !ws->ptr || ws->bytes < g.total) {
+        snprintf(mms::g_last_error, sizeof(mms::g_last_error),
+                 "mms_compute_stats needs %zu bytes of workspace", g.total);
+        return MMS_ERR_ARG;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char *scratch = (unsigned char *)ws->ptr;
+    mms::StatsArgs a;
+    a.arrivals = arrivals; a.model_ids = model_ids; a.finish = finish; a.good = good;
+    a.row_stride = row_stride; a.first = first; a.window = window; a.M = M; a.B = B;
+    a.counts = (int32_t *)(scratch + g.off_counts);
+    a.offsets = (int64_t *)(scratch + g.off_offsets);
+    a.leaf_off = (int64_t *)(scratch + g.off_leaf_off);
+    a.lat = (double *)(scratch + g.off_lat);
+    a.leaf_start = (int32_t *)(scratch + g.off_leaf_start);
+    a.leaf_merges = (uint8_t *)(scratch + g.off_leaf_merges);
+    a.leaf_sums = (double *)(scratch + g.off_leaf_sums);
+    a.leaf_cap = g.leaf_cap;
+    a.out = *out;
+#define MMS_STATS_CUDA(call)                                                              \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess) {                                                          \
+            snprintf(mms::g_last_error, sizeof(mms::g_last_error), "%s: %s", #call,       \
+                     cudaGetErrorString(e_));                                             \
+            return MMS_ERR_CUDA;                                                          \
+        }                                                                                 \
+    } while (0)
+    MMS_STATS_CUDA(cudaMemsetAsync(a.counts, 0, (size_t)(M + 1) * 4, st));
+    if (window > 0 && M > 0) {
+        const unsigned blocks = (unsigned)((window + 256 * 16 - 1) / (256 * 16));
+        mms::window_hist_kernel<<<blocks < 1024 ? blocks : 1024, mms::kStatsThreads, 0, st>>>(
+            model_ids, first, window, M, a.counts);
+        MMS_STATS_CUDA(cudaGetLastError());
+    }
+    mms::window_offsets_kernel<<<1, 32, 0, st>>>(a);
+    MMS_STATS_CUDA(cudaGetLastError());
+    if (M > 0) {
+        mms::compact_latency_kernel<<<dim3((unsigned)M, (unsigned)B), mms::kStatsThreads, 0, st>>>(a);
+        MMS_STATS_CUDA(cudaGetLastError());
+    }
+    mms::latency_moments_kernel<<<dim3((unsigned)M + 1, (unsigned)B), mms::kStatsThreads, 0, st>>>(a);
+    MMS_STATS_CUDA(cudaGetLastError());
+#undef MMS_STATS_CUDA
+    return MMS_OK;
+}
+
+}  // extern "C"

@@ -623,7 +623,11 @@ class BatchResult:
     """Outputs of one launch, as numpy arrays on the host."""
     __slots__ = ("model_num_requests", "model_num_good", "group_num_requests",
                  "group_num_good", "good_total", "latency_sum", "status", "finish", "good",
-                 "resimulated")
+                 "resimulated", "finish_device", "good_device")
+
+    def __init__(self):
+        # per-request outputs left on the GPU (f64[B][N], u8[B][N]) when a caller asked for that
+        self.finish_device = self.good_device = None
 
     @staticmethod
     def concatenate(parts):
@@ -780,9 +784,10 @@ def _prepare(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, grou
     return job
 
 
-def _download(job: _Pending):
+def _download(job: _Pending, rows_on_device=False):
     """Waits for the launch and copies its results to the host.  Returns
-    (BatchResult, d2h_bytes)."""
+    (BatchResult, d2h_bytes).  rows_on_device: the per-request outputs are not
+    downloaded; the result carries the device tensors instead."""
     (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_redo, o_fin, o_good) = job.out
     Bs, M, N, full = job.Bs, job.M, job.N, job.full
     res = BatchResult()
@@ -795,12 +800,15 @@ def _download(job: _Pending):
         res.latency_sum = o_lsum[:Bs].cpu().numpy()
         res.status = o_status[:Bs].cpu().numpy().astype(np.uint32)
         res.resimulated = o_redo[:Bs].cpu().numpy()
-        res.finish = o_fin[:Bs].cpu().numpy()[:, :N] if full else None
-        res.good = o_good[:Bs].cpu().numpy()[:, :N].astype(bool) if full else None
+        host_rows = full and not rows_on_device
+        res.finish = o_fin[:Bs].cpu().numpy()[:, :N] if host_rows else None
+        res.good = o_good[:Bs].cpu().numpy()[:, :N].astype(bool) if host_rows else None
+        if full and rows_on_device:
+            res.finish_device, res.good_device = o_fin[:Bs, :N], o_good[:Bs, :N]
     d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
                                  res.group_num_requests, res.good_total, res.latency_sum,
                                  res.status))
-    if full:
+    if host_rows:
         d2h += res.finish.nbytes + res.good.nbytes
     return res, d2h
 
@@ -820,7 +828,7 @@ def _check_status(res):
                            f"for candidate {bad} (bad table index or capacity overflow)")
 
 
-def _collect(job):
+def _collect(job, rows_on_device=False):
     """Waits for a submitted launch and downloads its results.  Returns
     (BatchResult, h2d_bytes, d2h_bytes)."""
     if isinstance(job, ResidentBatch):
@@ -829,17 +837,17 @@ def _collect(job):
         job.release()
         _check_status(res)
         return res, h2d, d2h
-    res, d2h = _download(job)
+    res, d2h = _download(job, rows_on_device)
     h2d = job.h2d
     _release(job)
     _check_status(res)
     return res, h2d, d2h
 
 
-def _launch(*args, **kwargs):
+def _launch(*args, rows_on_device=False, **kwargs):
     """_submit + _collect: uploads the tables, runs mms_sim_mixed on the current
     stream, downloads the results.  Returns (BatchResult, h2d_bytes, d2h_bytes)."""
-    return _collect(_submit(*args, **kwargs))
+    return _collect(_submit(*args, **kwargs), rows_on_device)
 
 
 SPLIT_MIN_EASY = 512      # placements without mirrors a batch must have to be split
@@ -978,12 +986,14 @@ collect_batch = _collect
 
 def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
               per_request=False, group_good=False, pinned=False, options=None, mirrors=True,
-              split=True, crowded=False):
+              split=True, crowded=False, rows_on_device=False):
     """Simulates every placement of `enc` against `trace`
     (simulate_requests_mixed, controller.py:561-628).  `mirrors`: placements
     with interchangeable groups get a mirror candidate (a speed-up of the
     time-parallel execution; results are the same with and without).
-    `crowded`: the MMS_FLAG_CROWDED hint (results are the same)."""
+    `crowded`: the MMS_FLAG_CROWDED hint (results are the same).
+    `rows_on_device` (with per_request): finish and good stay on the GPU, as
+    BatchResult.finish_device / .good_device."""
     if not per_request:
         return _collect(submit_batch(trace, enc, table, group_good, pinned, options, mirrors,
                                      split, crowded))
@@ -991,7 +1001,7 @@ def run_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
                    enc.model_off, enc.model_rep, enc.group_info,
                    table.device(trace.device), 0,
                    nat.FLAG_PER_REQUEST | (nat.FLAG_CROWDED if crowded else 0), group_good,
-                   pinned, options)
+                   pinned, options, rows_on_device=rows_on_device)
 
 
 def encode_dense(m_id2g_id, num_stages, num_models):
@@ -1106,8 +1116,9 @@ class ResidentBatching:
             nat.check(rc, "mms_sim_batching")
         return self
 
-    def results(self, per_request=True):
-        """Waits and downloads: (BatchResult, d2h bytes)."""
+    def results(self, per_request=True, rows_on_device=False):
+        """Waits and downloads: (BatchResult, d2h bytes).  rows_on_device: the
+        result carries the per-request outputs as device tensors."""
         (o_mreq, o_mgood, o_greq, o_ggood, o_total, o_lsum, o_status, o_fin, o_good,
          o_redo) = self.out
         M, N = self.M, self.N
@@ -1122,6 +1133,8 @@ class ResidentBatching:
         res.resimulated = o_redo.cpu().numpy()
         res.finish = o_fin.cpu().numpy()[:, :N] if per_request else None
         res.good = o_good.cpu().numpy()[:, :N].astype(bool) if per_request else None
+        if rows_on_device:
+            res.finish_device, res.good_device = o_fin[:, :N], o_good[:, :N]
         d2h = sum(x.nbytes for x in (res.model_num_requests, res.model_num_good,
                                      res.group_num_requests, res.group_num_good, res.good_total,
                                      res.latency_sum, res.status))
@@ -1131,19 +1144,20 @@ class ResidentBatching:
 
 
 def launch_batching(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
-                    latency, latency_stride, batch_sizes, heap_capacity=0, per_request=True):
+                    latency, latency_stride, batch_sizes, heap_capacity=0, per_request=True,
+                    rows_on_device=False):
     """simulate_requests_mixed_batching (controller.py:630-798) for every
     candidate.  The kernel always writes per-request outputs (the latency sums
     are formed from them); per_request=False does not download them."""
     job = ResidentBatching(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info, latency,
                            latency_stride, batch_sizes, heap_capacity).launch()
-    res, _ = job.results(per_request)
+    res, _ = job.results(per_request, rows_on_device)
     if heap_capacity == 0 and np.any(res.status & nat.STATUS_HEAP_OVERFLOW):
         # the default capacity (G + 16 pending events) is what the simulation was seen to
         # need; nothing bounds it, so a run that overflowed is repeated with room to spare
         job = ResidentBatching(trace, B, M, G, P, T, S, C, model_off, model_rep, group_info,
                                latency, latency_stride, batch_sizes, 8 * G + 64).launch()
-        res, _ = job.results(per_request)
+        res, _ = job.results(per_request, rows_on_device)
     if np.any(res.status):
         bad = int(np.flatnonzero(res.status)[0])
         what = {nat.STATUS_HEAP_OVERFLOW: "event heap overflow (raise heap_capacity)",
@@ -1166,7 +1180,7 @@ def resident_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable
 
 
 def run_batch_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable,
-                       heap_capacity=0, per_request=True):
+                       heap_capacity=0, per_request=True, rows_on_device=False):
     """Batching simulation of every placement of `enc`; `table` must have been
     built with batch sizes.  per_request=False leaves the per-request outputs
     (9 bytes per candidate and request) on the device."""
@@ -1174,4 +1188,60 @@ def run_batch_batching(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTabl
         raise ValueError("the latency table has no batch-size axis")
     return launch_batching(trace, enc.B, enc.M, enc.G, enc.P, enc.T, enc.S, enc.C, enc.model_off,
                            enc.model_rep, enc.group_info, table.device(trace.device), 0,
-                           table.batch_sizes, heap_capacity, per_request)
+                           table.batch_sizes, heap_capacity, per_request, rows_on_device)
+
+
+STATS_FIELDS = ("num_good", "first_start", "last_start", "latency_mean", "latency_std",
+                "latency_p90", "latency_p99")
+
+
+def device_compute_stats(arrivals, model_ids, num_models: int, finish, good, first: int,
+                         window: int):
+    """Workload.compute_stats (alpa_serve/simulator/workload.py:308-354) on the
+    GPU, through mms_compute_stats: statistics of the requests [first, first +
+    window) of per-request outputs that are already on the device.  arrivals
+    f64[N], model_ids i32[N] (index into the WORKLOAD's names), finish f64[B][N],
+    good u8[B][N]: torch tensors on one GPU.  Returns a dict of numpy arrays:
+    num_requests i32[M]; num_good, first_start, last_start, latency_mean,
+    latency_std, latency_p90, latency_p99 [B][M]; good_total i64[B],
+    latency_sum f64[B]; and "d2h_bytes"."""
+    _require_cuda()
+    L = nat.lib()
+    dev = finish.device
+    if finish.dim() != 2 or good.shape != finish.shape or finish.stride(1) != 1 \
+            or good.stride(1) != 1 or finish.stride(0) != good.stride(0):
+        raise ValueError("finish and good must be [B][N] rows of one pitch")
+    if finish.dtype != torch.float64 or good.dtype != torch.uint8:
+        raise ValueError("finish must be float64 and good uint8")
+    B, N = finish.shape
+    M = int(num_models)
+    first, window = int(first), int(window)
+    if first < 0 or window < 0 or first + window > N or arrivals.numel() < N \
+            or model_ids.numel() < N:
+        raise ValueError("window outside the trace")
+    with torch.cuda.device(dev):
+        need = L.mms_compute_stats_workspace_bytes(window, M, B)
+        if need == 0:
+            raise NotImplementedError("statistics outside the kernel limits")
+        ws_t = _take_scratch(dev, max(need, 256))
+        ws = nat.Workspace(_ptr(ws_t), need)
+        f64 = dict(dtype=torch.float64, device=dev)
+        o = {"num_requests": torch.zeros(max(M, 1), dtype=torch.int32, device=dev),
+             "num_good": torch.zeros((B, max(M, 1)), dtype=torch.int32, device=dev),
+             "good_total": torch.zeros(B, dtype=torch.int64, device=dev),
+             "latency_sum": torch.zeros(B, **f64)}
+        for name in STATS_FIELDS[1:]:
+            o[name] = torch.zeros((B, max(M, 1)), **f64)
+        out = nat.StatsOut(*[_ptr(o[k]) for k in ("num_requests",) + STATS_FIELDS
+                             + ("good_total", "latency_sum")])
+        rc = L.mms_compute_stats(_ptr(arrivals), _ptr(model_ids), M, _ptr(finish), _ptr(good),
+                                 finish.stride(0), B, first, window, ctypes.byref(ws),
+                                 ctypes.byref(out), _stream_ptr())
+        nat.check(rc, "mms_compute_stats")
+        res = {k: v.cpu().numpy() for k, v in o.items()}      # waits for the kernels
+        _return_scratch(dev, ws_t)
+    res["d2h_bytes"] = sum(v.nbytes for v in res.values())
+    res["num_requests"] = res["num_requests"][:M]
+    for name in STATS_FIELDS:
+        res[name] = res[name][:, :M]
+    return res

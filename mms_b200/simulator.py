@@ -118,14 +118,28 @@ def simulate_requests_mixed_batching(finish, good, tstamps, model_ids, slos, m_i
 
 
 def approximate_one_case_one_placement(placement, model_names, prof_ress, model_ids, slos,
-                                       arrivals, mixed=True, enable_batching=False):
+                                       arrivals, mixed=True, enable_batching=False,
+                                       rows_on_device=False):
     """controller.py:410-503: simulate one ModelPlacement on one trace.
     Returns (start, finish, good, model_num_requests, model_num_good_requests,
-    group_num_requests, group_num_good_requests)."""
+    group_num_requests, group_num_good_requests).  With rows_on_device (no
+    counterpart in the reference) finish and good are torch tensors on the GPU
+    (f64[N], u8[N]) instead of numpy arrays: nothing per request is downloaded."""
     M = len(model_names)
     G = len(placement.group_configs)
     N = len(arrivals)
     arrivals = np.asarray(arrivals, dtype=np.float64)
+    if rows_on_device and mixed and G > 0:
+        trace = engine.DeviceTrace(arrivals, model_ids, slos, M)
+        table = engine.LatencyTable(prof_ress, list(batchsize_config) if enable_batching else None)
+        enc = engine.encode_placements([placement], table, M)
+        if enable_batching:
+            res = engine.run_batch_batching(trace, enc, table, per_request=False,
+                                            rows_on_device=True)
+        else:
+            res, _, _ = engine.run_batch(trace, enc, table, per_request=True, group_good=True,
+                                         options=_options, rows_on_device=True)
+        return (arrivals, res.finish_device[0], res.good_device[0]) + tuple(_counters(res, M, G))
     finish = np.empty(N, dtype=np.float64)
     good = np.empty(N, dtype=bool)
     if not mixed:
@@ -238,6 +252,100 @@ def fast_stats(model_names, start, finish_minus_start_sum, good_total, model_num
                        n / interval)
 
 
+class DeviceColumn:
+    """Stands where compute_stats puts a per-request array of one model
+    (PerModelStatsResult.latency, .request_starts, .request_finishes,
+    workload.py:347-349).  The per-request outputs stay on the GPU; the array is
+    downloaded and cut out when somebody looks at it."""
+
+    def __init__(self, fetch, length):
+        self._fetch, self._length, self._value = fetch, int(length), None
+
+    def _get(self):
+        if self._value is None:
+            self._value = self._fetch()
+            self._fetch = None
+        return self._value
+
+    def __array__(self, dtype=None, copy=None):
+        v = np.asarray(self._get())
+        return v.astype(dtype) if dtype is not None and v.dtype != dtype else v
+
+    def __len__(self):
+        return self._length
+
+    def __getitem__(self, key):
+        return self._get()[key]
+
+    def __iter__(self):
+        return iter(self._get())
+
+
+def device_stats(workload, start, finish_dev, good_dev, warmup) -> StatsResult:
+    """Workload.compute_stats (workload.py:308-354) from per-request outputs
+    that are still on the GPU (finish f64[N], good u8[N] torch tensors): the
+    numbers come from mms_compute_stats, the per-request arrays of the result
+    are DeviceColumns."""
+    import torch
+    arrivals = np.asarray(workload.arrivals, dtype=np.float64)
+    which = np.asarray(workload.name_index, dtype=np.int32)
+    n = len(arrivals)
+    lo, hi = 0, n
+    if n > 1:
+        skip = int(warmup / (arrivals[-1] - arrivals[0]) * n)
+        if skip > 0:
+            lo, hi = skip, max(n - skip, skip)
+    window = hi - lo
+    dev = finish_dev.device
+    d_arr = torch.from_numpy(np.ascontiguousarray(start, dtype=np.float64)).to(dev)
+    d_which = torch.from_numpy(which).to(dev)
+    K = len(workload.names)
+    st = engine.device_compute_stats(d_arr, d_which, K, finish_dev.reshape(1, -1),
+                                     good_dev.reshape(1, -1), lo, window)
+    start_w, which_w = np.asarray(start)[lo:hi], which[lo:hi]
+    # names in order of first appearance, then a stable sort by request count (:321-326)
+    _, first = np.unique(which_w, return_index=True)
+    seen = [int(k) for k in which_w[np.sort(first)]]
+    ordered = sorted(seen, key=lambda k: int(st["num_requests"][k]))
+    host = {}
+
+    def rows():
+        if not host:
+            host["finish"] = finish_dev.cpu().numpy()[lo:hi]
+            host["good"] = good_dev.cpu().numpy()[lo:hi].astype(bool)
+        return host["finish"], host["good"]
+
+    def column(k, what):
+        def fetch():
+            fin, good = rows()
+            pick = (which_w == k) & good
+            if not pick.any():
+                return [0] if what == "latency" else start_w[pick]
+            return {"latency": lambda: fin[pick] - start_w[pick], "start": lambda: start_w[pick],
+                    "finish": lambda: fin[pick]}[what]()
+        return fetch
+
+    per_model = []
+    for k in ordered:
+        count, ok = int(st["num_requests"][k]), int(st["num_good"][0, k])
+        goodput = np.float64(ok) / count
+        if ok > 0:
+            with np.errstate(divide="ignore"):
+                throughput = ok / (st["last_start"][0, k] - st["first_start"][0, k])
+            mean, std = st["latency_mean"][0, k], st["latency_std"][0, k]
+            p90, p99 = st["latency_p90"][0, k], st["latency_p99"][0, k]
+        else:                      # latency = [0] in the reference (:339-341)
+            zero = np.sort([0])
+            throughput, mean, std, p90, p99 = 0, np.mean([0]), np.std([0]), zero[0], zero[0]
+        per_model.append(PerModelStatsResult(
+            workload.names[k], count, goodput, throughput, mean, std, p90, p99,
+            DeviceColumn(column(k, "latency"), max(ok, 1)), DeviceColumn(column(k, "start"), ok),
+            DeviceColumn(column(k, "finish"), ok)))
+    return StatsResult(per_model, None, np.float64(st["good_total"][0]) / window,
+                       st["latency_sum"][0] / window, window,
+                       window / (start_w[-1] - start_w[0]))
+
+
 def approximate_one_case(case, seed: int = 0, warmup: int = DEFAULT_WARMUP, debug: bool = False,
                          fast_stats: bool = False, enable_batching: bool = False):
     """controller.py:308-407.  `case` is the reference's ServingCase triple
@@ -257,7 +365,13 @@ def approximate_one_case(case, seed: int = 0, warmup: int = DEFAULT_WARMUP, debu
         if workload.enable_simulator_cache:
             workload.cached_data = (model_ids, slos, model_names, prof_ress)
 
-    run = partial(approximate_one_case_one_placement, enable_batching=enable_batching)
+    # compute_stats runs on the GPU when the workload is array-backed: the per-request
+    # outputs then never leave the device
+    on_device = (not fast_stats and hasattr(workload, "name_index") and len(workload) > 1
+                 and all(len(p.group_configs) > 0
+                         for p in getattr(placement, "placements", [placement])))
+    run = partial(approximate_one_case_one_placement, enable_batching=enable_batching,
+                  rows_on_device=on_device)
     if hasattr(placement, "placements"):          # ModelPlacementWithReplacement
         arrivals = workload.arrivals
         change_times = list(placement.start_times[1:]) + [inf]
@@ -274,8 +388,13 @@ def approximate_one_case(case, seed: int = 0, warmup: int = DEFAULT_WARMUP, debu
                      model_ids[bounds[k]:bounds[k + 1]], slos[bounds[k]:bounds[k + 1]],
                      arrivals[bounds[k]:bounds[k + 1]]) for k in range(len(bounds) - 1)]
         start = np.concatenate([p[0] for p in parts])
-        finish = np.concatenate([p[1] for p in parts])
-        good = np.concatenate([p[2] for p in parts])
+        if on_device:
+            import torch
+            finish = torch.cat([p[1] for p in parts])
+            good = torch.cat([p[2] for p in parts])
+        else:
+            finish = np.concatenate([p[1] for p in parts])
+            good = np.concatenate([p[2] for p in parts])
         model_num_requests = np.sum([p[3] for p in parts], axis=0)
         model_num_good = np.sum([p[4] for p in parts], axis=0)
         group_num_requests = np.sum([p[5] for p in parts], axis=0)
@@ -293,6 +412,9 @@ def approximate_one_case(case, seed: int = 0, warmup: int = DEFAULT_WARMUP, debu
             for i in range(len(model_names))]
         stats = StatsResult(per_model, tuple(group_num_requests), np.mean(good),
                             np.mean(finish - start), len(start), len(start) / interval)
+    elif on_device:
+        stats = device_stats(workload, start, finish, good, warmup)
+        stats.group_num_requests = tuple(group_num_requests)
     else:
         stats = workload.compute_stats(start, finish, good, warmup)
         stats.group_num_requests = tuple(group_num_requests)

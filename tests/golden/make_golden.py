@@ -272,7 +272,40 @@ def reference_loops():
         json.dump(out, f, indent=1, sort_keys=True)
 
 
+STATS_FIELDS = ("num_requests", "goodput", "throughput", "latency_mean", "latency_std",
+                "latency_p90", "latency_p99")
+
+
+def stats_fixture():
+    """case_stats.npz: Workload.compute_stats (workload.py:308-354) of the
+    reference, with warm-ups of 10 and 25 seconds, on the per-request outputs
+    the reference's simulator gave for four placements of the shrunk candidate
+    batch (case_candidates.npz holds those outputs)."""
+    ref = reference.load()
+    case = cases.candidate_batch_case(num_candidates=48, duration=120.0)
+    datas, env, rw, pls = reference.to_reference_case(case)
+    g = np.load(os.path.join(HERE, "case_candidates.npz"))
+    assert digest(rw.arrivals) == str(g["arrivals_sha256"])
+    start = np.asarray(rw.arrivals)
+    out = {"warmups": np.array([10.0, 25.0])}
+    for w, warmup in enumerate(out["warmups"]):
+        for b in range(4):
+            st = rw.compute_stats(start, g["finish_first4"][b], g["good_first4"][b], float(warmup))
+            tag = f"w{w}_b{b}"
+            out[f"{tag}_names"] = np.array([x.name for x in st.per_model_stats])
+            for field in STATS_FIELDS:
+                out[f"{tag}_{field}"] = np.array([getattr(x, field) for x in st.per_model_stats],
+                                                 np.float64)
+            out[f"{tag}_overall"] = np.array([st.goodput, st.latency_mean, st.num_requests,
+                                              st.request_rate], np.float64)
+    np.savez_compressed(os.path.join(HERE, "case_stats.npz"), **out)
+
+
 if __name__ == "__main__":
+    if "--only-stats" in sys.argv:
+        stats_fixture()
+        sys.exit(0)
     if "--only-loops" not in sys.argv:
         main()
+        stats_fixture()
     reference_loops()

@@ -159,3 +159,25 @@ def test_placement_schedule_fast_stats(golden):
     assert np.array_equal(mreq, g["fast_model_num_requests"])
     assert np.array_equal(mgood / (mreq + 1e-6), g["fast_model_goodput"])
     assert np.array_equal(mreq / interval, g["fast_model_throughput"])
+
+
+def test_compute_stats_checker_matches_reference(golden):
+    """oracle.stats.compute_stats against what the reference's
+    Workload.compute_stats (workload.py:308-354) returned for the simulator
+    outputs stored in case_candidates.npz, two warm-up lengths."""
+    from mms_b200 import cases
+    from oracle import stats
+    g, c = golden("case_stats"), golden("case_candidates")
+    w = cases.candidate_batch_case(num_candidates=48, duration=120.0).workload
+    assert sha(w.arrivals) == str(c["arrivals_sha256"])
+    for wi, warmup in enumerate(g["warmups"]):
+        for b in range(4):
+            per_model, overall = stats.compute_stats(
+                w.arrivals, w.name_index, w.names, w.arrivals, c["finish_first4"][b],
+                c["good_first4"][b], float(warmup))
+            tag = f"w{wi}_b{b}"
+            assert [p["name"] for p in per_model] == list(g[f"{tag}_names"])
+            for field in stats.FIELDS:
+                got = np.array([p[field] for p in per_model], np.float64)
+                assert np.array_equal(got, g[f"{tag}_{field}"]), (tag, field)
+            assert np.array_equal(np.array(overall, np.float64), g[f"{tag}_overall"])

@@ -82,7 +82,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="candidates",
-                    choices=["candidates", "batching", "greedy", "sweep"])
+                    choices=["candidates", "batching", "greedy", "sweep", "stats"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="candidates: a list per GPU (weak) or one list split over the GPUs")
     ap.add_argument("--candidates", type=int, default=0,
@@ -1110,6 +1110,82 @@ def run_sweep(args, D, traces=1024, duration=3600.0, steps=None, cpu=True):
     return line
 
 
+def run_stats(args, D, candidates=8, duration=3600.0, steps=5):
+    """Workload.compute_stats (workload.py:308-354) of `candidates` placements'
+    per-request outputs: mms_compute_stats on rows that never left the GPU,
+    against the host route (download 9 bytes per request, then the checker's
+    numpy statistics, which are the reference's own numpy calls)."""
+    import torch
+    from mms_b200 import cases, engine
+    from mms_b200.simulator import workload_arrays
+    from oracle import stats as ostats
+
+    dev = D.dev
+    case = cases.candidate_batch_case(num_candidates=candidates, duration=duration)
+    w = case.workload
+    names = [d.name for d in case.model_datas]
+    profs = [d.profiling_result for d in case.model_datas]
+    mids, slos = workload_arrays(w, names)
+    trace = engine.DeviceTrace(w.arrivals, mids, slos, len(names), dev)
+    table = engine.LatencyTable(profs)
+    enc = engine.encode_placements(case.placements, table, len(names))
+    res, _, _ = engine.run_batch(trace, enc, table, per_request=True, group_good=True,
+                                 rows_on_device=True)
+    B, N = res.finish_device.shape
+    lo, hi = ostats.window(w.arrivals, 10.0)
+    d_which = torch.from_numpy(np.asarray(w.name_index, np.int32)).to(dev)
+    K = len(w.names)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times, wall = [], []
+    for i in range(3 + steps):
+        flush.zero_()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        st = engine.device_compute_stats(trace.arrivals, d_which, K, res.finish_device,
+                                         res.good_device, lo, hi - lo)
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            times.append(e0.elapsed_time(e1))
+            wall.append((time.perf_counter() - t0) * 1e3)
+    # the host route, for every placement: download the rows, numpy statistics
+    t0 = time.perf_counter()
+    fin = res.finish_device.cpu().numpy()
+    good = res.good_device.cpu().numpy().astype(bool)
+    t_down = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    mismatches = 0
+    index = {n: k for k, n in enumerate(w.names)}
+    for b in range(B):
+        per_model, overall = ostats.compute_stats(w.arrivals, w.name_index, w.names, w.arrivals,
+                                                  fin[b], good[b], 10.0)
+        for p in per_model:
+            k = index[p["name"]]
+            for field in ("latency_mean", "latency_std", "latency_p90", "latency_p99"):
+                mismatches += st[field][b, k].tobytes() != np.float64(p[field]).tobytes()
+            mismatches += int(st["num_good"][b, k]) != round(p["goodput"] * p["num_requests"])
+        mismatches += (st["latency_sum"][b] / (hi - lo)) != overall[1]
+        mismatches += np.float64(st["good_total"][b]) / (hi - lo) != overall[0]
+    t_numpy = time.perf_counter() - t0
+    assert mismatches == 0, f"{mismatches} statistics differ from the checker's"
+    ms = float(np.mean(times))
+    # read once by the compaction per model and candidate from L2, from HBM about once:
+    # finish 8 + good 1 + arrivals 8 + model id 4 per request, plus the compacted latencies
+    # written once and read four times (two sums, two selections of eight passes each: L2)
+    return {
+        "workload": f"compute_stats of {B} placements, {N} requests, {K} models, warm-up 10 s",
+        "device_ms": ms, "device_wall_ms": float(np.mean(wall)),
+        "requests_per_s": B * (hi - lo) / (ms * 1e-3),
+        "d2h_bytes": int(st["d2h_bytes"]),
+        "host_route_ms": (t_down + t_numpy) * 1e3, "host_download_ms": t_down * 1e3,
+        "host_numpy_ms": t_numpy * 1e3, "host_d2h_bytes": int(fin.nbytes + good.nbytes),
+        "parity": {"against": "numpy statistics of the downloaded rows (checker)",
+                   "mismatches": int(mismatches)},
+    }
+
+
 def guarded(name, fn):
     """A short run of another workload inside the default line: its failure must
     not lose the headline."""
@@ -1154,6 +1230,9 @@ def main():
         else:
             line = run_greedy(args, D, float(args.slo_scale), args.greedy_steps, args.duration,
                               cpu=not args.no_cpu_baseline)
+    elif args.workload == "stats":
+        # not a contract line: the figures of the compute_stats path alone
+        line = run_stats(args, D, 8, args.duration, steps=args.steps) if D.rank == 0 else None
     elif args.workload == "sweep":
         line = run_sweep(args, D, args.traces or 1024, args.duration,
                          cpu=not args.no_cpu_baseline)
@@ -1169,6 +1248,7 @@ def main():
                     args, D, 5.0, max_steps=24, cpu=not args.no_cpu_baseline)),
                 "sweep": guarded("sweep", lambda: run_sweep(
                     args, D, 256, 360.0, steps=2, cpu=not args.no_cpu_baseline)),
+                "compute_stats": guarded("compute_stats", lambda: run_stats(args, D)),
             }
     if line is not None:
         emit(line)

@@ -41,7 +41,7 @@ def build_host(force=False):
     include = sysconfig.get_paths()["include"]
     if not os.path.exists(os.path.join(include, "Python.h")):
         return None
-    cmd = [os.environ.get("CC", "gcc"), "-O2", "-shared", "-fPIC", "-I", include,
+    cmd = [os.environ.get("CC", "gcc"), "-O2", "-pthread", "-shared", "-fPIC", "-I", include,
            "-o", HOST_LIB_PATH, HOST_SOURCE]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if res.returncode != 0:

@@ -16,7 +16,10 @@
  */
 #define PY_SSIZE_T_CLEAN
 #include <Python.h>
+#include <pthread.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 static PyObject *g_str_configs, *g_str_models;
 
@@ -67,8 +70,15 @@ int mms_host_scan(PyObject *placements, int64_t *n_groups, int64_t *n_pairs)
     return rc;
 }
 
-static int as_int64(PyObject *o, int64_t *out)
+static inline int as_int64(PyObject *o, int64_t *out)
 {
+#if PY_VERSION_HEX >= 0x030C0000
+    /* ints of one digit (every model id and parallel degree): read in place */
+    if (PyLong_CheckExact(o) && PyUnstable_Long_IsCompact((const PyLongObject *)o)) {
+        *out = (int64_t)PyUnstable_Long_CompactValue((const PyLongObject *)o);
+        return 0;
+    }
+#endif
     const long long v = PyLong_AsLongLong(o);      /* goes through __index__ for numpy ints */
     if (v == -1 && PyErr_Occurred()) return -1;
     *out = (int64_t)v;
@@ -209,28 +219,33 @@ int mms_host_flatten_once(PyObject *placements, int64_t *n_groups, int64_t *n_pa
 
 /* ---- plain C from here on: no Python objects ---- */
 
+/* Threads mms_host_encode may use (0: four).  One suffices for short lists. */
+int mms_host_threads = 0;
+
 /* Distinct (dp, op, pp) rows in order of first appearance: uniq[count][3],
  * inverse[n] = index into uniq.  Returns the count, or -1 when there are more
  * than cap. */
 int64_t mms_host_configs(const int64_t *cfg, int64_t n, int64_t *uniq, int64_t cap, int32_t *inverse)
 {
-    int64_t count = 0, last = -1;
+    int64_t count = 0;
+    int32_t slot_of[64];                  /* a small direct-mapped cache in front of the search */
+    for (int k = 0; k < 64; ++k) slot_of[k] = -1;
     for (int64_t i = 0; i < n; ++i) {
         const int64_t *c = cfg + 3 * i;
-        int64_t hit = -1;
-        if (last >= 0 && uniq[3 * last] == c[0] && uniq[3 * last + 1] == c[1] && uniq[3 * last + 2] == c[2]) {
-            hit = last;
-        } else {
+        const unsigned h = (unsigned)(c[0] * 31 + c[1] * 7 + c[2]) & 63u;
+        int64_t hit = slot_of[h];
+        if (hit < 0 || uniq[3 * hit] != c[0] || uniq[3 * hit + 1] != c[1] || uniq[3 * hit + 2] != c[2]) {
+            hit = -1;
             for (int64_t u = 0; u < count; ++u)
                 if (uniq[3 * u] == c[0] && uniq[3 * u + 1] == c[1] && uniq[3 * u + 2] == c[2]) { hit = u; break; }
-        }
-        if (hit < 0) {
-            if (count >= cap) return -1;
-            uniq[3 * count] = c[0]; uniq[3 * count + 1] = c[1]; uniq[3 * count + 2] = c[2];
-            hit = count++;
+            if (hit < 0) {
+                if (count >= cap) return -1;
+                uniq[3 * count] = c[0]; uniq[3 * count + 1] = c[1]; uniq[3 * count + 2] = c[2];
+                hit = count++;
+            }
+            slot_of[h] = (int32_t)hit;
         }
         inverse[i] = (int32_t)hit;
-        last = hit;
     }
     return count;
 }
@@ -259,21 +274,36 @@ static uint64_t mix64(uint64_t x)
  * a search nearly every placement is one.  counts is scratch of M + 1 entries,
  * mark of M.  Unused cells of the tables must come zeroed.
  * Returns 0, or 1 when a model id is outside [0, M). */
-int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
-                    const int64_t *n_groups, const int64_t *cfg, const int32_t *cfg_index,
-                    const int64_t *column_of, const int64_t *n_in_group, const int64_t *placed_model,
-                    uint16_t *model_off, uint32_t *model_rep, uint32_t *group_info,
-                    int64_t *slots, int32_t *twin_items, int64_t *n_twin_items,
-                    int64_t *counts, int64_t *mark, int64_t max_perms)
+struct encode_ctx {
+    int64_t M, G, P;
+    const int64_t *n_groups, *cfg, *column_of, *n_in_group, *placed_model;
+    const int32_t *cfg_index;
+    uint16_t *model_off;
+    uint32_t *model_rep, *group_info;
+    int64_t *slots;
+    int32_t *twin_items;
+    int64_t max_perms;
+};
+
+/* Placements [b0, b1), whose groups start at flat group gi and whose pairs start at flat
+ * pair pi.  Twin items go to twin_items rows [gi, ..) — a group appears in at most one
+ * item, so the rows of a range never reach the next range's; *n_out = rows written. */
+static int encode_range(const struct encode_ctx *c, int64_t b0, int64_t b1, int64_t gi, int64_t pi,
+                        int64_t *counts, int64_t *mark, int64_t *n_out)
 {
-    int64_t gi = 0, pi = 0, n_items = 0;
+    const int64_t M = c->M;
+    const int64_t *cfg = c->cfg, *column_of = c->column_of, *placed_model = c->placed_model;
+    const int32_t *cfg_index = c->cfg_index;
+    int32_t *twin_items = c->twin_items + 3 * gi;
+    const int64_t max_perms = c->max_perms;
+    int64_t n_items = 0;
     for (int64_t m = 0; m < M; ++m) mark[m] = -1;
-    for (int64_t b = 0; b < B; ++b) {
-        const int64_t ng = n_groups[b];
-        const int64_t *nin = n_in_group + gi;
-        uint16_t *off = model_off + b * (M + 1);
-        uint32_t *rep = model_rep + b * P;
-        uint32_t *info = group_info + b * G;
+    for (int64_t b = b0; b < b1; ++b) {
+        const int64_t ng = c->n_groups[b];
+        const int64_t *nin = c->n_in_group + gi;
+        uint16_t *off = c->model_off + b * (M + 1);
+        uint32_t *rep = c->model_rep + b * c->P;
+        uint32_t *info = c->group_info + b * c->G;
         /* replicas per model */
         for (int64_t m = 0; m <= M; ++m) counts[m] = 0;
         int64_t q = pi;
@@ -286,9 +316,9 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
         int64_t run = 0;
         off[0] = 0;
         for (int64_t m = 0; m < M; ++m) {
-            const int64_t c = counts[m + 1];
+            const int64_t cnt = counts[m + 1];
             counts[m + 1] = run;                      /* next free position of model m */
-            run += c;
+            run += cnt;
             off[m + 1] = (uint16_t)run;
         }
         /* groups in ascending id: positions inside a model's list come out ascending too */
@@ -310,7 +340,7 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
             if (g < 256) key[g] = h * 0x9E3779B97F4A7C15ull + (uint64_t)col * 0xC2B2AE3D27D4EB4Full + (uint64_t)nin[g];
             slot += pp;
         }
-        slots[b] = slot;
+        c->slots[b] = slot;
         /* interchangeable groups: same column, same set of models (non-empty) */
         if (ng <= 256) {
             int64_t first_of[256];                     /* start of each group's models */
@@ -358,6 +388,75 @@ int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
         pi = q;
         gi += ng;
     }
-    *n_twin_items = n_items;
+    *n_out = n_items;
     return 0;
+}
+
+struct encode_job {
+    const struct encode_ctx *ctx;
+    int64_t b0, b1, gi, pi, n_items;
+    int64_t *scratch;          /* counts (M + 1) then mark (M) */
+    int rc;
+};
+
+static void *encode_thread(void *arg)
+{
+    struct encode_job *j = (struct encode_job *)arg;
+    j->rc = encode_range(j->ctx, j->b0, j->b1, j->gi, j->pi, j->scratch, j->scratch + j->ctx->M + 1,
+                         &j->n_items);
+    return NULL;
+}
+
+#define MMS_ENCODE_MAX_THREADS 8
+
+int mms_host_encode(int64_t B, int64_t M, int64_t G, int64_t P,
+                    const int64_t *n_groups, const int64_t *cfg, const int32_t *cfg_index,
+                    const int64_t *column_of, const int64_t *n_in_group, const int64_t *placed_model,
+                    uint16_t *model_off, uint32_t *model_rep, uint32_t *group_info,
+                    int64_t *slots, int32_t *twin_items, int64_t *n_twin_items,
+                    int64_t *counts, int64_t *mark, int64_t max_perms)
+{
+    struct encode_ctx ctx = {M, G, P, n_groups, cfg, column_of, n_in_group, placed_model, cfg_index,
+                             model_off, model_rep, group_info, slots, twin_items, max_perms};
+    /* placements are independent: a long list is cut into ranges, one thread each (the
+     * caller holds the GIL; these threads touch no Python object) */
+    int threads = mms_host_threads > 0 ? mms_host_threads : 4;
+    if (threads > MMS_ENCODE_MAX_THREADS) threads = MMS_ENCODE_MAX_THREADS;
+    if (B < 512 * threads) threads = (int)(B / 512);
+    if (threads <= 1) return encode_range(&ctx, 0, B, 0, 0, counts, mark, n_twin_items);
+
+    struct encode_job jobs[MMS_ENCODE_MAX_THREADS];
+    pthread_t tid[MMS_ENCODE_MAX_THREADS];
+    int64_t *scratch = (int64_t *)malloc(sizeof(int64_t) * (size_t)threads * (size_t)(2 * M + 1));
+    if (!scratch) return encode_range(&ctx, 0, B, 0, 0, counts, mark, n_twin_items);
+    int64_t gi = 0, pi = 0, b = 0;
+    for (int t = 0; t < threads; ++t) {
+        const int64_t b1 = (t + 1 == threads) ? B : B * (t + 1) / threads;
+        jobs[t].ctx = &ctx; jobs[t].b0 = b; jobs[t].b1 = b1; jobs[t].gi = gi; jobs[t].pi = pi;
+        jobs[t].n_items = 0; jobs[t].rc = 0;
+        jobs[t].scratch = scratch + (size_t)t * (size_t)(2 * M + 1);
+        for (; b < b1; ++b)
+            for (int64_t g = 0; g < n_groups[b]; ++g) pi += n_in_group[gi++];
+    }
+    int started = 0;
+    for (int t = 1; t < threads; ++t) {
+        if (pthread_create(&tid[t], NULL, encode_thread, &jobs[t]) != 0) break;
+        started = t;
+    }
+    encode_thread(&jobs[0]);
+    for (int t = started + 1; t < threads; ++t) encode_thread(&jobs[t]);   /* threads that did not start */
+    for (int t = 1; t <= started; ++t) pthread_join(tid[t], NULL);
+    free(scratch);
+    /* the ranges' twin items, one after the other */
+    int64_t n_items = 0;
+    int rc = 0;
+    for (int t = 0; t < threads; ++t) {
+        if (jobs[t].rc) rc = jobs[t].rc;
+        if (jobs[t].n_items && 3 * jobs[t].gi != 3 * n_items)
+            memmove(twin_items + 3 * n_items, twin_items + 3 * jobs[t].gi,
+                    sizeof(int32_t) * 3 * (size_t)jobs[t].n_items);
+        n_items += jobs[t].n_items;
+    }
+    *n_twin_items = n_items;
+    return rc;
 }

@@ -55,6 +55,8 @@ struct StatsArgs {
     int32_t *leaf_start;       // [B][leaf_cap]
     uint8_t *leaf_merges;      // [B][leaf_cap]
     double *leaf_sums;         // [B][leaf_cap]
+    int32_t *node_n;           // [B][leaf_cap] second buffers of the leaf planner
+    uint8_t *node_m;           // [B][leaf_cap]
     int64_t leaf_cap;
     mms_stats_out out;
 };
@@ -173,38 +175,96 @@ compact_latency_kernel(StatsArgs a)
     }
 }
 
-// numpy's split of n elements into leaves, by one thread: leaf_start[0 .. count]
-// (the last entry is n) and, per leaf, how many pair sums follow it.
-__device__ inline int32_t plan_leaves(int64_t n, int32_t *leaf_start, uint8_t *merges)
+// Exclusive prefix sum of one value per thread over the block; `total` gets the sum.
+__device__ inline int block_exclusive_scan(int v, int &total)
 {
-    int64_t st_base[kStatsDepth], st_n[kStatsDepth];
-    uint8_t st_phase[kStatsDepth];
-    int sp = 0;
-    int32_t count = 0;
-    st_base[0] = 0; st_n[0] = n; st_phase[0] = 0; sp = 1;
-    while (sp > 0) {
-        const int t = sp - 1;
-        if (st_n[t] <= 128) {
-            leaf_start[count] = (int32_t)st_base[t];
-            merges[count] = 0;
-            ++count;
-            --sp;
-            continue;
-        }
-        int64_t half = st_n[t] / 2;
-        half -= half % 8;
-        if (st_phase[t] == 0) {
-            st_phase[t] = 1;
-            st_base[sp] = st_base[t]; st_n[sp] = half; st_phase[sp] = 0; ++sp;
-        } else if (st_phase[t] == 1) {
-            st_phase[t] = 2;
-            st_base[sp] = st_base[t] + half; st_n[sp] = st_n[t] - half; st_phase[sp] = 0; ++sp;
-        } else {
-            merges[count - 1] += 1;
-            --sp;
-        }
+    __shared__ int s_part[kStatsThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += o;
     }
-    leaf_start[count] = (int32_t)n;
+    if (lane == 31) s_part[warp] = incl;
+    __syncthreads();
+    int before = 0;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < kStatsThreads / 32; ++w) {
+        const int c = s_part[w];
+        if (w < warp) before += c;
+        total += c;
+    }
+    __syncthreads();                                   // s_part is rewritten by the next call
+    return before + incl - v;
+}
+
+// numpy's split of n elements into leaves, by the whole block: leaf_start[0 ..
+// count] (the last entry is n) and, per leaf, how many pair sums follow it.
+// The recursion (halves rounded down to multiples of eight until at most 128
+// elements are left) is unrolled level by level: every node of a level that is
+// still too long is replaced by its two halves, in place in the sequence, so
+// the sequence stays in element order; a right half inherits its parent's pair
+// sums and adds one.  node_n / node_m: a second pair of buffers of the same
+// size as leaf_start / merges.
+__device__ inline int32_t block_plan_leaves(int64_t n, int32_t *leaf_start, uint8_t *merges,
+                                            int32_t *node_n, uint8_t *node_m)
+{
+    __shared__ int s_any;
+    int32_t *src_n = leaf_start, *dst_n = node_n;
+    uint8_t *src_m = merges, *dst_m = node_m;
+    if (threadIdx.x == 0) { src_n[0] = (int32_t)n; src_m[0] = 0; s_any = 0; }
+    __syncthreads();
+    int32_t count = 1;
+    for (int level = 0; level < 40; ++level) {
+        int32_t made = 0;
+        bool split_any = false;
+        for (int32_t base = 0; base < count; base += kStatsThreads) {
+            const int32_t k = base + threadIdx.x;
+            const int32_t v = k < count ? src_n[k] : 0;
+            const bool split = v > 128;
+            int total;
+            const int pos = made + block_exclusive_scan(k < count ? (split ? 2 : 1) : 0, total);
+            if (k < count) {
+                const uint8_t m = src_m[k];
+                if (split) {
+                    int32_t half = v / 2;
+                    half -= half % 8;
+                    dst_n[pos] = half;         dst_m[pos] = 0;
+                    dst_n[pos + 1] = v - half; dst_m[pos + 1] = (uint8_t)(m + 1);
+                    split_any = true;
+                } else {
+                    dst_n[pos] = v; dst_m[pos] = m;
+                }
+            }
+            made += total;
+        }
+        if (split_any) s_any = 1;
+        __syncthreads();
+        const bool again = s_any != 0;
+        __syncthreads();
+        if (threadIdx.x == 0) s_any = 0;
+        if (!again) break;                              // src already holds the leaves
+        int32_t *tn = src_n; src_n = dst_n; dst_n = tn;
+        uint8_t *tm = src_m; src_m = dst_m; dst_m = tm;
+        count = made;
+        __syncthreads();
+    }
+    // sizes -> starts (in place when the leaves ended up in leaf_start's own buffer: every
+    // thread reads its entry before it writes it)
+    int32_t at = 0;
+    for (int32_t base = 0; base < count; base += kStatsThreads) {
+        const int32_t k = base + threadIdx.x;
+        const int32_t v = k < count ? src_n[k] : 0;
+        const uint8_t m = k < count ? src_m[k] : 0;
+        int total;
+        const int start = at + block_exclusive_scan(v, total);
+        if (k < count) { leaf_start[k] = start; merges[k] = m; }
+        at += total;
+    }
+    if (threadIdx.x == 0) leaf_start[count] = (int32_t)n;
+    __syncthreads();
     return count;
 }
 
@@ -318,18 +378,20 @@ latency_moments_kernel(StatsArgs a)
 {
     const int32_t u = blockIdx.x;
     const int64_t b = blockIdx.y;
-    __shared__ int32_t s_leaves;
-    int32_t *leaf_start = a.leaf_start + (size_t)b * a.leaf_cap + a.leaf_off[u];
-    uint8_t *merges = a.leaf_merges + (size_t)b * a.leaf_cap + a.leaf_off[u];
-    double *sums = a.leaf_sums + (size_t)b * a.leaf_cap + a.leaf_off[u];
+    const size_t region = (size_t)b * a.leaf_cap + a.leaf_off[u];
+    int32_t *leaf_start = a.leaf_start + region;
+    uint8_t *merges = a.leaf_merges + region;
+    double *sums = a.leaf_sums + region;
+    int32_t *node_n = a.node_n + region;
+    uint8_t *node_m = a.node_m + region;
     if (u == a.M) {
         // np.mean(good) and np.mean(finish - start) over the window (workload.py:352)
         const double *fin = a.finish + (size_t)b * a.row_stride + a.first;
         const uint8_t *good = a.good + (size_t)b * a.row_stride + a.first;
         const double *arr = a.arrivals + a.first;
-        if (threadIdx.x == 0) s_leaves = a.window > 0 ? plan_leaves(a.window, leaf_start, merges) : 0;
-        __syncthreads();
-        const double total = block_numpy_sum(s_leaves, leaf_start, merges, sums,
+        const int32_t num_leaves =
+            a.window > 0 ? block_plan_leaves(a.window, leaf_start, merges, node_n, node_m) : 0;
+        const double total = block_numpy_sum(num_leaves, leaf_start, merges, sums,
                                              [&](int64_t i) { return fin[i] - arr[i]; });
         __shared__ unsigned long long s_good;
         if (threadIdx.x == 0) s_good = 0;
@@ -354,9 +416,7 @@ latency_moments_kernel(StatsArgs a)
         return;
     }
     const double *x = a.lat + (size_t)b * a.window + a.offsets[u];
-    if (threadIdx.x == 0) s_leaves = plan_leaves(n, leaf_start, merges);
-    __syncthreads();
-    const int32_t num_leaves = s_leaves;
+    const int32_t num_leaves = block_plan_leaves(n, leaf_start, merges, node_n, node_m);
     // np.mean: the pairwise sum divided by the count
     const double mean = block_numpy_sum(num_leaves, leaf_start, merges, sums,
                                         [&](int64_t i) { return x[i]; }) / (double)n;
@@ -379,7 +439,7 @@ static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 struct StatsGeometry {
     int64_t leaf_cap;
     size_t off_counts, off_offsets, off_leaf_off, off_lat, off_leaf_start, off_leaf_merges,
-        off_leaf_sums, total;
+        off_leaf_sums, off_node_n, off_node_m, total;
 };
 
 static int plan_stats(int64_t window, int32_t M, int32_t B, StatsGeometry *g)
@@ -396,6 +456,8 @@ static int plan_stats(int64_t window, int32_t M, int32_t B, StatsGeometry *g)
     g->off_leaf_start = at;  at = align256(at + (size_t)B * g->leaf_cap * 4);
     g->off_leaf_merges = at; at = align256(at + (size_t)B * g->leaf_cap);
     g->off_leaf_sums = at;   at = align256(at + (size_t)B * g->leaf_cap * 8);
+    g->off_node_n = at;      at = align256(at + (size_t)B * g->leaf_cap * 4);
+    g->off_node_m = at;      at = align256(at + (size_t)B * g->leaf_cap);
     g->total = at;
     return MMS_OK;
 }
@@ -444,6 +506,8 @@ int mms_compute_stats(const double *arrivals, const int32_t *model_ids, int32_t 
     a.leaf_start = (int32_t *)(scratch + g.off_leaf_start);
     a.leaf_merges = (uint8_t *)(scratch + g.off_leaf_merges);
     a.leaf_sums = (double *)(scratch + g.off_leaf_sums);
+    a.node_n = (int32_t *)(scratch + g.off_node_n);
+    a.node_m = (uint8_t *)(scratch + g.off_node_m);
     a.leaf_cap = g.leaf_cap;
     a.out = *out;
 #define MMS_STATS_CUDA(call)                                                              \

@@ -138,6 +138,8 @@ class PlacementEvaluator:
         # part: one flag, or one per part.  Only the last part needs it: the
         # serial repairs of an earlier part run beside the parts behind it anyway.
         self.pipeline_split = (False, True)
+        # engine.sim_options per part (None: self.options for every part)
+        self.pipeline_options = None
         self._streams = []
         self.last_resimulated = None
         self.last_h2d_bytes = 0
@@ -181,9 +183,12 @@ class PlacementEvaluator:
             enc = engine.encode_placements(sols[bounds[k]:bounds[k + 1]], self.table,
                                            len(self.model_names))
             self._streams[k].wait_stream(main)           # the trace was uploaded there
+            opts_k = self.options
+            if self.pipeline_options is not None and len(self.pipeline_options) == parts:
+                opts_k = self.pipeline_options[k]
             with torch.cuda.stream(self._streams[k]):
                 jobs.append(engine.submit_batch(self.trace, enc, self.table, pinned=pinned,
-                                                options=self.options, split=split[k],
+                                                options=opts_k, split=split[k],
                                                 crowded=k + 1 < parts))
             encs.append(enc)
         done = [engine.collect_batch(job) for job in jobs]

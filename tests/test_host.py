@@ -300,3 +300,40 @@ def test_expansion_of_normalized_placements_equals_add_then_normalize():
             if not got:
                 break
             sol = rng.choice(got)
+
+
+def test_encoder_threads_change_nothing():
+    """The table builder cuts a long list into ranges, one thread each; the
+    tables and the lists of interchangeable groups are the same as from one
+    thread (and as from the numpy encoder)."""
+    import ctypes
+    from mms_b200 import _native as nat
+    from mms_b200 import cases, engine
+    H = nat.host_lib()
+    if H is None:
+        pytest.skip("host helper not built")
+    case = cases.candidate_batch_case(num_candidates=3000, duration=30.0)
+    profs = [d.profiling_result for d in case.model_datas]
+    knob = ctypes.c_int.in_dll(H, "mms_host_threads")
+    encs = []
+    try:
+        for threads in (1, 3, 5):
+            knob.value = threads
+            table = engine.LatencyTable(profs)
+            encs.append(engine.encode_placements(case.placements, table, len(profs)))
+    finally:
+        knob.value = 0
+    table = engine.LatencyTable(profs)
+    encs.append(engine.encode_placements(case.placements, table, len(profs), native=False))
+    first = encs[0]
+    assert len(first.twins) > 50
+    for e in encs[1:]:
+        assert np.array_equal(e.model_off, first.model_off)
+        assert np.array_equal(e.model_rep, first.model_rep)
+        assert np.array_equal(e.group_info, first.group_info)
+        assert (e.T, e.G, e.P) == (first.T, first.G, first.P)
+        # (the numpy encoder lists a placement's classes in another order)
+        assert [(b, sorted(list(c) for c in cl)) for b, cl in e.twins] == \
+            [(b, sorted(list(c) for c in cl)) for b, cl in first.twins]
+    for e in encs[1:3]:
+        assert e.twins == first.twins

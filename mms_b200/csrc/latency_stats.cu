@@ -35,7 +35,7 @@ namespace mms {
 extern thread_local char g_last_error[256];
 
 constexpr int kStatsThreads = 256;
-constexpr int kStatsItems = 4;                     // requests per thread and tile
+constexpr int kStatsItems = 8;                     // requests per thread and tile
 constexpr int kStatsSmemBins = 4096;               // models counted in shared memory
 constexpr int kStatsDepth = 48;                    // pair-sum stack
 
@@ -132,7 +132,10 @@ compact_latency_kernel(StatsArgs a)
 #pragma unroll
         for (int k = 0; k < kStatsItems; ++k) {
             const int64_t i = i0 + k;
-            take[k] = i < a.window && ids[i] == m && good[i] != 0;
+            // both loads issued whatever the first one returns
+            const int32_t id = i < a.window ? ids[i] : -1;
+            const uint8_t ok = i < a.window ? good[i] : (uint8_t)0;
+            take[k] = (id == m) & (ok != 0);
             mine += take[k];
         }
         int incl = mine;                                  // inclusive scan inside the warp
@@ -284,32 +287,72 @@ __device__ inline double leaf_sum(int64_t s, int64_t e, F value)
     return r;
 }
 
-__device__ inline double merge_leaves(int32_t num_leaves, const double *sums, const uint8_t *merges)
+// Leaves [lo, hi) combined by the pair sums that fall inside them (a subtree of
+// numpy's recursion: the pair sums its last leaf owes to nodes above it stay
+// undone).
+__device__ inline double merge_leaves(int32_t lo, int32_t hi, const double *sums,
+                                      const uint8_t *merges)
 {
     double stack[kStatsDepth];
     int sp = 0;
-    for (int32_t k = 0; k < num_leaves; ++k) {
+    for (int32_t k = lo; k < hi; ++k) {
         stack[sp++] = sums[k];
         for (int g = merges[k]; g > 0 && sp >= 2; --g) {
             --sp;
             stack[sp - 1] = stack[sp - 1] + stack[sp];
         }
     }
-    return num_leaves > 0 ? stack[0] : 0.0;
+    return hi > lo ? stack[0] : 0.0;
+}
+
+// First leaf that starts at element `at` (leaf_start is ascending; the entry exists).
+__device__ inline int32_t leaf_at(const int32_t *leaf_start, int32_t num_leaves, int64_t at)
+{
+    int32_t lo = 0, hi = num_leaves;
+    while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (leaf_start[mid] < at) lo = mid + 1; else hi = mid;
+    }
+    return lo;
 }
 
 // Block-wide numpy-ordered sum of value(0 .. n-1); every thread gets the result.
+// The leaves are added up one per thread.  The pair sums above them follow
+// numpy's recursion tree: its nodes at depth D (2^D of them, D chosen so that
+// every node above is still split) go one to a thread, which combines its
+// node's leaves; the 2^D results are then paired level by level, left + right.
 template <typename F>
 __device__ inline double block_numpy_sum(int32_t num_leaves, const int32_t *leaf_start,
                                          const uint8_t *merges, double *sums, F value)
 {
-    __shared__ double s_total;
+    __shared__ double s_node[kStatsThreads];
     for (int32_t k = threadIdx.x; k < num_leaves; k += blockDim.x)
         sums[k] = leaf_sum(leaf_start[k], leaf_start[k + 1], value);
     __syncthreads();
-    if (threadIdx.x == 0) s_total = merge_leaves(num_leaves, sums, merges);
+    const int64_t n = num_leaves > 0 ? leaf_start[num_leaves] : 0;
+    int depth = 0;                      // nodes at depth < `depth` have more than 256 elements
+    while ((1 << (depth + 1)) <= kStatsThreads && (n >> (depth + 1)) >= 256) ++depth;
+    const int nodes = 1 << depth;
+    if ((int)threadIdx.x < nodes) {
+        int64_t base = 0, len = n;
+        for (int d = depth - 1; d >= 0; --d) {          // the path to node threadIdx.x
+            int64_t half = len / 2;
+            half -= half % 8;
+            if ((threadIdx.x >> d) & 1) { base += half; len -= half; } else { len = half; }
+        }
+        const int32_t lo = leaf_at(leaf_start, num_leaves, base);
+        const int32_t hi = leaf_at(leaf_start, num_leaves, base + len);
+        s_node[threadIdx.x] = merge_leaves(lo, hi, sums, merges);
+    }
     __syncthreads();
-    const double total = s_total;
+    for (int width = nodes >> 1; width >= 1; width >>= 1) {
+        double pair = 0.0;
+        if ((int)threadIdx.x < width) pair = s_node[2 * threadIdx.x] + s_node[2 * threadIdx.x + 1];
+        __syncthreads();
+        if ((int)threadIdx.x < width) s_node[threadIdx.x] = pair;
+        __syncthreads();
+    }
+    const double total = s_node[0];
     __syncthreads();
     return total;
 }
@@ -340,30 +383,37 @@ __device__ inline double block_select(const double *x, int64_t n, int64_t rank)
         __syncthreads();
         const uint64_t prefix = s_prefix;
         const uint64_t above = shift == 56 ? 0 : (~0ull << (shift + 8));
-        const int64_t rounds = (n + blockDim.x - 1) / blockDim.x;
-        for (int64_t r = 0; r < rounds; ++r) {
-            const int64_t i = r * blockDim.x + threadIdx.x;
-            bool in = false;
-            unsigned int byte = 0;
-            if (i < n) {
-                const uint64_t k = order_key(x[i]);
-                in = (k & above) == prefix;
-                byte = (unsigned int)(k >> shift) & 255u;
+        for (int64_t base = 0; base < n; base += 4 * (int64_t)blockDim.x) {
+            double v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {                // four loads in flight per thread
+                const int64_t i = base + (int64_t)q * blockDim.x + threadIdx.x;
+                v[q] = i < n ? x[i] : 0.0;
             }
-            // equal bytes of a warp go in with one addition
-            const unsigned int live = __ballot_sync(0xFFFFFFFFu, in);
-            if (in) {
-                const unsigned int same = __match_any_sync(live, byte);
-                if ((int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&s_hist[byte], __popc(same));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int64_t i = base + (int64_t)q * blockDim.x + threadIdx.x;
+                const uint64_t k = order_key(v[q]);
+                const bool in = i < n && (k & above) == prefix;
+                const unsigned int byte = (unsigned int)(k >> shift) & 255u;
+                // equal bytes of a warp go in with one addition
+                const unsigned int live = __ballot_sync(0xFFFFFFFFu, in);
+                if (in) {
+                    const unsigned int same = __match_any_sync(live, byte);
+                    if ((int)(threadIdx.x & 31) == __ffs(same) - 1)
+                        atomicAdd(&s_hist[byte], __popc(same));
+                }
             }
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            long long left = s_rank;
-            int bin = 0;
-            while (bin < 255 && (long long)s_hist[bin] <= left) { left -= s_hist[bin]; ++bin; }
-            s_rank = left;
-            s_prefix = prefix | ((unsigned long long)bin << shift);
+        // the bin that holds the rank: thread t looks at bin t
+        const long long want = s_rank;
+        const int mine = threadIdx.x < 256 ? (int)s_hist[threadIdx.x] : 0;
+        int total;
+        const long long before = block_exclusive_scan(mine, total);
+        if (threadIdx.x < 256 && before <= want && want < before + mine) {
+            s_rank = want - before;
+            s_prefix = prefix | ((unsigned long long)threadIdx.x << shift);
         }
         __syncthreads();
     }
@@ -372,12 +422,15 @@ __device__ inline double block_select(const double *x, int64_t n, int64_t rank)
     return v;
 }
 
-// Block (u, b): u < M is model u, u == M the whole window.
+// Block (u, b, part): u < M is model u, u == M the whole window; part 0 forms
+// the sums, parts 1 and 2 select the 90th and the 99th percentile.
 __global__ void __launch_bounds__(kStatsThreads)
 latency_moments_kernel(StatsArgs a)
 {
     const int32_t u = blockIdx.x;
     const int64_t b = blockIdx.y;
+    const int part = blockIdx.z;
+    if (u == a.M && part != 0) return;
     const size_t region = (size_t)b * a.leaf_cap + a.leaf_off[u];
     int32_t *leaf_start = a.leaf_start + region;
     uint8_t *merges = a.leaf_merges + region;
@@ -409,13 +462,20 @@ latency_moments_kernel(StatsArgs a)
     const size_t cell = (size_t)b * a.M + u;
     const int64_t n = a.out.num_good[cell];
     if (n == 0) {            // the reference puts latency = [0] here (workload.py:339-341)
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0 && part == 0) {
             a.out.latency_mean[cell] = 0.0; a.out.latency_std[cell] = 0.0;
             a.out.latency_p90[cell] = 0.0; a.out.latency_p99[cell] = 0.0;
         }
         return;
     }
     const double *x = a.lat + (size_t)b * a.window + a.offsets[u];
+    if (part != 0) {
+        // sorted[int(0.90 * n)], sorted[int(0.99 * n)] (workload.py:344-345)
+        const double frac = part == 1 ? 0.90 : 0.99;
+        const double v = block_select(x, n, (int64_t)(frac * (double)n));
+        if (threadIdx.x == 0) (part == 1 ? a.out.latency_p90 : a.out.latency_p99)[cell] = v;
+        return;
+    }
     const int32_t num_leaves = block_plan_leaves(n, leaf_start, merges, node_n, node_m);
     // np.mean: the pairwise sum divided by the count
     const double mean = block_numpy_sum(num_leaves, leaf_start, merges, sums,
@@ -423,14 +483,9 @@ latency_moments_kernel(StatsArgs a)
     // np.std: sqrt(sum((x - mean) * (x - mean)) / n), the sum pairwise again
     const double sq = block_numpy_sum(num_leaves, leaf_start, merges, sums,
                                       [&](int64_t i) { const double d = x[i] - mean; return d * d; });
-    // sorted[int(0.90 * n)], sorted[int(0.99 * n)] (workload.py:344-345)
-    const double p90 = block_select(x, n, (int64_t)(0.90 * (double)n));
-    const double p99 = block_select(x, n, (int64_t)(0.99 * (double)n));
     if (threadIdx.x == 0) {
         a.out.latency_mean[cell] = mean;
         a.out.latency_std[cell] = sqrt(sq / (double)n);
-        a.out.latency_p90[cell] = p90;
-        a.out.latency_p99[cell] = p99;
     }
 }
 
@@ -532,7 +587,7 @@ int mms_compute_stats(const double *arrivals, const int32_t *model_ids, int32_t 
         mms::compact_latency_kernel<<<dim3((unsigned)M, (unsigned)B), mms::kStatsThreads, 0, st>>>(a);
         MMS_STATS_CUDA(cudaGetLastError());
     }
-    mms::latency_moments_kernel<<<dim3((unsigned)M + 1, (unsigned)B), mms::kStatsThreads, 0, st>>>(a);
+    mms::latency_moments_kernel<<<dim3((unsigned)M + 1, (unsigned)B, 3), mms::kStatsThreads, 0, st>>>(a);
     MMS_STATS_CUDA(cudaGetLastError());
 #undef MMS_STATS_CUDA
     return MMS_OK;

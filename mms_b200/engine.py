@@ -106,6 +106,101 @@ class DeviceTrace:
         return nat.SumPlan(self.num_leaves, 0, _ptr(self.leaf_start), _ptr(self.leaf_merges))
 
 
+class LazyArray:
+    """A host array that is produced piece by piece, straight into an upload
+    buffer: fill(out, lo, hi) writes elements [lo, hi) into `out` (a numpy view
+    of hi - lo elements of `dtype`).  Saves the pass that would materialise it."""
+
+    def __init__(self, size, dtype, fill):
+        self.size, self.dtype, self.fill = int(size), np.dtype(dtype), fill
+
+    def __len__(self):
+        return self.size
+
+    def materialize(self):
+        out = np.empty(self.size, self.dtype)
+        self.fill(out, 0, self.size)
+        return out
+
+
+class PinnedStager:
+    """Uploads many host arrays through pinned staging buffers: a few threads
+    copy pieces of the arrays into page-locked buffers (numpy copies run
+    outside the interpreter lock) and enqueue the transfers from there, each on
+    a stream of its own.  Pageable memory goes to the device at about a third
+    of the rate of page-locked memory, whatever the number of threads that
+    ask; staging by hand is what lets the threads help.  One instance per
+    device is kept (page-locked allocations are slow)."""
+
+    _instances = {}
+
+    @classmethod
+    def get(cls, dev, threads=8, piece_bytes=16 << 20):
+        key = (torch.device(dev), threads, piece_bytes)
+        if key not in cls._instances:
+            cls._instances[key] = cls(*key)
+        return cls._instances[key]
+
+    def __init__(self, dev, threads, piece_bytes):
+        from concurrent.futures import ThreadPoolExecutor
+        self.device, self.threads, self.piece = torch.device(dev), int(threads), int(piece_bytes)
+        self.pool = ThreadPoolExecutor(self.threads)
+        self.streams = [torch.cuda.Stream(device=self.device) for _ in range(self.threads)]
+        self.buffers = [[torch.empty(self.piece, dtype=torch.uint8).pin_memory() for _ in range(2)]
+                        for _ in range(self.threads)]
+
+    def upload(self, tasks):
+        """tasks: [(device tensor, numpy array or LazyArray)] of equal byte sizes
+        pairwise, contiguous.  Returns when every transfer has been enqueued;
+        the current stream waits for them."""
+        pieces = [[] for _ in range(self.threads)]
+        load = [0] * self.threads
+        for dst, src in tasks:
+            d8 = dst.reshape(-1).view(torch.uint8)
+            lazy = isinstance(src, LazyArray)
+            if lazy:
+                item, count = src.dtype.itemsize, src.size
+            else:
+                src = np.ascontiguousarray(src).reshape(-1)
+                item, count = src.dtype.itemsize, src.size
+            if d8.numel() != item * count:
+                raise ValueError("upload: sizes differ")
+            step = max(self.piece // item, 1)
+            for lo in range(0, count, step):
+                k = load.index(min(load))
+                hi = min(lo + step, count)
+                pieces[k].append((d8[lo * item:hi * item], src, lo, hi))
+                load[k] += (hi - lo) * item
+        main = torch.cuda.current_stream(self.device)
+
+        def work(k):
+            stream, bufs = self.streams[k], self.buffers[k]
+            events = [None, None]
+            stream.wait_stream(main)            # the destinations were allocated there
+            with torch.cuda.device(self.device), torch.cuda.stream(stream):
+                for j, (d8, src, lo, hi) in enumerate(pieces[k]):
+                    if events[j & 1] is not None:
+                        events[j & 1].synchronize()      # the buffer's last transfer is done
+                    buf = bufs[j & 1][:d8.numel()]
+                    view = buf.numpy().view(src.dtype)
+                    if isinstance(src, LazyArray):
+                        src.fill(view, lo, hi)
+                    else:
+                        np.copyto(view, src[lo:hi])
+                    d8.copy_(buf, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    events[j & 1] = ev
+            for ev in events:                   # the buffers are free for the next upload
+                if ev is not None:
+                    ev.synchronize()
+
+        list(self.pool.map(work, [k for k in range(self.threads) if pieces[k]]))
+        for k in range(self.threads):
+            if pieces[k]:
+                main.wait_stream(self.streams[k])
+
+
 class DeviceTraceBatch:
     """T request traces resident on one GPU for runs in which every candidate
     has a trace of its own (one placement scored on many traces).  The traces
@@ -117,7 +212,8 @@ class DeviceTraceBatch:
     Duck-type compatible with DeviceTrace where launches are concerned."""
 
     def __init__(self, arrivals: Sequence, model_ids: Sequence, slos: Sequence, num_models: int,
-                 device=None):
+                 device=None, staged=False):
+        """staged: upload through PinnedStager (worth it from about a gigabyte)."""
         _require_cuda()
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
             else torch.device(device)
@@ -139,15 +235,25 @@ class DeviceTraceBatch:
             cat_arr = torch.empty(max(total, 1), dtype=torch.float64, device=dev)
             cat_mid = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
             cat_slo = torch.empty(max(total, 1), dtype=torch.float32, device=dev)
+            tasks = []
             for t in range(T):
                 lo, hi = int(offsets[t]), int(offsets[t + 1])
                 if hi > lo:
-                    cat_arr[lo:hi].copy_(torch.from_numpy(
-                        np.ascontiguousarray(arrivals[t], np.float64)), non_blocking=True)
-                    cat_mid[lo:hi].copy_(torch.from_numpy(
-                        np.ascontiguousarray(model_ids[t], np.int32)), non_blocking=True)
-                    cat_slo[lo:hi].copy_(torch.from_numpy(
-                        np.ascontiguousarray(slos[t], np.float32)), non_blocking=True)
+                    for dst, src, dtype in ((cat_arr, arrivals[t], np.float64),
+                                            (cat_mid, model_ids[t], np.int32),
+                                            (cat_slo, slos[t], np.float32)):
+                        if isinstance(src, LazyArray):
+                            if src.dtype != dtype:
+                                raise ValueError("lazy trace array of the wrong type")
+                            src = src if staged else src.materialize()
+                        else:
+                            src = np.ascontiguousarray(src, dtype)
+                        tasks.append((dst[lo:hi], src))
+            if staged:
+                PinnedStager.get(dev).upload(tasks)
+            else:
+                for dst, src in tasks:
+                    dst.copy_(torch.from_numpy(src), non_blocking=True)
             d_off = _to_device(offsets, dev)
             self.arrivals = torch.empty((max(N, 1), T), dtype=torch.float64, device=dev)
             self.model_ids = torch.empty((max(N, 1), T), dtype=torch.int32, device=dev)

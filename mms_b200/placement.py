@@ -255,7 +255,11 @@ class ResidentSweep:
     """The traces of a sweep on the GPU, grouped by length, every group ready to
     be launched (any number of times) on a stream of its own."""
 
-    def __init__(self, sweep, workloads, cells):
+    def __init__(self, sweep, workloads, cells, eager=False):
+        """eager: every group is launched as soon as its traces are on their way
+        (longest traces first), so that the uploads of the later groups run
+        beside the kernels of the earlier ones; `tally_launched` then joins
+        them.  Uploads go through pinned staging buffers."""
         import torch
         self.sweep = sweep
         self.T = len(workloads)
@@ -263,21 +267,30 @@ class ResidentSweep:
         dev = sweep.device if sweep.device is not None else torch.device(
             "cuda", torch.cuda.current_device())
         self.device = torch.device(dev)
-        arrays = sweep._arrays(workloads)
+        arrays = sweep._arrays(workloads, lazy=eager)
         lengths = np.array([len(w.arrivals) for w in workloads], np.int64)
         self.lengths = lengths
         self.groups = length_groups(lengths)
+        if eager:                                   # the longest walk starts first
+            self.groups.sort(key=lambda idx: -int(lengths[idx].max()))
         self.h2d_bytes = 0
         self.jobs, self.streams, self.meta = [], [], []
+        main = torch.cuda.current_stream(self.device)
         for idx in self.groups:
-            traces = engine.DeviceTraceBatch([workloads[t].arrivals for t in idx],
-                                             [arrays[t][0] for t in idx],
-                                             [arrays[t][1] for t in idx], M, device=self.device)
-            job = engine.ResidentBatch(traces, sweep.enc.repeat(len(idx)), sweep.table,
-                                       options=sweep.options, split=False)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side if eager else main):
+                traces = engine.DeviceTraceBatch([workloads[t].arrivals for t in idx],
+                                                 [arrays[t][0] for t in idx],
+                                                 [arrays[t][1] for t in idx], M,
+                                                 device=self.device, staged=eager)
+                job = engine.ResidentBatch(traces, sweep.enc.repeat(len(idx)), sweep.table,
+                                           options=sweep.options, split=False)
+                if eager:
+                    job.launch()
             self.h2d_bytes += traces.h2d_bytes + job.h2d_bytes
             self.jobs.append(job)
-            self.streams.append(torch.cuda.Stream(device=self.device))
+            self.streams.append(side)
             cell = torch.from_numpy(((sweep.first_trace + idx) % cells).astype(np.int64)).to(
                 self.device)
             n = torch.from_numpy(lengths[idx]).to(self.device)
@@ -296,6 +309,13 @@ class ResidentSweep:
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 job.launch()
+        return self.tally_launched()
+
+    def tally_launched(self):
+        """Joins the groups' streams behind the current one and tallies per cell."""
+        import torch
+        main = torch.cuda.current_stream(self.device)
+        self.tally.zero_()
         for side in self.streams:
             main.wait_stream(side)
         for job, (cell, n) in zip(self.jobs, self.meta):
@@ -352,17 +372,43 @@ class TraceSweep:
         self.batch = int(batch)
         self.cells = int(cells)
         self.first_trace = int(first_trace)
+        # evaluate(): launch each group of traces as soon as it is uploaded (through pinned
+        # staging buffers) instead of uploading everything first
+        self.eager = True
         self.last_h2d_bytes = self.last_d2h_bytes = 0
 
-    def _arrays(self, workloads):
+    def _arrays(self, workloads, lazy=False):
         """(model_ids, slos) of every workload; numpy does the work outside the
-        interpreter lock, so a few threads share it."""
+        interpreter lock, so a few threads share it.  lazy: as engine.LazyArrays
+        that the upload fills piece by piece (array-backed workloads only)."""
         from concurrent.futures import ThreadPoolExecutor
         import os
+        if lazy:
+            return [self._lazy_arrays(w) for w in workloads]
         if len(workloads) < 8:
             return [workload_arrays(w, self.model_names) for w in workloads]
         with ThreadPoolExecutor(min(16, os.cpu_count() or 1)) as pool:
             return list(pool.map(lambda w: workload_arrays(w, self.model_names), workloads))
+
+    def _lazy_arrays(self, w):
+        if not hasattr(w, "name_index"):
+            return workload_arrays(w, self.model_names)
+        name2id = {m: i for i, m in enumerate(self.model_names)}
+        lut = np.array([name2id.get(n, -1) for n in w.names] or [-1], dtype=np.int32)
+        which, slo = w.name_index, w.request_slo
+
+        same = np.array_equal(lut, np.arange(len(lut), dtype=np.int32))
+
+        def fill_ids(out, lo, hi):
+            if same:                # the workload lists the models in registration order
+                np.copyto(out, which[lo:hi])
+            else:
+                np.take(lut, which[lo:hi], out=out, mode="clip")    # indices are always in range
+
+        def fill_slos(out, lo, hi):
+            np.copyto(out, slo[lo:hi], casting="same_kind")     # f64 -> f32 as astype rounds it
+        return (engine.LazyArray(len(which), np.int32, fill_ids),
+                engine.LazyArray(len(slo), np.float32, fill_slos))
 
     def resident(self, workloads: Sequence[Workload]) -> ResidentSweep:
         return ResidentSweep(self, workloads, self.cells)
@@ -379,10 +425,10 @@ class TraceSweep:
             first = self.first_trace
             self.first_trace = first + lo
             try:
-                run = ResidentSweep(self, part, self.cells)
+                run = ResidentSweep(self, part, self.cells, eager=self.eager)
             finally:
                 self.first_trace = first
-            t = run.launch().clone()
+            t = (run.tally_launched() if self.eager else run.launch()).clone()
             tally = t if tally is None else tally + t
             res = run.results()
             engine._check_status(res)

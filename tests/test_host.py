@@ -337,3 +337,30 @@ def test_encoder_threads_change_nothing():
             [(b, sorted(list(c) for c in cl)) for b, cl in first.twins]
     for e in encs[1:3]:
         assert e.twins == first.twins
+
+
+def test_lazy_trace_arrays_equal_workload_arrays():
+    """The piecewise producers the sweep uploads from give the arrays of
+    workload_arrays (controller.py:335-336), whatever the piece boundaries."""
+    from mms_b200 import cases
+    from mms_b200.placement import TraceSweep
+    from mms_b200.simulator import workload_arrays
+    case = cases.sweep_case(duration=20.0)
+    sweep = TraceSweep.__new__(TraceSweep)
+    sweep.model_names = tuple(d.name for d in case.model_datas[:-3])      # three unknown models
+    w = case.trace(5)
+    ids, slos = workload_arrays(w, sweep.model_names)
+    lazy_ids, lazy_slos = sweep._lazy_arrays(w)
+    assert len(lazy_ids) == len(ids) and (ids == -1).any()
+    assert np.array_equal(lazy_ids.materialize(), ids) and lazy_ids.dtype == np.int32
+    assert lazy_slos.materialize().tobytes() == slos.tobytes()
+    out = np.empty(1000, np.int32)
+    lazy_ids.fill(out, 37, 1037)
+    assert np.array_equal(out, ids[37:1037])
+    out = np.empty(1000, np.float32)
+    lazy_slos.fill(out, 37, 1037)
+    assert np.array_equal(out, slos[37:1037])
+    # all models known and in the workload's order: the ids are the workload's own index
+    sweep.model_names = tuple(d.name for d in case.model_datas)
+    ids, _ = workload_arrays(w, sweep.model_names)
+    assert np.array_equal(sweep._lazy_arrays(w)[0].materialize(), ids) and (ids >= 0).all()

@@ -171,8 +171,8 @@ static int plan_call(int64_t N, const mms_placements *c, const mms_sim_options *
                                      c->max_stages, group_good, g->lat_smem_elems,
                                      g->lat_smem_elems != 0 && g->lat_f64 != 0);
     g->smem_stream = L.warp0 + (size_t)g->block_warps * L.warp_bytes;
-    g->smem_repair = L.total + (sizeof(double) * (size_t)c->max_slots + (size_t)c->max_groups) * kLanes;
-    g->smem_repair = (g->smem_repair + 15) & ~(size_t)15;
+    // ... the repair scratch, then the decoded-request records of the step that decodes ahead
+    g->smem_repair = staging_offset(L.total, c->max_slots, c->max_groups) + kStagedBytes;
     if (g->smem_repair > 227 * 1024) return MMS_ERR_UNSUPPORTED;
     // the tally's per-lane histograms (count_kernel)
     g->smem_count = sizeof(uint32_t) * (size_t)(c->max_groups + (c->num_models + 1) / 2) * kLanes;

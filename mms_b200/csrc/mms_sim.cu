@@ -188,6 +188,7 @@ __device__ inline Lane setup_lane(const KernelArgs &a, int64_t b, int lane, int 
     ln.lat_f64 = a.lat_f64 != 0;
     ln.M = a.M; ln.C = a.C; ln.S = a.S;
     ln.status = 0;
+    ln.staging = 0;
     for (int t = 0; t < a.T + kClockPad; ++t) SM_F64(ln.clk + t * kLanes) = 0.0;
     return ln;
 }
@@ -224,6 +225,25 @@ __device__ inline void init_pipe(const KernelArgs &a, Pipe &p, int64_t b)
 __device__ inline bool slim_shape(const KernelArgs &a)
 {
     return a.lat_smem_elems != 0 && a.lat_f64 != 0 && !a.dec_wide;
+}
+
+// Byte offset of the decoded-request records behind the repair scratch.
+__host__ __device__ inline size_t staging_offset(size_t layout_total, int T, int G)
+{
+    return (layout_total + (sizeof(double) * (size_t)T + (size_t)G) * kLanes + 15) & ~(size_t)15;
+}
+
+// What the step that decodes ahead (staged_step) takes for granted, beyond the slim step:
+// every shared-memory index fits 16 bits, and no model of candidate b has more than eight
+// replicas.  Called by all 32 lanes of a warp; the answer is the same in all of them.
+__device__ inline bool staged_shape(const KernelArgs &a, const SmemLayout &L, int64_t b)
+{
+    if (!slim_shape(a) || a.trace_pitch < 1) return false;
+    if ((staging_offset(L.total, a.T, a.G) + kStagedBytes) / sizeof(double) >= 65536) return false;
+    const uint16_t *off = a.model_off + (size_t)b * (a.M + 1);
+    bool many = false;
+    for (int m = threadIdx.x & (kLanes - 1); m < a.M; m += kLanes) many |= off[m + 1] - off[m] > 8;
+    return !__any_sync(0xFFFFFFFFu, many);
 }
 
 // Extra shared memory of the kernels that repair: the state the previous run
@@ -414,15 +434,21 @@ sim_repair_kernel(const KernelArgs a)
     if ((uint64_t)blockIdx.x * (kNarrow ? 1 : kLanes) >= count) return;
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0);
     stage_latency_table(a, L);
-    if (kNarrow && threadIdx.x != 0) return;
     const uint32_t w = kNarrow ? blockIdx.x : blockIdx.x * kLanes + lane;
     if (w >= count) return;
     const uint32_t item = a.work_items[w] & 0x7FFFFFFFu;
     const bool resume = (a.work_items[w] >> 31) != 0;
     const int32_t j = (int32_t)(item / (uint32_t)a.B);
     const int64_t b = item % (uint32_t)a.B;
+    // one chunk to a warp: the lone lane, or — where the step that decodes ahead applies —
+    // all 32 lanes as copies of it
+    constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
+    bool staged = false;
+    if constexpr (kCanSlim) staged = staged_shape(a, L, b);
+    if (kNarrow && !staged && threadIdx.x != 0) return;
 
     Lane ln = setup_lane<kGroupGood>(a, b, lane);
+    ln.staging = staged ? (uint32_t)staging_offset(L.total, a.T, a.G) : 0u;
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
     // start of the chunk from the copied-in true state, or where a capped
@@ -437,9 +463,14 @@ sim_repair_kernel(const KernelArgs a)
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
     const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
+    if (staged) __syncwarp();            // every copy has read the flag before one sets it
     a.own_rewritten[(size_t)j * a.B + b] = 1;
-    constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
-    if (kCanSlim && slim_shape(a))
+    if (kCanSlim && staged)
+        a.repair_from[(size_t)j * a.B + b] =
+            run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim, kCanSlim>(
+                a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
+                a.repair_cap, ~0ull, m_first, m_end, own_pure);
+    else if (kCanSlim && slim_shape(a))
         a.repair_from[(size_t)j * a.B + b] =
             run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim>(
                 a, ln, p, b, j, first, true, true, old_state, stale_buf, q_begin,
@@ -468,14 +499,20 @@ sim_chain_kernel(const KernelArgs a)
     if (kNarrow && a.compat[blockIdx.x]) return;          // whole block: nothing to stage for
     const SmemLayout L = smem_layout(a.M, a.G, a.P, a.T, a.S, kGroupGood, a.lat_smem_elems, a.lat_f64 != 0);
     stage_latency_table(a, L);
-    if (kNarrow && threadIdx.x != 0) return;
     const int64_t b = kNarrow ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kLanes + lane;
     if (b >= a.Bs) return;
     if (a.compat[b]) return;             // settled by the last walk of resolve_kernel
+    // one candidate to a warp: the lone lane, or all 32 lanes as copies of it (see
+    // sim_repair_kernel)
+    constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
+    bool staged = false;
+    if constexpr (kCanSlim) staged = staged_shape(a, L, b);
+    if (kNarrow && !staged && threadIdx.x != 0) return;
     int64_t m_end;
     const int64_t m_first = mirrors_of(a, b, m_end);
 
     Lane ln = setup_lane<kGroupGood>(a, b, lane);
+    ln.staging = staged ? (uint32_t)staging_offset(L.total, a.T, a.G) : 0u;
     uint32_t old_state, stale_buf;
     repair_scratch(a, L, lane, old_state, stale_buf);
     Pipe p;
@@ -521,15 +558,20 @@ sim_chain_kernel(const KernelArgs a)
                 for (int32_t q = q0; q < q1; ++q) a.seg_src[(size_t)q * a.B + b] = (int32_t)found;
                 continue;
             }
+            if (staged) __syncwarp();    // the comparisons above read what is written now
             for (int t = 0; t < a.T; ++t)
                 a.chunk_start[((size_t)j * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);
             forget_capped_repair(a, b, j);
         }
         ++redone;
         const bool own_pure = !a.own_rewritten[(size_t)j * a.B + b];
+        if (staged) __syncwarp();        // every copy has read the flag before one sets it
         a.own_rewritten[(size_t)j * a.B + b] = 1;
-        constexpr bool kCanSlim = kNarrow && !kFull && !kLegacy;
-        if (kCanSlim && slim_shape(a))
+        if (kCanSlim && staged)
+            run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim, kCanSlim>(
+                a, ln, p, b, j, begin, true, true, old_state, stale_buf, q_begin, 0, ~0ull,
+                m_first, m_end, own_pure);
+        else if (kCanSlim && slim_shape(a))
             run_chunk<kFull, kGroupGood, kLegacy, kNarrow, kCanSlim>(
                 a, ln, p, b, j, begin, true, true, old_state, stale_buf, q_begin, 0, ~0ull,
                 m_first, m_end, own_pure);
@@ -539,7 +581,8 @@ sim_chain_kernel(const KernelArgs a)
                                                            m_first, m_end, own_pure);
         a.repair_from[(size_t)j * a.B + b] = -1;
     }
-    if (a.resimulated && redone) atomicAdd(&a.resimulated[b], redone);
+    if (a.resimulated && redone && (!kNarrow || threadIdx.x == 0))
+        atomicAdd(&a.resimulated[b], redone);
     if (ln.status) atomicOr(&a.status[b], ln.status);
 }
 

@@ -226,7 +226,11 @@ __device__ inline bool states_equivalent(const KernelArgs &a, int64_t b, LoadX X
 //       segments (0 = no cap).
 // Returns -1 when the chunk is finished (ran to its end, or settled), else
 // the segment at which the capped repair has to be continued.
-template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false, bool kSlim = false>
+//
+// kStaged (with kSlim): the step that lets the warp decode ahead (staged_step);
+// every lane of the warp must be here, set up as lane 0 (see sim_core.cuh).
+template <bool kFull, bool kGroupGood, bool kLegacy, bool kNarrow = false, bool kSlim = false,
+          bool kStaged = false>
 __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                                     int64_t b, int32_t j, int32_t begin,
                                     bool repair, bool snapshots, uint32_t old_state,
@@ -246,7 +250,9 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
     int32_t i = begin, span_end = first;
     bool record = false;
     int32_t done = 0;
-    pipe_prime(ln, p, begin);
+    static_assert(!kStaged || kSlim, "the staged step is a form of the slim step");
+    Staged st;
+    if constexpr (kStaged) st = staged_init(ln); else pipe_prime(ln, p, begin);
     for (;;) {
         // Within a leaf the latency of request k goes to partial sum k mod 8
         // (leaves start at multiples of 8).  The latencies of eight requests
@@ -258,8 +264,12 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
         double p0 = 0.0, p1 = 0.0, p2 = 0.0, p3 = 0.0, p4 = 0.0, p5 = 0.0, p6 = 0.0, p7 = 0.0;
         double r = 0.0;
         auto one = [&](int32_t ii) {
-            const double d = sim_step<kFull, kGroupGood, kLegacy, kNarrow, kSlim>(
-                ln, p, ii, record, fin_out, good_out);
+            double d;
+            if constexpr (kStaged)
+                d = staged_step(ln, p, st, ii, record);
+            else
+                d = sim_step<kFull, kGroupGood, kLegacy, kNarrow, kSlim>(ln, p, ii, record,
+                                                                         fin_out, good_out);
             if (ii < body_end) {
                 SM_F64(ring + (uint32_t)(ii & 7) * kLanes) = d;
                 if ((ii & 7) == 7) {
@@ -277,7 +287,7 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
 #ifndef MMS_SLIM_UNROLL
 #define MMS_SLIM_UNROLL 1
 #endif
-        if constexpr (kSlim && MMS_SLIM_UNROLL) {
+        if constexpr (kSlim && !kStaged && MMS_SLIM_UNROLL) {
             // three requests per turn: the values fetched ahead rotate through three sets of
             // registers, and after three steps every set is back where it was — no moves
             for (; i + 3 <= span_end; i += 3) { one(i); one(i + 1); one(i + 2); }
@@ -335,6 +345,9 @@ __device__ inline int32_t run_chunk(const KernelArgs &a, Lane &ln, Pipe &p,
                         if (settled && r > 0) { reselect = true; settle_src = v == b ? -1 : (int32_t)v; }
                     }
                 }
+                // (all lanes of a staged warp run this code as copies of one another: none
+                // may overwrite what another has yet to compare)
+                if constexpr (kStaged) __syncwarp();
                 if (snapshots) {
                     for (int t = 0; t < a.T; ++t)
                         a.seg_end[((size_t)q * a.T + t) * a.B + b] = SM_F64(ln.clk + t * kLanes);

@@ -106,6 +106,8 @@ struct Lane {
     bool lat_f64;             // on chip as doubles
     int32_t M, C, S;
     uint32_t status;
+    uint32_t staging;         // byte offset of the warp's decoded-request records (kStagedBytes),
+                              //   for the step that decodes ahead (staged_step); 0 = none
 };
 
 // Row words that are not replicas.  Both address clock slot 0 / one stage /
@@ -451,6 +453,215 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
     p.ts = p.ts1; p.slo = p.slo1; p.m = p.m1; p.r = p.r1; p.rb = rb1;
     p.ts1 = p.ts2; p.slo1 = p.slo2; p.m1 = p.m2; p.r1 = r2;
     p.ts2 = ts3; p.slo2 = slo3; p.m2 = m3raw;      // unchecked until the next step fetches its row
+    return fin - ts;
+}
+
+// ---- the one-lane step with the warp decoding ahead ---------------------------
+//
+// Serial repairs, the chain kernel and every sweep over an overloaded placement
+// walk ONE dependent chain per warp, and most of what sim_step executes per
+// request there does not depend on the simulator's state: fetching the trace,
+// the model's replica row, turning its entries into clock and latency
+// addresses.  Here the 32 lanes of the warp do that part for 32 consecutive
+// requests at once (staged_decode: one record per request in shared memory),
+// and the recurrence then runs over the records (staged_step: replica choice,
+// max/add chain, SLO test, clock stores, decision record) with less than half
+// the instructions per request.  Every lane executes the recurrence, on the
+// same addresses with the same values (the caller sets all lanes up as lane 0):
+// a warp issues one instruction for 32 lanes or for one at the same cost, and
+// control flow that is the same in every lane needs no lane to wait for
+// another.  Needs what the slim step needs (table on chip as doubles, byte
+// decisions), models with at most eight replicas, and every shared-memory index
+// below 65536.
+constexpr int kStageAhead = 32;
+constexpr size_t kStagedBytes = (size_t)kStageAhead * (4 * 16 + 8 + 8);
+
+// A request's record: 80 bytes — uint4 a, b, a2, b2 and two doubles:
+//   a, a2   per replica (first four, next four): f64 index of its last-stage clock |
+//           f64 index of its first clock << 16; 0xFFFFFFFF = no replica
+//   b, b2   per replica: f64 index of its latency row | stages << 16 | group << 24
+//   ts, slo arrival time and SLO (widened)
+constexpr uint32_t kRecordBytes = 80;
+static_assert(kStagedBytes == kStageAhead * kRecordBytes, "record size");
+
+struct Staged {
+    uint32_t rec;             // byte offset of record 0
+    int32_t base;             // requests [base, base + kStageAhead) are decoded
+    int32_t next;             // the request whose record is in the registers below
+    uint4 a, b, a2, b2;
+    double ts, slo;
+};
+
+__device__ __forceinline__ Staged staged_init(const Lane &ln)
+{
+    Staged st;
+    st.rec = ln.staging;
+    st.base = -0x40000000;
+    st.next = -1;
+    st.a = st.b = st.a2 = st.b2 = make_uint4(0, 0, 0, 0);
+    st.ts = st.slo = 0.0;
+    return st;
+}
+
+__device__ __forceinline__ void staged_load(Staged &st, uint32_t k)
+{
+    const unsigned char *r = smem + st.rec + k * kRecordBytes;
+    st.a = *reinterpret_cast<const uint4 *>(r);
+    st.b = *reinterpret_cast<const uint4 *>(r + 16);
+    st.a2 = *reinterpret_cast<const uint4 *>(r + 32);
+    st.b2 = *reinterpret_cast<const uint4 *>(r + 48);
+    st.ts = *reinterpret_cast<const double *>(r + 64);
+    st.slo = *reinterpret_cast<const double *>(r + 72);
+}
+
+// Decodes requests [i0, i0 + 32), one per lane (those past the end of the trace repeat the
+// last one and are never executed).
+__device__ __forceinline__ void staged_decode(Lane &ln, const Pipe &p, Staged &st, int32_t i0)
+{
+    const int lane = threadIdx.x & (kLanes - 1);
+    __syncwarp();                                // nobody still reads the old records
+    const int32_t i = i0 + lane < p.last ? i0 + lane : p.last;
+    const size_t o = (size_t)i * p.pitch;
+    const double ts = __ldg(p.arrivals + o);
+    const float slo = __ldg(p.slos + o);
+    const int32_t m = clean_model(ln, __ldg(p.model_ids + o));
+    const uint4 r = fetch_row(ln, m);
+    const uint4 r2 = fetch_row_b(ln, m, r);
+    const uint32_t e[8] = {r.x, r.y, r.z, r.w, r2.x, r2.y, r2.z, r2.w};
+    const uint32_t mrow = (uint32_t)(m < 0 ? 0 : m) * ln.C;
+    uint32_t wa[8], wb[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        if (e[k] < kMoreReplicas) {
+            const uint32_t last = rep_last(e[k]), ns = rep_stages(e[k]);
+            wa[k] = (ln.clk + last * kLanes) | ((ln.clk + (last + 1 - ns) * kLanes) << 16);
+            wb[k] = (ln.lat_sm + (mrow + rep_column(e[k])) * ln.S) | (ns << 16) |
+                    (rep_group(e[k]) << 24);
+        } else {
+            wa[k] = 0xFFFFFFFFu;
+            wb[k] = 0;
+        }
+    }
+    unsigned char *rec = smem + st.rec + (uint32_t)lane * kRecordBytes;
+    *reinterpret_cast<uint4 *>(rec) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+    *reinterpret_cast<uint4 *>(rec + 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+    *reinterpret_cast<uint4 *>(rec + 32) = make_uint4(wa[4], wa[5], wa[6], wa[7]);
+    *reinterpret_cast<uint4 *>(rec + 48) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
+    *reinterpret_cast<double *>(rec + 64) = ts;
+    *reinterpret_cast<double *>(rec + 72) = (double)slo;
+    st.base = i0;
+    st.next = -1;
+    __syncwarp();
+}
+
+// Executes request i from its record (controller.py:579-622) and returns finish - arrival.
+__device__ __forceinline__ double staged_step(Lane &ln, const Pipe &p, Staged &st, int32_t i,
+                                              bool record)
+{
+    if ((uint32_t)(i - st.base) >= (uint32_t)kStageAhead) staged_decode(ln, p, st, i);
+    const uint32_t k = (uint32_t)(i - st.base);
+    if (st.next != i) staged_load(st, k);
+    const uint4 A = st.a, B = st.b, A2 = st.a2, B2 = st.b2;
+    const double ts = st.ts, slo = st.slo;
+    // the next request's record, before this request's stores (which the compiler could not
+    // move the loads across)
+    const uint32_t kn = k + 1 < (uint32_t)kStageAhead ? k + 1 : k;
+    staged_load(st, kn);
+    st.next = kn == k + 1 ? i + 1 : -1;
+
+    // :589-598 replica whose last-stage clock is strictly smallest (a row is filled from
+    // word 0 on)
+    double best = kInf;
+    uint32_t pa = 0xFFFFFFFFu, pb = 0;
+    if (A.x != 0xFFFFFFFFu) {
+        const double c0 = SM_F64(A.x & 0xFFFFu);
+        if (c0 < best) { best = c0; pa = A.x; pb = B.x; }
+        if (A.y != 0xFFFFFFFFu) {
+            const double c1 = SM_F64(A.y & 0xFFFFu);
+            if (c1 < best) { best = c1; pa = A.y; pb = B.y; }
+            if (A.z != 0xFFFFFFFFu) {
+                const double c2 = SM_F64(A.z & 0xFFFFu);
+                if (c2 < best) { best = c2; pa = A.z; pb = B.z; }
+                if (A.w != 0xFFFFFFFFu) {
+                    const double c3 = SM_F64(A.w & 0xFFFFu);
+                    if (c3 < best) { best = c3; pa = A.w; pb = B.w; }
+                    if (A2.x != 0xFFFFFFFFu) {               // replicas five to eight
+                        const double c4 = SM_F64(A2.x & 0xFFFFu);
+                        if (c4 < best) { best = c4; pa = A2.x; pb = B2.x; }
+                        if (A2.y != 0xFFFFFFFFu) {
+                            const double c5 = SM_F64(A2.y & 0xFFFFu);
+                            if (c5 < best) { best = c5; pa = A2.y; pb = B2.y; }
+                            if (A2.z != 0xFFFFFFFFu) {
+                                const double c6 = SM_F64(A2.z & 0xFFFFu);
+                                if (c6 < best) { best = c6; pa = A2.z; pb = B2.z; }
+                                if (A2.w != 0xFFFFFFFFu) {
+                                    const double c7 = SM_F64(A2.w & 0xFFFFu);
+                                    if (c7 < best) { best = c7; pa = A2.w; pb = B2.w; }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    double fin = ts;
+    uint32_t rec = 0;
+    if (pa != 0xFFFFFFFFu) {
+        const uint32_t ck = pa >> 16, lr = pb & 0xFFFFu, ns = (pb >> 16) & 0xFFu;
+        bool accept = false;
+        double f = ts;
+        auto run = [&](auto depth) {
+            constexpr int kDepth = decltype(depth)::value;
+            double c[kDepth], l[kDepth], t[kDepth];
+#pragma unroll
+            for (int s = 0; s < kDepth; ++s) {
+                c[s] = SM_F64(ck + s * kLanes);
+                l[s] = SM_F64(lr + s);
+            }
+            double cur = ts;
+#pragma unroll
+            for (int s = 0; s < kDepth; ++s) {           // :605-608
+                cur = tmax(cur, c[s]) + l[s];
+                t[s] = cur;
+            }
+            f = cur + kOverhead;                         // :610
+            accept = f - ts <= slo;                      // :613
+            if (accept) {
+#pragma unroll
+                for (int s = 0; s < kDepth; ++s) SM_F64(ck + s * kLanes) = t[s];
+            }
+        };
+        switch (ns) {
+            case 1: run(std::integral_constant<int, 1>{}); break;
+            case 2: run(std::integral_constant<int, 2>{}); break;
+            case 4: run(std::integral_constant<int, 4>{}); break;
+            case 8: run(std::integral_constant<int, 8>{}); break;
+            default: {
+                double cur = ts;
+                for (uint32_t s = 0; s < ns; ++s)
+                    cur = tmax(cur, SM_F64(ck + s * kLanes)) + SM_F64(lr + s);
+                f = cur + kOverhead;
+                accept = f - ts <= slo;
+                if (accept) {                             // the same chain again, stored
+                    cur = ts;
+                    for (uint32_t s = 0; s < ns; ++s) {
+                        cur = tmax(cur, SM_F64(ck + s * kLanes)) + SM_F64(lr + s);
+                        SM_F64(ck + s * kLanes) = cur;
+                    }
+                }
+            }
+        }
+        if (accept) fin = f;
+        rec = ((pb >> 24) + 1u) | (accept ? 0x80u : 0u);
+    }
+    if (record) {
+        ln.dec_word |= rec << (8 * (i & 3));
+        if ((i & 3) == 3 || i == p.last) {
+            static_cast<uint32_t *>(ln.dec)[(size_t)(i >> 2) * ln.dec_pitch] = ln.dec_word;
+            ln.dec_word = 0;
+        }
+    }
     return fin - ts;
 }
 

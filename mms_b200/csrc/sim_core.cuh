@@ -488,7 +488,7 @@ struct Staged {
     uint32_t rec;             // byte offset of record 0
     int32_t base;             // requests [base, base + kStageAhead) are decoded
     int32_t next;             // the request whose record is in the registers below
-    uint4 a, b, a2, b2;
+    uint4 a, b;
     double ts, slo;
 };
 
@@ -498,20 +498,21 @@ __device__ __forceinline__ Staged staged_init(const Lane &ln)
     st.rec = ln.staging;
     st.base = -0x40000000;
     st.next = -1;
-    st.a = st.b = st.a2 = st.b2 = make_uint4(0, 0, 0, 0);
+    st.a = st.b = make_uint4(0, 0, 0, 0);
     st.ts = st.slo = 0.0;
     return st;
 }
 
+// The record's first half and its times; the second half (replicas five to eight) is read
+// by the step, where a model has that many.
 __device__ __forceinline__ void staged_load(Staged &st, uint32_t k)
 {
     const unsigned char *r = smem + st.rec + k * kRecordBytes;
     st.a = *reinterpret_cast<const uint4 *>(r);
     st.b = *reinterpret_cast<const uint4 *>(r + 16);
-    st.a2 = *reinterpret_cast<const uint4 *>(r + 32);
-    st.b2 = *reinterpret_cast<const uint4 *>(r + 48);
-    st.ts = *reinterpret_cast<const double *>(r + 64);
-    st.slo = *reinterpret_cast<const double *>(r + 72);
+    const double2 t = *reinterpret_cast<const double2 *>(r + 64);
+    st.ts = t.x;
+    st.slo = t.y;
 }
 
 // Decodes requests [i0, i0 + 32), one per lane (those past the end of the trace repeat the
@@ -547,8 +548,7 @@ __device__ __forceinline__ void staged_decode(Lane &ln, const Pipe &p, Staged &s
     *reinterpret_cast<uint4 *>(rec + 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
     *reinterpret_cast<uint4 *>(rec + 32) = make_uint4(wa[4], wa[5], wa[6], wa[7]);
     *reinterpret_cast<uint4 *>(rec + 48) = make_uint4(wb[4], wb[5], wb[6], wb[7]);
-    *reinterpret_cast<double *>(rec + 64) = ts;
-    *reinterpret_cast<double *>(rec + 72) = (double)slo;
+    *reinterpret_cast<double2 *>(rec + 64) = make_double2(ts, (double)slo);
     st.base = i0;
     st.next = -1;
     __syncwarp();
@@ -561,8 +561,9 @@ __device__ __forceinline__ double staged_step(Lane &ln, const Pipe &p, Staged &s
     if ((uint32_t)(i - st.base) >= (uint32_t)kStageAhead) staged_decode(ln, p, st, i);
     const uint32_t k = (uint32_t)(i - st.base);
     if (st.next != i) staged_load(st, k);
-    const uint4 A = st.a, B = st.b, A2 = st.a2, B2 = st.b2;
+    const uint4 A = st.a, B = st.b;
     const double ts = st.ts, slo = st.slo;
+    const unsigned char *second = smem + st.rec + k * kRecordBytes + 32;
     // the next request's record, before this request's stores (which the compiler could not
     // move the loads across)
     const uint32_t kn = k + 1 < (uint32_t)kStageAhead ? k + 1 : k;
@@ -585,6 +586,8 @@ __device__ __forceinline__ double staged_step(Lane &ln, const Pipe &p, Staged &s
                 if (A.w != 0xFFFFFFFFu) {
                     const double c3 = SM_F64(A.w & 0xFFFFu);
                     if (c3 < best) { best = c3; pa = A.w; pb = B.w; }
+                    const uint4 A2 = *reinterpret_cast<const uint4 *>(second);
+                    const uint4 B2 = *reinterpret_cast<const uint4 *>(second + 16);
                     if (A2.x != 0xFFFFFFFFu) {               // replicas five to eight
                         const double c4 = SM_F64(A2.x & 0xFFFFu);
                         if (c4 < best) { best = c4; pa = A2.x; pb = B2.x; }

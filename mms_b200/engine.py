@@ -366,16 +366,36 @@ class EncodedBatch:
         # (candidate index, [[group ids of one class of interchangeable groups], ...])
         # for every placement that has such groups, see twin_groups()
         self.twins = twins
+        self._mirror_table = None         # see mirror_table()
+
+    def mirror_table(self):
+        """(counts i64[len(twins)], words u64[sum(counts)]): the exchange lists of
+        every placement's mirrors (mirror_swaps), placement after placement in the
+        order of `twins`; made once, for all placements of one class pattern together."""
+        if self._mirror_table is None:
+            self._mirror_table = mirror_swaps_batch([classes for _, classes in (self.twins or [])])
+        return self._mirror_table
 
     def take(self, index):
         """The sub-batch of the placements `index` (ascending)."""
         index = np.asarray(index, np.int64)
         new_id = np.full(self.B, -1, np.int64)
         new_id[index] = np.arange(len(index))
-        twins = [(int(new_id[b]), classes) for b, classes in (self.twins or []) if new_id[b] >= 0]
-        return EncodedBatch(len(index), self.M, self.G, self.P, self.T, self.S, self.C,
-                            self.model_off[index], self.model_rep[index], self.group_info[index],
-                            self.num_groups[index], self.num_replicas[index], twins)
+        keep = [k for k, (b, _) in enumerate(self.twins or []) if new_id[b] >= 0]
+        twins = [(int(new_id[self.twins[k][0]]), self.twins[k][1]) for k in keep]
+        sub = EncodedBatch(len(index), self.M, self.G, self.P, self.T, self.S, self.C,
+                           self.model_off[index], self.model_rep[index], self.group_info[index],
+                           self.num_groups[index], self.num_replicas[index], twins)
+        if self._mirror_table is not None:
+            counts, words = self._mirror_table
+            keep = np.asarray(keep, np.int64)
+            start = np.concatenate(([0], np.cumsum(counts)))[:-1]
+            sub_counts = counts[keep]
+            # the kept placements' stretches of `words`, one after the other
+            pos = np.repeat(start[keep] - (np.cumsum(sub_counts) - sub_counts), sub_counts) \
+                + np.arange(int(sub_counts.sum()))
+            sub._mirror_table = (sub_counts, words[pos])
+        return sub
 
     def repeat(self, count: int):
         """This batch `count` times over (placement 0 .. B-1, then again ...):
@@ -395,26 +415,20 @@ class EncodedBatch:
         has any."""
         if not self.twins:
             return None
-        owners, swaps, first = [], [], []
-        at = self.B
-        has = []
-        for b, classes in self.twins:
-            words = mirror_swaps(classes)
-            if not words:
-                continue
-            has.append(b)
-            first.append(at)
-            at += len(words)
-            owners.extend([b] * len(words))
-            swaps.extend(words)
-        if not has:
+        counts, words = self.mirror_table()
+        total = int(counts.sum())
+        if total == 0:
             return None
-        owners = np.asarray(owners, np.int64)
+        twin_b = np.fromiter((b for b, _ in self.twins), np.int64, len(self.twins))
+        has = counts > 0
+        first = self.B + np.cumsum(counts) - counts
+        owners = np.repeat(twin_b, counts)
+        at = self.B + total
         partner = np.full(at, -1, np.int32)
-        partner[has] = first
+        partner[twin_b[has]] = first[has]
         partner[self.B:] = owners
         swap = np.full((at, 2), NO_SWAP, np.uint32)
-        swap[self.B:] = np.asarray(swaps, np.uint64).view(np.uint32).reshape(-1, 2)
+        swap[self.B:] = words.view(np.uint32).reshape(-1, 2)
         return (np.concatenate((self.model_off, self.model_off[owners])),
                 np.concatenate((self.model_rep, self.model_rep[owners])),
                 np.concatenate((self.group_info, self.group_info[owners])), partner, swap)
@@ -481,6 +495,44 @@ def mirror_swaps(classes):
             w |= (groups[i] | (groups[j] << 8)) << (16 * k)
         words.append(w)
     return words
+
+
+def mirror_swaps_batch(class_lists):
+    """mirror_swaps for many placements at once: (counts i64[n], words u64[sum])
+    with the words of placement k at [sum(counts[:k]), sum(counts[:k + 1])), in
+    the order mirror_swaps gives them.  Placements with the same class sizes
+    share their permutations, so their words are formed together."""
+    n = len(class_lists)
+    counts = np.zeros(n, np.int64)
+    by_sizes = {}
+    for k, classes in enumerate(class_lists):
+        by_sizes.setdefault(tuple(map(len, classes)), []).append(k)
+    made = {}
+    for sizes, members in by_sizes.items():
+        ways = 1
+        for size in sizes:
+            ways *= factorial(size) if size < 5 else MAX_MIRRORS + 2
+        if ways - 1 > MAX_MIRRORS:
+            continue
+        perms = _perm_swaps(sizes)
+        if not perms:
+            continue
+        groups = np.array([[g for c in class_lists[k] for g in c] for k in members], np.uint64)
+        words = np.empty((len(members), len(perms)), np.uint64)
+        for q, ex in enumerate(perms):
+            w = np.full(len(members), 0xFFFFFFFFFFFFFFFF, np.uint64)
+            for t, (i, j) in enumerate(ex):
+                w &= np.uint64(~(0xFFFF << (16 * t)) & 0xFFFFFFFFFFFFFFFF)
+                w |= (groups[:, i] | (groups[:, j] << np.uint64(8))) << np.uint64(16 * t)
+            words[:, q] = w
+        counts[members] = len(perms)
+        made[sizes] = (np.asarray(members, np.int64), words)
+    out = np.empty(int(counts.sum()), np.uint64)
+    start = np.cumsum(counts) - counts
+    for members, words in made.values():
+        pos = start[members][:, None] + np.arange(words.shape[1])[None, :]
+        out[pos] = words
+    return counts, out
 
 
 def _arrangements(classes) -> int:
@@ -991,28 +1043,42 @@ class ResidentBatch:
 
     def __init__(self, trace, enc: EncodedBatch, table: LatencyTable, group_good=False,
                  pinned=False, options=None, mirrors=True, split=True, crowded=False,
-                 hard_options=None):
+                 hard_options=None, launch_now=False):
         """crowded: other launches will be filling the GPU while this batch
         repairs its chunks (a pipelined part that is not the last).
         hard_options: sim_options for the launch that holds the placements with
-        mirrors, when the batch is split (default: `options`)."""
+        mirrors, when the batch is split (default: `options`).
+        launch_now: every call is enqueued as soon as its tables are uploaded
+        (as launch() would afterwards), so that the GPU starts on the first
+        while the host prepares the second."""
         self.trace, self.enc = trace, enc
         dev = trace.device
-        ext_owner = [b for b, cl in (enc.twins or []) if mirror_swaps(cl)] if mirrors else []
+        ext_owner = []
+        if mirrors and enc.twins:
+            counts, _ = enc.mirror_table()
+            ext_owner = [b for (b, _), c in zip(enc.twins, counts.tolist()) if c]
         parts = [(None, enc)]
         if (split and len(ext_owner) >= SPLIT_MIN_HARD
                 and enc.B - len(ext_owner) >= SPLIT_MIN_EASY):
             hard = np.asarray(ext_owner, np.int64)
-            easy = np.setdiff1d(np.arange(enc.B), hard)
+            rest = np.ones(enc.B, bool)
+            rest[hard] = False
+            easy = np.flatnonzero(rest)
             parts = [(hard, enc.take(hard)), (easy, enc.take(easy))]
         self.index = [p[0] for p in parts]
         self.jobs = []
         self.h2d_bytes = 0
+        self.launched = False
         lat = table.device(dev)
+        main = sides = None
+        if launch_now and len(parts) > 1:
+            main = torch.cuda.current_stream(dev)
+            sides = _side_streams(main)
         for k, (_, e) in enumerate(parts):
             # the first of two calls repairs while the second one fills the GPU
             flags = nat.FLAG_CROWDED if (crowded or k + 1 < len(parts)) else 0
-            ext = e.with_mirrors() if mirrors else None
+            # (the second of two parts holds the placements without mirrors)
+            ext = e.with_mirrors() if mirrors and not (len(parts) > 1 and k == 1) else None
             opts_k = options
             if len(parts) > 1 and k == 0:
                 if hard_options is not None:
@@ -1030,6 +1096,20 @@ class ResidentBatch:
                                e.group_info, lat, 0, flags, group_good, pinned, opts_k)
             self.jobs.append(job)
             self.h2d_bytes += job.h2d
+            if launch_now:              # the GPU starts on this call while the next is prepared
+                if sides is None:
+                    _enqueue(job)
+                else:
+                    sides[k].wait_stream(main)
+                    with torch.cuda.stream(sides[k]):
+                        _enqueue(job)
+        if launch_now:
+            if sides is not None:
+                for side in sides:
+                    main.wait_stream(side)
+                for job in self.jobs:   # results are read in order behind the join
+                    job.stream = main
+            self.launched = True
 
     def launch(self):
         """Enqueues the call(s); stream-ordered with respect to the current
@@ -1084,7 +1164,7 @@ def submit_batch(trace: DeviceTrace, enc: EncodedBatch, table: LatencyTable, gro
                  crowded=False) -> ResidentBatch:
     """run_batch without waiting: returns a handle for collect_batch."""
     return ResidentBatch(trace, enc, table, group_good, pinned, options, mirrors, split,
-                         crowded).launch()
+                         crowded, launch_now=True)
 
 
 collect_batch = _collect

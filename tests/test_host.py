@@ -364,3 +364,32 @@ def test_lazy_trace_arrays_equal_workload_arrays():
     sweep.model_names = tuple(d.name for d in case.model_datas)
     ids, _ = workload_arrays(w, sweep.model_names)
     assert np.array_equal(sweep._lazy_arrays(w)[0].materialize(), ids) and (ids >= 0).all()
+
+
+def test_mirror_words_in_batches_equal_one_by_one():
+    """The exchange lists of the mirror candidates, formed for all placements of a
+    class pattern together, are those of mirror_swaps, in the same order; a
+    sub-batch carries its part of them."""
+    from mms_b200 import cases, engine
+    case = cases.candidate_batch_case(num_candidates=1500, duration=5.0, placement_seed=3)
+    profs = [d.profiling_result for d in case.model_datas]
+    enc = engine.encode_placements(case.placements, engine.LatencyTable(profs), len(profs))
+    counts, words = enc.mirror_table()
+    assert len(enc.twins) > 50 and counts.sum() > 50
+    at = 0
+    for (_, classes), c in zip(enc.twins, counts.tolist()):
+        one = engine.mirror_swaps(classes)
+        assert [int(w) for w in words[at:at + c]] == one
+        at += c
+    pick = np.array(sorted({b for b, _ in enc.twins[::3]} | {0, 1, 2}), np.int64)
+    sub = enc.take(pick)
+    carried = sub._mirror_table
+    sub._mirror_table = None
+    fresh = sub.mirror_table()
+    assert np.array_equal(carried[0], fresh[0]) and np.array_equal(carried[1], fresh[1])
+    off, rep, info, partner, swap = enc.with_mirrors()
+    assert len(partner) == enc.B + counts.sum() and (partner[enc.B:] >= 0).all()
+    owners = partner[enc.B:]
+    assert np.array_equal(rep[enc.B:], enc.model_rep[owners])
+    firsts = partner[[b for (b, _), c in zip(enc.twins, counts.tolist()) if c]]
+    assert np.array_equal(firsts, enc.B + (np.cumsum(counts) - counts)[counts > 0])

@@ -49,8 +49,8 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE sim_stream_kernel launch (ncu) on the
 # default workload: only valid for the library version and the launch shape it was taken
 # with, and reported as null for any other.
-STREAM_KERNEL_TRAFFIC = {"abi_version": 8, "candidates": 3695, "requests": 180715,
-                         "bytes": 34292480 + 1052756224}
+STREAM_KERNEL_TRAFFIC = {"abi_version": 9, "candidates": 3695, "requests": 180715,
+                         "bytes": 41885184 + 1057393152}
 
 _REAL_STDOUT = None
 

@@ -326,7 +326,7 @@ static int launch_sim(KernelArgs &ka, const ClearArgs &ca, const Geometry &g, cu
 
 extern "C" {
 
-int mms_abi_version(void) { return 8; }
+int mms_abi_version(void) { return 9; }
 
 const char *mms_last_error(void) { return mms::g_last_error; }
 

@@ -671,7 +671,8 @@ count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t
     // stays in a bank of its own whatever it counts
     extern __shared__ uint32_t hist[];
     uint32_t *grp = hist;
-    uint16_t *mod = reinterpret_cast<uint16_t *>(hist + (size_t)a.G * kLanes);
+    uint32_t *modw = hist + (size_t)a.G * kLanes;          // two 16-bit counts to a word
+    uint16_t *mod = reinterpret_cast<uint16_t *>(modw);
     const int lane = threadIdx.x;
     const int64_t b = (int64_t)blockIdx.x * kLanes + lane;
     for (int g = 0; g < a.G; ++g) grp[g * kLanes + lane] = 0;
@@ -712,9 +713,12 @@ count_kernel(const KernelArgs a, int32_t seg_per_block, bool group_good, int32_t
                 if (u >= valid || rec == 0) continue;
                 const uint32_t g = (rec & (kAccepted - 1)) - 1;
                 const uint32_t accepted = rec >> kAcceptedBit;
-                grp[g * kLanes + lane] += 1u + (accepted << 16);
+                // shared-memory atomics whose result nobody reads: one instruction each and
+                // nothing to wait for, where load + add + store was a dependent chain (a lane
+                // only ever meets its own words, so there is no contention)
+                atomicAdd(&grp[g * kLanes + lane], 1u + (accepted << 16));
                 if (accepted)
-                    mod[(((uint32_t)m[u] >> 1) * kLanes + lane) * 2 + (m[u] & 1)] += 1;
+                    atomicAdd(&modw[((uint32_t)m[u] >> 1) * kLanes + lane], 1u << (16 * (m[u] & 1)));
             }
         }
     }

@@ -392,16 +392,23 @@ __device__ __forceinline__ double sim_step(Lane &ln, Pipe &p, int32_t i, bool re
         } else {
             // :605-610, written without branches: stages past the group's last one
             // are computed and thrown away
+            // the chain runs through all eight slots; the finish time is picked from the
+            // group's last stage afterwards, so that no select sits between two stages
             t0 = tmax(ts, k0) + l0;
             t1 = tmax(t0, k1) + l1;
-            double t = ns > 1 ? t1 : t0;
-            t2 = tmax(t, k2) + l2; t = ns > 2 ? t2 : t;
-            t3 = tmax(t, k3) + l3; t = ns > 3 ? t3 : t;
-            t4 = tmax(t, k4) + l4; t = ns > 4 ? t4 : t;
-            t5 = tmax(t, k5) + l5; t = ns > 5 ? t5 : t;
-            t6 = tmax(t, k6) + l6; t = ns > 6 ? t6 : t;
-            t7 = tmax(t, k7) + l7; t = ns > 7 ? t7 : t;
+            t2 = tmax(t1, k2) + l2;
+            t3 = tmax(t2, k3) + l3;
+            t4 = tmax(t3, k4) + l4;
+            t5 = tmax(t4, k5) + l5;
+            t6 = tmax(t5, k6) + l6;
+            t7 = tmax(t6, k7) + l7;
+            const uint32_t d = ns - 1;
+            const double ta = (d & 1) ? t1 : t0, tb = (d & 1) ? t3 : t2;
+            const double tc = (d & 1) ? t5 : t4, td = (d & 1) ? t7 : t6;
+            const double te = (d & 2) ? tb : ta, tf = (d & 2) ? td : tc;
+            double t = (d & 4) ? tf : te;
             if (ns > 8) {
+                t = t7;
                 for (uint32_t k = 8; k < ns; ++k) {
                     const double lk = lat_at(ln, row + k);
                     t = tmax(t, SM_F64(ck + k * kLanes)) + lk;

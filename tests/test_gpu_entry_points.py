@@ -248,3 +248,35 @@ def test_compute_stats_full_size_from_device_rows():
     assert len(x.latency) == int(pick.sum())
     assert np.array_equal(np.asarray(x.latency), (fin[2] - w.arrivals)[lo:hi][pick])
     assert np.array_equal(np.asarray(x.request_starts), np.asarray(w.arrivals)[lo:hi][pick])
+
+
+def test_pinned_stager_uploads_arrays_and_lazy_arrays():
+    """engine.PinnedStager: arrays of awkward sizes, cut into pieces smaller than
+    they are, and arrays produced piece by piece (engine.LazyArray) arrive
+    unchanged; a second upload reuses the buffers."""
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from mms_b200 import engine
+    dev = torch.device("cuda", 0)
+    stager = engine.PinnedStager.get(dev, threads=3, piece_bytes=1 << 16)
+    rng = np.random.default_rng(2)
+    for _ in range(2):
+        srcs = [rng.random(n) for n in (1, 8191, 8192, 8193, 100003)]
+        ids = rng.integers(0, 50, 70001).astype(np.int32)
+        lut = rng.permutation(50).astype(np.int32)
+        lazy = engine.LazyArray(len(ids), np.int32,
+                                lambda out, lo, hi: np.take(lut, ids[lo:hi], out=out))
+        slo64 = rng.random(12345)
+        lazy32 = engine.LazyArray(len(slo64), np.float32,
+                                  lambda out, lo, hi: np.copyto(out, slo64[lo:hi], casting="same_kind"))
+        dsts = [torch.empty(len(a), dtype=torch.float64, device=dev) for a in srcs]
+        d_ids = torch.empty(len(ids), dtype=torch.int32, device=dev)
+        d_slo = torch.empty(len(slo64), dtype=torch.float32, device=dev)
+        stager.upload(list(zip(dsts, srcs)) + [(d_ids, lazy), (d_slo, lazy32)])
+        torch.cuda.synchronize()
+        for d, a in zip(dsts, srcs):
+            assert d.cpu().numpy().tobytes() == a.tobytes()
+        assert np.array_equal(d_ids.cpu().numpy(), lut[ids])
+        assert d_slo.cpu().numpy().tobytes() == slo64.astype(np.float32).tobytes()
+    with pytest.raises(ValueError):
+        stager.upload([(torch.empty(3, dtype=torch.float64, device=dev), np.zeros(4))])

@@ -595,6 +595,13 @@ def test_trace_sweep_one_placement_many_traces(loaded):
             assert goodput == np.mean(good), t
             assert np.array_equal(per_model, mgood / (mreq + eps)), t
             assert np.array_equal(np.array(group_req), greq), t
+        # everything uploaded first from pageable memory, then launched: the same results as
+        # the groups launched as they arrive through the staging buffers (the default)
+        plain = TraceSweep(datas, base.cluster_env, p, batch=32)
+        plain.eager = False
+        again = plain.evaluate(workloads)
+        for a, b in zip(got, again):
+            assert a[0] == b[0] and np.array_equal(a[1], b[1]) and a[2] == b[2]
 
 
 def test_split_launch_equals_one_launch(loaded, monkeypatch):

@@ -366,6 +366,29 @@ __global__ void resolve_kernel(const KernelArgs a)
     const int64_t m_first = mirrors_of(a, b, m_end);
     const size_t B = (size_t)a.B;
     int32_t redone = 0;
+    // A candidate nearly all of whose boundaries fail (a placement under sustained overload:
+    // no state ever settles, a repaired chunk only moves the failure to the next boundary)
+    // gains nothing from the rounds: every chunk would be re-simulated in each of them and
+    // once more by the chain kernel.  It is left to the chain kernel as it is.
+    {
+        int32_t fails = 0;
+        for (int32_t j = 1 + lane; j < a.K; j += kLanes) {
+            const int32_t q0 = j * a.seg_per_chunk;
+            const int32_t e = a.seg_src[(size_t)(q0 - 1) * B + b];
+            const int32_t s0 = a.seg_src[(size_t)q0 * B + b];
+            const uint32_t mask = a.compat[(size_t)j * B + (e < 0 ? b : e)];
+            const uint32_t bit = s0 < 0 ? 0u : (uint32_t)(s0 - m_first + 1);
+            fails += !((bit < 16 && ((mask >> bit) & 1u)) || mask != 0);
+        }
+        fails = __reduce_add_sync(0xFFFFFFFFu, fails);
+        if (a.K > 8 && (int64_t)fails * 8 >= (int64_t)(a.K - 1) * 7) {
+            if (lane == 0) {
+                a.compat[b] = 0;
+                atomicAdd(&a.work_count[kMaxRepairRounds], 1u);
+            }
+            return;
+        }
+    }
     for (int32_t j = 1; j < a.K; ++j) {
         const int32_t q0 = j * a.seg_per_chunk;
         const int32_t q1 = q0 + a.seg_per_chunk < a.NS ? q0 + a.seg_per_chunk : a.NS;

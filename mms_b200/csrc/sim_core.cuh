@@ -497,6 +497,12 @@ struct Staged {
     int32_t next;             // the request whose record is in the registers below
     uint4 a, b;
     double ts, slo;
+    // this lane's trace element of the block behind the decoded one, loaded while that one is
+    // worked through (a block of steps is ample time for the loads to arrive)
+    int32_t ahead_base;
+    double ahead_ts;
+    float ahead_slo;
+    int32_t ahead_m;          // unchecked
 };
 
 __device__ __forceinline__ Staged staged_init(const Lane &ln)
@@ -507,6 +513,8 @@ __device__ __forceinline__ Staged staged_init(const Lane &ln)
     st.next = -1;
     st.a = st.b = make_uint4(0, 0, 0, 0);
     st.ts = st.slo = 0.0;
+    st.ahead_base = -0x40000000;
+    st.ahead_ts = 0.0; st.ahead_slo = 0.0f; st.ahead_m = -1;
     return st;
 }
 
@@ -528,11 +536,25 @@ __device__ __forceinline__ void staged_decode(Lane &ln, const Pipe &p, Staged &s
 {
     const int lane = threadIdx.x & (kLanes - 1);
     __syncwarp();                                // nobody still reads the old records
-    const int32_t i = i0 + lane < p.last ? i0 + lane : p.last;
-    const size_t o = (size_t)i * p.pitch;
-    const double ts = __ldg(p.arrivals + o);
-    const float slo = __ldg(p.slos + o);
-    const int32_t m = clean_model(ln, __ldg(p.model_ids + o));
+    auto element = [&](int64_t first, double &ts, float &slo, int32_t &m) {
+        const int64_t want = first + lane;
+        const size_t o = (size_t)(want < p.last ? want : (int64_t)p.last) * p.pitch;
+        ts = __ldg(p.arrivals + o);
+        slo = __ldg(p.slos + o);
+        m = __ldg(p.model_ids + o);
+    };
+    double ts;
+    float slo;
+    int32_t m_raw;
+    if (st.ahead_base == i0) {                   // fetched while the previous block ran
+        ts = st.ahead_ts; slo = st.ahead_slo; m_raw = st.ahead_m;
+    } else {
+        element(i0, ts, slo, m_raw);
+    }
+    const int64_t next0 = (int64_t)i0 + kStageAhead;
+    element(next0, st.ahead_ts, st.ahead_slo, st.ahead_m);
+    st.ahead_base = next0 < 0x7FFFFFFF ? (int32_t)next0 : -0x40000000;
+    const int32_t m = clean_model(ln, m_raw);
     const uint4 r = fetch_row(ln, m);
     const uint4 r2 = fetch_row_b(ln, m, r);
     const uint32_t e[8] = {r.x, r.y, r.z, r.w, r2.x, r2.y, r2.z, r2.w};

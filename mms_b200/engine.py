@@ -43,6 +43,38 @@ def _to_device(arr: np.ndarray, device, pinned=False):
     return t.to(device, non_blocking=pinned)
 
 
+_UPLOAD_STAGE = {}       # device -> page-locked staging buffer of _to_device_many
+
+
+def _to_device_many(arrays, device):
+    """Several host arrays to the device as ONE transfer from a page-locked staging
+    buffer (kept per device): a launch uploads half a dozen small tables, and each
+    transfer from pageable memory costs tens of microseconds whatever its size.
+    Returns device tensors that are views of one buffer, each 16-byte aligned."""
+    device = torch.device(device)
+    arrays = [np.ascontiguousarray(a) for a in arrays]
+    offsets, total = [], 0
+    for a in arrays:
+        offsets.append(total)
+        total += (a.nbytes + 15) & ~15
+    total = max(total, 16)
+    stage = _UPLOAD_STAGE.get(device)
+    if stage is None or stage.numel() < total:
+        stage = torch.empty(max(2 * total, 1 << 20), dtype=torch.uint8).pin_memory()
+        _UPLOAD_STAGE[device] = stage
+    host = stage.numpy()
+    for a, o in zip(arrays, offsets):
+        if a.nbytes:
+            host[o:o + a.nbytes] = a.reshape(-1).view(np.uint8)
+    buf = torch.empty(total, dtype=torch.uint8, device=device)
+    buf.copy_(stage[:total])              # returns when the copy is done: the stage is free again
+    out = []
+    for a, o in zip(arrays, offsets):
+        dtype = torch.from_numpy(np.empty(0, a.dtype)).dtype
+        out.append(buf[o:o + a.nbytes].view(dtype).reshape(a.shape))
+    return out
+
+
 class DeviceTrace:
     """A request trace resident on one GPU: arrivals f64[N], model ids i32[N]
     (-1 = unknown model), SLOs f32[N] — the arrays controller.py:335-336
@@ -64,9 +96,6 @@ class DeviceTrace:
         self.h2d_bytes = arrivals.nbytes + model_ids.nbytes + slos.nbytes
         L = nat.lib()
         with torch.cuda.device(self.device):
-            self.arrivals = _to_device(arrivals, self.device)
-            self.model_ids = _to_device(model_ids, self.device)
-            self.slos = _to_device(slos, self.device)
             n_leaves = L.mms_sum_plan_leaves(self.num_requests)
             if n_leaves < 0:
                 nat.check(n_leaves, "mms_sum_plan_leaves")
@@ -75,8 +104,9 @@ class DeviceTrace:
             nat.check(L.mms_sum_plan_fill(self.num_requests, leaf_start.ctypes.data,
                                           leaf_merges.ctypes.data), "mms_sum_plan_fill")
             self.num_leaves = n_leaves
-            self.leaf_start = _to_device(leaf_start, self.device)
-            self.leaf_merges = _to_device(leaf_merges, self.device)
+            (self.arrivals, self.model_ids, self.slos, self.leaf_start,
+             self.leaf_merges) = _to_device_many(
+                (arrivals, model_ids, slos, leaf_start, leaf_merges), self.device)
             self.model_hist = torch.zeros(self.num_models + 1, dtype=torch.int32,
                                           device=self.device)
             tr = self.c_trace()
@@ -896,16 +926,24 @@ def _prepare(trace: DeviceTrace, B, M, G, P, T, S, C, model_off, model_rep, grou
         flags |= nat.FLAG_NO_GROUP_GOOD
     job = _Pending()
     with torch.cuda.device(dev):
-        d_off = _to_device(model_off, dev, pinned)
-        d_rep = _to_device(model_rep, dev, pinned)
-        d_info = _to_device(group_info, dev, pinned)
-        d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev, pinned)
         h2d = model_off.nbytes + model_rep.nbytes + group_info.nbytes
         Bs = B if num_scored is None else int(num_scored)
         d_partner = d_swap = None
+        if pinned:
+            d_off = _to_device(model_off, dev, pinned)
+            d_rep = _to_device(model_rep, dev, pinned)
+            d_info = _to_device(group_info, dev, pinned)
+            if Bs != B:
+                d_partner = _to_device(partner, dev, pinned)
+                d_swap = _to_device(mirror_swap, dev, pinned)
+        elif Bs != B:
+            d_off, d_rep, d_info, d_partner, d_swap = _to_device_many(
+                (model_off, model_rep, group_info, partner, mirror_swap), dev)
+        else:
+            d_off, d_rep, d_info = _to_device_many((model_off, model_rep, group_info), dev)
         if Bs != B:
-            d_partner, d_swap = _to_device(partner, dev, pinned), _to_device(mirror_swap, dev, pinned)
             h2d += partner.nbytes + mirror_swap.nbytes
+        d_lat = latency if isinstance(latency, torch.Tensor) else _to_device(latency, dev, pinned)
         cands = nat.Placements(B, M, G, P, T, S, C, Bs if Bs != B else 0, _ptr(d_off), _ptr(d_rep),
                                _ptr(d_info), _ptr(d_lat), int(latency_stride), _ptr(d_partner),
                                _ptr(d_swap))

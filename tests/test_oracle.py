@@ -181,3 +181,35 @@ def test_compute_stats_checker_matches_reference(golden):
                 got = np.array([p[field] for p in per_model], np.float64)
                 assert np.array_equal(got, g[f"{tag}_{field}"]), (tag, field)
             assert np.array_equal(np.array(overall, np.float64), g[f"{tag}_overall"])
+
+
+def test_host_compute_stats_equals_checker_on_awkward_data():
+    """The package's host mirror of Workload.compute_stats (used for workloads
+    given as Request lists) against the checker's statement of it: models with
+    no good request, a single good request, unequal counts that tie, a window
+    that the warm-up cuts on both sides."""
+    from mms_b200.workload import Workload
+    from oracle import stats
+    rng = np.random.default_rng(23)
+    names = [f"m{k}" for k in range(9)]
+    counts = [0, 1, 5, 5, 40, 129, 129, 700, 3000]          # ties keep first-appearance order
+    which = np.concatenate([np.full(c, k, np.int32) for k, c in enumerate(counts)])
+    which = which[rng.permutation(len(which))]
+    n = len(which)
+    arrivals = np.cumsum(rng.gamma(0.5, 0.02, n))
+    good = rng.random(n) < 0.7
+    good[which == 2] = False                                   # a model without a good request
+    good[which == 1] = True                                    # ... and one with exactly one request
+    finish = arrivals + np.where(good, rng.gamma(2.0, 0.04, n), 0.0)
+    w = Workload.from_arrays(arrivals, which, np.full(n, 0.5), names)
+    for warmup in (0.0, 3.0, 12.0):
+        with np.errstate(divide="ignore", invalid="ignore"):
+            got = w.compute_stats(arrivals, finish, good, warmup)
+            per_model, overall = stats.compute_stats(arrivals, which, names, arrivals, finish,
+                                                     good, warmup)
+        assert [x.name for x in got.per_model_stats] == [p["name"] for p in per_model]
+        for x, p in zip(got.per_model_stats, per_model):
+            for field in stats.FIELDS:
+                a, b = np.float64(getattr(x, field)), np.float64(p[field])
+                assert a.tobytes() == b.tobytes() or (np.isnan(a) and np.isnan(b)), (x.name, field)
+        assert (got.goodput, got.latency_mean, got.num_requests, got.request_rate) == tuple(overall)

@@ -44,6 +44,7 @@ def _to_device(arr: np.ndarray, device, pinned=False):
 
 
 _UPLOAD_STAGE = {}       # device -> page-locked staging buffer of _to_device_many
+_UPLOAD_STAGE_MAX = 128 << 20
 
 
 def _to_device_many(arrays, device):
@@ -58,9 +59,12 @@ def _to_device_many(arrays, device):
         offsets.append(total)
         total += (a.nbytes + 15) & ~15
     total = max(total, 16)
+    if total > _UPLOAD_STAGE_MAX:         # not worth holding that much page-locked memory
+        return [_to_device(a, device) for a in arrays]
     stage = _UPLOAD_STAGE.get(device)
     if stage is None or stage.numel() < total:
-        stage = torch.empty(max(2 * total, 1 << 20), dtype=torch.uint8).pin_memory()
+        stage = torch.empty(min(max(2 * total, 1 << 20), _UPLOAD_STAGE_MAX),
+                            dtype=torch.uint8).pin_memory()
         _UPLOAD_STAGE[device] = stage
     host = stage.numpy()
     for a, o in zip(arrays, offsets):
